@@ -1,0 +1,64 @@
+/*
+ * pmsis.h - stand-in for the PULP runtime header that code written for PULP-TrainLib
+ * includes (lib/include/pulp_train.h:29 of the reference).  It declares the part of
+ * the PMSIS surface such code uses; libtrainlib_b200.so defines it.
+ *
+ * pi_cl_team_fork(n, fn, arg): on PULP this runs fn on n cores, each taking a slice
+ * by pi_core_id().  Here a library worker (any exported pulp_* / mm* function) is run
+ * ONCE - it performs the whole-tensor operation in one GPU launch - while a
+ * user-defined fn is run n times on the host with pi_core_id() = 0..n-1.
+ */
+#ifndef TRAINLIB_B200_PMSIS_H
+#define TRAINLIB_B200_PMSIS_H
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <math.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef NUM_CORES
+#define NUM_CORES 1
+#endif
+#define PI_L1
+#define PI_L2
+#define PI_CL_DMA_DIR_EXT2LOC 1
+#define PI_CL_DMA_DIR_LOC2EXT 0
+#define PI_PERF_CYCLES 0
+#define PI_PERF_INSTR  1
+
+#ifndef __CUDACC__
+typedef _Float16 float16alt;
+typedef _Float16 float16;
+typedef short v2s __attribute__((vector_size(4)));
+#endif
+
+typedef struct { int dir, merge, stride, length, size, id; uintptr_t ext, loc; } pi_cl_dma_copy_2d_t;
+typedef struct { int dir, merge, size, id; uintptr_t ext, loc; } pi_cl_dma_copy_t;
+typedef struct { int id; } pi_cl_dma_cmd_t;
+
+int  pi_core_id(void);
+void pi_cl_team_fork(int n, void (*fn)(void *), void *arg);
+void pi_cl_team_barrier(void);
+
+/* cluster DMA: plain (strided) memcpy between host arrays */
+void pi_cl_dma_cmd(uintptr_t ext, uintptr_t loc, int size, int dir, pi_cl_dma_cmd_t *cmd);
+void pi_cl_dma_cmd_2d(uintptr_t ext, uintptr_t loc, int size, int stride, int length, int dir, pi_cl_dma_cmd_t *cmd);
+void pi_cl_dma_cmd_wait(pi_cl_dma_cmd_t *cmd);
+
+/* performance counters: "cycles" are elapsed nanoseconds on the library's stream */
+void pi_perf_conf(unsigned events);
+void pi_perf_reset(void);
+void pi_perf_start(void);
+void pi_perf_stop(void);
+unsigned pi_perf_read(int event);
+
+void *pi_l2_malloc(int bytes);
+void  pi_l2_free(void *p, int bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,78 @@
+/*
+ * trainlib_b200.h - entry points of libtrainlib_b200.so that have no counterpart in
+ * the reference library: device/memory management, error reporting, the batched
+ * "streams" mode and timing.  Plain C ABI: pointers, sizes and ints only.
+ */
+#ifndef TRAINLIB_B200_H
+#define TRAINLIB_B200_H
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- error state.  The reference reports errors with printf + return
+ * (e.g. lib/sources/pulp_im2col_fp32.c:125-127); entry points here do the same and
+ * also latch a code that the caller can read.  CUDA errors are sticky. */
+enum {
+    TL_OK = 0,
+    TL_ERR_NO_DEVICE = 1,      /* no CUDA device / driver: there is no CPU fallback */
+    TL_ERR_CUDA = 2,           /* a CUDA runtime call failed */
+    TL_ERR_BAD_ARGS = 3,       /* inconsistent sizes, unsupported flag combination */
+    TL_ERR_UNSUPPORTED = 4,    /* a branch the reference itself leaves unimplemented */
+    TL_ERR_TOO_LARGE = 5,      /* request exceeds a fixed capacity */
+    TL_ERR_TIMEOUT = 6         /* a bounded device-side wait gave up */
+};
+int         trainlib_last_error(void);
+const char *trainlib_last_error_string(void);
+void        trainlib_clear_error(void);
+
+/* ---- device.  One host thread drives one device; all work is queued on one stream,
+ * so call order is execution order.  trainlib_init is implicit in every entry point. */
+int   trainlib_init(int device);              /* returns TL_OK or an error code */
+int   trainlib_device(void);
+void  trainlib_set_stream(void *cuda_stream); /* NULL = the library's own stream */
+void *trainlib_stream(void);
+void  trainlib_synchronize(void);
+
+/* ---- memory modes.  The reference's tensors are host arrays handed over through
+ * struct blob.  Each pointer reaching an entry point is either
+ *   - a device address (from trainlib_malloc, cudaMalloc or a torch CUDA tensor):
+ *     used in place, nothing is copied, the call returns without synchronising; or
+ *   - a host address: the bytes the call reads are copied to a device staging arena
+ *     first, the bytes it writes are copied back before the call returns.
+ * TL_MEM_AUTO asks the driver per pointer; TL_MEM_DEVICE / TL_MEM_HOST assert that all
+ * pointers are of one kind and skip the query. */
+enum { TL_MEM_AUTO = 0, TL_MEM_DEVICE = 1, TL_MEM_HOST = 2 };
+void  trainlib_set_memory_mode(int mode);
+int   trainlib_memory_mode(void);
+void *trainlib_malloc(size_t bytes);          /* device memory, 256-byte aligned */
+void  trainlib_free(void *dev_ptr);
+void *trainlib_malloc_host(size_t bytes);     /* pinned host memory (fast staging) */
+void  trainlib_free_host(void *host_ptr);
+int   trainlib_memcpy_h2d(void *dev, const void *host, size_t bytes);
+int   trainlib_memcpy_d2h(void *host, const void *dev, size_t bytes);
+int   trainlib_memset(void *dev, int byte, size_t bytes);
+
+/* ---- streams mode.  With n > 1, every activation blob (input, output, and their
+ * diffs) holds n independent batch-1 tensors back to back ([n][blob.dim]); weight
+ * blobs stay single and weight gradients are the sum over the n streams, taken in
+ * stream order inside one launch.  Losses write n values.  n = 1 is the reference's
+ * behaviour.  Applies to conv2d, linear, instnorm/batchnorm, relu, residual,
+ * avgpool, CrossEntropy/MSE and the SGD step. */
+void  trainlib_set_streams(int n);
+int   trainlib_streams(void);
+
+/* ---- timing on the library's stream (CUDA events).  pi_perf_* map onto these. */
+void   trainlib_timer_start(void);
+double trainlib_timer_stop_ms(void);          /* synchronises; elapsed milliseconds */
+long long trainlib_kernel_launches(void);     /* kernels launched by this library so far */
+
+/* ---- GEMM path selection for diagnostics and profiling.
+ * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force tcgen05 tensor-core tiles. */
+void  trainlib_set_gemm_path(int path);
+int   trainlib_gemm_path(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRAINLIB_B200_H */

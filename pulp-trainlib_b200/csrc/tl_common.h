@@ -1,0 +1,66 @@
+// Internal header of libtrainlib_b200: runtime context, staging scopes and launch helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cstddef>
+#include <cstdio>
+#include <vector>
+
+typedef __half fp16;   // device-side storage type of the ABI's fp16 (IEEE binary16)
+#define TRAINLIB_NO_FP16_TYPEDEF
+#include "../../include/trainlib_b200_abi.h"
+#include "../../include/trainlib_b200.h"
+
+namespace tl {
+
+// ---------------------------------------------------------------- errors
+void set_error(int code, const char *fmt, ...);
+bool cuda_ok(cudaError_t e, const char *what);
+bool ready();                       // lazily initialises the device; false => error latched
+
+#define TL_CUDA(call) ::tl::cuda_ok((call), #call)
+
+// ---------------------------------------------------------------- context
+cudaStream_t stream();
+int streams();                      // number of independent batch-1 streams (>= 1)
+int sm_count();
+int gemm_path();
+void count_launch();
+
+// Launch a kernel on the library stream, count it, latch launch errors.
+#define TL_LAUNCH(kernel, grid, block, smem, ...)                                   \
+    do {                                                                            \
+        kernel<<<(grid), (block), (smem), ::tl::stream()>>>(__VA_ARGS__);           \
+        ::tl::count_launch();                                                       \
+        ::tl::cuda_ok(cudaGetLastError(), #kernel);                                 \
+    } while (0)
+
+// ---------------------------------------------------------------- staging
+// A Scope maps the pointers of one entry-point call to device addresses.
+// Device pointers pass through; host pointers get a mirror in the staging arena that is
+// filled before (in / inout) and copied back after (out / inout) the kernels of the call.
+class Scope {
+public:
+    Scope();
+    ~Scope();                       // copies outputs back, synchronises if anything was staged
+    template <class T> const T *in(const T *p, size_t n) { return (const T *)map((void *)p, n * sizeof(T), true, false); }
+    template <class T> T *out(T *p, size_t n) { return (T *)map((void *)p, n * sizeof(T), false, true); }
+    template <class T> T *inout(T *p, size_t n) { return (T *)map((void *)p, n * sizeof(T), true, true); }
+    template <class T> T *scratch(size_t n) { return (T *)alloc(n * sizeof(T)); }   // device-only temporary
+    bool ok() const { return ok_; }
+private:
+    struct Entry { void *host; void *dev; size_t bytes; bool write_back; };
+    void *map(void *p, size_t bytes, bool copy_in, bool copy_out);
+    void *alloc(size_t bytes);
+    std::vector<Entry> entries_;
+    size_t arena_mark_;
+    bool ok_;
+    bool staged_;
+};
+
+bool is_device_pointer(const void *p);
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+} // namespace tl

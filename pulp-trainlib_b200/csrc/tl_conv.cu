@@ -1,0 +1,580 @@
+// Convolution kernels.  The reference lowers Conv2D to im2col + matmul
+// [ref: lib/sources/pulp_conv2d_fp32.c:85-113 (FW), :294-333 (WG), :504-549 (IG)] or runs
+// naive 7-deep loops [ref: lib/sources/pulp_conv_naive_fp32.c:198,302,410].  Here each step is
+// one implicit-GEMM kernel: the receptive fields are gathered from a zero-filled input patch
+// in shared memory, so no column buffer ever exists in global memory.  All kernels take
+// `n` independent batch-1 streams ([n][C][H][W] activations, shared weights).
+#include "tl_kernels.h"
+
+namespace tl {
+
+static constexpr int CONV_THREADS = 256;
+static constexpr int CO_T = 16;            // output channels per thread (register tile)
+
+// ------------------------------------------------------------------ forward
+// CTA = S_T streams x (TH x TW) output pixels x CO_T output channels; one thread per pixel.
+// Loop over input-channel chunks: stage patch [S_T][cc][PH][PW] and weights [cc][Hk*Wk][CO_T].
+template <class T>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_fw_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ w, const T *__restrict__ bias,
+               T *__restrict__ y, int TH, int TW, int S_T, int CC, int tiles_w, int tiles_h)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int PH = (TH - 1) * g.sh + g.Hk, PW = (TW - 1) * g.sw + g.Wk;
+    const int PWp = PW | 1;                                  // odd row pitch: fewer bank conflicts
+    const int KK = g.Hk * g.Wk;
+    float *patch = smem;                                     // [S_T][CC][PH][PWp]
+    float *wsm = smem + (size_t)S_T * CC * PH * PWp;         // [CC][KK][CO_T]
+
+    const int tid = threadIdx.x;
+    const int tile = blockIdx.x;
+    const int tw0 = (tile % tiles_w) * TW, th0 = ((tile / tiles_w) % tiles_h) * TH;
+    const int s0 = (tile / (tiles_w * tiles_h)) * S_T;
+    const int co0 = blockIdx.y * CO_T;
+
+    const int pix = tid % (TH * TW), sl = tid / (TH * TW);   // local pixel / local stream
+    const int ph = pix / TW, pw = pix % TW;
+    const bool active = (sl < S_T) && (s0 + sl < g.n) && (th0 + ph < g.Hout) && (tw0 + pw < g.Wout);
+
+    float acc[CO_T];
+#pragma unroll
+    for (int c = 0; c < CO_T; c++) acc[c] = 0.f;
+
+    const int h_in0 = th0 * g.sh - g.padU, w_in0 = tw0 * g.sw - g.padL;
+    const long long in_plane = (long long)g.Hin * g.Win;
+
+    for (int ci0 = 0; ci0 < g.Cin; ci0 += CC) {
+        const int cc = min(CC, g.Cin - ci0);
+        // stage the input patch (zero outside the image = padding)
+        const int patch_elems = S_T * cc * PH * PW;
+        for (int e = tid; e < patch_elems; e += CONV_THREADS) {
+            int c = e % PW, r = (e / PW) % PH, ci = (e / (PW * PH)) % cc, s = e / (PW * PH * cc);
+            int hi = h_in0 + r, wi = w_in0 + c;
+            float v = 0.f;
+            if (s0 + s < g.n && hi >= 0 && hi < g.Hin && wi >= 0 && wi < g.Win)
+                v = ld(x + ((long long)(s0 + s) * g.Cin + ci0 + ci) * in_plane + (long long)hi * g.Win + wi);
+            patch[((s * CC + ci) * PH + r) * PWp + c] = v;
+        }
+        // stage weights as [ci][tap][co]
+        const int w_elems = cc * KK * CO_T;
+        for (int e = tid; e < w_elems; e += CONV_THREADS) {
+            int co = e % CO_T, t = (e / CO_T) % KK, ci = e / (CO_T * KK);
+            float v = 0.f;
+            if (co0 + co < g.Cout) v = ld(w + ((long long)(co0 + co) * g.Cin + ci0 + ci) * KK + t);
+            wsm[(ci * KK + t) * CO_T + co] = v;
+        }
+        __syncthreads();
+        if (active) {
+            const float *pbase = patch + ((sl * CC) * PH + ph * g.sh) * PWp + pw * g.sw;
+            for (int ci = 0; ci < cc; ci++) {
+                const float *prow = pbase + ci * PH * PWp;
+                const float4 *wrow = (const float4 *)(wsm + ci * KK * CO_T);
+                for (int kh = 0; kh < g.Hk; kh++) {
+                    for (int kw = 0; kw < g.Wk; kw++) {
+                        float xv = prow[kh * PWp + kw];
+                        const float4 *w4 = wrow + (kh * g.Wk + kw) * (CO_T / 4);
+#pragma unroll
+                        for (int q = 0; q < CO_T / 4; q++) {
+                            float4 wv = w4[q];
+                            acc[4 * q + 0] = fmaf(xv, wv.x, acc[4 * q + 0]);
+                            acc[4 * q + 1] = fmaf(xv, wv.y, acc[4 * q + 1]);
+                            acc[4 * q + 2] = fmaf(xv, wv.z, acc[4 * q + 2]);
+                            acc[4 * q + 3] = fmaf(xv, wv.w, acc[4 * q + 3]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (active) {
+        const long long out_plane = (long long)g.Hout * g.Wout;
+        T *yp = y + ((long long)(s0 + sl) * g.Cout + co0) * out_plane + (long long)(th0 + ph) * g.Wout + tw0 + pw;
+#pragma unroll
+        for (int c = 0; c < CO_T; c++) {
+            if (co0 + c < g.Cout) {
+                float v = acc[c];
+                if (bias) v += ld(bias + co0 + c);
+                st(yp + c * out_plane, v);
+            }
+        }
+    }
+}
+
+// Depthwise forward / weight grad / input grad: one filter per channel
+// [ref: lib/sources/pulp_conv_naive_fp32.c:29,113,153].
+template <class T>
+__global__ void dw_fw_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ w, T *__restrict__ y)
+{
+    long long total = (long long)g.n * g.Cin * g.Hout * g.Wout;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        int wo = e % g.Wout, ho = (e / g.Wout) % g.Hout;
+        long long sc = e / ((long long)g.Wout * g.Hout);        // stream*C + ch
+        int ch = sc % g.Cin;
+        const T *xp = x + sc * g.Hin * g.Win;
+        const T *wp = w + (long long)ch * g.Hk * g.Wk;
+        float acc = 0.f;
+        for (int kh = 0; kh < g.Hk; kh++) {
+            int hi = ho * g.sh + kh - g.padU;
+            if (hi < 0 || hi >= g.Hin) continue;
+            for (int kw = 0; kw < g.Wk; kw++) {
+                int wi = wo * g.sw + kw - g.padL;
+                if (wi < 0 || wi >= g.Win) continue;
+                acc = fmaf(ld(wp + kh * g.Wk + kw), ld(xp + hi * g.Win + wi), acc);
+            }
+        }
+        st(y + e, acc);
+    }
+}
+
+template <class T>
+__global__ void dw_ig_kernel(ConvGeom g, const T *__restrict__ dy, const T *__restrict__ w, T *__restrict__ dx)
+{
+    long long total = (long long)g.n * g.Cin * g.Hin * g.Win;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        int wi = e % g.Win, hi = (e / g.Win) % g.Hin;
+        long long sc = e / ((long long)g.Win * g.Hin);
+        int ch = sc % g.Cin;
+        const T *dyp = dy + sc * g.Hout * g.Wout;
+        const T *wp = w + (long long)ch * g.Hk * g.Wk;
+        float acc = 0.f;
+        for (int kh = 0; kh < g.Hk; kh++) {
+            int t = hi + g.padU - kh;
+            if (t < 0 || t % g.sh) continue;
+            int ho = t / g.sh;
+            if (ho >= g.Hout) continue;
+            for (int kw = 0; kw < g.Wk; kw++) {
+                int u = wi + g.padL - kw;
+                if (u < 0 || u % g.sw) continue;
+                int wo = u / g.sw;
+                if (wo >= g.Wout) continue;
+                acc = fmaf(ld(wp + kh * g.Wk + kw), ld(dyp + ho * g.Wout + wo), acc);
+            }
+        }
+        st(dx + e, acc);
+    }
+}
+
+// One CTA per (channel, tap): block-wide sum over streams and output pixels.
+template <class T>
+__global__ void __launch_bounds__(256) dw_wg_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, T *__restrict__ dw)
+{
+    __shared__ float red[256];
+    const int tap = blockIdx.x % (g.Hk * g.Wk), ch = blockIdx.x / (g.Hk * g.Wk);
+    const int kh = tap / g.Wk, kw = tap % g.Wk;
+    const long long per = (long long)g.Hout * g.Wout, total = per * g.n;
+    float acc = 0.f;
+    for (long long e = threadIdx.x; e < total; e += blockDim.x) {
+        int s = e / per, p = e % per, ho = p / g.Wout, wo = p % g.Wout;
+        int hi = ho * g.sh + kh - g.padU, wi = wo * g.sw + kw - g.padL;
+        if (hi < 0 || hi >= g.Hin || wi < 0 || wi >= g.Win) continue;
+        acc = fmaf(ld(x + (((long long)s * g.Cin + ch) * g.Hin + hi) * g.Win + wi),
+                   ld(dy + ((long long)s * g.Cin + ch) * per + p), acc);
+    }
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
+    if (threadIdx.x == 0) st(dw + blockIdx.x, red[0]);
+}
+
+static bool conv_fw_plan(const ConvGeom &g, int &TH, int &TW, int &S_T, int &CC, size_t &smem)
+{
+    TW = g.Wout >= 32 ? 32 : (g.Wout >= 16 ? 16 : (g.Wout >= 8 ? 8 : (g.Wout >= 4 ? 4 : (g.Wout >= 2 ? 2 : 1))));
+    TH = CONV_THREADS / TW;
+    while (TH / 2 >= g.Hout && TH > 1) TH /= 2;
+    S_T = CONV_THREADS / (TH * TW);
+    if (S_T > g.n) S_T = g.n;
+    if (S_T < 1) S_T = 1;
+    const int PH = (TH - 1) * g.sh + g.Hk, PW = ((TW - 1) * g.sw + g.Wk) | 1, KK = g.Hk * g.Wk;
+    CC = g.Cin;
+    for (;;) {
+        smem = ((size_t)S_T * CC * PH * PW + (size_t)CC * KK * CO_T) * sizeof(float);
+        if (smem <= 40 * 1024 || CC == 1) break;
+        CC = (CC + 1) / 2;
+    }
+    return smem <= 200 * 1024;
+}
+
+template <class T> void conv_fw(const ConvGeom &g, const T *x, const T *w, const T *bias, T *y)
+{
+    if (g.depthwise) {
+        long long total = (long long)g.n * g.Cin * g.Hout * g.Wout;
+        int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+        TL_LAUNCH((dw_fw_kernel<T>), blocks, 256, 0, g, x, w, y);
+        return;
+    }
+    int TH, TW, S_T, CC; size_t smem;
+    if (!conv_fw_plan(g, TH, TW, S_T, CC, smem)) { set_error(TL_ERR_TOO_LARGE, "conv forward: kernel window too large for shared memory"); return; }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(conv_fw_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH), tiles_s = ceil_div(g.n, S_T);
+    dim3 grid(tiles_w * tiles_h * tiles_s, ceil_div(g.Cout, CO_T));
+    TL_LAUNCH((conv_fw_kernel<T>), grid, CONV_THREADS, smem, g, x, w, bias, y, TH, TW, S_T, CC, tiles_w, tiles_h);
+}
+
+// ------------------------------------------------------------------ input gradient
+// dX[ci][hi][wi] = sum_{co,kh,kw} W[co][ci][kh][kw] * dY[co][(hi+padU-kh)/sh][(wi+padL-kw)/sw]
+// over the taps where both divisions are exact and in range.  Same tiling as the forward with
+// the roles of the channel dimensions swapped; CI_T = 16 input channels per thread.
+template <class T>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_ig_kernel(ConvGeom g, const T *__restrict__ dy, const T *__restrict__ w, T *__restrict__ dx,
+               int TH, int TW, int S_T, int CC, int tiles_w, int tiles_h, int PH, int PW)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int PWp = PW | 1;
+    const int KK = g.Hk * g.Wk;
+    float *patch = smem;                                     // [S_T][CC][PH][PWp] of dY
+    float *wsm = smem + (size_t)S_T * CC * PH * PWp;         // [CC(co)][KK][CO_T(ci)]
+
+    const int tid = threadIdx.x;
+    const int tile = blockIdx.x;
+    const int tw0 = (tile % tiles_w) * TW, th0 = ((tile / tiles_w) % tiles_h) * TH;
+    const int s0 = (tile / (tiles_w * tiles_h)) * S_T;
+    const int ci0 = blockIdx.y * CO_T;
+
+    const int pix = tid % (TH * TW), sl = tid / (TH * TW);
+    const int ph = pix / TW, pw = pix % TW;
+    const int hi = th0 + ph, wi = tw0 + pw;
+    const bool active = (sl < S_T) && (s0 + sl < g.n) && (hi < g.Hin) && (wi < g.Win);
+
+    // first output row/col that any pixel of the tile can touch (floor division, may be negative)
+    const int t_lo = th0 + g.padU - (g.Hk - 1), u_lo = tw0 + g.padL - (g.Wk - 1);
+    const int ho_base = (t_lo >= 0) ? t_lo / g.sh : -((-t_lo + g.sh - 1) / g.sh);
+    const int wo_base = (u_lo >= 0) ? u_lo / g.sw : -((-u_lo + g.sw - 1) / g.sw);
+
+    float acc[CO_T];
+#pragma unroll
+    for (int c = 0; c < CO_T; c++) acc[c] = 0.f;
+    const long long out_plane = (long long)g.Hout * g.Wout;
+
+    for (int co0 = 0; co0 < g.Cout; co0 += CC) {
+        const int cc = min(CC, g.Cout - co0);
+        const int patch_elems = S_T * cc * PH * PW;
+        for (int e = tid; e < patch_elems; e += CONV_THREADS) {
+            int c = e % PW, r = (e / PW) % PH, co = (e / (PW * PH)) % cc, s = e / (PW * PH * cc);
+            int ho = ho_base + r, wo = wo_base + c;
+            float v = 0.f;
+            if (s0 + s < g.n && ho >= 0 && ho < g.Hout && wo >= 0 && wo < g.Wout)
+                v = ld(dy + ((long long)(s0 + s) * g.Cout + co0 + co) * out_plane + (long long)ho * g.Wout + wo);
+            patch[((s * CC + co) * PH + r) * PWp + c] = v;
+        }
+        const int w_elems = cc * KK * CO_T;
+        for (int e = tid; e < w_elems; e += CONV_THREADS) {
+            int ci = e % CO_T, t = (e / CO_T) % KK, co = e / (CO_T * KK);
+            float v = 0.f;
+            if (ci0 + ci < g.Cin) v = ld(w + ((long long)(co0 + co) * g.Cin + ci0 + ci) * KK + t);
+            wsm[(co * KK + t) * CO_T + ci] = v;
+        }
+        __syncthreads();
+        if (active) {
+            for (int kh = 0; kh < g.Hk; kh++) {
+                int t = hi + g.padU - kh;
+                if (t < 0 || (t % g.sh) != 0) continue;
+                int r = t / g.sh - ho_base;
+                if (r < 0 || r >= PH) continue;
+                for (int kw = 0; kw < g.Wk; kw++) {
+                    int u = wi + g.padL - kw;
+                    if (u < 0 || (u % g.sw) != 0) continue;
+                    int c = u / g.sw - wo_base;
+                    if (c < 0 || c >= PW) continue;
+                    const float *pp = patch + ((sl * CC) * PH + r) * PWp + c;
+                    const float4 *w4 = (const float4 *)(wsm + (kh * g.Wk + kw) * CO_T);
+                    for (int co = 0; co < cc; co++) {
+                        float dv = pp[co * PH * PWp];
+                        const float4 *wq = w4 + co * KK * (CO_T / 4);
+#pragma unroll
+                        for (int q = 0; q < CO_T / 4; q++) {
+                            float4 wv = wq[q];
+                            acc[4 * q + 0] = fmaf(dv, wv.x, acc[4 * q + 0]);
+                            acc[4 * q + 1] = fmaf(dv, wv.y, acc[4 * q + 1]);
+                            acc[4 * q + 2] = fmaf(dv, wv.z, acc[4 * q + 2]);
+                            acc[4 * q + 3] = fmaf(dv, wv.w, acc[4 * q + 3]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (active) {
+        const long long in_plane = (long long)g.Hin * g.Win;
+        T *xp = dx + ((long long)(s0 + sl) * g.Cin + ci0) * in_plane + (long long)hi * g.Win + wi;
+#pragma unroll
+        for (int c = 0; c < CO_T; c++)
+            if (ci0 + c < g.Cin) st(xp + c * in_plane, acc[c]);
+    }
+}
+
+template <class T> void conv_ig(const ConvGeom &g, const T *dy, const T *w, T *dx)
+{
+    if (g.depthwise) {
+        long long total = (long long)g.n * g.Cin * g.Hin * g.Win;
+        int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+        TL_LAUNCH((dw_ig_kernel<T>), blocks, 256, 0, g, dy, w, dx);
+        return;
+    }
+    int TW = g.Win >= 32 ? 32 : (g.Win >= 16 ? 16 : (g.Win >= 8 ? 8 : (g.Win >= 4 ? 4 : (g.Win >= 2 ? 2 : 1))));
+    int TH = CONV_THREADS / TW;
+    while (TH / 2 >= g.Hin && TH > 1) TH /= 2;
+    int S_T = CONV_THREADS / (TH * TW);
+    if (S_T > g.n) S_T = g.n;
+    if (S_T < 1) S_T = 1;
+    const int PH = (TH - 1 + g.Hk - 1) / g.sh + 2, PW = (TW - 1 + g.Wk - 1) / g.sw + 2;
+    const int KK = g.Hk * g.Wk;
+    int CC = g.Cout; size_t smem;
+    for (;;) {
+        smem = ((size_t)S_T * CC * PH * (PW | 1) + (size_t)CC * KK * CO_T) * sizeof(float);
+        if (smem <= 40 * 1024 || CC == 1) break;
+        CC = (CC + 1) / 2;
+    }
+    if (smem > 200 * 1024) { set_error(TL_ERR_TOO_LARGE, "conv input grad: kernel window too large for shared memory"); return; }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(conv_ig_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    int tiles_w = ceil_div(g.Win, TW), tiles_h = ceil_div(g.Hin, TH), tiles_s = ceil_div(g.n, S_T);
+    dim3 grid(tiles_w * tiles_h * tiles_s, ceil_div(g.Cin, CO_T));
+    TL_LAUNCH((conv_ig_kernel<T>), grid, CONV_THREADS, smem, g, dy, w, dx, TH, TW, S_T, CC, tiles_w, tiles_h, PH, PW);
+}
+
+// ------------------------------------------------------------------ weight gradient
+// dW[co][ci][kh][kw] = sum over streams and output pixels of dY[co][ho][wo] * X[ci][ho*sh+kh-padU][wo*sw+kw-padL].
+// The reduction dimension (streams x pixels) is split over `groups` CTAs per 16x16 (co,ci) tile.
+// Thread (co,ci) keeps the Hk*Wk taps of its filter in registers while its CTA walks its share of
+// (stream, pixel-tile) work items in ascending order; CTA partials go to scratch
+// [group][Cout*Cin*KK] and a second kernel adds them in group order, so the result does not
+// depend on scheduling (no atomics).
+template <class T, int KH, int KW>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_wg_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
+                       int TH, int TW, int tiles_w, int tiles_h, int ci_tiles)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int PH = (TH - 1) * g.sh + g.Hk, PW = (TW - 1) * g.sw + g.Wk;
+    const int PWp = PW | 1;
+    const int PLANE = (PH * PWp) | 1;
+    const int TP = TH * TW;
+    float *xs = smem;                          // [16 ci][PLANE]
+    float *dys = smem + 16 * PLANE;            // [16 co][TP + 1]
+    constexpr int KK = KH * KW;
+
+    const int tid = threadIdx.x;
+    const int co_l = tid / 16, ci_l = tid % 16;
+    const int ci0 = (blockIdx.x % ci_tiles) * 16, co0 = (blockIdx.x / ci_tiles) * 16;
+    const int group = blockIdx.y, groups = gridDim.y;
+
+    float acc[KK];
+#pragma unroll
+    for (int t = 0; t < KK; t++) acc[t] = 0.f;
+
+    const long long in_plane = (long long)g.Hin * g.Win, out_plane = (long long)g.Hout * g.Wout;
+    const long long items = (long long)g.n * tiles_h * tiles_w;
+    // contiguous share of the work list, so partial sums follow stream order
+    const long long per = (items + groups - 1) / groups;
+    const long long it_begin = (long long)group * per, it_end = min(items, it_begin + per);
+
+    for (long long it = it_begin; it < it_end; it++) {
+        const int s = (int)(it / (tiles_h * tiles_w));
+        const int trem = (int)(it % (tiles_h * tiles_w));
+        const int th0 = (trem / tiles_w) * TH, tw0 = (trem % tiles_w) * TW;
+        const int h_in0 = th0 * g.sh - g.padU, w_in0 = tw0 * g.sw - g.padL;
+        for (int e = tid; e < 16 * PH * PW; e += CONV_THREADS) {
+            int c = e % PW, r = (e / PW) % PH, ci = e / (PW * PH);
+            int hi = h_in0 + r, wi = w_in0 + c;
+            float v = 0.f;
+            if (ci0 + ci < g.Cin && hi >= 0 && hi < g.Hin && wi >= 0 && wi < g.Win)
+                v = ld(x + ((long long)s * g.Cin + ci0 + ci) * in_plane + (long long)hi * g.Win + wi);
+            xs[ci * PLANE + r * PWp + c] = v;
+        }
+        for (int e = tid; e < 16 * TP; e += CONV_THREADS) {
+            int p = e % TP, co = e / TP;
+            int ho = th0 + p / TW, wo = tw0 + p % TW;
+            float v = 0.f;
+            if (co0 + co < g.Cout && ho < g.Hout && wo < g.Wout)
+                v = ld(dy + ((long long)s * g.Cout + co0 + co) * out_plane + (long long)ho * g.Wout + wo);
+            dys[co * (TP + 1) + p] = v;
+        }
+        __syncthreads();
+        const float *xc = xs + ci_l * PLANE;
+        const float *dc = dys + co_l * (TP + 1);
+        for (int ph = 0; ph < TH; ph++) {
+            for (int pw = 0; pw < TW; pw++) {
+                float d = dc[ph * TW + pw];
+                const float *xp = xc + (ph * g.sh) * PWp + pw * g.sw;
+#pragma unroll
+                for (int kh = 0; kh < KH; kh++)
+#pragma unroll
+                    for (int kw = 0; kw < KW; kw++) acc[kh * KW + kw] = fmaf(d, xp[kh * PWp + kw], acc[kh * KW + kw]);
+            }
+        }
+        __syncthreads();
+    }
+    if (co0 + co_l < g.Cout && ci0 + ci_l < g.Cin) {
+        float *pp = part + (long long)group * g.Cout * g.Cin * KK + ((long long)(co0 + co_l) * g.Cin + ci0 + ci_l) * KK;
+#pragma unroll
+        for (int t = 0; t < KK; t++) pp[t] = acc[t];
+    }
+}
+
+template <class T>
+__global__ void reduce_partials_kernel(const float *__restrict__ part, T *__restrict__ out, long long n, int groups)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = 0.f;
+    for (int gidx = 0; gidx < groups; gidx++) s += part[(long long)gidx * n + i];
+    st(out + i, s);
+}
+
+// Fallback for filter windows above 5x5: one CTA per weight, block-wide reduction.
+template <class T>
+__global__ void __launch_bounds__(256) conv_wg_direct_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, T *__restrict__ dw)
+{
+    __shared__ float red[256];
+    const int KK = g.Hk * g.Wk;
+    const int tap = blockIdx.x % KK, ci = (blockIdx.x / KK) % g.Cin, co = blockIdx.x / (KK * g.Cin);
+    const int kh = tap / g.Wk, kw = tap % g.Wk;
+    const long long per = (long long)g.Hout * g.Wout, total = per * g.n;
+    float acc = 0.f;
+    for (long long e = threadIdx.x; e < total; e += blockDim.x) {
+        int s = e / per, p = e % per, ho = p / g.Wout, wo = p % g.Wout;
+        int hi = ho * g.sh + kh - g.padU, wi = wo * g.sw + kw - g.padL;
+        if (hi < 0 || hi >= g.Hin || wi < 0 || wi >= g.Win) continue;
+        acc = fmaf(ld(x + (((long long)s * g.Cin + ci) * g.Hin + hi) * g.Win + wi),
+                   ld(dy + ((long long)s * g.Cout + co) * per + p), acc);
+    }
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
+    if (threadIdx.x == 0) st(dw + blockIdx.x, red[0]);
+}
+
+// db[co] = sum over streams and pixels of dY[co]   [ref: lib/sources/pulp_conv_naive_fp32.c:354-361]
+template <class T>
+__global__ void __launch_bounds__(256) channel_sum_kernel(const T *__restrict__ dy, T *__restrict__ db, int n, int C, long long plane)
+{
+    __shared__ float red[256];
+    const int c = blockIdx.x;
+    float acc = 0.f;
+    for (long long e = threadIdx.x; e < plane * n; e += blockDim.x) {
+        long long s = e / plane, p = e % plane;
+        acc += ld(dy + (s * C + c) * plane + p);
+    }
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
+    if (threadIdx.x == 0) st(db + c, red[0]);
+}
+
+template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const T *dy, T *dw, T *dbias)
+{
+    if (dbias) TL_LAUNCH((channel_sum_kernel<T>), g.Cout, 256, 0, dy, dbias, g.n, g.Cout, (long long)g.Hout * g.Wout);
+    const int KK = g.Hk * g.Wk;
+    if (g.depthwise) {
+        TL_LAUNCH((dw_wg_kernel<T>), g.Cin * KK, 256, 0, g, x, dy, dw);
+        return;
+    }
+    // pixel tile: whole rows, about 256 pixels
+    int TW = g.Wout < 64 ? g.Wout : 64;
+    int TH = 256 / TW; if (TH < 1) TH = 1; if (TH > g.Hout) TH = g.Hout;
+    const int PH = (TH - 1) * g.sh + g.Hk, PW = ((TW - 1) * g.sw + g.Wk) | 1;
+    size_t smem = ((size_t)16 * ((PH * PW) | 1) + (size_t)16 * (TH * TW + 1)) * sizeof(float);
+    const bool tiled = (g.Hk == g.Wk) && (g.Hk == 1 || g.Hk == 3 || g.Hk == 5) && smem <= 200 * 1024;
+    if (!tiled) {
+        TL_LAUNCH((conv_wg_direct_kernel<T>), g.Cout * g.Cin * KK, 256, 0, g, x, dy, dw);
+        return;
+    }
+    int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH);
+    int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
+    long long items = (long long)g.n * tiles_w * tiles_h;
+    int groups = ceil_div(4 * sm_count(), ci_tiles * co_tiles);
+    if (groups > items) groups = (int)items;
+    if (groups < 1) groups = 1;
+    const long long nw = (long long)g.Cout * g.Cin * KK;
+    float *part = sc.scratch<float>((size_t)groups * nw);
+    if (!part) return;
+    dim3 grid(ci_tiles * co_tiles, groups);
+#define TL_WG_LAUNCH(KH_, KW_)                                                                                        \
+    do {                                                                                                              \
+        if (smem > 48 * 1024)                                                                                         \
+            cudaFuncSetAttribute(conv_wg_partial_kernel<T, KH_, KW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        TL_LAUNCH((conv_wg_partial_kernel<T, KH_, KW_>), grid, CONV_THREADS, smem, g, x, dy, part, TH, TW, tiles_w, tiles_h, ci_tiles); \
+    } while (0)
+    if (g.Hk == 1) TL_WG_LAUNCH(1, 1);
+    else if (g.Hk == 3) TL_WG_LAUNCH(3, 3);
+    else TL_WG_LAUNCH(5, 5);
+#undef TL_WG_LAUNCH
+    TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
+}
+
+// ------------------------------------------------------------------ explicit im2row / im2col / blocktranspose
+// Kept for API completeness (the conv entry points never call them); index arithmetic is
+// bit-exact with [ref: lib/sources/pulp_im2col_fp32.c:157-189 (FW/WG), :193-232 (IG), :668-1012, :1020-1072]
+// wherever the reference's own pad test is right (pad <= 1), and mathematically correct beyond.
+template <class T>
+__global__ void im2row_kernel(const T *__restrict__ src, T *__restrict__ buf, int C, int H, int W, int Hk, int Wk,
+                              int Ho, int Wo, int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed)
+{
+    // mode 0: rows = output pixels (Ho x Wo), columns = (c,hk,wk) [CHW] or (hk,wk,c) [HWC], source = input.
+    // mode 1: rows = input pixels (H x W), columns = (co,hk,wk) / (hk,wk,co), source = output gradient of
+    //         size C x Ho x Wo, "full" correlation window starting at (hi-(Hk-1), wi-(Wk-1)).
+    const int rows_h = mode_ig ? H : Ho, rows_w = mode_ig ? W : Wo;
+    const long long K = (long long)C * Hk * Wk, total = K * rows_h * rows_w;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        long long row = e / K; int col = (int)(e % K);
+        int rh = (int)(row / rows_w), rw = (int)(row % rows_w);
+        int c, hk, wk;
+        if (!hwc) { wk = col % Wk; hk = (col / Wk) % Hk; c = col / (Wk * Hk); }
+        else { c = col % C; wk = (col / C) % Wk; hk = col / (C * Wk); }
+        int sh_ = mode_ig ? rh - (Hk - 1) + hk : rh * sh + hk - padU;
+        int sw_ = mode_ig ? rw - (Wk - 1) + wk : rw * sw + wk - padL;
+        const int SH = mode_ig ? Ho : H, SW = mode_ig ? Wo : W;
+        float v = 0.f;
+        if (sh_ >= 0 && sh_ < SH && sw_ >= 0 && sw_ < SW)
+            v = hwc ? ld(src + ((long long)sh_ * SW + sw_) * C + c) : ld(src + ((long long)c * SH + sh_) * SW + sw_);
+        long long dst = transposed ? (long long)col * rows_h * rows_w + row : e;
+        st(buf + dst, v);
+    }
+}
+
+template <class T>
+void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
+            int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf)
+{
+    long long total = (long long)C * Hk * Wk * (mode_ig ? (long long)H * W : (long long)Ho * Wo);
+    int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+    if (blocks < 1) return;
+    TL_LAUNCH((im2row_kernel<T>), blocks, 256, 0, src, buf, C, H, W, Hk, Wk, Ho, Wo, sh, sw, padU, padL, mode_ig, hwc, transposed_buf);
+}
+
+template <class T>
+__global__ void blocktransp_kernel(const T *__restrict__ w, T *__restrict__ bt, int Cin, int Cout, int Hk, int Wk, int hwc)
+{
+    const int HW = Hk * Wk;
+    const long long total = (long long)Cin * Cout * HW;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        if (!hwc) {
+            int i = e % HW, k = (e / HW) % Cout, c = e / ((long long)HW * Cout);      // destination order [c][k][i]
+            bt[e] = w[(HW - 1 - i) + (long long)c * HW + (long long)k * Cin * HW];
+        } else {
+            int co = e % Cout, wk = (e / Cout) % Wk, hk = (e / ((long long)Cout * Wk)) % Hk, ci = e / ((long long)Cout * HW);
+            bt[e] = w[ci + (long long)(Wk - 1 - wk) * Cin + (long long)(Hk - 1 - hk) * Wk * Cin + (long long)co * HW * Cin];
+        }
+    }
+}
+
+template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk, int Wk, int hwc)
+{
+    long long total = (long long)Cin * Cout * Hk * Wk;
+    int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 8);
+    if (blocks < 1) return;
+    TL_LAUNCH((blocktransp_kernel<T>), blocks, 256, 0, w, bt, Cin, Cout, Hk, Wk, hwc);
+}
+
+#define INST(T)                                                                                             \
+    template void conv_fw<T>(const ConvGeom &, const T *, const T *, const T *, T *);                       \
+    template void conv_wg<T>(Scope &, const ConvGeom &, const T *, const T *, T *, T *);                    \
+    template void conv_ig<T>(const ConvGeom &, const T *, const T *, T *);                                  \
+    template void im2row<T>(const T *, T *, int, int, int, int, int, int, int, int, int, int, int, int, int, int); \
+    template void blocktransp<T>(const T *, T *, int, int, int, int, int);
+INST(float)
+INST(__half)
+
+} // namespace tl

@@ -1,0 +1,687 @@
+// Bandwidth-bound kernels around the matmul-centred training step: activations, softmax,
+// instance / batch / layer norm, MSE and CrossEntropy, SGD, residual adds, average pooling
+// and the index-shuffling helpers (transpose, pad, broadcast add).  Each kernel cites the
+// reference loop it replaces; reductions use warp shuffles, streams use 16-byte accesses.
+#include "tl_kernels.h"
+#include <cfloat>
+
+namespace tl {
+
+// ------------------------------------------------------------------ helpers
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over the whole CTA; every thread gets the result.  `red` holds >= 33 floats.
+__device__ __forceinline__ float block_sum(float v, float *red)
+{
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+    if (wid == 0) { t = warp_sum(t); if (lane == 0) red[32] = t; }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float *red)
+{
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    float t = (threadIdx.x < nw) ? red[threadIdx.x] : -FLT_MAX;
+    if (wid == 0) { t = warp_max(t); if (lane == 0) red[32] = t; }
+    __syncthreads();
+    return red[32];
+}
+
+// Schraudolph exponential exactly as the reference computes it: multiply and add are
+// rounded separately, the float is truncated to an unsigned and reinterpreted
+// [ref: lib/sources/pulp_train_utils_fp32.c:1223-1231].
+__device__ __forceinline__ float fastexp_gist_dev(float x)
+{
+    x = __fadd_rn(__fmul_rn(GIST_A, x), GIST_B);
+    if (x < (float)GIST_C || x > (float)GIST_D) x = (x < (float)GIST_C) ? 0.0f : (float)GIST_D;
+    return __uint_as_float((unsigned)x);
+}
+
+static inline int grid_for(long long n, int per_block = 256, int waves = 16)
+{
+    long long b = (n + per_block - 1) / per_block;
+    long long cap = (long long)sm_count() * waves;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+#define GRID_STRIDE(i, n) for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (n); i += (long long)gridDim.x * blockDim.x)
+
+// ------------------------------------------------------------------ activations
+// [ref: lib/sources/pulp_act_fp32.c:37-180 (sigmoid, relu, leaky relu), :714-746 (GELU, rational tanh)]
+__device__ __forceinline__ float act_apply(int kind, float x, float slope)
+{
+    switch (kind) {
+    case ACT_RELU: return x > 0.f ? x : 0.f;
+    case ACT_LEAKY: return x > 0.f ? x : x * slope;
+    case ACT_SIGMOID: return 1.f / (1.f + expf(-x));
+    default: {
+        float half_x = 0.5f * x;
+        float val = __fmul_rn(__fadd_rn(__fmul_rn(__fmul_rn(__fmul_rn(x, x), x), 0.044715f), x), 0.7978f);
+        float v2 = __fmul_rn(val, val);
+        float a = __fmul_rn(__fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(__fadd_rn(v2, 378.0f), v2), 17325.0f), v2), 135135.0f), val);
+        float b = __fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(__fadd_rn(__fmul_rn(28.0f, v2), 3150.0f), v2), 62370.0f), v2), 135135.0f);
+        val = __fdiv_rn(a, b);
+        val = val > 1.f ? 1.f : (val < -1.f ? -1.f : val);
+        return __fadd_rn(__fmul_rn(val, half_x), half_x);
+    }
+    }
+}
+
+template <class T> __global__ void act_fw_kernel(int kind, const T *__restrict__ x, T *__restrict__ y, long long n, float slope)
+{
+    GRID_STRIDE(i, n) st(y + i, act_apply(kind, ld(x + i), slope));
+}
+
+// Backward of the reference activations.  GELU has no backward in the reference; the
+// derivative of its own rational approximation is used (clamped region: 0.5 * (1 +- 1)).
+template <class T>
+__global__ void act_bw_kernel(int kind, const T *__restrict__ x, const T *__restrict__ y, const T *__restrict__ dy,
+                              T *__restrict__ dx, long long n, float slope)
+{
+    GRID_STRIDE(i, n) {
+        float g = ld(dy + i), r;
+        if (kind == ACT_RELU) r = ld(x + i) > 0.f ? g : 0.f;
+        else if (kind == ACT_LEAKY) r = ld(x + i) > 0.f ? g : g * slope;
+        else if (kind == ACT_SIGMOID) { float s = ld(y + i); r = g * (s * (1.f - s)); }
+        else {
+            float xv = ld(x + i);
+            float u = (xv * xv * xv * 0.044715f + xv) * 0.7978f;
+            float du = (3.f * 0.044715f * xv * xv + 1.f) * 0.7978f;
+            float u2 = u * u;
+            float a = (((u2 + 378.0f) * u2 + 17325.0f) * u2 + 135135.0f) * u;
+            float b = ((28.0f * u2 + 3150.0f) * u2 + 62370.0f) * u2 + 135135.0f;
+            float da = ((7.f * u2 + 5.f * 378.0f) * u2 + 3.f * 17325.0f) * u2 + 135135.0f;
+            float db = ((6.f * 28.0f * u2 + 4.f * 3150.0f) * u2 + 2.f * 62370.0f) * u;
+            float t = a / b, dt = (da * b - a * db) / (b * b);
+            if (t > 1.f) { t = 1.f; dt = 0.f; } else if (t < -1.f) { t = -1.f; dt = 0.f; }
+            r = g * (0.5f * (1.f + t) + 0.5f * xv * dt * du);
+        }
+        st(dx + i, r);
+    }
+}
+
+template <class T> void act_fw(int kind, const T *x, T *y, long long n, float slope)
+{
+    if (n <= 0) return;
+    TL_LAUNCH((act_fw_kernel<T>), grid_for(n), 256, 0, kind, x, y, n, slope);
+}
+template <class T> void act_bw(int kind, const T *x, const T *y, const T *dy, T *dx, long long n, float slope)
+{
+    if (n <= 0) return;
+    TL_LAUNCH((act_bw_kernel<T>), grid_for(n), 256, 0, kind, x, y, dy, dx, n, slope);
+}
+
+// ------------------------------------------------------------------ softmax
+// Row softmax: max, Schraudolph exp of (x - max), divide by the row sum
+// [ref: lib/sources/pulp_act_fp32.c:187-245; pieces pulp_train_utils_fp32.c:1046-1138].
+// One CTA per row; maxes/sums (caller scratch in the reference API) are written when given.
+template <class T>
+__global__ void __launch_bounds__(128) softmax_fw_kernel(const T *__restrict__ in, T *__restrict__ out,
+                                                         T *__restrict__ maxes, T *__restrict__ sums, int width, int rows_per_batch)
+{
+    __shared__ float red[33];
+    const long long row = blockIdx.x;
+    const T *ip = in + row * width;
+    T *op = out + row * width;
+    float m = -FLT_MAX;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) m = fmaxf(m, ld(ip + j));
+    m = block_max(m, red);
+    float s = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) s += fastexp_gist_dev(__fsub_rn(ld(ip + j), m));
+    s = block_sum(s, red);
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        st(op + j, __fdiv_rn(fastexp_gist_dev(__fsub_rn(ld(ip + j), m)), s));
+    if (threadIdx.x == 0 && blockIdx.x < rows_per_batch) {       // scratch rows are shared across heads
+        if (maxes) st(maxes + row, m);
+        if (sums) st(sums + row, s);
+    }
+}
+
+// dIn = (dOut - sum_j dOut_j * Out_j) * Out   [ref: lib/sources/pulp_act_fp32.c:335-392]
+template <class T>
+__global__ void __launch_bounds__(128) softmax_bw_kernel(const T *__restrict__ out, const T *__restrict__ dout,
+                                                         T *__restrict__ din, T *__restrict__ sums, int width, int rows_per_batch)
+{
+    __shared__ float red[33];
+    const long long row = blockIdx.x;
+    const T *op = out + row * width, *gp = dout + row * width;
+    T *ip = din + row * width;
+    float s = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) s = fmaf(ld(gp + j), ld(op + j), s);
+    s = block_sum(s, red);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) st(ip + j, __fmul_rn(__fsub_rn(ld(gp + j), s), ld(op + j)));
+    if (threadIdx.x == 0 && sums && blockIdx.x < rows_per_batch) st(sums + row, s);
+}
+
+template <class T> void softmax_fw(const T *in, T *out, T *maxes, T *sums, int rows, int width, int batch)
+{
+    if (rows <= 0 || width <= 0) return;
+    TL_LAUNCH((softmax_fw_kernel<T>), rows * batch, 128, 0, in, out, maxes, sums, width, rows);
+}
+template <class T> void softmax_bw(const T *out, const T *dout, T *din, T *sums, int rows, int width, int batch)
+{
+    if (rows <= 0 || width <= 0) return;
+    TL_LAUNCH((softmax_bw_kernel<T>), rows * batch, 128, 0, out, dout, din, sums, width, rows);
+}
+
+template <class T> __global__ void row_max_kernel(const T *__restrict__ in, T *__restrict__ maxes, int width)
+{
+    __shared__ float red[33];
+    const T *ip = in + (long long)blockIdx.x * width;
+    float m = ld(maxes + blockIdx.x);                  // reference semantics: running maximum
+    for (int j = threadIdx.x; j < width; j += blockDim.x) m = fmaxf(m, ld(ip + j));
+    m = block_max(m, red);
+    if (threadIdx.x == 0) st(maxes + blockIdx.x, m);
+}
+template <class T> __global__ void exp_sum_kernel(const T *__restrict__ in, T *__restrict__ out, const T *__restrict__ maxes, T *__restrict__ sums, int width)
+{
+    __shared__ float red[33];
+    const long long row = blockIdx.x;
+    float m = ld(maxes + row), s = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float o = fastexp_gist_dev(__fsub_rn(ld(in + row * width + j), m));
+        st(out + row * width + j, o);
+        s += o;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) st(sums + row, ld(sums + row) + s);   // reference accumulates into sums
+}
+template <class T> __global__ void row_div_kernel(T *__restrict__ io, const T *__restrict__ sums, int width, long long n)
+{
+    GRID_STRIDE(i, n) st(io + i, __fdiv_rn(ld(io + i), ld(sums + i / width)));
+}
+template <class T> void row_max(const T *in, T *maxes, int rows, int width) { if (rows > 0) TL_LAUNCH((row_max_kernel<T>), rows, 128, 0, in, maxes, width); }
+template <class T> void exp_sum(const T *in, T *out, const T *maxes, T *sums, int rows, int width) { if (rows > 0) TL_LAUNCH((exp_sum_kernel<T>), rows, 128, 0, in, out, maxes, sums, width); }
+template <class T> void row_div(T *io, const T *sums, int rows, int width)
+{
+    long long n = (long long)rows * width;
+    if (n > 0) TL_LAUNCH((row_div_kernel<T>), grid_for(n), 256, 0, io, sums, width, n);
+}
+
+// ------------------------------------------------------------------ instance norm
+// One CTA per (stream, channel) plane of D elements.  mean = sum/D, var = sum(x^2)/D - mean^2 + eps
+// (clamped to eps when negative), stdev = sqrt(var); y = gamma/stdev * (x - mean) + beta
+// [ref: lib/sources/pulp_instnorm_fp32.c:33-115, pulp_train_utils_fp32.c:1685-1728].
+template <class T>
+__global__ void __launch_bounds__(256) instnorm_fw_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ gb,
+                                                          T *__restrict__ mean_o, T *__restrict__ var_o, T *__restrict__ std_o,
+                                                          int C, int D, int frozen, float eps)
+{
+    __shared__ float red[33];
+    const long long plane = blockIdx.x;
+    const int ch = (int)(plane % C);
+    const T *xp = x + plane * D;
+    T *yp = y + plane * D;
+    float mean, var, sd;
+    if (!frozen) {
+        float s = 0.f, q = 0.f;
+        for (int d = threadIdx.x; d < D; d += blockDim.x) { float t = ld(xp + d); s += t; q = fmaf(t, t, q); }
+        s = block_sum(s, red);
+        q = block_sum(q, red);
+        const float inv = 1.f / (float)D;
+        mean = s * inv;
+        var = q * inv;
+        var = __fsub_rn(var, __fmul_rn(mean, mean));
+        var = var + eps;
+        if (var < 0.f) var = eps;
+        sd = sqrtf(var);
+        if (threadIdx.x == 0) { st(mean_o + plane, mean); st(var_o + plane, var); st(std_o + plane, sd); }
+    } else {
+        mean = ld(mean_o + plane); var = ld(var_o + plane); sd = ld(std_o + plane);
+    }
+    const float gamma = __fdiv_rn(ld(gb + ch), sd), beta = ld(gb + C + ch);
+    for (int d = threadIdx.x; d < D; d += blockDim.x)
+        st(yp + d, __fadd_rn(__fmul_rn(gamma, __fsub_rn(ld(xp + d), mean)), beta));
+}
+
+// dx = (-(sum dy) - (sum (x-mean) dy) * (x-mean)/var + D*dy) * gamma / (D*stdev)
+// [ref: lib/sources/pulp_instnorm_fp32.c:117-175]
+template <class T>
+__global__ void __launch_bounds__(256) instnorm_bw_input_kernel(const T *__restrict__ x, const T *__restrict__ dy, T *__restrict__ dx,
+                                                                const T *__restrict__ gamma, const T *__restrict__ mean_i,
+                                                                const T *__restrict__ var_i, const T *__restrict__ std_i, int C, int D)
+{
+    __shared__ float red[33];
+    const long long plane = blockIdx.x;
+    const int ch = (int)(plane % C);
+    const T *xp = x + plane * D, *gp = dy + plane * D;
+    T *dp = dx + plane * D;
+    const float mean = ld(mean_i + plane), var = ld(var_i + plane), sd = ld(std_i + plane), gm = ld(gamma + ch);
+    float s = 0.f, p = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) { float g = ld(gp + d); s -= g; p -= (ld(xp + d) - mean) * g; }
+    s = block_sum(s, red);
+    p = block_sum(p, red);
+    const float fD = (float)D, denom = fD * sd;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float grad = s;
+        float md = (ld(xp + d) - mean) / var;
+        grad += p * md;
+        grad += fD * ld(gp + d);
+        st(dp + d, grad * gm / denom);
+    }
+}
+
+// Per-plane partials of dgamma = sum dy (x-mean) / stdev and dbeta = sum dy
+// [ref: lib/sources/pulp_instnorm_fp32.c:182-230]; summed over streams in stream order below.
+template <class T>
+__global__ void __launch_bounds__(256) instnorm_bw_param_kernel(const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
+                                                                const T *__restrict__ mean_i, const T *__restrict__ std_i, int D)
+{
+    __shared__ float red[33];
+    const long long plane = blockIdx.x;
+    const T *xp = x + plane * D, *gp = dy + plane * D;
+    const float mean = ld(mean_i + plane), sd = ld(std_i + plane);
+    float a = 0.f, b = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) { float g = ld(gp + d); a = fmaf(g, ld(xp + d) - mean, a); b += g; }
+    a = block_sum(a, red);
+    b = block_sum(b, red);
+    if (threadIdx.x == 0) { part[2 * plane] = a / sd; part[2 * plane + 1] = b; }
+}
+template <class T>
+__global__ void instnorm_param_reduce_kernel(const float *__restrict__ part, T *__restrict__ dgb, int n, int C)
+{
+    int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float a = 0.f, b = 0.f;
+    for (int s = 0; s < n; s++) { a += part[2 * ((long long)s * C + c)]; b += part[2 * ((long long)s * C + c) + 1]; }
+    st(dgb + c, a);
+    st(dgb + C + c, b);
+}
+
+template <class T>
+void instnorm_fw(const T *x, T *y, const T *gb, T *mean, T *var, T *stdev, int n, int C, int D, bool frozen, float eps)
+{
+    if (n * C <= 0) return;
+    TL_LAUNCH((instnorm_fw_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, y, gb, mean, var, stdev, C, D, frozen ? 1 : 0, eps);
+}
+template <class T>
+void instnorm_bw_input(const T *x, const T *dy, T *dx, const T *gamma, const T *mean, const T *var, const T *stdev, int n, int C, int D)
+{
+    if (n * C <= 0) return;
+    TL_LAUNCH((instnorm_bw_input_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, dx, gamma, mean, var, stdev, C, D);
+}
+template <class T>
+void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgb, const T *mean, const T *stdev, int n, int C, int D)
+{
+    if (n * C <= 0) return;
+    float *part = sc.scratch<float>((size_t)2 * n * C);
+    if (!part) return;
+    TL_LAUNCH((instnorm_bw_param_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, part, mean, stdev, D);
+    TL_LAUNCH((instnorm_param_reduce_kernel<T>), ceil_div(C, 128), 128, 0, part, dgb, n, C);
+}
+
+// ------------------------------------------------------------------ batch norm / layer norm (forward)
+// mean = S1/n; sqrt_var = sqrt((S2 - 2*S1*mean)/n + mean^2 + eps); y = (x-mean)/sqrt_var * w + b
+// [ref: lib/sources/pulp_batchnorm_fp32.c:84-109, pulp_layernorm_fp32.c:60-77].
+template <class T>
+__global__ void __launch_bounds__(256) batchnorm_fw_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ w,
+                                                           const T *__restrict__ b, int B, int C, int HW, float eps)
+{
+    __shared__ float red[33];
+    const int c = blockIdx.x % C;
+    const long long s = blockIdx.x / C;                  // stream
+    const T *xs = x + s * (long long)B * C * HW;
+    T *ys = y + s * (long long)B * C * HW;
+    const int cnt = B * HW;
+    float s1 = 0.f, s2 = 0.f;
+    for (int e = threadIdx.x; e < cnt; e += blockDim.x) {
+        float t = ld(xs + ((long long)(e / HW) * C + c) * HW + e % HW);
+        s1 += t; s2 = fmaf(t, t, s2);
+    }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    const float mean = s1 / (float)cnt;
+    const float sv = sqrtf(__fadd_rn(__fadd_rn(__fdiv_rn(__fsub_rn(s2, __fmul_rn(__fmul_rn(2.f, s1), mean)), (float)cnt), __fmul_rn(mean, mean)), eps));
+    const float wc = ld(w + c), bc = ld(b + c);
+    for (int e = threadIdx.x; e < cnt; e += blockDim.x) {
+        long long idx = ((long long)(e / HW) * C + c) * HW + e % HW;
+        st(ys + idx, __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(ld(xs + idx), mean), sv), wc), bc));
+    }
+}
+template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps)
+{
+    if (n * C <= 0) return;
+    TL_LAUNCH((batchnorm_fw_kernel<T>), n * C, (B * HW) >= 256 ? 256 : 64, 0, x, y, w, b, B, C, HW, eps);
+}
+
+template <class T>
+__global__ void __launch_bounds__(128) layernorm_fw_kernel(const T *__restrict__ x, T *__restrict__ y, const T *__restrict__ w,
+                                                           const T *__restrict__ b, int width, float eps)
+{
+    __shared__ float red[33];
+    const T *xp = x + (long long)blockIdx.x * width;
+    T *yp = y + (long long)blockIdx.x * width;
+    float s1 = 0.f, s2 = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) { float t = ld(xp + j); s1 += t; s2 = fmaf(t, t, s2); }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    const float mean = s1 / (float)width;
+    const float sv = sqrtf(__fadd_rn(__fadd_rn(__fdiv_rn(__fsub_rn(s2, __fmul_rn(__fmul_rn(2.f, s1), mean)), (float)width), __fmul_rn(mean, mean)), eps));
+    for (int j = threadIdx.x; j < width; j += blockDim.x)
+        st(yp + j, __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(ld(xp + j), mean), sv), ld(w + j)), ld(b + j)));
+}
+template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps)
+{
+    if (rows <= 0) return;
+    TL_LAUNCH((layernorm_fw_kernel<T>), rows, 128, 0, x, y, w, b, width, eps);
+}
+
+template <class T> __global__ void mean_std_kernel(const T *__restrict__ x, T *mean, T *var, T *stdev, int D, float eps)
+{
+    __shared__ float red[33];
+    float s = 0.f, q = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) { float t = ld(x + d); s += t; q = fmaf(t, t, q); }
+    s = block_sum(s, red);
+    q = block_sum(q, red);
+    if (threadIdx.x == 0) {
+        const float inv = 1.f / (float)D;
+        float m = s * inv, v = q * inv;
+        v = __fsub_rn(v, __fmul_rn(m, m));
+        v += eps;
+        if (v < 0.f) v = eps;
+        st(mean, m); st(var, v); st(stdev, sqrtf(v));
+    }
+}
+template <class T> void mean_std(const T *x, T *mean, T *var, T *stdev, int D, float eps)
+{
+    TL_LAUNCH((mean_std_kernel<T>), 1, 256, 0, x, mean, var, stdev, D, eps);
+}
+
+// ------------------------------------------------------------------ losses
+// MSE: loss = sum (1/dim) (t - y)^2; dy = (1/dim) * 2 * (y - t)   [ref: lib/sources/pulp_losses_fp32.c:214-275]
+template <class T>
+__global__ void __launch_bounds__(256) mse_fw_kernel(const T *__restrict__ y, const T *__restrict__ t, T *__restrict__ loss, int dim)
+{
+    __shared__ float red[33];
+    const T *yp = y + (long long)blockIdx.x * dim, *tp = t + (long long)blockIdx.x * dim;
+    const float meanval = 1.0f / (float)dim;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) { float d = ld(tp + i) - ld(yp + i); s += meanval * d * d; }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) st(loss + blockIdx.x, s);
+}
+template <class T> __global__ void mse_bw_kernel(const T *__restrict__ y, const T *__restrict__ t, T *__restrict__ dy, int dim, long long total)
+{
+    const float meanval = 1.0f / (float)dim;
+    GRID_STRIDE(i, total) st(dy + i, __fmul_rn(__fmul_rn(meanval, 2.0f), __fsub_rn(ld(y + i), ld(t + i))));
+}
+template <class T> void mse_fw(const T *y, const T *t, T *loss, int dim, int n) { if (n > 0) TL_LAUNCH((mse_fw_kernel<T>), n, 256, 0, y, t, loss, dim); }
+template <class T> void mse_bw(const T *y, const T *t, T *dy, int dim, int n)
+{
+    long long total = (long long)dim * n;
+    if (total > 0) TL_LAUNCH((mse_bw_kernel<T>), grid_for(total), 256, 0, y, t, dy, dim, total);
+}
+
+// CrossEntropy on raw logits with a probability-vector target: one thread per stream walks
+// the class vector in the reference's order (log-sum-exp with max shift)
+// [ref: lib/sources/pulp_losses_fp32.c:26-137].
+template <class T>
+__global__ void ce_kernel(const T *__restrict__ z, const T *__restrict__ t, T *__restrict__ loss, T *__restrict__ dz, int dim, int n)
+{
+    int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= n) return;
+    const T *zp = z + (long long)s * dim, *tp = t + (long long)s * dim;
+    float mx = ld(zp);
+    for (int i = 1; i < dim; i++) mx = fmaxf(mx, ld(zp + i));
+    float se = 0.f;
+    for (int i = 0; i < dim; i++) se += expf(ld(zp + i) - mx);
+    float dot = 0.f, sy = 0.f;
+    for (int i = 0; i < dim; i++) { float yi = ld(tp + i); dot = __fadd_rn(dot, __fmul_rn(yi, ld(zp + i))); sy += yi; }
+    if (sy == 0.f) sy = 1.f;
+    if (loss) st(loss + s, -(dot - (logf(se) + mx) * sy));
+    if (dz) {
+        const float inv = 1.0f / se;
+        for (int i = 0; i < dim; i++) st(dz + (long long)s * dim + i, expf(ld(zp + i) - mx) * inv * sy - ld(tp + i));
+    }
+}
+template <class T> void ce_fw(const T *z, const T *t, T *loss, int dim, int n) { if (n > 0) TL_LAUNCH((ce_kernel<T>), ceil_div(n, 128), 128, 0, z, t, loss, (T *)nullptr, dim, n); }
+template <class T> void ce_bw(const T *z, const T *t, T *dz, int dim, int n) { if (n > 0) TL_LAUNCH((ce_kernel<T>), ceil_div(n, 128), 128, 0, z, t, (T *)nullptr, dz, dim, n); }
+
+// ------------------------------------------------------------------ SGD and vector ops
+// w -= lr*g; with weight decay the gradient is first replaced by g + lambda*w, as the reference
+// does in place [ref: lib/sources/pulp_optimizers_fp32.c:48-62].
+template <class T> __global__ void sgd_kernel(T *__restrict__ w, T *__restrict__ g, long long n, float lr, float lambda)
+{
+    GRID_STRIDE(i, n) {
+        float wv = ld(w + i), gv = ld(g + i);
+        if (lambda != 0.f) { gv = __fadd_rn(gv, __fmul_rn(lambda, wv)); st(g + i, gv); }
+        st(w + i, __fsub_rn(wv, __fmul_rn(lr, gv)));
+    }
+}
+template <class T> void sgd(T *w, T *g, long long n, float lr, float lambda) { if (n > 0) TL_LAUNCH((sgd_kernel<T>), grid_for(n), 256, 0, w, g, n, lr, lambda); }
+
+template <class T> __global__ void add_kernel(const T *a, const T *b, T *c, long long n) { GRID_STRIDE(i, n) st(c + i, __fadd_rn(ld(a + i), ld(b + i))); }
+template <class T> void add(const T *a, const T *b, T *c, long long n) { if (n > 0) TL_LAUNCH((add_kernel<T>), grid_for(n), 256, 0, a, b, c, n); }
+template <class T> __global__ void copy_kernel(const T *__restrict__ f, T *__restrict__ t, long long n) { GRID_STRIDE(i, n) t[i] = f[i]; }
+template <class T> void copy_n(const T *from, T *to, long long n) { if (n > 0 && from != to) TL_LAUNCH((copy_kernel<T>), grid_for(n), 256, 0, from, to, n); }
+template <class T> __global__ void fill_kernel(T *t, float v, long long n) { GRID_STRIDE(i, n) st(t + i, v); }
+template <class T> void fill(T *to, float v, long long n) { if (n > 0) TL_LAUNCH((fill_kernel<T>), grid_for(n), 256, 0, to, v, n); }
+template <class T> __global__ void scale_kernel(T *x, float s, long long n) { GRID_STRIDE(i, n) st(x + i, __fmul_rn(ld(x + i), s)); }
+template <class T> void scale(T *x, float s, long long n) { if (n > 0) TL_LAUNCH((scale_kernel<T>), grid_for(n), 256, 0, x, s, n); }
+// mat[H x W] += bias: per_row -> bias[row] [ref: lib/sources/pulp_train_utils_fp32.c:1286-1327], else bias[col]
+template <class T> __global__ void bias_add_kernel(T *mat, const T *bias, int W, long long n, int per_row)
+{
+    GRID_STRIDE(i, n) st(mat + i, __fadd_rn(ld(mat + i), ld(bias + (per_row ? i / W : i % W))));
+}
+template <class T> void bias_add_rows(T *mat, const T *bias, int H, int W, int per_row)
+{
+    long long n = (long long)H * W;
+    if (n > 0) TL_LAUNCH((bias_add_kernel<T>), grid_for(n), 256, 0, mat, bias, W, n, per_row);
+}
+__global__ void cast_h2f_kernel(const __half *s, float *d, long long n) { GRID_STRIDE(i, n) d[i] = __half2float(s[i]); }
+__global__ void cast_f2h_kernel(const float *s, __half *d, long long n) { GRID_STRIDE(i, n) d[i] = __float2half_rn(s[i]); }
+void cast_h2f(const __half *src, float *dst, long long n) { if (n > 0) TL_LAUNCH(cast_h2f_kernel, grid_for(n), 256, 0, src, dst, n); }
+void cast_f2h(const float *src, __half *dst, long long n) { if (n > 0) TL_LAUNCH(cast_f2h_kernel, grid_for(n), 256, 0, src, dst, n); }
+
+// ------------------------------------------------------------------ average pooling
+// [ref: lib/sources/pulp_pooling_fp32.c:24-66 (FW), :69-115 (BW: every window adds dy/HWk to its pixels)]
+template <class T>
+__global__ void avgpool_fw_kernel(const T *__restrict__ x, T *__restrict__ y, long long total, int H, int W, int Ho, int Wo,
+                                  int Hk, int Wk, int sh, int sw)
+{
+    GRID_STRIDE(e, total) {
+        int wo = e % Wo, ho = (e / Wo) % Ho;
+        long long plane = e / ((long long)Wo * Ho);
+        const T *xp = x + plane * H * W;
+        float s = 0.f;
+        for (int hk = 0; hk < Hk; hk++)
+            for (int wk = 0; wk < Wk; wk++) s += ld(xp + (hk + ho * sh) * W + wk + wo * sw);
+        st(y + e, __fdiv_rn(s, (float)(Hk * Wk)));
+    }
+}
+template <class T>
+__global__ void avgpool_bw_kernel(const T *__restrict__ dy, T *__restrict__ dx, long long total, int H, int W, int Ho, int Wo,
+                                  int Hk, int Wk, int sh, int sw)
+{
+    GRID_STRIDE(e, total) {
+        int wi = e % W, hi = (e / W) % H;
+        long long plane = e / ((long long)W * H);
+        const T *gp = dy + plane * Ho * Wo;
+        const float inv_cnt = (float)(Hk * Wk);
+        float s = 0.f;
+        // windows (ho, wo) covering this pixel, visited in the reference's (ho, wo) order
+        for (int ho = 0; ho < Ho; ho++) {
+            int hk = hi - ho * sh;
+            if (hk < 0 || hk >= Hk) continue;
+            for (int wo = 0; wo < Wo; wo++) {
+                int wk = wi - wo * sw;
+                if (wk < 0 || wk >= Wk) continue;
+                s += __fdiv_rn(ld(gp + ho * Wo + wo), inv_cnt);
+            }
+        }
+        st(dx + e, s);
+    }
+}
+template <class T> void avgpool_fw(const T *x, T *y, int n, int C, int H, int W, int Ho, int Wo, int Hk, int Wk, int sh, int sw)
+{
+    long long total = (long long)n * C * Ho * Wo;
+    if (total > 0) TL_LAUNCH((avgpool_fw_kernel<T>), grid_for(total), 256, 0, x, y, total, H, W, Ho, Wo, Hk, Wk, sh, sw);
+}
+template <class T> void avgpool_bw(const T *dy, T *dx, int n, int C, int H, int W, int Ho, int Wo, int Hk, int Wk, int sh, int sw)
+{
+    long long total = (long long)n * C * H * W;
+    if (total > 0) TL_LAUNCH((avgpool_bw_kernel<T>), grid_for(total), 256, 0, dy, dx, total, H, W, Ho, Wo, Hk, Wk, sh, sw);
+}
+
+// ------------------------------------------------------------------ N-d transpose, broadcast add, pad
+struct Shape8 { int n; int d[8]; long long s[8]; };   // extents and source strides, in output order
+
+// out = in.transpose(axes): out extent i = dims[axes[i]]  [ref: lib/sources/pulp_train_utils_fp32.c:79-185]
+template <class T> __global__ void transpose_kernel(const T *__restrict__ in, T *__restrict__ out, Shape8 sh, long long total)
+{
+    GRID_STRIDE(e, total) {
+        long long rem = e, src = 0;
+#pragma unroll
+        for (int k = 7; k >= 0; k--) {
+            if (k < sh.n) { src += (rem % sh.d[k]) * sh.s[k]; rem /= sh.d[k]; }
+        }
+        out[e] = in[src];
+    }
+}
+// 2-D case: 32x32 tiles through shared memory so that both sides are coalesced.
+template <class T> __global__ void transpose2d_kernel(const T *__restrict__ in, T *__restrict__ out, int R, int Ccols)
+{
+    __shared__ T tile[32][33];
+    int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y)
+        if (r0 + r < R && c0 + threadIdx.x < Ccols) tile[r][threadIdx.x] = in[(long long)(r0 + r) * Ccols + c0 + threadIdx.x];
+    __syncthreads();
+    for (int c = threadIdx.y; c < 32; c += blockDim.y)
+        if (c0 + c < Ccols && r0 + threadIdx.x < R) out[(long long)(c0 + c) * R + r0 + threadIdx.x] = tile[threadIdx.x][c];
+}
+template <class T> void transpose_nd(const T *in, T *out, const int *dims, const int *axes, int nd)
+{
+    if (nd < 1 || nd > 8) { set_error(TL_ERR_BAD_ARGS, "transpose: n_dim %d outside 1..8", nd); return; }
+    long long total = 1;
+    long long in_stride[8];
+    for (int i = nd - 1; i >= 0; i--) { in_stride[i] = total; total *= dims[i]; }
+    if (total <= 0) return;
+    if (nd == 2 && axes[0] == 1 && axes[1] == 0) {
+        dim3 grid(ceil_div(dims[1], 32), ceil_div(dims[0], 32));
+        TL_LAUNCH((transpose2d_kernel<T>), grid, dim3(32, 8), 0, in, out, dims[0], dims[1]);
+        return;
+    }
+    Shape8 sh; sh.n = nd;
+    for (int i = 0; i < 8; i++) { sh.d[i] = 1; sh.s[i] = 0; }
+    for (int i = 0; i < nd; i++) {
+        int a = axes[i];
+        if (a < 0 || a >= nd) { set_error(TL_ERR_BAD_ARGS, "transpose: axis %d out of range", a); return; }
+        sh.d[i] = dims[a]; sh.s[i] = in_stride[a];
+    }
+    TL_LAUNCH((transpose_kernel<T>), grid_for(total), 256, 0, in, out, sh, total);
+}
+
+// dest = op_1 + op_2 with NumPy broadcasting (extents aligned from the last axis, 1 repeats)
+// [ref: lib/sources/pulp_train_utils_fp32.c:225-806]
+struct Bcast8 { int n; int d[8]; long long sa[8]; long long sb[8]; };
+template <class T> __global__ void broadcast_add_kernel(const T *__restrict__ a, const T *__restrict__ b, T *__restrict__ c, Bcast8 bc, long long total)
+{
+    GRID_STRIDE(e, total) {
+        long long rem = e, ia = 0, ib = 0;
+#pragma unroll
+        for (int k = 7; k >= 0; k--) {
+            if (k < bc.n) { long long q = rem % bc.d[k]; ia += q * bc.sa[k]; ib += q * bc.sb[k]; rem /= bc.d[k]; }
+        }
+        st(c + e, __fadd_rn(ld(a + ia), ld(b + ib)));
+    }
+}
+template <class T> void broadcast_add(const T *a, const T *b, T *c, const int *da, int na, const int *db, int nb)
+{
+    int n = na > nb ? na : nb;
+    if (n < 1 || n > 8 || na < 1 || nb < 1) { set_error(TL_ERR_BAD_ARGS, "array_broadcast_sum: rank outside 1..8"); return; }
+    if (na == nb) {
+        bool same = true; long long tot = 1;
+        for (int i = 0; i < n; i++) { same &= (da[i] == db[i]); tot *= da[i]; }
+        if (same) { add<T>(a, b, c, tot); return; }
+    }
+    Bcast8 bc; bc.n = n;
+    long long total = 1, stra = 1, strb = 1;
+    for (int i = 0; i < 8; i++) { bc.d[i] = 1; bc.sa[i] = 0; bc.sb[i] = 0; }
+    for (int k = 0; k < n; k++) {                         // k-th axis from the end
+        int ea = k < na ? da[na - 1 - k] : 1, eb = k < nb ? db[nb - 1 - k] : 1;
+        int e = ea > eb ? ea : eb;
+        if ((ea != e && ea != 1) || (eb != e && eb != 1)) { set_error(TL_ERR_BAD_ARGS, "array_broadcast_sum: extents %d and %d do not broadcast", ea, eb); return; }
+        bc.d[n - 1 - k] = e;
+        bc.sa[n - 1 - k] = (ea == 1) ? 0 : stra;
+        bc.sb[n - 1 - k] = (eb == 1) ? 0 : strb;
+        stra *= ea; strb *= eb; total *= e;
+    }
+    if (total > 0) TL_LAUNCH((broadcast_add_kernel<T>), grid_for(total), 256, 0, a, b, c, bc, total);
+}
+
+// Zero padding of a C x H x W (or H x W x C) tensor [ref: lib/sources/pulp_train_utils_fp32.c:929-988]
+template <class T>
+__global__ void pad_kernel(const T *__restrict__ src, T *__restrict__ dst, int C, int H, int W, int padL, int padU, int Ho, int Wo, int hwc, long long total)
+{
+    GRID_STRIDE(e, total) {
+        int c, ht, wt;
+        if (!hwc) { wt = e % Wo; ht = (e / Wo) % Ho; c = e / ((long long)Wo * Ho); }
+        else { c = e % C; wt = (e / C) % Wo; ht = e / ((long long)C * Wo); }
+        int hs = ht - padU, ws = wt - padL;
+        T v = src[0];
+        bool inside = hs >= 0 && hs < H && ws >= 0 && ws < W;
+        if (inside) v = hwc ? src[((long long)hs * W + ws) * C + c] : src[((long long)c * H + hs) * W + ws];
+        if (inside) dst[e] = v; else st(dst + e, 0.f);
+    }
+}
+template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int padL, int padR, int padU, int padD, int hwc)
+{
+    int Ho = H + padU + padD, Wo = W + padL + padR;
+    long long total = (long long)C * Ho * Wo;
+    if (total > 0) TL_LAUNCH((pad_kernel<T>), grid_for(total), 256, 0, src, dst, C, H, W, padL, padU, Ho, Wo, hwc, total);
+}
+
+#define INST(T)                                                                                                    \
+    template void act_fw<T>(int, const T *, T *, long long, float);                                                \
+    template void act_bw<T>(int, const T *, const T *, const T *, T *, long long, float);                          \
+    template void softmax_fw<T>(const T *, T *, T *, T *, int, int, int);                                          \
+    template void softmax_bw<T>(const T *, const T *, T *, T *, int, int, int);                                    \
+    template void instnorm_fw<T>(const T *, T *, const T *, T *, T *, T *, int, int, int, bool, float);            \
+    template void instnorm_bw_input<T>(const T *, const T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
+    template void instnorm_bw_param<T>(Scope &, const T *, const T *, T *, const T *, const T *, int, int, int);   \
+    template void batchnorm_fw<T>(const T *, T *, const T *, const T *, int, int, int, int, float);                \
+    template void layernorm_fw<T>(const T *, T *, const T *, const T *, int, int, float);                          \
+    template void mse_fw<T>(const T *, const T *, T *, int, int);                                                  \
+    template void mse_bw<T>(const T *, const T *, T *, int, int);                                                  \
+    template void ce_fw<T>(const T *, const T *, T *, int, int);                                                   \
+    template void ce_bw<T>(const T *, const T *, T *, int, int);                                                   \
+    template void sgd<T>(T *, T *, long long, float, float);                                                       \
+    template void add<T>(const T *, const T *, T *, long long);                                                    \
+    template void copy_n<T>(const T *, T *, long long);                                                            \
+    template void fill<T>(T *, float, long long);                                                                  \
+    template void scale<T>(T *, float, long long);                                                                 \
+    template void bias_add_rows<T>(T *, const T *, int, int, int);                                                 \
+    template void avgpool_fw<T>(const T *, T *, int, int, int, int, int, int, int, int, int, int);                 \
+    template void avgpool_bw<T>(const T *, T *, int, int, int, int, int, int, int, int, int, int);                 \
+    template void transpose_nd<T>(const T *, T *, const int *, const int *, int);                                  \
+    template void broadcast_add<T>(const T *, const T *, T *, const int *, int, const int *, int);                 \
+    template void pad2d<T>(const T *, T *, int, int, int, int, int, int, int, int);                                \
+    template void row_max<T>(const T *, T *, int, int);                                                            \
+    template void exp_sum<T>(const T *, T *, const T *, T *, int, int);                                            \
+    template void row_div<T>(T *, const T *, int, int);                                                            \
+    template void mean_std<T>(const T *, T *, T *, T *, int, float);
+INST(float)
+INST(__half)
+
+} // namespace tl

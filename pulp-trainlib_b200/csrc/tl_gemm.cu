@@ -1,0 +1,306 @@
+// GEMM family on CUDA cores: register-tiled FFMA kernel with arbitrary operand strides
+// (so that no transposed copy of an operand is ever materialised) and the three
+// bandwidth-bound batch-1 Linear kernels.  Replaces the mm / mm_M / mm_unroll_* family
+// [ref: lib/sources/pulp_matmul_fp32.c:190-3697, pulp_matmul_fp16.c:191-1908].
+#include "tl_kernels.h"
+
+namespace tl {
+
+// ------------------------------------------------------------------ tiled FFMA GEMM
+// CTA tile BM x BN, K step 16, each thread a TM x TN register tile, fp32 accumulate.
+// Operand tiles are staged in shared memory as [k][row] so the inner product reads
+// contiguous, conflict-free vectors.  k runs ascending inside a thread, i.e. the same
+// summation order per output as the reference's single-accumulator loop
+// [ref: lib/sources/pulp_matmul_fp32.c:247-259].
+template <class T, int BM, int BN, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_ffma_kernel(GemmDesc<T> d)
+{
+    constexpr int BK = 16;
+    constexpr int NT = (BM / TM) * (BN / TN);
+    __shared__ __align__(16) float As[BK][BM + 4];
+    __shared__ __align__(16) float Bs[BK][BN + 4];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int i0 = blockIdx.y * BM, j0 = blockIdx.x * BN;
+    const int b = blockIdx.z;
+    const T *A = d.A + (long long)b * d.a_bs;
+    const T *B = d.B + (long long)b * d.b_bs;
+    T *C = d.C + (long long)b * d.c_bs;
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int r = 0; r < TM; r++)
+#pragma unroll
+        for (int c = 0; c < TN; c++) acc[r][c] = 0.f;
+
+    const bool a_k_contig = (d.a_cs == 1);
+    const bool b_k_contig = (d.b_rs == 1);
+
+    for (int k0 = 0; k0 < d.K; k0 += BK) {
+        // A tile: BM x BK elements
+        for (int e = tid; e < BM * BK; e += NT) {
+            int i, k;
+            if (a_k_contig) { i = e / BK; k = e % BK; } else { k = e / BM; i = e % BM; }
+            float v = 0.f;
+            if (i0 + i < d.N && k0 + k < d.K) v = ld(A + (long long)(i0 + i) * d.a_rs + (long long)(k0 + k) * d.a_cs);
+            As[k][i] = v;
+        }
+        for (int e = tid; e < BN * BK; e += NT) {
+            int j, k;
+            if (b_k_contig) { j = e / BK; k = e % BK; } else { k = e / BN; j = e % BN; }
+            float v = 0.f;
+            if (j0 + j < d.M && k0 + k < d.K) v = ld(B + (long long)(k0 + k) * d.b_rs + (long long)(j0 + j) * d.b_cs);
+            Bs[k][j] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            float a[TM], bb[TN];
+#pragma unroll
+            for (int r = 0; r < TM; r++) a[r] = As[k][ty * TM + r];
+#pragma unroll
+            for (int c = 0; c < TN; c++) bb[c] = Bs[k][tx * TN + c];
+#pragma unroll
+            for (int r = 0; r < TM; r++)
+#pragma unroll
+                for (int c = 0; c < TN; c++) acc[r][c] = fmaf(a[r], bb[c], acc[r][c]);
+        }
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int r = 0; r < TM; r++) {
+        int i = i0 + ty * TM + r;
+        if (i >= d.N) continue;
+#pragma unroll
+        for (int c = 0; c < TN; c++) {
+            int j = j0 + tx * TN + c;
+            if (j >= d.M) continue;
+            T *p = C + (long long)i * d.c_rs + (long long)j * d.c_cs;
+            float v = acc[r][c] * d.alpha;
+            if (d.accumulate) v += ld(p);
+            if (d.bias_mode == 1) v += ld(d.bias + i);
+            else if (d.bias_mode == 2) v += ld(d.bias + j);
+            st(p, v);
+        }
+    }
+}
+
+// Tensor-core path (tl_gemm_tc.cu); returns false when the shape/layout does not qualify.
+template <class T> bool gemm_tensor_core(const GemmDesc<T> &d);
+
+template <class T> void gemm(const GemmDesc<T> &d)
+{
+    if (d.N <= 0 || d.M <= 0 || d.batch <= 0) return;
+    if (gemm_path() != 1 && gemm_tensor_core<T>(d)) return;
+    long long tiles64 = (long long)ceil_div(d.N, 64) * ceil_div(d.M, 64) * d.batch;
+    if (tiles64 >= sm_count() || (d.N > 32 && d.M > 32 && tiles64 * 4 >= 2 * sm_count())) {
+        dim3 grid(ceil_div(d.M, 64), ceil_div(d.N, 64), d.batch);
+        TL_LAUNCH((gemm_ffma_kernel<T, 64, 64, 4, 4>), grid, 256, 0, d);
+    } else {
+        dim3 grid(ceil_div(d.M, 32), ceil_div(d.N, 32), d.batch);
+        TL_LAUNCH((gemm_ffma_kernel<T, 32, 32, 2, 2>), grid, 256, 0, d);
+    }
+}
+
+template <class T> void mm_contract(const T *A, const T *B, T *C, int N, int K, int M, int trans_B, bool accumulate)
+{
+    GemmDesc<T> d;
+    d.A = A; d.B = B; d.C = C; d.N = N; d.M = M; d.K = K;
+    d.a_rs = K; d.a_cs = 1;
+    if (trans_B) { d.b_rs = 1; d.b_cs = K; } else { d.b_rs = M; d.b_cs = 1; }
+    d.c_rs = M; d.c_cs = 1;
+    d.accumulate = accumulate;
+    gemm<T>(d);
+}
+
+// ------------------------------------------------------------------ batch-1 Linear (HBM-bound)
+// y[o] = sum_i W[o][i] x[i] (+ b[o]).  One warp per output row: each lane streams 16-byte
+// pieces of the row, partial sums meet in a shuffle tree.  Rows are `in` elements apart, so
+// 16-byte loads need in % (16/sizeof(T)) == 0; otherwise the scalar tail loop does all of it.
+template <class T, int VEC>
+__device__ __forceinline__ float dot_row(const T *__restrict__ w, const T *__restrict__ x, int n, int lane);
+
+template <> __device__ __forceinline__ float dot_row<float, 4>(const float *__restrict__ w, const float *__restrict__ x, int n, int lane)
+{
+    float s = 0.f;
+    int n4 = ((((uintptr_t)w | (uintptr_t)x) & 15) == 0) ? n / 4 : 0;
+    const float4 *w4 = (const float4 *)w, *x4 = (const float4 *)x;
+    for (int i = lane; i < n4; i += 32) {
+        float4 a = __ldcs(w4 + i), b = __ldg(x4 + i);
+        s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
+    }
+    for (int i = n4 * 4 + lane; i < n; i += 32) s = fmaf(w[i], x[i], s);
+    return s;
+}
+template <> __device__ __forceinline__ float dot_row<__half, 8>(const __half *__restrict__ w, const __half *__restrict__ x, int n, int lane)
+{
+    float s = 0.f;
+    int n8 = ((((uintptr_t)w | (uintptr_t)x) & 15) == 0) ? n / 8 : 0;
+    const uint4 *w8 = (const uint4 *)w, *x8 = (const uint4 *)x;
+    for (int i = lane; i < n8; i += 32) {
+        uint4 a = __ldcs(w8 + i), b = __ldg(x8 + i);
+        const __half2 *ah = (const __half2 *)&a, *bh = (const __half2 *)&b;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float2 af = __half22float2(ah[q]), bf = __half22float2(bh[q]);
+            s = fmaf(af.x, bf.x, s); s = fmaf(af.y, bf.y, s);
+        }
+    }
+    for (int i = n8 * 8 + lane; i < n; i += 32) s = fmaf(__half2float(w[i]), __half2float(x[i]), s);
+    return s;
+}
+
+template <class T, int VEC>
+__global__ void __launch_bounds__(256) linear_fw_kernel(const T *__restrict__ W, const T *__restrict__ x,
+                                                        const T *__restrict__ bias, T *__restrict__ y, int out, int in)
+{
+    const int lane = threadIdx.x & 31;
+    const int warps_per_block = blockDim.x >> 5;
+    for (int o = blockIdx.x * warps_per_block + (threadIdx.x >> 5); o < out; o += gridDim.x * warps_per_block) {
+        float s = dot_row<T, VEC>(W + (long long)o * in, x, in, lane);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+        if (lane == 0) st(y + o, bias ? s + ld(bias + o) : s);
+    }
+}
+
+template <class T> void linear_fw_gemv(const T *W, const T *x, const T *bias, T *y, int out, int in)
+{
+    int blocks = ceil_div(out, 8);
+    int cap = sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    if (sizeof(T) == 4) TL_LAUNCH((linear_fw_kernel<T, sizeof(T) == 4 ? 4 : 8>), blocks, 256, 0, W, x, bias, y, out, in);
+    else TL_LAUNCH((linear_fw_kernel<T, sizeof(T) == 4 ? 4 : 8>), blocks, 256, 0, W, x, bias, y, out, in);
+}
+
+// dW[o][i] = dy[o] * x[i]: a pure 16-byte-store stream over the out x in matrix.
+template <class T>
+__global__ void __launch_bounds__(256) linear_wg_kernel(const T *__restrict__ dy, const T *__restrict__ x,
+                                                        T *__restrict__ dW, int out, int in)
+{
+    constexpr int V = 16 / sizeof(T);
+    const long long total = (long long)out * in;
+    const bool vec_ok = (in % V == 0) && (((uintptr_t)dW & 15) == 0) && (((uintptr_t)x & 15) == 0);
+    if (vec_ok) {
+        const long long nvec = total / V;
+        const int row_vecs = in / V;
+        for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < nvec; e += (long long)gridDim.x * blockDim.x) {
+            int o = (int)(e / row_vecs), iv = (int)(e % row_vecs);
+            float g = ld(dy + o);
+            if (sizeof(T) == 4) {
+                float4 xv = __ldg((const float4 *)x + iv);
+                float4 r = make_float4(g * xv.x, g * xv.y, g * xv.z, g * xv.w);
+                __stcs((float4 *)dW + e, r);
+            } else {
+                uint4 xv = __ldg((const uint4 *)x + iv);
+                const __half2 *xh = (const __half2 *)&xv;
+                uint4 r; __half2 *rh = (__half2 *)&r;
+#pragma unroll
+                for (int q = 0; q < 4; q++) { float2 f = __half22float2(xh[q]); rh[q] = __floats2half2_rn(g * f.x, g * f.y); }
+                __stcs((uint4 *)dW + e, r);
+            }
+        }
+    } else {
+        for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+            int o = (int)(e / in), i = (int)(e % in);
+            st(dW + e, ld(dy + o) * ld(x + i));
+        }
+    }
+}
+
+template <class T> void linear_wg_outer(const T *dy, const T *x, T *dW, int out, int in)
+{
+    long long work = ((long long)out * in) / (16 / sizeof(T)) + 1;
+    int blocks = (int)((work + 255) / 256);
+    int cap = sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    TL_LAUNCH((linear_wg_kernel<T>), blocks, 256, 0, dy, x, dW, out, in);
+}
+
+// dx[i] = sum_o W[o][i] dy[o].  The matrix is cut into row slabs; a CTA owns one slab and a
+// 16-byte-wide column strip per thread, so every load is coalesced and W is read exactly once.
+// Slab partials land in `part[slab][in]` and a second kernel adds them in slab order
+// (deterministic; no atomics).
+template <class T>
+__global__ void __launch_bounds__(128) linear_ig_partial_kernel(const T *__restrict__ W, const T *__restrict__ dy,
+                                                                float *__restrict__ part, int out, int in, int rows_per_slab)
+{
+    constexpr int V = 16 / sizeof(T);
+    const int slab = blockIdx.y;
+    const int o_begin = slab * rows_per_slab;
+    const int o_end = min(out, o_begin + rows_per_slab);
+    const int col0 = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (col0 >= in) return;
+    float acc[V];
+#pragma unroll
+    for (int q = 0; q < V; q++) acc[q] = 0.f;
+    const bool vec_ok = (in % V == 0) && (((uintptr_t)W & 15) == 0);
+    if (vec_ok) {
+        for (int o = o_begin; o < o_end; o++) {
+            float g = ld(dy + o);
+            if (sizeof(T) == 4) {
+                float4 w = __ldcs((const float4 *)(W + (long long)o * in + col0));
+                acc[0] = fmaf(w.x, g, acc[0]); acc[1] = fmaf(w.y, g, acc[1]);
+                acc[2] = fmaf(w.z, g, acc[2]); acc[3] = fmaf(w.w, g, acc[3]);
+            } else {
+                uint4 w = __ldcs((const uint4 *)(W + (long long)o * in + col0));
+                const __half2 *wh = (const __half2 *)&w;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float2 f = __half22float2(wh[q]);
+                    acc[2 * q] = fmaf(f.x, g, acc[2 * q]); acc[2 * q + 1] = fmaf(f.y, g, acc[2 * q + 1]);
+                }
+            }
+        }
+    } else {
+        for (int o = o_begin; o < o_end; o++) {
+            float g = ld(dy + o);
+#pragma unroll
+            for (int q = 0; q < V; q++)
+                if (col0 + q < in) acc[q] = fmaf(ld(W + (long long)o * in + col0 + q), g, acc[q]);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < V; q++)
+        if (col0 + q < in) part[(long long)slab * in + col0 + q] = acc[q];
+}
+
+template <class T>
+__global__ void linear_ig_reduce_kernel(const float *__restrict__ part, T *__restrict__ dx, int in, int slabs)
+{
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= in) return;
+    float s = 0.f;
+    for (int b = 0; b < slabs; b++) s += part[(long long)b * in + i];
+    st(dx + i, s);
+}
+
+template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx, int out, int in)
+{
+    constexpr int V = 16 / sizeof(T);
+    int col_blocks = ceil_div(ceil_div(in, V), 128);
+    // enough slabs to put ~4 CTAs on every SM, at least 8 rows each
+    int slabs = ceil_div(4 * sm_count(), col_blocks);
+    if (slabs > ceil_div(out, 8)) slabs = ceil_div(out, 8);
+    if (slabs < 1) slabs = 1;
+    int rows_per_slab = ceil_div(out, slabs);
+    slabs = ceil_div(out, rows_per_slab);
+    float *part = sc.scratch<float>((size_t)slabs * in);
+    if (!part) return;
+    TL_LAUNCH((linear_ig_partial_kernel<T>), dim3(col_blocks, slabs), 128, 0, W, dy, part, out, in, rows_per_slab);
+    TL_LAUNCH((linear_ig_reduce_kernel<T>), ceil_div(in, 256), 256, 0, part, dx, in, slabs);
+}
+
+#define INST(T)                                                                                             \
+    template void gemm<T>(const GemmDesc<T> &);                                                             \
+    template void mm_contract<T>(const T *, const T *, T *, int, int, int, int, bool);                      \
+    template void linear_fw_gemv<T>(const T *, const T *, const T *, T *, int, int);                        \
+    template void linear_wg_outer<T>(const T *, const T *, T *, int, int);                                  \
+    template void linear_ig_gemv<T>(Scope &, const T *, const T *, T *, int, int);
+INST(float)
+INST(__half)
+
+} // namespace tl

@@ -1,0 +1,100 @@
+// Launchers of the device kernels (one declaration per operation; defined in the tl_*.cu files).
+#pragma once
+#include "tl_common.h"
+
+namespace tl {
+
+// ---------------------------------------------------------------- GEMM
+// C[i][j] (+)= alpha * sum_k A(i,k) * B(k,j) (+ bias), i < N, j < M, k < K, per batch b:
+//   A(i,k) = A[b*a_bs + i*a_rs + k*a_cs],  B(k,j) = B[b*b_bs + k*b_rs + j*b_cs],
+//   C(i,j) = C[b*c_bs + i*c_rs + j*c_cs].
+// Accumulation is fp32 for every storage type.
+template <class T> struct GemmDesc {
+    const T *A = nullptr; const T *B = nullptr; T *C = nullptr;
+    int N = 0, M = 0, K = 0;
+    long long a_rs = 0, a_cs = 1, b_rs = 0, b_cs = 1, c_rs = 0, c_cs = 1;
+    int batch = 1; long long a_bs = 0, b_bs = 0, c_bs = 0;
+    float alpha = 1.f;
+    bool accumulate = false;        // C += result instead of C = result
+    const T *bias = nullptr;        // added after the product
+    int bias_mode = 0;              // 1: bias[i] (per row), 2: bias[j] (per column)
+};
+template <class T> void gemm(const GemmDesc<T> &d);
+
+// Reference-contract product: C[N x M] = A[N x K] * B, B is [K x M] or (trans_B) [M x K].
+template <class T> void mm_contract(const T *A, const T *B, T *C, int N, int K, int M, int trans_B, bool accumulate);
+
+// Batch-1 Linear kernels (HBM-bound): y = W x (+b), dW = dy (x) x, dx = W^T dy.
+template <class T> void linear_fw_gemv(const T *W, const T *x, const T *bias, T *y, int out, int in);
+template <class T> void linear_wg_outer(const T *dy, const T *x, T *dW, int out, int in);
+template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx, int out, int in);
+
+// ---------------------------------------------------------------- convolution
+struct ConvGeom {
+    int Cin, Hin, Win, Cout, Hk, Wk, Hout, Wout;
+    int sh, sw, padU, padL;
+    int n;                 // independent streams
+    bool depthwise;        // Cout == Cin, one filter per channel
+    bool hwc;              // activations HWC, weights [Cout][Hk][Wk][Cin]
+};
+template <class T> void conv_fw(const ConvGeom &g, const T *x, const T *w, const T *bias, T *y);
+template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const T *dy, T *dw, T *dbias);
+template <class T> void conv_ig(const ConvGeom &g, const T *dy, const T *w, T *dx);
+template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
+                               int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
+template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk, int Wk, int hwc);
+
+// ---------------------------------------------------------------- elementwise / reductions
+enum ActKind { ACT_RELU = 0, ACT_LEAKY = 1, ACT_SIGMOID = 2, ACT_GELU = 3 };
+template <class T> void act_fw(int kind, const T *x, T *y, long long n, float slope);
+template <class T> void act_bw(int kind, const T *x, const T *y, const T *dy, T *dx, long long n, float slope);
+template <class T> void softmax_fw(const T *in, T *out, T *maxes, T *sums, int rows, int width, int batch);
+template <class T> void softmax_bw(const T *out, const T *dout, T *din, T *sums, int rows, int width, int batch);
+// groups = streams * channels, each of D contiguous elements.
+template <class T> void instnorm_fw(const T *x, T *y, const T *gamma_beta, T *mean, T *var, T *stdev,
+                                    int n, int C, int D, bool frozen, float eps);
+template <class T> void instnorm_bw_input(const T *x, const T *dy, T *dx, const T *gamma, const T *mean,
+                                          const T *var, const T *stdev, int n, int C, int D);
+template <class T> void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgamma_beta, const T *mean,
+                                          const T *stdev, int n, int C, int D);
+template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps);
+template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps);
+template <class T> void mse_fw(const T *y, const T *t, T *loss, int dim, int n);
+template <class T> void mse_bw(const T *y, const T *t, T *dy, int dim, int n);
+template <class T> void ce_fw(const T *z, const T *t, T *loss, int dim, int n);
+template <class T> void ce_bw(const T *z, const T *t, T *dz, int dim, int n);
+template <class T> void sgd(T *w, T *g, long long n, float lr, float lambda);
+template <class T> void add(const T *a, const T *b, T *c, long long n);
+template <class T> void copy_n(const T *from, T *to, long long n);
+template <class T> void fill(T *to, float v, long long n);
+template <class T> void scale(T *x, float s, long long n);
+template <class T> void bias_add_rows(T *mat, const T *bias, int H, int W, int per_row);
+template <class T> void avgpool_fw(const T *x, T *y, int n, int C, int H, int W, int Ho, int Wo, int Hk, int Wk, int sh, int sw);
+template <class T> void avgpool_bw(const T *dy, T *dx, int n, int C, int H, int W, int Ho, int Wo, int Hk, int Wk, int sh, int sw);
+template <class T> void transpose_nd(const T *in, T *out, const int *dims, const int *axes, int nd);
+template <class T> void broadcast_add(const T *a, const T *b, T *c, const int *da, int na, const int *db, int nb);
+template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int padL, int padR, int padU, int padD, int hwc);
+template <class T> void row_max(const T *in, T *maxes, int rows, int width);
+template <class T> void exp_sum(const T *in, T *out, const T *maxes, T *sums, int rows, int width);
+template <class T> void row_div(T *io, const T *sums, int rows, int width);
+template <class T> void mean_std(const T *x, T *mean, T *var, T *stdev, int D, float eps);
+void cast_h2f(const __half *src, float *dst, long long n);
+void cast_f2h(const float *src, __half *dst, long long n);
+
+// ---------------------------------------------------------------- attention
+struct MhsaDims { int L, E, F, heads; };
+template <class T> void mhsa_fw(Scope &sc, const MhsaDims &d, const T *x, const T *wq, const T *wk, const T *wv,
+                                const T *bq, const T *bk, const T *bv, const T *wo,
+                                T *q, T *k, T *v, T *softmax, T *att, T *y);
+template <class T> void mhsa_bw(Scope &sc, const MhsaDims &d, const T *x, const T *wq, const T *wk, const T *wv,
+                                const T *wo, const T *q, const T *k, const T *v, const T *softmax, const T *att,
+                                const T *dy, T *dq, T *dk, T *dv, T *dsoftmax, T *datt, T *grad_scratch,
+                                T *dwq, T *dwk, T *dwv, T *dwo, T *dx);
+
+// ---------------------------------------------------------------- device scalar helpers
+__device__ __forceinline__ float ld(const float *p) { return *p; }
+__device__ __forceinline__ float ld(const __half *p) { return __half2float(*p); }
+__device__ __forceinline__ void st(float *p, float v) { *p = v; }
+__device__ __forceinline__ void st(__half *p, float v) { *p = __float2half_rn(v); }
+
+} // namespace tl

@@ -1,0 +1,120 @@
+// Multi-head self-attention, forward and backward, composed from strided GEMMs and the row
+// softmax kernels.  The reference materialises eight transposes per pass
+// [ref: lib/sources/pulp_mhsa_fp32.c:20-644 (FW), :648-1745 (BW)]; here every transposed
+// operand is expressed through GEMM strides and the per-head products run as one batched launch.
+//
+// Layouts (reference convention): x, y are E x L (token index fastest); Wq/Wk/Wv/Wo are E x F;
+// q, k, v, att are F x L; softmax is heads x L x L indexed [head][query][key].
+#include "tl_kernels.h"
+
+namespace tl {
+
+// 32-bit restatement of the reference's fast inverse square root (one Newton step)
+// [ref: lib/sources/pulp_train_utils_fp32.c:1234-1247; the `long` pun there is 64-bit on LP64].
+static float q_rsqrt_host(float number)
+{
+    union { float f; int32_t i; } u;
+    float x2 = number * 0.5f;
+    u.f = number;
+    u.i = 0x5f3759df - (u.i >> 1);
+    return u.f * (1.5f - (x2 * u.f * u.f));
+}
+
+template <class T>
+void mhsa_fw(Scope &sc, const MhsaDims &d, const T *x, const T *wq, const T *wk, const T *wv,
+             const T *bq, const T *bk, const T *bv, const T *wo,
+             T *q, T *k, T *v, T *softmax, T *att, T *y)
+{
+    const int L = d.L, E = d.E, F = d.F, NH = d.heads, H = F / NH;
+    const float scaling = q_rsqrt_host((float)H);
+
+    // projections: q = Wq^T x (+ bq per row)  [ref: pulp_mhsa_fp32.c:87-158 and twins for k, v]
+    const T *ws[3] = {wq, wk, wv}; const T *bs[3] = {bq, bk, bv}; T *outs[3] = {q, k, v};
+    for (int p = 0; p < 3; p++) {
+        GemmDesc<T> g;
+        g.A = ws[p]; g.a_rs = 1; g.a_cs = F;
+        g.B = x; g.b_rs = L; g.b_cs = 1;
+        g.C = outs[p]; g.c_rs = L;
+        g.N = F; g.K = E; g.M = L;
+        if (bs[p]) { g.bias = bs[p]; g.bias_mode = 1; }
+        gemm<T>(g);
+    }
+    // scores[h][query][key] = scaling * sum_d q[h,d,query] k[h,d,key]   [ref: :348-431]
+    T *scores = sc.scratch<T>((size_t)NH * L * L);
+    if (!scores) return;
+    {
+        GemmDesc<T> g;
+        g.A = q; g.a_rs = 1; g.a_cs = L; g.a_bs = (long long)H * L;
+        g.B = k; g.b_rs = L; g.b_cs = 1; g.b_bs = (long long)H * L;
+        g.C = scores; g.c_rs = L; g.c_bs = (long long)L * L;
+        g.N = L; g.K = H; g.M = L; g.batch = NH; g.alpha = scaling;
+        gemm<T>(g);
+    }
+    // softmax over keys   [ref: :464-491]
+    softmax_fw<T>(scores, softmax, (T *)nullptr, (T *)nullptr, L, L, NH);
+    // att[h,d,query] = sum_key v[h,d,key] P[h,query,key]   [ref: :530-560]
+    {
+        GemmDesc<T> g;
+        g.A = v; g.a_rs = L; g.a_cs = 1; g.a_bs = (long long)H * L;
+        g.B = softmax; g.b_rs = 1; g.b_cs = L; g.b_bs = (long long)L * L;
+        g.C = att; g.c_rs = L; g.c_bs = (long long)H * L;
+        g.N = H; g.K = L; g.M = L; g.batch = NH;
+        gemm<T>(g);
+    }
+    // y = Wo att   [ref: :612]
+    mm_contract<T>(wo, att, y, E, F, L, 0, false);
+}
+
+template <class T>
+void mhsa_bw(Scope &sc, const MhsaDims &d, const T *x, const T *wq, const T *wk, const T *wv,
+             const T *wo, const T *q, const T *k, const T *v, const T *softmax, const T *att,
+             const T *dy, T *dq, T *dk, T *dv, T *dsoftmax, T *datt, T *grad_scratch,
+             T *dwq, T *dwk, T *dwv, T *dwo, T *dx)
+{
+    (void)grad_scratch;
+    const int L = d.L, E = d.E, F = d.F, NH = d.heads, H = F / NH;
+    const float scaling = q_rsqrt_host((float)H);
+    const long long HL = (long long)H * L, LL = (long long)L * L;
+
+    // dWo = dY att^T   [ref: pulp_mhsa_fp32.c:704-760]
+    { GemmDesc<T> g; g.A = dy; g.a_rs = L; g.B = att; g.b_rs = 1; g.b_cs = L; g.C = dwo; g.c_rs = F; g.N = E; g.K = L; g.M = F; gemm<T>(g); }
+    // datt = Wo^T dY   [ref: :783-837]
+    { GemmDesc<T> g; g.A = wo; g.a_rs = 1; g.a_cs = F; g.B = dy; g.b_rs = L; g.C = datt; g.c_rs = L; g.N = F; g.K = E; g.M = L; gemm<T>(g); }
+    // dv[h,d,key] = sum_query datt[h,d,query] P[h,query,key]   [ref: :842-895]
+    { GemmDesc<T> g; g.A = datt; g.a_rs = L; g.a_bs = HL; g.B = softmax; g.b_rs = L; g.b_bs = LL; g.C = dv; g.c_rs = L; g.c_bs = HL;
+      g.N = H; g.K = L; g.M = L; g.batch = NH; gemm<T>(g); }
+    // dP[h,query,key] = sum_d datt[h,d,query] v[h,d,key]   [ref: :923-1050, with the corrected V transpose]
+    { GemmDesc<T> g; g.A = datt; g.a_rs = 1; g.a_cs = L; g.a_bs = HL; g.B = v; g.b_rs = L; g.b_bs = HL; g.C = dsoftmax; g.c_rs = L; g.c_bs = LL;
+      g.N = L; g.K = H; g.M = L; g.batch = NH; gemm<T>(g); }
+    // dS = softmax backward   [ref: :1052-1100]
+    T *dS = sc.scratch<T>((size_t)NH * LL);
+    if (!dS) return;
+    softmax_bw<T>(softmax, dsoftmax, dS, (T *)nullptr, L, L, NH);
+    // dk[h,d,key] = scaling * sum_query q[h,d,query] dS[h,query,key]   [ref: :1140-1330]
+    { GemmDesc<T> g; g.A = q; g.a_rs = L; g.a_bs = HL; g.B = dS; g.b_rs = L; g.b_bs = LL; g.C = dk; g.c_rs = L; g.c_bs = HL;
+      g.N = H; g.K = L; g.M = L; g.batch = NH; g.alpha = scaling; gemm<T>(g); }
+    // dq[h,d,query] = scaling * sum_key k[h,d,key] dS[h,query,key]   [ref: :1340-1400]
+    { GemmDesc<T> g; g.A = k; g.a_rs = L; g.a_bs = HL; g.B = dS; g.b_rs = 1; g.b_cs = L; g.b_bs = LL; g.C = dq; g.c_rs = L; g.c_bs = HL;
+      g.N = H; g.K = L; g.M = L; g.batch = NH; g.alpha = scaling; gemm<T>(g); }
+    // projection weight grads, stored F x E: dW = dproj x^T   [ref: :1426-1600]
+    const T *dps[3] = {dq, dk, dv}; T *dws[3] = {dwq, dwk, dwv}; const T *ws[3] = {wq, wk, wv};
+    for (int p = 0; p < 3; p++) {
+        GemmDesc<T> g; g.A = dps[p]; g.a_rs = L; g.B = x; g.b_rs = 1; g.b_cs = L; g.C = dws[p]; g.c_rs = E; g.N = F; g.K = L; g.M = E;
+        gemm<T>(g);
+    }
+    // dx += Wq dq + Wk dk + Wv dv (the caller zeroes dx; same order as the reference)   [ref: :1605-1745]
+    for (int p = 0; p < 3; p++) {
+        GemmDesc<T> g; g.A = ws[p]; g.a_rs = F; g.B = dps[p]; g.b_rs = L; g.C = dx; g.c_rs = L; g.N = E; g.K = F; g.M = L; g.accumulate = true;
+        gemm<T>(g);
+    }
+}
+
+#define INST(T)                                                                                                        \
+    template void mhsa_fw<T>(Scope &, const MhsaDims &, const T *, const T *, const T *, const T *, const T *, const T *, \
+                             const T *, const T *, T *, T *, T *, T *, T *, T *);                                      \
+    template void mhsa_bw<T>(Scope &, const MhsaDims &, const T *, const T *, const T *, const T *, const T *, const T *, \
+                             const T *, const T *, const T *, const T *, const T *, T *, T *, T *, T *, T *, T *, T *, T *, T *, T *, T *);
+INST(float)
+INST(__half)
+
+} // namespace tl

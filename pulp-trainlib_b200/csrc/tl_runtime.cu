@@ -1,0 +1,304 @@
+// Runtime of libtrainlib_b200: device context, error state, staging arena, memory modes,
+// streams mode, timers and the PMSIS stand-in (pi_cl_team_fork & friends).
+#include "tl_common.h"
+#include "../../include/pmsis.h"
+#include <cstdarg>
+#include <cstring>
+#include <cstdlib>
+#include <mutex>
+
+namespace tl {
+
+struct Chunk { char *base; size_t cap; size_t off; };
+
+struct Context {
+    bool inited = false;
+    bool failed = false;
+    int device = 0;
+    int sms = 148;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t cur_stream = nullptr;
+    int mem_mode = TL_MEM_AUTO;
+    int n_streams = 1;
+    int gemm_path = 0;
+    long long launches = 0;
+    std::vector<Chunk> chunks;     // staging arena; normally exactly one chunk
+    int scope_depth = 0;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int err = TL_OK;
+    char err_msg[512] = {0};
+};
+static Context g;
+
+void set_error(int code, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    char buf[480];
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "[trainlib_b200] %s\n", buf);
+    if (g.err == TL_OK || code == TL_ERR_CUDA) {     // first error wins; CUDA errors are sticky
+        if (!(g.err == TL_ERR_CUDA)) { g.err = code; snprintf(g.err_msg, sizeof g.err_msg, "%s", buf); }
+    }
+}
+
+bool cuda_ok(cudaError_t e, const char *what)
+{
+    if (e == cudaSuccess) return true;
+    set_error(TL_ERR_CUDA, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+    return false;
+}
+
+static int init_device(int device)
+{
+    if (g.inited) return g.failed ? g.err : TL_OK;
+    g.inited = true;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n <= 0) {
+        g.failed = true;
+        set_error(TL_ERR_NO_DEVICE, "no CUDA device available (%s); this library has no CPU fallback",
+                  e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+        return g.err;
+    }
+    if (device < 0) {
+        const char *env = getenv("TRAINLIB_B200_DEVICE");
+        device = env ? atoi(env) : -1;
+        if (device < 0) { if (cudaGetDevice(&device) != cudaSuccess) device = 0; }
+    }
+    if (!TL_CUDA(cudaSetDevice(device))) { g.failed = true; return g.err; }
+    g.device = device;
+    cudaDeviceProp prop;
+    if (TL_CUDA(cudaGetDeviceProperties(&prop, device))) g.sms = prop.multiProcessorCount;
+    if (!TL_CUDA(cudaStreamCreateWithFlags(&g.own_stream, cudaStreamNonBlocking))) { g.failed = true; return g.err; }
+    g.cur_stream = g.own_stream;
+    TL_CUDA(cudaEventCreate(&g.ev0));
+    TL_CUDA(cudaEventCreate(&g.ev1));
+    return TL_OK;
+}
+
+bool ready() { return init_device(-1) == TL_OK && g.err != TL_ERR_CUDA && g.err != TL_ERR_NO_DEVICE; }
+cudaStream_t stream() { return g.cur_stream; }
+int streams() { return g.n_streams; }
+int sm_count() { return g.sms; }
+int gemm_path() { return g.gemm_path; }
+void count_launch() { g.launches++; }
+
+bool is_device_pointer(const void *p)
+{
+    if (p == nullptr) return false;
+    if (g.mem_mode == TL_MEM_DEVICE) return true;
+    if (g.mem_mode == TL_MEM_HOST) return false;
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, p);
+    if (e != cudaSuccess) { cudaGetLastError(); return false; }
+    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+// ---------------------------------------------------------------- arena
+static size_t arena_mark()
+{
+    // position encoded as (chunk index << 48) | offset; scopes nest in stack order
+    if (g.chunks.empty()) return 0;
+    return ((size_t)(g.chunks.size() - 1) << 48) | g.chunks.back().off;
+}
+
+static void arena_release(size_t mark)
+{
+    if (g.chunks.empty()) return;
+    size_t idx = mark >> 48, off = mark & (((size_t)1 << 48) - 1);
+    if (g.scope_depth == 0) {
+        // top level: merge a fragmented arena into one chunk of the total size
+        if (g.chunks.size() > 1) {
+            size_t total = 0;
+            cudaStreamSynchronize(g.cur_stream);
+            for (auto &c : g.chunks) { total += c.cap; cudaFree(c.base); }
+            g.chunks.clear();
+            char *base = nullptr;
+            if (TL_CUDA(cudaMalloc(&base, total))) g.chunks.push_back({base, total, 0});
+        } else {
+            g.chunks[0].off = 0;
+        }
+        return;
+    }
+    if (idx < g.chunks.size()) {
+        for (size_t i = idx + 1; i < g.chunks.size(); i++) g.chunks[i].off = 0;
+        g.chunks[idx].off = off;
+    }
+}
+
+static void *arena_alloc(size_t bytes)
+{
+    bytes = (bytes + 255) & ~(size_t)255;
+    if (bytes == 0) bytes = 256;
+    for (size_t i = g.chunks.empty() ? 0 : g.chunks.size() - 1; i < g.chunks.size(); i++) {
+        Chunk &c = g.chunks[i];
+        if (c.off + bytes <= c.cap) { void *p = c.base + c.off; c.off += bytes; return p; }
+    }
+    size_t cap = (size_t)64 << 20;
+    if (!g.chunks.empty()) cap = g.chunks.back().cap * 2;
+    while (cap < bytes) cap *= 2;
+    char *base = nullptr;
+    if (!TL_CUDA(cudaMalloc(&base, cap))) return nullptr;
+    g.chunks.push_back({base, cap, bytes});
+    return base;
+}
+
+Scope::Scope() : arena_mark_(0), ok_(true), staged_(false)
+{
+    ok_ = ready();
+    arena_mark_ = arena_mark();
+    g.scope_depth++;
+}
+
+void *Scope::alloc(size_t bytes)
+{
+    void *p = arena_alloc(bytes);
+    if (!p) ok_ = false;
+    return p;
+}
+
+void *Scope::map(void *p, size_t bytes, bool copy_in, bool copy_out)
+{
+    if (p == nullptr || !ok_) return nullptr;
+    if (is_device_pointer(p)) return p;
+    for (auto &e : entries_) {
+        if (e.host == p && e.bytes >= bytes) { e.write_back |= copy_out; return e.dev; }
+    }
+    void *d = arena_alloc(bytes);
+    if (!d) { ok_ = false; return nullptr; }
+    staged_ = true;
+    if (copy_in) {
+        if (!TL_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, g.cur_stream))) ok_ = false;
+    }
+    entries_.push_back({p, d, bytes, copy_out});
+    return d;
+}
+
+Scope::~Scope()
+{
+    if (staged_) {
+        for (auto &e : entries_)
+            if (e.write_back) TL_CUDA(cudaMemcpyAsync(e.host, e.dev, e.bytes, cudaMemcpyDeviceToHost, g.cur_stream));
+        TL_CUDA(cudaStreamSynchronize(g.cur_stream));
+    }
+    g.scope_depth--;
+    arena_release(arena_mark_);
+}
+
+} // namespace tl
+
+using namespace tl;
+
+// ==================================================================== public C ABI
+#pragma GCC visibility push(default)
+extern "C" {
+
+int trainlib_last_error(void) { return g.err; }
+const char *trainlib_last_error_string(void) { return g.err_msg; }
+void trainlib_clear_error(void) { if (g.err != TL_ERR_CUDA && g.err != TL_ERR_NO_DEVICE) { g.err = TL_OK; g.err_msg[0] = 0; } }
+
+int trainlib_init(int device) { return init_device(device); }
+int trainlib_device(void) { return g.device; }
+void trainlib_set_stream(void *s) { if (ready()) g.cur_stream = s ? (cudaStream_t)s : g.own_stream; }
+void *trainlib_stream(void) { return ready() ? (void *)g.cur_stream : nullptr; }
+void trainlib_synchronize(void) { if (ready()) TL_CUDA(cudaStreamSynchronize(g.cur_stream)); }
+
+void trainlib_set_memory_mode(int mode) { if (mode >= TL_MEM_AUTO && mode <= TL_MEM_HOST) g.mem_mode = mode; }
+int trainlib_memory_mode(void) { return g.mem_mode; }
+void *trainlib_malloc(size_t bytes)
+{
+    if (!ready()) return nullptr;
+    void *p = nullptr;
+    if (!TL_CUDA(cudaMalloc(&p, bytes ? bytes : 256))) return nullptr;
+    return p;
+}
+void trainlib_free(void *p) { if (p && ready()) { cudaStreamSynchronize(g.cur_stream); TL_CUDA(cudaFree(p)); } }
+void *trainlib_malloc_host(size_t bytes)
+{
+    if (!ready()) return nullptr;
+    void *p = nullptr;
+    if (!TL_CUDA(cudaMallocHost(&p, bytes ? bytes : 256))) return nullptr;
+    return p;
+}
+void trainlib_free_host(void *p) { if (p && ready()) TL_CUDA(cudaFreeHost(p)); }
+int trainlib_memcpy_h2d(void *dev, const void *host, size_t bytes)
+{
+    if (!ready()) return g.err;
+    if (!TL_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, g.cur_stream))) return g.err;
+    return TL_CUDA(cudaStreamSynchronize(g.cur_stream)) ? TL_OK : g.err;
+}
+int trainlib_memcpy_d2h(void *host, const void *dev, size_t bytes)
+{
+    if (!ready()) return g.err;
+    if (!TL_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, g.cur_stream))) return g.err;
+    return TL_CUDA(cudaStreamSynchronize(g.cur_stream)) ? TL_OK : g.err;
+}
+int trainlib_memset(void *dev, int byte, size_t bytes)
+{
+    if (!ready()) return g.err;
+    return TL_CUDA(cudaMemsetAsync(dev, byte, bytes, g.cur_stream)) ? TL_OK : g.err;
+}
+
+void trainlib_set_streams(int n) { g.n_streams = n < 1 ? 1 : n; }
+int trainlib_streams(void) { return g.n_streams; }
+
+void trainlib_timer_start(void) { if (ready()) TL_CUDA(cudaEventRecord(g.ev0, g.cur_stream)); }
+double trainlib_timer_stop_ms(void)
+{
+    if (!ready()) return -1.0;
+    float ms = 0.f;
+    if (!TL_CUDA(cudaEventRecord(g.ev1, g.cur_stream))) return -1.0;
+    if (!TL_CUDA(cudaEventSynchronize(g.ev1))) return -1.0;
+    if (!TL_CUDA(cudaEventElapsedTime(&ms, g.ev0, g.ev1))) return -1.0;
+    return (double)ms;
+}
+long long trainlib_kernel_launches(void) { return g.launches; }
+void trainlib_set_gemm_path(int p) { g.gemm_path = (p >= 0 && p <= 2) ? p : 0; }
+int trainlib_gemm_path(void) { return g.gemm_path; }
+
+// -------------------------------------------------------------------- PMSIS stand-in
+static thread_local int t_core_id = 0;
+int pi_core_id(void) { return t_core_id; }
+void pi_cl_team_barrier(void) {}
+
+bool tl_is_library_worker(void (*fn)(void *));   // defined with the entry-point table
+
+void pi_cl_team_fork(int n, void (*fn)(void *), void *arg)
+{
+    if (fn == nullptr) return;
+    if (tl_is_library_worker(fn)) { fn(arg); return; }        // one launch does the whole tensor
+    for (int i = 0; i < (n < 1 ? 1 : n); i++) { t_core_id = i; fn(arg); }
+    t_core_id = 0;
+}
+
+void pi_cl_dma_cmd(uintptr_t ext, uintptr_t loc, int size, int dir, pi_cl_dma_cmd_t *cmd)
+{
+    (void)cmd;
+    if (dir == PI_CL_DMA_DIR_EXT2LOC) memcpy((void *)loc, (const void *)ext, (size_t)size);
+    else memcpy((void *)ext, (const void *)loc, (size_t)size);
+}
+void pi_cl_dma_cmd_2d(uintptr_t ext, uintptr_t loc, int size, int stride, int length, int dir, pi_cl_dma_cmd_t *cmd)
+{
+    (void)cmd;
+    if (length <= 0) return;
+    for (int done = 0, row = 0; done < size; done += length, row++) {
+        int n = size - done < length ? size - done : length;
+        char *e = (char *)ext + (size_t)row * (size_t)stride, *l = (char *)loc + done;
+        if (dir == PI_CL_DMA_DIR_EXT2LOC) memcpy(l, e, (size_t)n); else memcpy(e, l, (size_t)n);
+    }
+}
+void pi_cl_dma_cmd_wait(pi_cl_dma_cmd_t *cmd) { (void)cmd; }
+
+static double g_perf_ns = 0.0;
+void pi_perf_conf(unsigned events) { (void)events; }
+void pi_perf_reset(void) { g_perf_ns = 0.0; }
+void pi_perf_start(void) { trainlib_timer_start(); }
+void pi_perf_stop(void) { double ms = trainlib_timer_stop_ms(); if (ms > 0) g_perf_ns += ms * 1e6; }
+unsigned pi_perf_read(int event) { (void)event; return g_perf_ns > 4294967295.0 ? 4294967295u : (unsigned)g_perf_ns; }
+void *pi_l2_malloc(int bytes) { return malloc((size_t)(bytes > 0 ? bytes : 1)); }
+void pi_l2_free(void *p, int bytes) { (void)bytes; free(p); }
+
+} // extern "C"
+#pragma GCC visibility pop
