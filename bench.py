@@ -1,0 +1,294 @@
+#!/usr/bin/env python
+"""Benchmark of the matmul-centred training step (FW + WG-BW + IG-BW) through the C ABI.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c5|c2|c1|c3] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  `value` is measured with all tensors resident in HBM;
+`e2e` is the same step through the reference-facing C ABI with HOST buffers (pinned), so the
+host<->device copies are inside the timed region.  `--impl reference` times the reference's own
+C code (oracle/_ref/libpulp_ref_mt.so, pthread team of 8) on the host cores on a bounded sample.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+from __graft_entry__ import load_pkg  # noqa: E402
+
+F = np.float32
+REF_MT = os.path.join(ROOT, "oracle", "_ref", "libpulp_ref_mt.so")
+REF_MT_CORES = 8
+
+
+def peaks():
+    p = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            j = json.load(open(path))
+            p.update({k: j[k] for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained") if k in j})
+            p["source"] = "measured"
+        except Exception:
+            pass
+    return p
+
+
+class ClockSampler(object):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in self.lines:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ workloads
+class LinearSweep(object):
+    """config 2: Linear FW + WG + IG at batch 1 over (in,out) in {(256,256),(1024,1024),(4096,1024),(1024,4096)}."""
+    SHAPES = [(256, 256), (1024, 1024), (4096, 1024), (1024, 4096)]
+    name = "c2_linear_sweep_fw_wg_ig_batch1"
+
+    def __init__(self, pkg, lib, half):
+        self.pkg, self.lib, self.half = pkg, lib, half
+        self.dt = np.float16 if half else np.float32
+        self.es = 2 if half else 4
+        self.flops = sum(5.0 * i * o for i, o in self.SHAPES)
+        self.bytes = sum(3.0 * i * o * self.es for i, o in self.SHAPES)
+        self.units = 1
+        self.keep = pkg.Keep()
+        self.sfx = "_fp16" if half else ""
+
+    def _inputs(self, rng, inn, out):
+        return ((rng.standard_normal((out, inn)) / np.sqrt(inn)).astype(self.dt), rng.standard_normal(inn).astype(self.dt), rng.standard_normal(out).astype(self.dt))
+
+    def _args(self, W, x, dy, y, dW, dx, inn, out):
+        pk, k = self.pkg, self.keep
+        b = lambda d, g, dim: pk.make_blob(k, d, g, dim=dim, W=dim, half=self.half)
+        one = np.zeros(1, self.dt) if not isinstance(W, int) else W
+        return pk.make_args(k, "Linear_args" + self.sfx, input=b(x, dx, inn), coeff=pk.make_blob(k, W, dW, C=1, H=out, W=inn, half=self.half),
+                            bias=b(one, one, out), output=b(y, dy, out), skip_wg_grad=0, skip_in_grad=0, use_biases=0)
+
+    def setup_device(self):
+        rng = np.random.default_rng(2)
+        self.dev, self.args_dev = [], []
+        for inn, out in self.SHAPES:
+            W, x, dy = self._inputs(rng, inn, out)
+            bufs = [self.pkg.DeviceBuffer(self.lib, a) for a in (W, x, dy)] + [self.pkg.DeviceBuffer(self.lib, nbytes=n * self.es) for n in (out, out * inn, inn)]
+            self.dev.append(bufs)
+            self.args_dev.append(self._args(*[b.ptr for b in bufs], inn, out))
+        self.flush = self.pkg.DeviceBuffer(self.lib, nbytes=256 << 20)
+
+    def l2_flush(self):
+        self.lib.trainlib_memset(self.flush.ptr, 1, self.flush.nbytes)
+
+    def step_device(self):
+        for a in self.args_dev:
+            p = ctypes.byref(a)
+            getattr(self.lib, "pulp_linear_%s_fw_cl" % ("fp16" if self.half else "fp32"))(p)
+            getattr(self.lib, "pulp_linear_%s_bw_param_grads_cl" % ("fp16" if self.half else "fp32"))(p)
+            getattr(self.lib, "pulp_linear_%s_bw_input_grads_cl" % ("fp16" if self.half else "fp32"))(p)
+
+    def setup_host(self, lib):
+        """host-pointer arguments (pinned when our library provides the allocator)"""
+        rng = np.random.default_rng(2)
+        self.host, self.args_host = [], []
+        for inn, out in self.SHAPES:
+            W, x, dy = self._inputs(rng, inn, out)
+            arrs = [W, x, dy, np.zeros(out, self.dt), np.zeros((out, inn), self.dt), np.zeros(inn, self.dt)]
+            if lib is self.lib:
+                arrs = [pinned_like(self.pkg, lib, a) for a in arrs]
+            self.host.append(arrs)
+            self.args_host.append(self._args(*arrs, inn, out))
+        self.h2d = sum((2.0 * i * o + 2 * i + 2 * o) * self.es for i, o in self.SHAPES)
+        self.d2h = sum((o + i * o + i) * self.es for i, o in self.SHAPES)
+
+    def step_host(self, lib):
+        for a in self.args_host:
+            p = ctypes.byref(a)
+            getattr(lib, "pulp_linear_%s_fw_cl" % ("fp16" if self.half else "fp32"))(p)
+            getattr(lib, "pulp_linear_%s_bw_param_grads_cl" % ("fp16" if self.half else "fp32"))(p)
+            getattr(lib, "pulp_linear_%s_bw_input_grads_cl" % ("fp16" if self.half else "fp32"))(p)
+
+    def metric(self, ms):
+        return {"metric": "train_step_tflops", "unit": "TFLOP/s", "value": self.flops / (ms * 1e-3) / 1e12}
+
+    def roofline(self, ms, pk):
+        gbs = self.bytes / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                "peak_source": pk["source"], "kernel": "linear_fw/wg/ig (whole step)", "algorithmic_bytes": self.bytes}
+
+
+_pinned = []
+
+
+def pinned_like(pkg, lib, a):
+    """numpy array over pinned host memory from the library's allocator"""
+    ptr = lib.trainlib_malloc_host(max(a.nbytes, 16))
+    pkg.check(lib)
+    buf = (ctypes.c_char * a.nbytes).from_address(ptr)
+    out = np.frombuffer(buf, dtype=a.dtype).reshape(a.shape)
+    out[...] = a
+    _pinned.append((ptr, buf))
+    return out
+
+
+def make_workload(cfg, pkg, lib, dtype):
+    if cfg == "c2":
+        return LinearSweep(pkg, lib, dtype == "fp16")
+    if cfg == "c5":
+        from bench_nets import ResNet8Streams
+        return ResNet8Streams(pkg, lib)
+    raise SystemExit("unknown --config %s" % cfg)
+
+
+# ------------------------------------------------------------------------------------------------ runs
+def time_host_lib(wl, lib, steps, warmup):
+    wl.setup_host(lib)
+    for _ in range(warmup):
+        wl.step_host(lib)
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter(); wl.step_host(lib); ts.append(time.perf_counter() - t0)
+    return 1e3 * float(np.mean(ts))
+
+
+def run_reference(args, pkg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if not os.path.exists(REF_MT):
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libpulp_ref_mt.so was not built (needs the reference checkout at build time)"}))
+        return
+    ref = pkg.bind(ctypes.CDLL(REF_MT))
+    wl = make_workload(args.config, pkg, ref, args.dtype)
+    if hasattr(wl, "run_reference"):
+        line = wl.run_reference(ref, args)
+    else:
+        ms = time_host_lib(wl, ref, max(1, min(args.steps, 5)), max(1, min(args.warmup, 2)))
+        m = wl.metric(ms)
+        line = dict(m)
+        line.update({"ms_per_step": ms, "cpu_baseline": {"value": m["value"], "unit": m["unit"], "cores": REF_MT_CORES, "kind": "reference", "sample": "the full step, %s" % wl.name},
+                     "config": {"workload": wl.name}, "dtype": args.dtype})
+    line.update({"impl": "reference", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "strong",
+                 "vs_baseline": None, "data": "synthetic", "gpu_launches": 0,
+                 "e2e": {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default=os.environ.get("TRAINLIB_BENCH_CONFIG", "c2"))
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "fp16"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    pkg = load_pkg()
+    if args.impl == "reference":
+        run_reference(args, pkg)
+        return
+
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = pkg.load()
+    rc = lib.trainlib_init(local)
+    if rc != 0:
+        raise SystemExit("trainlib_init failed: %s" % lib.trainlib_last_error_string().decode())
+    wl = make_workload(args.config, pkg, lib, args.dtype)
+    if hasattr(wl, "run"):
+        line = wl.run(args, rank, world, dist)
+    else:
+        line = run_single(args, pkg, lib, wl)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier(); dist.destroy_process_group()
+
+
+def run_single(args, pkg, lib, wl):
+    pk = peaks()
+    wl.setup_device()
+    for _ in range(args.warmup):
+        wl.step_device()
+    lib.trainlib_synchronize(); pkg.check(lib)
+    sampler = ClockSampler(lib.trainlib_device()); sampler.start()
+    launches0 = lib.trainlib_kernel_launches()
+    ms = []
+    for _ in range(args.steps):
+        wl.l2_flush()
+        lib.trainlib_timer_start()
+        wl.step_device()
+        ms.append(lib.trainlib_timer_stop_ms())
+    launches = lib.trainlib_kernel_launches() - launches0
+    clocks = sampler.stop()
+    pkg.check(lib)
+    ms_step = float(np.mean(ms))
+    # end to end through the C ABI with pinned host buffers (copies inside the timed region)
+    e2e_ms = time_host_lib(wl, lib, args.steps, args.warmup)
+    pkg.check(lib)
+    m = wl.metric(ms_step); e = wl.metric(e2e_ms)
+    line = {"metric": m["metric"], "value": m["value"], "unit": m["unit"], "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16" if args.dtype == "fp16" else "f32",
+            "data": "synthetic", "config": {"workload": wl.name, "l2": "flushed between timed steps (256 MiB memset)"},
+            "roofline": wl.roofline(ms_step, pk), "gpu_launches": int(launches), "clocks": clocks,
+            "e2e": {"value": e["value"], "unit": e["unit"], "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h), "ms_per_step": e2e_ms}}
+    if not args.no_cpu_baseline and os.path.exists(REF_MT):
+        ref = pkg.bind(ctypes.CDLL(REF_MT))
+        wr = make_workload(args.config, pkg, ref, args.dtype)
+        cms = time_host_lib(wr, ref, 3, 1)
+        c = wr.metric(cms)
+        line["cpu_baseline"] = {"value": c["value"], "unit": c["unit"], "cores": REF_MT_CORES, "kind": "reference", "sample": "3 full steps of %s" % wl.name, "ms_per_step": cms}
+    return line
+
+
+if __name__ == "__main__":
+    main()
+EOF
+git add -A; git commit -qm "Tests (CPU oracle pinning, golden fixtures, ABI layout, GPU parity), graft entry, first bench" ; echo ok

@@ -1,0 +1,107 @@
+"""CPU: the drop-in boundary.  Struct layouts equal the reference's, the library loads without a
+GPU, exports every symbol the header declares, and refuses to compute without a device."""
+import ctypes
+import json
+import os
+import subprocess
+import tempfile
+
+import numpy as np
+import pytest
+
+import abi_layout
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(ROOT, "tests", "golden")
+
+
+def test_struct_layout_matches_reference_golden(pkg):
+    want = json.load(open(os.path.join(GOLD, "abi_layout.json")))
+    got = abi_layout.ours(pkg.abi.STRUCT_FIELDS)
+    assert set(got) == set(want)
+    for name in sorted(want):
+        assert got[name] == want[name], "struct %s differs: %s vs %s" % (name, got[name], want[name])
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/lib/include"), reason="reference checkout not present")
+def test_struct_layout_matches_reference_headers(pkg):
+    assert abi_layout.reference(pkg.abi.STRUCT_FIELDS) == abi_layout.ours(pkg.abi.STRUCT_FIELDS)
+
+
+def test_ctypes_mirror_matches_header(pkg):
+    got = abi_layout.ours(pkg.abi.STRUCT_FIELDS)
+    for name, cls in pkg.STRUCTS.items():
+        assert ctypes.sizeof(cls) == got[name]["sizeof"], name
+        for f, _ in pkg.abi.STRUCT_FIELDS[name]:
+            assert getattr(cls, f).offset == got[name][f], (name, f)
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    assert os.path.exists(pkg.LIB_PATH), "build the library first: make -C pulp-trainlib_b200/csrc"
+    lib = ctypes.CDLL(pkg.LIB_PATH)
+    missing = [f for f in pkg.FUNCTIONS if not hasattr(lib, f)]
+    assert not missing, missing
+    ext = ["trainlib_init", "trainlib_last_error", "trainlib_last_error_string", "trainlib_clear_error", "trainlib_device",
+           "trainlib_set_stream", "trainlib_stream", "trainlib_synchronize", "trainlib_set_memory_mode", "trainlib_memory_mode",
+           "trainlib_malloc", "trainlib_free", "trainlib_malloc_host", "trainlib_free_host", "trainlib_memcpy_h2d", "trainlib_memcpy_d2h",
+           "trainlib_memset", "trainlib_set_streams", "trainlib_streams", "trainlib_timer_start", "trainlib_timer_stop_ms",
+           "trainlib_kernel_launches", "trainlib_set_gemm_path", "trainlib_gemm_path",
+           "pi_core_id", "pi_cl_team_fork", "pi_cl_team_barrier", "pi_cl_dma_cmd", "pi_cl_dma_cmd_2d", "pi_cl_dma_cmd_wait",
+           "pi_perf_conf", "pi_perf_reset", "pi_perf_start", "pi_perf_stop", "pi_perf_read", "pi_l2_malloc", "pi_l2_free",
+           "fastexp_gist", "q_rsqrt", "verify_tensor"]
+    assert not [f for f in ext if not hasattr(lib, f)]
+
+
+def test_host_scalars_and_state(pkg):
+    lib = pkg.load()
+    assert np.float32(lib.q_rsqrt(64.0)).view(np.uint32) == 0x3DFF910F
+    assert lib.fastexp_gist(-200.0) == 0.0
+    lib.trainlib_set_streams(7); assert lib.trainlib_streams() == 7
+    lib.trainlib_set_streams(0); assert lib.trainlib_streams() == 1
+    lib.trainlib_set_memory_mode(pkg.TL_MEM_HOST); assert lib.trainlib_memory_mode() == pkg.TL_MEM_HOST
+    lib.trainlib_set_memory_mode(pkg.TL_MEM_AUTO)
+
+
+def test_generated_style_c_code_links_unchanged():
+    """A net.c-style translation unit written against the reference API compiles against include/
+    and links against the library (nothing is executed: there may be no GPU here)."""
+    src = r'''
+    #include "pulp_train.h"
+    PI_L1 float in[16*8*8], out[8*6*6], ker[8*16*3*3], b[8], din[16*8*8], dout[8*6*6], dker[8*16*3*3], db[8], i2c[1], bt[1];
+    PI_L1 struct blob bi, bo, bk, bb; PI_L1 struct Conv2D_args a; PI_L1 struct optim_args opt;
+    static void user_worker(void *p) { (void)p; }
+    int main(int argc, char **argv) {
+        bi.data = in; bi.diff = din; bi.dim = 16*8*8; bi.C = 16; bi.H = 8; bi.W = 8;
+        bo.data = out; bo.diff = dout; bo.dim = 8*6*6; bo.C = 8; bo.H = 6; bo.W = 6;
+        bk.data = ker; bk.diff = dker; bk.dim = 8*16*9; bk.C = 16; bk.H = 3; bk.W = 3;
+        bb.data = b; bb.diff = db; bb.dim = 8;
+        a.input = &bi; a.coeff = &bk; a.bias = &bb; a.output = &bo; a.stride_h = a.stride_w = 1;
+        a.i2c_buffer = i2c; a.bt_buffer = bt; a.USE_IM2COL = 1;
+        opt.weights = &bk; opt.learning_rate = 1e-3f;
+        if (argc > 100) {          /* never true: link check only */
+            pulp_conv2d_fp32_fw_cl(&a); pulp_conv2d_fp32_bw_cl(&a);
+            pi_cl_team_fork(NUM_CORES, pulp_gradient_descent_fp32, &opt);
+            pi_cl_team_fork(NUM_CORES, user_worker, &opt);
+        }
+        return trainlib_streams() == 1 ? 0 : 1;
+    }'''
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "net.c"); exe = os.path.join(d, "net")
+        open(c, "w").write(src)
+        libdir = os.path.join(ROOT, "pulp-trainlib_b200")
+        subprocess.check_call(["gcc", "-std=gnu11", "-Wall", "-DNUM_CORES=8", "-I" + os.path.join(ROOT, "include"), c,
+                               "-L" + libdir, "-ltrainlib_b200", "-Wl,-rpath," + libdir, "-o", exe])
+        assert subprocess.call([exe]) == 0
+
+
+def test_no_cpu_fallback_without_device(pkg):
+    """On a box without a GPU a compute call must latch TL_ERR_NO_DEVICE and leave outputs untouched."""
+    lib = pkg.load()
+    if lib.trainlib_init(-1) == 0:
+        pytest.skip("a CUDA device is present")
+    keep = pkg.Keep()
+    x = np.ones(8, np.float32); y = np.full(8, 5.0, np.float32)
+    args = pkg.make_args(keep, "act_args", input=pkg.make_blob(keep, x, None, dim=8, W=8), output=pkg.make_blob(keep, y, None, dim=8, W=8), H=1, W=8)
+    pkg.call(lib, "pulp_relu_fp32_fw_cl", args)
+    assert lib.trainlib_last_error() == 1          # TL_ERR_NO_DEVICE
+    assert np.all(y == 5.0)

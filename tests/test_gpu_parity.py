@@ -1,0 +1,271 @@
+"""GPU parity: libtrainlib_b200 called through the C ABI, against (1) the committed golden vectors
+of the reference's own C code, (2) the CPU oracle on seeded inputs at further sizes, and (3) the
+reference library itself when oracle/_ref/libpulp_ref.so travelled with the repository.
+fp32 bar: max|a-b|/max|b| <= 1e-5.  fp16 (storage fp16, accumulation fp32): <= 1e-2 against the
+oracle run in fp32 on the fp16-rounded inputs.  Index helpers: bit-exact."""
+import os
+
+import numpy as np
+import pytest
+
+import golden_cases
+from abi_runner import AbiRunner
+from metrics import FP16_TOL, FP32_TOL, assert_close, assert_exact, rel_err, seeded
+from oracle_bind import geom, out_hw
+from test_golden_cpu import load_case
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+
+
+@pytest.fixture()
+def run(pkg, gpulib):
+    rs = []
+
+    def make(device=False, half=False):
+        gpulib.trainlib_set_streams(1)
+        r = AbiRunner(pkg, gpulib, device=device, half=half)
+        rs.append(r)
+        return r
+    yield make
+    for r in rs:
+        r.close()
+    gpulib.trainlib_set_streams(1)
+
+
+@pytest.mark.parametrize("name", [c[0] for c in golden_cases.CASES])
+def test_golden_vectors(run, oracle, name):
+    _, _, run_abi, run_oracle, tol = next(c for c in golden_cases.CASES if c[0] == name)
+    inp, want = load_case(name)
+    got_host = run_abi(run(device=False), inp)
+    got_dev = run_abi(run(device=True), inp)
+    orc = run_oracle(oracle, inp)
+    for k, v in want.items():
+        g = np.asarray(got_host[k]).reshape(v.shape)
+        if tol is None and name == "index_helpers":
+            assert_exact(g.astype(v.dtype), v, "%s.%s" % (name, k))
+        else:
+            assert_close(g, v, FP32_TOL, "%s.%s vs reference golden" % (name, k))
+            assert_close(g, np.asarray(orc[k]).reshape(v.shape), FP32_TOL, "%s.%s vs oracle" % (name, k))
+        assert_exact(np.asarray(got_dev[k]).reshape(v.shape), g, "%s.%s device-pointer mode vs host-pointer mode" % (name, k))
+
+
+def test_torch_golden_model_of_mhsa(run):
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "mhsa_torch_gm.npz"))
+    L, E, Fd, heads = int(z["L"]), int(z["E"]), int(z["F"]), int(z["heads"])
+    r = run().mhsa(z["in_x"], z["in_wq"], z["in_wk"], z["in_wv"], z["in_bq"], z["in_bk"], z["in_bv"], z["in_wo"], z["in_dy"], L, E, Fd, heads)
+    for k in ("y", "dx", "dwq", "dwk", "dwv", "dwo"):
+        assert_close(r[k], z["out_" + k], FP32_TOL, "mhsa vs torch gm %s" % k)
+
+
+@pytest.mark.parametrize("trans_B", [0, 1])
+def test_mm_small_shape_sweep(run, oracle, trans_B):
+    """every N, M, K in a set with odd leftovers, incl. K=1, M=1, N=1"""
+    rng = seeded(99 + trans_B)
+    r = run(device=True)
+    dims = (1, 2, 3, 5, 8, 17, 33, 65)
+    worst = 0.0
+    for N in dims:
+        for K in dims:
+            for M in dims:
+                A = rng.standard_normal((N, K)).astype(F)
+                B = rng.standard_normal((M, K) if trans_B else (K, M)).astype(F)
+                e = rel_err(r.mm(A, B, N, K, M, trans_B), oracle.mm(A, B, N, K, M, trans_B))
+                worst = max(worst, e)
+                assert e <= FP32_TOL, (N, K, M, e)
+        r.close()
+
+
+@pytest.mark.parametrize("N,K,M", [(32, 144, 1024), (32, 1024, 144), (16, 288, 1024), (256, 256, 256), (300, 700, 130)])
+def test_mm_config_shapes(run, oracle, N, K, M):
+    rng = seeded(N + K + M)
+    A = rng.standard_normal((N, K)).astype(F); B = rng.standard_normal((K, M)).astype(F); Bt = np.ascontiguousarray(B.T)
+    r = run(device=True)
+    want = oracle.mm(A, B, N, K, M, 0)
+    assert_close(r.mm(A, B, N, K, M, 0), want, FP32_TOL, "mm")
+    assert_close(r.mm(A, Bt, N, K, M, 1, fn="mm_unroll_2x4"), want, FP32_TOL, "mm trans_B")
+    C0 = rng.standard_normal((N, M)).astype(F)
+    assert_close(r.mm(A, B, N, K, M, 0, fn="mm_add", C0=C0), want + C0, FP32_TOL, "mm_add")
+
+
+@pytest.mark.parametrize("inn,out", [(256, 256), (1024, 1024), (4096, 1024), (1024, 4096), (1000, 37)])
+@pytest.mark.parametrize("half", [False, True])
+def test_linear_config2(run, oracle, inn, out, half):
+    """config 2: W ~ N(0, 1/in), x ~ N(0,1), dy ~ N(0,1); FW, WG, IG"""
+    rng = seeded(inn * 3 + out)
+    W = (rng.standard_normal((out, inn)) / np.sqrt(inn)).astype(F); x = rng.standard_normal(inn).astype(F); dy = rng.standard_normal(out).astype(F)
+    bias = rng.standard_normal(out).astype(F)
+    if half:
+        W, x, dy, bias = [a.astype(np.float16).astype(F) for a in (W, x, dy, bias)]
+    want = oracle.linear(W, x, dy, bias)
+    got = run(device=True, half=half).linear(W, x, dy, bias)
+    tol = FP16_TOL if half else FP32_TOL
+    for k in ("y", "dW", "dx", "db"):
+        assert_close(got[k].astype(F).reshape(want[k].shape), want[k], tol, "linear %s" % k)
+
+
+CONV_CASES = [geom(16, 32, 32, 32, 3, pad=1), geom(3, 32, 32, 16, 3, pad=1), geom(16, 32, 32, 32, 3, stride=2, pad=1),
+              geom(32, 16, 16, 64, 3, stride=2, pad=1), geom(64, 8, 8, 64, 3, pad=1), geom(16, 32, 32, 32, 1, stride=2),
+              geom(5, 11, 13, 7, 3, stride=2, pad=1), geom(3, 9, 9, 4, 5, stride=1, pad=2), geom(2, 12, 12, 3, 7, pad=3),
+              geom(1, 5, 5, 1, 3), geom(20, 6, 6, 33, 3, pad=1), geom(4, 8, 8, 4, 2)]
+
+
+@pytest.mark.parametrize("g", CONV_CASES, ids=lambda g: "c%d_%dx%d_o%d_k%d_s%d_p%d" % (g["Cin"], g["Hin"], g["Win"], g["Cout"], g["Hk"], g["sh"], g["padU"]))
+@pytest.mark.parametrize("half", [False, True])
+def test_conv2d_sweep(run, oracle, g, half):
+    rng = seeded(g["Cin"] * 31 + g["Hin"] + g["Hk"])
+    Ho, Wo = out_hw(g)
+    x = rng.uniform(-1, 1, (g["Cin"], g["Hin"], g["Win"])).astype(F)
+    w = rng.uniform(-1, 1, (g["Cout"], g["Cin"], g["Hk"], g["Wk"])).astype(F)
+    dy = rng.standard_normal((g["Cout"], Ho, Wo)).astype(F); bias = rng.standard_normal(g["Cout"]).astype(F)
+    if half:
+        x, w, dy, bias = [a.astype(np.float16).astype(F) for a in (x, w, dy, bias)]
+    got = run(device=True, half=half).conv2d(x, w, dy, g, use_im2col=0, bias=bias)
+    tol = FP16_TOL if half else FP32_TOL
+    assert_close(got["y"].astype(F), oracle.conv2d_fw(x, w, bias, g), tol, "fw")
+    dw, db = oracle.conv2d_wg(x, dy, g, with_bias=True)
+    assert_close(got["dw"].astype(F), dw, tol, "wg")
+    assert_close(got["db"].astype(F), db, tol, "bias grad")
+    assert_close(got["dx"].astype(F), oracle.conv2d_ig(dy, w, g), tol, "ig")
+
+
+def test_mhsa_config3(run, oracle):
+    """config 3: L = E = F = 256, 4 heads of 64; x ~ N(0,1), W ~ N(0, 1/E), dy ~ N(0,1), zero biases"""
+    rng = seeded(3)
+    L = E = Fd = 256; heads = 4
+    x = rng.standard_normal((E, L)).astype(F); dy = rng.standard_normal((E, L)).astype(F)
+    ws = [(rng.standard_normal((E, Fd)) / np.sqrt(E)).astype(F) for _ in range(4)]
+    zb = np.zeros(Fd, F)
+    want = oracle.mhsa(x, ws[0], ws[1], ws[2], zb, zb, zb, ws[3], dy, L, E, Fd, heads)
+    got = run(device=True).mhsa(x, ws[0], ws[1], ws[2], zb, zb, zb, ws[3], dy, L, E, Fd, heads)
+    for k in ("q", "k", "v", "softmax", "att", "y", "dwo", "datt", "dv", "dsoftmax", "dk", "dq", "dwq", "dwk", "dwv", "dx"):
+        assert_close(got[k], want[k], FP32_TOL, "mhsa c3 %s" % k)
+
+
+def test_mhsa_fp16(run, oracle):
+    rng = seeded(4)
+    L, E, Fd, heads = 128, 128, 128, 4
+    h = lambda a: a.astype(np.float16).astype(F)
+    x = h(rng.standard_normal((E, L))); dy = h(rng.standard_normal((E, L)))
+    ws = [h(rng.standard_normal((E, Fd)) / np.sqrt(E)) for _ in range(4)]
+    bs = [h(0.1 * rng.standard_normal(Fd)) for _ in range(3)]
+    want = oracle.mhsa(x, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dy, L, E, Fd, heads)
+    got = run(device=True, half=True).mhsa(x, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dy, L, E, Fd, heads)
+    for k in ("y", "softmax", "dx", "dwq", "dwk", "dwv", "dwo"):
+        assert_close(got[k].astype(F), want[k], 2e-2, "mhsa fp16 %s" % k)     # intermediates are rounded to fp16 between the GEMMs
+
+
+def test_fp16_elementwise(run, oracle):
+    rng = seeded(5)
+    h = lambda a: a.astype(np.float16).astype(F)
+    x = h(2 * rng.standard_normal(4096)); dy = h(rng.standard_normal(4096))
+    r = run(device=True, half=True)
+    for k, kind in enumerate(("relu", "leakyrelu", "sigmoid")):
+        res = r.act(kind, x, dy, slope=0.01)
+        y = oracle.act_fw(k, x, h(np.array([0.01]))[0])
+        assert_close(res["y"].astype(F), y, FP16_TOL, kind)
+        assert_close(res["dx"].astype(F), oracle.act_bw(k, x, y, dy, h(np.array([0.01]))[0]), FP16_TOL, kind + " bw")
+    assert_close(r.act("gelu", x, dy)["y"].astype(F), oracle.act_fw(3, x), FP16_TOL, "gelu")
+    xi = h(rng.standard_normal((8, 16, 16))); dyi = h(rng.standard_normal((8, 16, 16))); gb = h(rng.standard_normal(16))
+    res = r.instnorm(xi, gb, dyi); want = oracle.instnorm(xi, gb, dyi)
+    for k in ("y", "dx", "dgb"):
+        assert_close(res[k].astype(F), want[k], FP16_TOL, "instnorm fp16 %s" % k)
+    y = h(rng.standard_normal(512)); t = h(rng.standard_normal(512))
+    loss, dyl = r.loss("MSELoss", y, t); lo, dyo = oracle.mse(y, t)
+    assert abs(float(loss) - float(lo)) <= FP16_TOL * abs(float(lo)); assert_close(dyl.astype(F), dyo, FP16_TOL, "mse bw fp16")
+    s = r.sgd(x, dy, 0.01); wo, _ = oracle.sgd(x, dy, h(np.array([0.01]))[0])
+    assert_close(s["w"].astype(F), wo, FP16_TOL, "sgd fp16")
+
+
+def test_streams_mode(pkg, gpulib, oracle):
+    """n independent batch-1 streams in one call: activations per stream, weight gradients summed."""
+    rng = seeded(6)
+    n = 5
+    g = geom(6, 12, 12, 10, 3, pad=1)
+    Ho, Wo = out_hw(g)
+    xs = rng.uniform(-1, 1, (n, 6, 12, 12)).astype(F); w = rng.uniform(-1, 1, (10, 6, 3, 3)).astype(F); dys = rng.standard_normal((n, 10, Ho, Wo)).astype(F)
+    gpulib.trainlib_set_streams(n)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        # the runner's blobs describe one stream; the tensors hold n of them back to back
+        X, W_, dY = r.t(xs), r.t(w), r.t(dys)
+        Y, dX, dW = r.zeros(n, 10, Ho, Wo), r.zeros(n, 6, 12, 12), r.zeros(10, 6, 3, 3)
+        one = r.zeros(1)
+        args = r.args("Conv2D_args", input=r.blob(X, dX, C=6, H=12, W=12), coeff=r.blob(W_, dW, C=6, H=3, W=3, dim=w.size), bias=r.blob(one, one),
+                      output=r.blob(Y, dY, C=10, H=Ho, W=Wo), Lpad=1, Rpad=1, Upad=1, Dpad=1, stride_h=1, stride_w=1, i2c_buffer=one, bt_buffer=one,
+                      USE_BIASES=0, USE_IM2COL=1, HWC=0)
+        r.call("pulp_conv2d_fp32_fw_cl", args); r.call("pulp_conv2d_fp32_bw_cl", args)
+        y, dx, dw = Y.get(), dX.get(), dW.get()
+        dw_want = np.zeros_like(w)
+        for s in range(n):
+            assert_close(y[s], oracle.conv2d_fw(xs[s], w, None, g), FP32_TOL, "stream %d fw" % s)
+            assert_close(dx[s], oracle.conv2d_ig(dys[s], w, g), FP32_TOL, "stream %d ig" % s)
+            dw_want += oracle.conv2d_wg(xs[s], dys[s], g)[0]
+        assert_close(dw, dw_want, FP32_TOL, "summed weight grad")
+        # instance norm + relu + CE + linear over streams
+        gb = rng.standard_normal(12).astype(F)
+        xi = xs; dyi = rng.standard_normal(xs.shape).astype(F)
+        Xi, dXi, Yi, dYi, GB, dGB = r.t(xi), r.zeros(*xi.shape), r.zeros(*xi.shape), r.t(dyi), r.t(gb), r.zeros(12)
+        m, v, sd = r.zeros(n, 6), r.zeros(n, 6), r.zeros(n, 6)
+        a2 = r.args("InstNorm_args", input=r.blob(Xi, dXi, C=6, H=12, W=12), output=r.blob(Yi, dYi, C=6, H=12, W=12), coeff=r.blob(GB, dGB, dim=12, W=12),
+                    running_mean=m, running_var=v, running_stdev=sd, freeze_running_params=0, skip_wg_grad=0, skip_in_grad=0)
+        r.call("pulp_instnorm_fp32_fw_cl", a2); r.call("pulp_instnorm_fp32_bw_cl", a2)
+        dgb_want = np.zeros(12, F)
+        for s in range(n):
+            o = oracle.instnorm(xi[s], gb, dyi[s])
+            assert_close(Yi.get()[s], o["y"], FP32_TOL, "instnorm stream fw"); assert_close(dXi.get()[s], o["dx"], FP32_TOL, "instnorm stream ig")
+            dgb_want += o["dgb"]
+        assert_close(dGB.get(), dgb_want, FP32_TOL, "instnorm summed param grad")
+        Wl = (rng.standard_normal((10, 64)) / 8).astype(F); xl = rng.standard_normal((n, 64)).astype(F); lab = np.zeros((n, 10), F)
+        lab[np.arange(n), rng.integers(0, 10, n)] = 1
+        res = r.linear(Wl, xl, np.zeros((n, 10), F), n=n)            # forward only matters here
+        z = res["y"].reshape(n, 10)
+        for s in range(n):
+            assert_close(z[s], oracle.linear(Wl, xl[s], np.zeros(10, F))["y"], FP32_TOL, "linear stream fw")
+        Z, dZ, T, Ls = r.t(z), r.zeros(n, 10), r.t(lab), r.zeros(n)
+        a3 = r.args("loss_args", output=r.blob(Z, dZ, dim=10, W=10), target=T, wr_loss=Ls)
+        r.call("pulp_CrossEntropyLoss", a3); r.call("pulp_CrossEntropyLoss_backward", a3)
+        for s in range(n):
+            lo, dzo = oracle.ce(z[s], lab[s])
+            assert abs(Ls.get()[s] - lo) <= 1e-5 * max(1.0, abs(lo)); assert_close(dZ.get()[s], dzo, FP32_TOL, "ce stream bw")
+        dzs = dZ.get()
+        res = r.linear(Wl, xl, dzs, n=n)
+        dW_want = sum(np.outer(dzs[s], xl[s]) for s in range(n))
+        assert_close(res["dW"], dW_want, FP32_TOL, "linear summed weight grad")
+        for s in range(n):
+            assert_close(res["dx"].reshape(n, 64)[s], oracle.linear(Wl, xl[s], dzs[s])["dx"], FP32_TOL, "linear stream ig")
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1)
+
+
+def test_reference_library_side_by_side(pkg, gpulib, reflib):
+    """Same structs, same seeded inputs, the reference's own code on the host vs the GPU library."""
+    rng = seeded(8)
+    g = geom(8, 16, 16, 12, 3, stride=2, pad=1)
+    x = rng.uniform(-1, 1, (8, 16, 16)).astype(F); w = rng.uniform(-1, 1, (12, 8, 3, 3)).astype(F); dy = rng.standard_normal((12,) + out_hw(g)).astype(F)
+    ref = AbiRunner(pkg, reflib, is_ref=True).conv2d(x, w, dy, g, use_im2col=0)
+    got = AbiRunner(pkg, gpulib).conv2d(x, w, dy, g, use_im2col=0)
+    for k in ("y", "dw", "dx"):
+        assert_close(got[k], ref[k], FP32_TOL, "conv s2p1 %s vs reference" % k)
+    L, E, Fd, heads = 48, 32, 64, 4
+    xm = rng.standard_normal((E, L)).astype(F); dym = rng.standard_normal((E, L)).astype(F)
+    ws = [(rng.standard_normal((E, Fd)) / np.sqrt(E)).astype(F) for _ in range(4)]; bs = [(0.1 * rng.standard_normal(Fd)).astype(F) for _ in range(3)]
+    ref = AbiRunner(pkg, reflib, is_ref=True).mhsa(xm, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dym, L, E, Fd, heads)
+    got = AbiRunner(pkg, gpulib).mhsa(xm, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dym, L, E, Fd, heads)
+    for k in ("y", "dx", "dwq", "dwk", "dwv", "dwo"):
+        assert_close(got[k], ref[k].reshape(got[k].shape), FP32_TOL, "mhsa %s vs reference" % k)
+
+
+def test_error_paths(pkg, gpulib):
+    """bad arguments latch an error code and leave outputs untouched, as the reference prints and returns"""
+    r = AbiRunner(pkg, gpulib)
+    x = np.ones((2, 4, 4), F)
+    with pytest.raises(RuntimeError):
+        r.conv2d(x, np.ones((3, 2, 3, 3), F), None, dict(geom(2, 4, 4, 3, 3), sh=0, sw=0))
+    assert gpulib.trainlib_last_error() == 0           # check() cleared it
+    keep = pkg.Keep()
+    a = pkg.make_args(keep, "mm_manager_args", mm_args=pkg.make_args(keep, "matMul_args", N=1, M=1, K=1), layer_type=1, step_type=0, matmul_type=0)
+    pkg.call(gpulib, "mm_manager", a)
+    assert gpulib.trainlib_last_error() == 3
+    gpulib.trainlib_clear_error()
