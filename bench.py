@@ -134,7 +134,7 @@ class LinearSweep(object):
         for inn, out in self.SHAPES:
             W, x, dy = self._inputs(rng, inn, out)
             arrs = [W, x, dy, np.zeros(out, self.dt), np.zeros((out, inn), self.dt), np.zeros(inn, self.dt)]
-            if lib is self.lib:
+            if hasattr(lib, "trainlib_malloc_host"):
                 arrs = [pinned_like(self.pkg, lib, a) for a in arrs]
             self.host.append(arrs)
             self.args_host.append(self._args(*arrs, inn, out))
@@ -291,4 +291,3 @@ def run_single(args, pkg, lib, wl):
 if __name__ == "__main__":
     main()
 EOF
-git add -A; git commit -qm "Tests (CPU oracle pinning, golden fixtures, ABI layout, GPU parity), graft entry, first bench" ; echo ok

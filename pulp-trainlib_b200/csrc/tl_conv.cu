@@ -24,7 +24,7 @@ conv_fw_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ w, con
     const int PWp = PW | 1;                                  // odd row pitch: fewer bank conflicts
     const int KK = g.Hk * g.Wk;
     float *patch = smem;                                     // [S_T][CC][PH][PWp]
-    float *wsm = smem + (size_t)S_T * CC * PH * PWp;         // [CC][KK][CO_T]
+    float *wsm = smem + (((size_t)S_T * CC * PH * PWp + 3) & ~(size_t)3);   // [CC][KK][CO_T], 16-byte aligned for float4 reads
 
     const int tid = threadIdx.x;
     const int tile = blockIdx.x;
@@ -188,7 +188,7 @@ static bool conv_fw_plan(const ConvGeom &g, int &TH, int &TW, int &S_T, int &CC,
     const int PH = (TH - 1) * g.sh + g.Hk, PW = ((TW - 1) * g.sw + g.Wk) | 1, KK = g.Hk * g.Wk;
     CC = g.Cin;
     for (;;) {
-        smem = ((size_t)S_T * CC * PH * PW + (size_t)CC * KK * CO_T) * sizeof(float);
+        smem = ((((size_t)S_T * CC * PH * PW + 3) & ~(size_t)3) + (size_t)CC * KK * CO_T) * sizeof(float);
         if (smem <= 40 * 1024 || CC == 1) break;
         CC = (CC + 1) / 2;
     }
@@ -224,7 +224,7 @@ conv_ig_kernel(ConvGeom g, const T *__restrict__ dy, const T *__restrict__ w, T 
     const int PWp = PW | 1;
     const int KK = g.Hk * g.Wk;
     float *patch = smem;                                     // [S_T][CC][PH][PWp] of dY
-    float *wsm = smem + (size_t)S_T * CC * PH * PWp;         // [CC(co)][KK][CO_T(ci)]
+    float *wsm = smem + (((size_t)S_T * CC * PH * PWp + 3) & ~(size_t)3);   // [CC(co)][KK][CO_T(ci)], 16-byte aligned
 
     const int tid = threadIdx.x;
     const int tile = blockIdx.x;
@@ -323,7 +323,7 @@ template <class T> void conv_ig(const ConvGeom &g, const T *dy, const T *w, T *d
     const int KK = g.Hk * g.Wk;
     int CC = g.Cout; size_t smem;
     for (;;) {
-        smem = ((size_t)S_T * CC * PH * (PW | 1) + (size_t)CC * KK * CO_T) * sizeof(float);
+        smem = ((((size_t)S_T * CC * PH * (PW | 1) + 3) & ~(size_t)3) + (size_t)CC * KK * CO_T) * sizeof(float);
         if (smem <= 40 * 1024 || CC == 1) break;
         CC = (CC + 1) / 2;
     }

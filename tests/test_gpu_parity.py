@@ -262,7 +262,7 @@ def test_error_paths(pkg, gpulib):
     r = AbiRunner(pkg, gpulib)
     x = np.ones((2, 4, 4), F)
     with pytest.raises(RuntimeError):
-        r.conv2d(x, np.ones((3, 2, 3, 3), F), None, dict(geom(2, 4, 4, 3, 3), sh=0, sw=0))
+        r.conv2d(x, np.ones((3, 2, 3, 3), F), None, dict(geom(2, 4, 4, 3, 3), Hk=5, Wk=5))      # kernel larger than the input
     assert gpulib.trainlib_last_error() == 0           # check() cleared it
     keep = pkg.Keep()
     a = pkg.make_args(keep, "mm_manager_args", mm_args=pkg.make_args(keep, "matMul_args", N=1, M=1, K=1), layer_type=1, step_type=0, matmul_type=0)
