@@ -219,7 +219,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--config", default=os.environ.get("TRAINLIB_BENCH_CONFIG", "c2"))
+    ap.add_argument("--config", default=os.environ.get("TRAINLIB_BENCH_CONFIG", "c5"))
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "fp16"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -290,4 +290,3 @@ def run_single(args, pkg, lib, wl):
 
 if __name__ == "__main__":
     main()
-EOF

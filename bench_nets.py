@@ -1,0 +1,227 @@
+"""The batched workload of bench.py: the small ResNet of pulp-trainlib_b200/nets/resnet8_streams.c
+trained on 4096 independent batch-1 streams (FW + WG-BW + IG-BW + SGD), streams sharded over the
+ranks, weight gradients summed across ranks with one NCCL all-reduce per step."""
+import ctypes
+import json
+import os
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+NETS = os.path.join(ROOT, "pulp-trainlib_b200", "nets")
+NET_B200 = os.path.join(NETS, "libresnet8_b200.so")
+NET_REF_MT = os.path.join(ROOT, "oracle", "_ref", "libresnet8_ref.so")
+NET_REF_SEQ = os.path.join(ROOT, "oracle", "_ref", "libresnet8_ref_seq.so")
+STREAMS = 4096
+LR = 1e-2
+F = np.float32
+
+
+def bind_net(path):
+    net = ctypes.CDLL(path)
+    net.resnet8_param_count.restype = ctypes.c_size_t
+    net.resnet8_workspace_floats.restype = ctypes.c_size_t; net.resnet8_workspace_floats.argtypes = [ctypes.c_int]
+    net.resnet8_init_params.argtypes = [ctypes.c_void_p, ctypes.c_uint]
+    net.resnet8_bind.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]; net.resnet8_bind.restype = ctypes.c_int
+    net.resnet8_forward.argtypes = [ctypes.c_void_p] * 3
+    net.resnet8_forward_host.argtypes = [ctypes.c_void_p] * 3
+    net.resnet8_update.argtypes = [ctypes.c_float]
+    net.resnet8_logits.restype = ctypes.c_void_p
+    net.resnet8_flops_per_stream.restype = ctypes.c_double
+    return net
+
+
+def synthetic_batch(n, first_stream=0):
+    """images ~ N(0,1) [n,3,32,32], labels uniform over 10 classes as one-hot rows; keyed by stream index"""
+    img = np.empty((n, 3, 32, 32), F); lab = np.zeros((n, 10), F)
+    for s in range(n):
+        rng = np.random.default_rng(1000003 + first_stream + s)
+        img[s] = rng.standard_normal((3, 32, 32)).astype(F)
+        lab[s, rng.integers(0, 10)] = 1
+    return img, lab
+
+
+def host_params(net, seed=0):
+    p = np.zeros(net.resnet8_param_count(), F)
+    net.resnet8_init_params(p.ctypes.data, seed)
+    return p
+
+
+def reference_step(net_ref, n, first_stream=0, lr=LR, params=None, steps=1):
+    """Run the same C network against the reference library on the host; returns dict of results."""
+    p = host_params(net_ref) if params is None else params.copy()
+    g = np.zeros_like(p)
+    ws = np.zeros(net_ref.resnet8_workspace_floats(n), F)
+    img, lab = synthetic_batch(n, first_stream)
+    loss = np.zeros(n, F)
+    assert net_ref.resnet8_bind(n, p.ctypes.data, g.ctypes.data, ws.ctypes.data) == 0
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        net_ref.resnet8_forward(img.ctypes.data, lab.ctypes.data, loss.ctypes.data)
+        net_ref.resnet8_backward()
+        grads = g.copy()
+        net_ref.resnet8_update(lr)
+    dt = (time.perf_counter() - t0) / steps
+    logits = np.ctypeslib.as_array(ctypes.cast(net_ref.resnet8_logits(), ctypes.POINTER(ctypes.c_float)), shape=(n, 10)).copy()
+    return dict(loss=loss, logits=logits, grads=grads, params=p, seconds_per_step=dt)
+
+
+class ResNet8Streams(object):
+    name = "c5_resnet8_4096_streams_fp32_fw_bw_sgd"
+
+    def __init__(self, pkg, lib):
+        self.pkg, self.lib = pkg, lib
+
+    # ------------------------------------------------------------------ GPU arm
+    def run(self, args, rank, world, dist):
+        from bench import ClockSampler, peaks
+        pkg, lib = self.pkg, self.lib
+        net = bind_net(NET_B200)
+        total = int(os.environ.get("TRAINLIB_BENCH_STREAMS", STREAMS))
+        n = total // world
+        first = rank * n
+        torch = None
+        if world > 1:
+            import torch
+            lib.trainlib_set_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        P = net.resnet8_param_count()
+        hp = host_params(net)
+        if torch is not None:
+            t_params = torch.from_numpy(hp).cuda(); t_grads = torch.zeros(P, device="cuda")
+            d_params, d_grads = t_params.data_ptr(), t_grads.data_ptr()
+        else:
+            b_params = pkg.DeviceBuffer(lib, hp); b_grads = pkg.DeviceBuffer(lib, nbytes=4 * P)
+            d_params, d_grads = b_params.ptr, b_grads.ptr
+        ws = pkg.DeviceBuffer(lib, nbytes=4 * net.resnet8_workspace_floats(n)); ws.zero()
+        img, lab = synthetic_batch(n, first)
+        d_img, d_lab = pkg.DeviceBuffer(lib, img), pkg.DeviceBuffer(lib, lab)
+        d_loss = pkg.DeviceBuffer(lib, nbytes=4 * n)
+        assert net.resnet8_bind(n, d_params, d_grads, ws.ptr) == 0
+
+        def step():
+            net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr)
+            net.resnet8_backward()
+            if torch is not None:
+                dist.all_reduce(t_grads)
+            net.resnet8_update(LR)
+
+        def sync():
+            lib.trainlib_synchronize()
+            if torch is not None:
+                torch.cuda.synchronize(); dist.barrier()
+
+        for _ in range(args.warmup):
+            step()
+        sync(); pkg.check(lib)
+        sampler = ClockSampler(lib.trainlib_device()); sampler.start()
+        l0 = lib.trainlib_kernel_launches()
+        sync()
+        lib.trainlib_timer_start()
+        for _ in range(args.steps):
+            step()
+        ms_total = lib.trainlib_timer_stop_ms()
+        sync()
+        launches = lib.trainlib_kernel_launches() - l0
+        clocks = sampler.stop()
+        pkg.check(lib)
+        if torch is not None:
+            t = torch.tensor([ms_total], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms_total = float(t.item())
+        ms_step = ms_total / args.steps
+        loss_host = d_loss.download(F, (n,))
+
+        # end to end: the batch starts in pinned host memory every step, the losses come back
+        from bench import pinned_like
+        h_img, h_lab, h_loss = pinned_like(pkg, lib, img), pinned_like(pkg, lib, lab), pinned_like(pkg, lib, np.zeros(n, F))
+
+        def step_e2e():
+            net.resnet8_forward_host(h_img.ctypes.data, h_lab.ctypes.data, h_loss.ctypes.data)
+            net.resnet8_backward()
+            if torch is not None:
+                dist.all_reduce(t_grads)
+            net.resnet8_update(LR)
+
+        for _ in range(2):
+            step_e2e()
+        sync()
+        lib.trainlib_timer_start()
+        e2e_steps = max(3, args.steps // 2)
+        for _ in range(e2e_steps):
+            step_e2e()
+        e2e_ms = lib.trainlib_timer_stop_ms()
+        sync()
+        if torch is not None:
+            t = torch.tensor([e2e_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_ms = float(t.item())
+        e2e_ms /= e2e_steps
+        pkg.check(lib)
+
+        # per-kernel durations of one more step, CUDA events around every launch on the library stream
+        lib.trainlib_profile(1)
+        net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr); net.resnet8_backward(); net.resnet8_update(LR)
+        lib.trainlib_profile(0)
+        table = pkg.profile_table(lib)
+        pkg.check(lib)
+        if rank != 0:
+            return None
+        pk = peaks()
+        flops_step = net.resnet8_flops_per_stream() * total
+        line = {"metric": "train_step_samples_per_s", "value": total / (ms_step * 1e-3), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "tflops": flops_step / (ms_step * 1e-3) / 1e12,
+                "config": {"workload": self.name, "streams_total": total, "streams_per_gpu": n, "lr": LR,
+                           "l2": "per-step working set (%.1f GB) exceeds L2; no flush needed" % (4e-9 * net.resnet8_workspace_floats(n)),
+                           "parallelism": "streams sharded over %d rank(s); one NCCL all-reduce of %d gradient floats per step" % (world, P)},
+                "gpu_launches": int(launches), "clocks": clocks, "mean_loss": float(loss_host.mean()),
+                "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
+                        "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n)},
+                "roofline": self.roofline(table, n, pk),
+                "kernel_table": [{"kernel": k, "launches": c, "ms": round(ms, 4)} for k, c, ms in table[:8]]}
+        if world == 1 and not args.no_cpu_baseline and os.path.exists(NET_REF_MT):
+            line["cpu_baseline"] = self.cpu_baseline()
+        return line
+
+    def roofline(self, table, n, pk):
+        """Dominant kernel of the profiled step against the bound that limits it."""
+        if not table:
+            return None
+        name, count, ms = table[0]
+        total_ms = sum(r[2] for r in table)
+        # algorithmic work of the convolution kernels per step (all layers of that direction)
+        spec = [(3, 32, 16, 3, 1), (16, 32, 16, 3, 1), (16, 32, 16, 3, 1), (16, 32, 32, 3, 2), (32, 16, 32, 3, 1), (16, 32, 32, 1, 2), (32, 16, 64, 3, 2), (64, 8, 64, 3, 1), (32, 16, 64, 1, 2)]
+        conv_flops = sum(2.0 * co * ci * k * k * (h // s) ** 2 for ci, h, co, k, s in spec) * n
+        ig_flops = conv_flops - 2.0 * 16 * 3 * 9 * 32 * 32 * n
+        r = {"kernel": name, "launches_per_step": count, "ms_per_step": ms, "share_of_kernel_time": ms / total_ms if total_ms else None, "traffic": None,
+             "peak_source": pk["source"]}
+        if "conv_fw" in name or "conv_wg" in name or "conv_ig" in name:
+            fl = ig_flops if "conv_ig" in name else conv_flops
+            ach = fl / (ms * 1e-3) / 1e12
+            # fp32 on the tensor cores is 3xTF32: one third of the TF32 rate, TF32 = half the bf16 rate
+            peak = pk["bf16_tflops_sustained"] / 6.0
+            r.update({"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "algorithmic_flops": fl,
+                      "peak_note": "3xTF32-effective fp32 peak = measured sustained bf16 / 6"})
+        else:
+            r.update({"bound": "hbm", "achieved": None, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": None})
+        return r
+
+    # ------------------------------------------------------------------ reference arm (host cores)
+    def cpu_baseline(self, sample=32, steps=1):
+        net = bind_net(NET_REF_MT)
+        r = reference_step(net, sample, steps=steps)
+        return {"value": sample / r["seconds_per_step"], "unit": "samples/s", "cores": 8, "kind": "reference",
+                "sample": "%d of the %d streams, %d step(s), reference C sources with a pthread team of 8" % (sample, STREAMS, steps),
+                "ms_per_step_sample": 1e3 * r["seconds_per_step"]}
+
+    def run_reference(self, ref_lib, args):
+        if not os.path.exists(NET_REF_MT):
+            return {"unavailable": "oracle/_ref/libresnet8_ref.so was not built (needs the reference checkout at build time)", "value": None, "unit": "samples/s"}
+        sample = 32
+        steps = max(1, min(args.steps, 3))
+        net = bind_net(NET_REF_MT)
+        for _ in range(max(0, min(args.warmup, 1))):
+            reference_step(net, sample)
+        r = reference_step(net, sample, steps=steps)
+        v = sample / r["seconds_per_step"]
+        return {"metric": "train_step_samples_per_s", "value": v, "unit": "samples/s", "ms_per_step": 1e3 * r["seconds_per_step"] * STREAMS / sample, "dtype": "f32",
+                "config": {"workload": self.name, "streams_total": STREAMS, "sample_streams": sample},
+                "cpu_baseline": {"value": v, "unit": "samples/s", "cores": 8, "kind": "reference",
+                                 "sample": "%d of the %d streams per step (streams are independent, so samples/s does not depend on the count)" % (sample, STREAMS)}}

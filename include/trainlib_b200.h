@@ -67,6 +67,13 @@ void   trainlib_timer_start(void);
 double trainlib_timer_stop_ms(void);          /* synchronises; elapsed milliseconds */
 long long trainlib_kernel_launches(void);     /* kernels launched by this library so far */
 
+/* ---- per-kernel timing.  While on, every kernel launch is bracketed by CUDA events on the
+ * library's stream; entries are keyed by kernel name.  Adds launch overhead: use it for a
+ * profiling step, not inside a timed region. */
+void        trainlib_profile(int on);          /* 1 = clear and start, 0 = stop */
+int         trainlib_profile_entries(void);
+const char *trainlib_profile_entry(int i, long long *launches, double *total_ms);
+
 /* ---- GEMM path selection for diagnostics and profiling.
  * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force tcgen05 tensor-core tiles. */
 void  trainlib_set_gemm_path(int path);

@@ -64,6 +64,10 @@ def load(path=LIB_PATH):
     lib.trainlib_streams.restype = ctypes.c_int
     lib.trainlib_timer_stop_ms.restype = ctypes.c_double
     lib.trainlib_kernel_launches.restype = ctypes.c_longlong
+    lib.trainlib_profile.argtypes = [ctypes.c_int]
+    lib.trainlib_profile_entries.restype = ctypes.c_int
+    lib.trainlib_profile_entry.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_double)]
+    lib.trainlib_profile_entry.restype = ctypes.c_char_p
     lib.trainlib_set_gemm_path.argtypes = [ctypes.c_int]
     lib.trainlib_gemm_path.restype = ctypes.c_int
     lib.fastexp_gist.argtypes = [ctypes.c_float]; lib.fastexp_gist.restype = ctypes.c_float
@@ -123,6 +127,16 @@ def make_args(keep, struct_name, **fields):
 
 def call(lib, name, args):
     getattr(lib, name)(ctypes.byref(args))
+
+
+def profile_table(lib):
+    """[(kernel name, launches, total ms)] gathered since trainlib_profile(1), longest first."""
+    rows = []
+    for i in range(lib.trainlib_profile_entries()):
+        n = ctypes.c_longlong(0); ms = ctypes.c_double(0.0)
+        name = lib.trainlib_profile_entry(i, ctypes.byref(n), ctypes.byref(ms))
+        rows.append((name.decode(), int(n.value), float(ms.value)))
+    return sorted(rows, key=lambda r: -r[2])
 
 
 class DeviceBuffer(object):

@@ -27,11 +27,19 @@ int streams();                      // number of independent batch-1 streams (>=
 int sm_count();
 int gemm_path();
 void count_launch();
+// Per-kernel timing (off by default): when on, every launch is bracketed by CUDA events on the
+// library stream and its duration is added to the entry of its kernel name.
+bool profiling();
+void profile_begin(const char *kernel_name);
+void profile_end();
 
 // Launch a kernel on the library stream, count it, latch launch errors.
 #define TL_LAUNCH(kernel, grid, block, smem, ...)                                   \
     do {                                                                            \
+        const bool tl_prof_ = ::tl::profiling();                                    \
+        if (tl_prof_) ::tl::profile_begin(#kernel);                                 \
         kernel<<<(grid), (block), (smem), ::tl::stream()>>>(__VA_ARGS__);           \
+        if (tl_prof_) ::tl::profile_end();                                          \
         ::tl::count_launch();                                                       \
         ::tl::cuda_ok(cudaGetLastError(), #kernel);                                 \
     } while (0)

@@ -85,6 +85,55 @@ int sm_count() { return g.sms; }
 int gemm_path() { return g.gemm_path; }
 void count_launch() { g.launches++; }
 
+// ---------------------------------------------------------------- per-kernel profile
+struct ProfEntry { const char *name; long long launches; double ms; };
+struct ProfPending { int entry; cudaEvent_t a, b; };
+static bool g_prof_on = false;
+static std::vector<ProfEntry> g_prof;
+static std::vector<ProfPending> g_prof_pending;
+static std::vector<cudaEvent_t> g_prof_free;
+static int g_prof_cur = -1;
+static const size_t PROF_MAX_PENDING = 8192;
+
+bool profiling() { return g_prof_on; }
+
+static void prof_drain()
+{
+    for (auto &p : g_prof_pending) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(p.b) == cudaSuccess && cudaEventElapsedTime(&ms, p.a, p.b) == cudaSuccess) g_prof[p.entry].ms += ms;
+        g_prof_free.push_back(p.a); g_prof_free.push_back(p.b);
+    }
+    g_prof_pending.clear();
+}
+
+static cudaEvent_t prof_event()
+{
+    if (!g_prof_free.empty()) { cudaEvent_t e = g_prof_free.back(); g_prof_free.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
+void profile_begin(const char *name)
+{
+    if (g_prof_pending.size() >= PROF_MAX_PENDING) prof_drain();
+    int idx = -1;
+    for (size_t i = 0; i < g_prof.size(); i++) if (g_prof[i].name == name || strcmp(g_prof[i].name, name) == 0) { idx = (int)i; break; }
+    if (idx < 0) { g_prof.push_back({name, 0, 0.0}); idx = (int)g_prof.size() - 1; }
+    g_prof[idx].launches++;
+    ProfPending p; p.entry = idx; p.a = prof_event(); p.b = prof_event();
+    cudaEventRecord(p.a, g.cur_stream);
+    g_prof_pending.push_back(p);
+    g_prof_cur = (int)g_prof_pending.size() - 1;
+}
+
+void profile_end()
+{
+    if (g_prof_cur >= 0) cudaEventRecord(g_prof_pending[g_prof_cur].b, g.cur_stream);
+    g_prof_cur = -1;
+}
+
 bool is_device_pointer(const void *p)
 {
     if (p == nullptr) return false;
@@ -255,6 +304,20 @@ double trainlib_timer_stop_ms(void)
     return (double)ms;
 }
 long long trainlib_kernel_launches(void) { return g.launches; }
+void trainlib_profile(int on)
+{
+    if (!ready()) return;
+    if (on) { g_prof.clear(); g_prof_on = true; }
+    else { prof_drain(); g_prof_on = false; }
+}
+int trainlib_profile_entries(void) { prof_drain(); return (int)g_prof.size(); }
+const char *trainlib_profile_entry(int i, long long *launches, double *total_ms)
+{
+    if (i < 0 || i >= (int)g_prof.size()) return nullptr;
+    if (launches) *launches = g_prof[i].launches;
+    if (total_ms) *total_ms = g_prof[i].ms;
+    return g_prof[i].name;
+}
 void trainlib_set_gemm_path(int p) { g.gemm_path = (p >= 0 && p <= 2) ? p : 0; }
 int trainlib_gemm_path(void) { return g.gemm_path; }
 

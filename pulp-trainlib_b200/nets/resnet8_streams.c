@@ -185,6 +185,7 @@ static float dummy1[1];
 static size_t p_off[2 * N_CONV + 8], p_cnt[2 * N_CONV + 8];
 static int p_n;
 static float *g_params, *g_grads;
+static float *g_img, *g_lab, *g_loss;                  /* resident copies used by resnet8_forward_host */
 
 static size_t conv_w_count(int i) { return (size_t)SPEC[i].cout * SPEC[i].cin * SPEC[i].k * SPEC[i].k; }
 
@@ -223,6 +224,7 @@ size_t resnet8_workspace_floats(int n)
     per += 2 * (act_floats(C2) + act_floats(C4) + act_floats(C6));             /* residual sums */
     per += act_floats(C2) + act_floats(C4);                                     /* shortcut input-gradient temporaries */
     per += 2 * 64 + 2 * RESNET8_CLASSES;                                        /* pooled features, logits */
+    per += RESNET8_IMAGE_FLOATS + RESNET8_CLASSES + 1;                          /* resident copy of a host batch: images, labels, losses */
     return per * (size_t)n + 64;
 }
 
@@ -298,6 +300,7 @@ int resnet8_bind(int n, float *params, float *grads, float *ws)
     mkblob(&b_tmp[1], NULL, take(&ws, N * act_floats(C4)), 32, 16, 16);      /* dX of P3 before it is added to sum 2 */
     { float *d = take(&ws, N * 64), *g = take(&ws, N * 64); mkblob(&b_gap, d, g, 64, 1, 1); }
     { float *d = take(&ws, N * RESNET8_CLASSES), *g = take(&ws, N * RESNET8_CLASSES); mkblob(&b_z, d, g, 1, 1, RESNET8_CLASSES); }
+    g_img = take(&ws, N * RESNET8_IMAGE_FLOATS); g_lab = take(&ws, N * RESNET8_CLASSES); g_loss = take(&ws, N);
 
     /* conv wiring: input blob of every conv */
     struct blob *conv_in[N_CONV] = {&b_x, &b_norm[0], &b_norm[1], &b_sum[0], &b_norm[3], &b_sum[0], &b_sum[1], &b_norm[5], &b_sum[1]};
@@ -350,6 +353,18 @@ void resnet8_forward(const float *images, const float *labels, float *loss)
     linear_fw(&a_fc);
     a_loss.target = (float *)labels; a_loss.wr_loss = loss;
     loss_call(&a_loss, pulp_CrossEntropyLoss);
+}
+
+void resnet8_forward_host(const float *host_images, const float *host_labels, float *host_loss)
+{
+#ifdef NET_REFERENCE
+    resnet8_forward(host_images, host_labels, host_loss);
+#else
+    trainlib_memcpy_h2d(g_img, host_images, sizeof(float) * (size_t)g_n * RESNET8_IMAGE_FLOATS);
+    trainlib_memcpy_h2d(g_lab, host_labels, sizeof(float) * (size_t)g_n * RESNET8_CLASSES);
+    resnet8_forward(g_img, g_lab, g_loss);
+    trainlib_memcpy_d2h(host_loss, g_loss, sizeof(float) * (size_t)g_n);
+#endif
 }
 
 static void conv_bw(int i) { conv_wg(&a_conv[i]); if (!a_conv[i].skip_in_grad) conv_ig(&a_conv[i]); }

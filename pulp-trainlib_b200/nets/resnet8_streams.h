@@ -28,6 +28,10 @@ void   resnet8_init_params(float *host_params, unsigned seed);
 int    resnet8_bind(int n_streams, float *params, float *grads, float *workspace);
 /* images [n][3][32][32], labels one-hot [n][10]; loss [n] receives the per-stream CrossEntropy. */
 void   resnet8_forward(const float *images, const float *labels, float *loss);
+/* Same step for callers whose batch lives in host memory: the images and labels are copied into
+ * the workspace once (they are read by the forward, the loss backward and the stem's weight
+ * gradient), the losses are copied back. */
+void   resnet8_forward_host(const float *host_images, const float *host_labels, float *host_loss);
 void   resnet8_backward(void);                    /* fills the flat gradient buffer (sum over streams) */
 void   resnet8_update(float lr);                  /* SGD on every parameter blob */
 float *resnet8_logits(void);                      /* [n][10], inside the workspace */
