@@ -77,6 +77,9 @@ const char *trainlib_profile_entry(int i, long long *launches, double *total_ms)
 /* ---- GEMM path selection for diagnostics and profiling.
  * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force tcgen05 tensor-core tiles. */
 void  trainlib_set_gemm_path(int path);
+/* 0 while every tensor-core kernel so far finished normally; otherwise the id of the bounded
+ * device-side wait that gave up (the kernel then returned early and its output is invalid). */
+int   trainlib_tc_status(void);
 int   trainlib_gemm_path(void);
 
 #ifdef __cplusplus

@@ -146,7 +146,7 @@ template <class F> void conv2d_fw_impl(void *args)
     const T *b = (a->USE_BIASES == 1 && a->bias) ? sc.in(a->bias->data, (size_t)g.Cout) : nullptr;
     T *y = sc.out(a->output->data, (size_t)g.n * g.Cout * g.Hout * g.Wout);
     if (!sc.ok()) return;
-    conv_fw<T>(g, x, w, b, y);
+    conv_fw<T>(sc, g, x, w, b, y);
 }
 template <class F> void conv2d_wg_impl(void *args)
 {
@@ -171,7 +171,7 @@ template <class F> void conv2d_ig_impl(void *args)
     const T *w = sc.in(a->coeff->data, (size_t)g.Cout * g.Cin * g.Hk * g.Wk);
     T *dx = sc.out(a->input->diff, (size_t)g.n * g.Cin * g.Hin * g.Win);
     if (!sc.ok()) return;
-    conv_ig<T>(g, dy, w, dx);
+    conv_ig<T>(sc, g, dy, w, dx);
 }
 
 // Naive kernels on matMul_args [ref: lib/sources/pulp_conv_naive_fp32.c:198-515]:
@@ -197,7 +197,7 @@ template <class F> void naive_impl(void *args, int step)
     if (step == STEP_FW) {
         const T *x = sc.in(a->A, nx), *w = sc.in(a->B, nw), *b = ub ? sc.in(a->bias, (size_t)g.Cout) : nullptr;
         T *y = sc.out(a->C, ny);
-        if (sc.ok()) conv_fw<T>(g, x, w, b, y);
+        if (sc.ok()) conv_fw<T>(sc, g, x, w, b, y);
     } else if (step == STEP_WGT_GRAD) {
         const T *x = sc.in(a->A, nx), *dy = sc.in(a->C, ny);
         T *dw = sc.out(a->B, nw), *db = ub ? sc.out(a->bias, (size_t)g.Cout) : nullptr;
@@ -205,7 +205,7 @@ template <class F> void naive_impl(void *args, int step)
     } else {
         const T *dy = sc.in(a->C, ny), *w = sc.in(a->B, nw);
         T *dx = sc.out(a->A, nx);
-        if (sc.ok()) conv_ig<T>(g, dy, w, dx);
+        if (sc.ok()) conv_ig<T>(sc, g, dy, w, dx);
     }
 }
 
@@ -264,9 +264,9 @@ template <class F> void pw_impl(void *args, int step)
     const size_t nx = (size_t)n * Cin * HW, ny = (size_t)n * Cout * HW, nw = (size_t)Cin * Cout;
     if (a->HWC == 0 && n > 1) {                      // many streams: the conv kernels batch over streams
         ConvGeom g = {Cin, a->input->H, a->input->W, Cout, 1, 1, a->input->H, a->input->W, 1, 1, 0, 0, n, false, false};
-        if (step == STEP_FW) { const T *x = sc.in(a->input->data, nx), *w = sc.in(a->coeff->data, nw); T *y = sc.out(a->output->data, ny); if (sc.ok()) conv_fw<T>(g, x, w, (const T *)nullptr, y); }
+        if (step == STEP_FW) { const T *x = sc.in(a->input->data, nx), *w = sc.in(a->coeff->data, nw); T *y = sc.out(a->output->data, ny); if (sc.ok()) conv_fw<T>(sc, g, x, w, (const T *)nullptr, y); }
         else if (step == STEP_WGT_GRAD) { const T *x = sc.in(a->input->data, nx), *dy = sc.in(a->output->diff, ny); T *dw = sc.out(a->coeff->diff, nw); if (sc.ok()) conv_wg<T>(sc, g, x, dy, dw, (T *)nullptr); }
-        else { const T *dy = sc.in(a->output->diff, ny), *w = sc.in(a->coeff->data, nw); T *dx = sc.out(a->input->diff, nx); if (sc.ok()) conv_ig<T>(g, dy, w, dx); }
+        else { const T *dy = sc.in(a->output->diff, ny), *w = sc.in(a->coeff->data, nw); T *dx = sc.out(a->input->diff, nx); if (sc.ok()) conv_ig<T>(sc, g, dy, w, dx); }
         return;
     }
     GemmDesc<T> d;
@@ -304,9 +304,9 @@ template <class F> void dw_impl(void *args, int step)
                "pulp_conv_dw: output blob %dx%d does not match the geometry", g.Hout, g.Wout);
     Scope sc;
     const size_t nx = (size_t)g.n * g.Cin * g.Hin * g.Win, ny = (size_t)g.n * g.Cin * g.Hout * g.Wout, nw = (size_t)g.Cin * g.Hk * g.Wk;
-    if (step == STEP_FW) { const T *x = sc.in(a->input->data, nx), *w = sc.in(a->coeff->data, nw); T *y = sc.out(a->output->data, ny); if (sc.ok()) conv_fw<T>(g, x, w, (const T *)nullptr, y); }
+    if (step == STEP_FW) { const T *x = sc.in(a->input->data, nx), *w = sc.in(a->coeff->data, nw); T *y = sc.out(a->output->data, ny); if (sc.ok()) conv_fw<T>(sc, g, x, w, (const T *)nullptr, y); }
     else if (step == STEP_WGT_GRAD) { const T *x = sc.in(a->input->data, nx), *dy = sc.in(a->output->diff, ny); T *dw = sc.out(a->coeff->diff, nw); if (sc.ok()) conv_wg<T>(sc, g, x, dy, dw, (T *)nullptr); }
-    else { const T *dy = sc.in(a->output->diff, ny), *w = sc.in(a->coeff->data, nw); T *dx = sc.out(a->input->diff, nx); if (sc.ok()) conv_ig<T>(g, dy, w, dx); }
+    else { const T *dy = sc.in(a->output->diff, ny), *w = sc.in(a->coeff->data, nw); T *dx = sc.out(a->input->diff, nx); if (sc.ok()) conv_ig<T>(sc, g, dy, w, dx); }
 }
 
 // ------------------------------------------------------------------ linear

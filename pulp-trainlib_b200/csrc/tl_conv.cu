@@ -195,8 +195,23 @@ static bool conv_fw_plan(const ConvGeom &g, int &TH, int &TW, int &S_T, int &CC,
     return smem <= 200 * 1024;
 }
 
-template <class T> void conv_fw(const ConvGeom &g, const T *x, const T *w, const T *bias, T *y)
+template <class T> static bool try_tc_fw(Scope &, const ConvGeom &, const T *, const T *, const T *, T *) { return false; }
+template <> bool try_tc_fw<float>(Scope &sc, const ConvGeom &g, const float *x, const float *w, const float *bias, float *y)
 {
+    return conv_tc_run(sc, x, w, bias, y, g.n, g.Cin, g.Hin, g.Win, g.Cout, g.Hout, g.Wout, g.Hk, g.Wk, g.sh, g.sw, g.padU, g.padL, g.Cout, g.Cin, false);
+}
+template <class T> static bool try_tc_ig(Scope &, const ConvGeom &, const T *, const T *, T *) { return false; }
+template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy, const float *w, float *dx)
+{
+    // stride 1 only: dX is a stride-1 convolution of dY with the rotated filters and padding k-1-pad
+    if (g.sh != 1 || g.sw != 1 || g.Hk - 1 - g.padU < 0 || g.Wk - 1 - g.padL < 0) return false;
+    return conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
+                       g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
+}
+
+template <class T> void conv_fw(Scope &sc, const ConvGeom &g, const T *x, const T *w, const T *bias, T *y)
+{
+    if (!g.depthwise && try_tc_fw<T>(sc, g, x, w, bias, y)) return;
     if (g.depthwise) {
         long long total = (long long)g.n * g.Cin * g.Hout * g.Wout;
         int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
@@ -305,8 +320,9 @@ conv_ig_kernel(ConvGeom g, const T *__restrict__ dy, const T *__restrict__ w, T 
     }
 }
 
-template <class T> void conv_ig(const ConvGeom &g, const T *dy, const T *w, T *dx)
+template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx)
 {
+    if (!g.depthwise && try_tc_ig<T>(sc, g, dy, w, dx)) return;
     if (g.depthwise) {
         long long total = (long long)g.n * g.Cin * g.Hin * g.Win;
         int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
@@ -569,9 +585,9 @@ template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk
 }
 
 #define INST(T)                                                                                             \
-    template void conv_fw<T>(const ConvGeom &, const T *, const T *, const T *, T *);                       \
+    template void conv_fw<T>(Scope &, const ConvGeom &, const T *, const T *, const T *, T *);                       \
     template void conv_wg<T>(Scope &, const ConvGeom &, const T *, const T *, T *, T *);                    \
-    template void conv_ig<T>(const ConvGeom &, const T *, const T *, T *);                                  \
+    template void conv_ig<T>(Scope &, const ConvGeom &, const T *, const T *, T *);                                  \
     template void im2row<T>(const T *, T *, int, int, int, int, int, int, int, int, int, int, int, int, int, int); \
     template void blocktransp<T>(const T *, T *, int, int, int, int, int);
 INST(float)

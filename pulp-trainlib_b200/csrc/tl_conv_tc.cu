@@ -1,0 +1,378 @@
+// Convolution on the 5th-generation tensor cores: implicit GEMM with 3xTF32 split-precision fp32.
+//
+//   D[pixel][co] = sum_{tap, ci} A[pixel][(tap,ci)] * B[co][(tap,ci)]
+//
+// One persistent CTA per SM walks tiles of 128 output pixels.  Per tile and 16-channel group a TMA
+// tensor copy (cp.async.bulk.tensor, 4-D, out-of-bounds elements = the zero padding) drops the raw
+// input patch into shared memory.  Converter warps read it once per filter tap, split every value into
+// a TF32 "big" and "small" part (x ~= hi + lo) and store both straight into TENSOR MEMORY as the A
+// operand (tcgen05.st): thread = pixel = TMEM lane, 16 columns of hi and 16 of lo per tap, so the im2col
+// matrix never exists in shared or global memory.  One thread issues tcgen05.mma kind::tf32 with A from
+// TMEM and B (the prepared weights [hi rows | lo rows]) from shared memory:
+//     D'[:, 0:2N] += A_hi * [B_hi | B_lo]^T        D'[:, 0:N] += A_lo * B_hi^T
+// i.e. the three products of 3xTF32 (the lo*lo term is below fp32 resolution) with fp32 accumulation in
+// TMEM.  Epilogue warps read D' with tcgen05.ld, add the two halves and store the output.  The same
+// kernel computes the stride-1 input gradient when it is handed the output gradient as "input" and the
+// flipped, channel-swapped weights as "B".
+//
+// Replaces the im2col + mm lowering [ref: lib/sources/pulp_conv2d_fp32.c:85-113, :504-549;
+// lib/sources/pulp_im2col_fp32.c:157-232; lib/sources/pulp_matmul_fp32.c:190-262].
+#include "tl_kernels.h"
+#include "tl_tc.cuh"
+
+namespace tl {
+
+using namespace tc;
+
+struct ConvTcParams {
+    int n, Cin, Cout, Hout, Wout;
+    int Wk, taps, sh, sw;
+    int TH, TW, S_T, tiles_w, tiles_h, n_tiles;
+    int groups;                 // ceil(Cin / 16)
+    int PH, PWB, xoff;          // patch rows, patch row pitch in floats, first used column
+    int x_base, y_base;         // input coordinate of patch column 0 / row 0 for the tile at the origin
+    int NT;                     // output channels per CTA (16, 32 or 64); blockIdx.y picks the slice
+    const float *bprep;         // [Cout tiles][groups][taps][4][2*NT][4]
+    const float *bias;
+    float *y;
+    int *status;                // 0 = ok; set to a wait id when a bounded wait gave up
+};
+
+static constexpr int TC_THREADS = 14 * 32;
+static constexpr int PS = 3;    // raw patch ring
+static constexpr int AS = 4;    // A-operand ring in tensor memory (32 columns each)
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
+{
+    for (uint32_t i = 0; i < (1u << 21); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 32) __nanosleep(64);
+        if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, id);
+    return false;
+}
+
+// Whole-warp variant: lane 0 polls, every lane gets the same answer (the callers then run
+// warp-collective tcgen05 instructions, which need the warp converged).
+__device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, int lane)
+{
+    int ok = 1;
+    if (lane == 0) ok = wait_or_abort(bar, parity, abort_flag, status, id) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
+{
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NT = p.NT, N2 = 2 * NT;
+    const int chunks = p.groups * p.taps;
+    const int patch_floats = p.S_T * 16 * p.PH * p.PWB;
+    const uint32_t patch_bytes = (uint32_t)patch_floats * 4u;
+
+    // shared memory carve-up
+    float *Bs = reinterpret_cast<float *>(smem_raw);                                   // chunks * 32 * NT floats
+    const size_t b_floats = (size_t)chunks * 32 * NT;
+    float *patch = Bs + ((b_floats + 31) & ~(size_t)31);                               // PS * patch_floats (128-byte aligned)
+    const size_t patch_stride = ((size_t)patch_floats + 31) & ~(size_t)31;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(patch + PS * patch_stride);
+    uint64_t *patch_full = bars, *patch_empty = bars + PS, *a_full = bars + 2 * PS, *a_empty = bars + 2 * PS + AS;
+    uint64_t *d_full = bars + 2 * PS + 2 * AS, *d_empty = d_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t tmem_cols = (4 * NT + AS * 32) <= 256 ? 256u : 512u;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < PS; i++) { mbar_init(&patch_full[i], 1); mbar_init(&patch_empty[i], 8); }
+        for (int i = 0; i < AS; i++) { mbar_init(&a_full[i], 8); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap);
+    }
+    if (warp == 0) { tmem_alloc(tmem_slot, tmem_cols); tmem_relinquish(); }
+    // prepared weights of this CTA's output-channel slice -> shared memory (read by the tensor cores)
+    {
+        const float4 *src = reinterpret_cast<const float4 *>(p.bprep + (size_t)blockIdx.y * b_floats);
+        float4 *dst = reinterpret_cast<float4 *>(Bs);
+        for (size_t i = threadIdx.x; i < b_floats / 4; i += TC_THREADS) dst[i] = __ldg(src + i);
+        fence_proxy_async();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t d_col0 = tmem_base, a_col0 = tmem_base + 4 * NT;
+    const int co0 = blockIdx.y * NT;
+    const int tiles_per_stream_group = p.tiles_w * p.tiles_h;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t pc = 0;
+            for (int t = blockIdx.x; t < p.n_tiles && !*abort_flag; t += gridDim.x) {
+                const int tw0 = (t % p.tiles_w) * p.TW, th0 = ((t / p.tiles_w) % p.tiles_h) * p.TH, s0 = (t / tiles_per_stream_group) * p.S_T;
+                for (int g = 0; g < p.groups; g++, pc++) {
+                    const int slot = pc % PS;
+                    if (!wait_or_abort(&patch_empty[slot], ((pc / PS) & 1) ^ 1, abort_flag, p.status, 1)) break;
+                    mbar_arrive_expect_tx(&patch_full[slot], patch_bytes);
+                    tma_load_4d(patch + slot * patch_stride, &tmap, &patch_full[slot], p.x_base + tw0 * p.sw, p.y_base + th0 * p.sh, g * 16, s0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_2n = mma_idesc(FMT_TF32, 128, N2), idesc_n = mma_idesc(FMT_TF32, 128, NT);
+            const uint32_t bs_addr = smem_u32(Bs);
+            const uint32_t lbo = N2 * 16, sbo = 128;
+            uint32_t ac = 0, tcnt = 0;
+            for (int t = blockIdx.x; t < p.n_tiles && !*abort_flag; t += gridDim.x, tcnt++) {
+                const int dbuf = tcnt & 1;
+                if (!wait_or_abort(&d_empty[dbuf], ((tcnt >> 1) & 1) ^ 1, abort_flag, p.status, 2)) break;
+                tc_fence_after();
+                const uint32_t d_addr = d_col0 + dbuf * N2;
+                bool ok = true;
+                for (int c = 0; c < chunks; c++, ac++) {
+                    const int abuf = ac % AS;
+                    if (!wait_or_abort(&a_full[abuf], (ac / AS) & 1, abort_flag, p.status, 3)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = a_col0 + abuf * 32;
+                    const uint32_t b_chunk = bs_addr + (uint32_t)c * (32u * NT * 4u);
+#pragma unroll
+                    for (int kk = 0; kk < 2; kk++) {
+                        const uint64_t bdesc = smem_desc_kmajor(b_chunk + kk * 2 * lbo, lbo, sbo);
+                        mma_tf32_ts(d_addr, a_addr + kk * 8, bdesc, idesc_2n, (c | kk) ? 1u : 0u);
+                        mma_tf32_ts(d_addr, a_addr + 16 + kk * 8, bdesc, idesc_n, 1u);
+                    }
+                    mma_commit(&a_empty[abuf]);
+                }
+                if (!ok) break;
+                mma_commit(&d_full[dbuf]);
+            }
+        }
+    } else if (warp < 10) {
+        // ------------------------------------------------------------ converters: raw patch -> (hi, lo) -> tensor memory
+        const int cw = warp - 2;
+        const int q = warp & 3;                 // TMEM lane quarter this warp may access
+        const int h = cw >> 2;                  // which 8 of the 16 channels of a group
+        const int m = q * 32 + lane;            // pixel of the tile = TMEM lane
+        const int tp = p.TH * p.TW;
+        const int sl = m / tp, ph = (m % tp) / p.TW, pw = m % p.TW;
+        const int plane = p.PH * p.PWB;
+        const int base_off = ((sl * 16 + h * 8) * p.PH + ph * p.sh) * p.PWB + p.xoff + pw * p.sw;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        uint32_t pc = 0, ac = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+            for (int g = 0; g < p.groups && ok; g++, pc++) {
+                const int slot = pc % PS;
+                if (!warp_wait_or_abort(&patch_full[slot], (pc / PS) & 1, abort_flag, p.status, 4, lane)) { ok = false; break; }
+                const float *src = patch + slot * patch_stride + base_off;
+                for (int tap = 0; tap < p.taps; tap++, ac++) {
+                    const int abuf = ac % AS;
+                    const int kh = tap / p.Wk, kw = tap % p.Wk;
+                    uint32_t hi[8], lo[8];
+                    const float *s2 = src + kh * p.PWB + kw;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) split_tf32(s2[j * plane], hi[j], lo[j]);
+                    if (!warp_wait_or_abort(&a_empty[abuf], ((ac / AS) & 1) ^ 1, abort_flag, p.status, 5, lane)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = a_col0 + abuf * 32 + lane_addr + h * 8;
+                    tmem_st8(a_addr, hi);
+                    tmem_st8(a_addr + 16, lo);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[abuf]);
+                }
+                __syncwarp();
+                if (ok && lane == 0) mbar_arrive(&patch_empty[slot]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue: tensor memory -> global
+        const int q = warp & 3;
+        const int m = q * 32 + lane;
+        const int tp = p.TH * p.TW;
+        const int sl = m / tp, ph = (m % tp) / p.TW, pw = m % p.TW;
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const long long plane = (long long)p.Hout * p.Wout;
+        uint32_t tcnt = 0;
+        for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, tcnt++) {
+            const int dbuf = tcnt & 1;
+            const int tw0 = (t % p.tiles_w) * p.TW, th0 = ((t / p.tiles_w) % p.tiles_h) * p.TH, s0 = (t / tiles_per_stream_group) * p.S_T;
+            if (!warp_wait_or_abort(&d_full[dbuf], (tcnt >> 1) & 1, abort_flag, p.status, 6, lane)) break;
+            tc_fence_after();
+            const int s = s0 + sl, ho = th0 + ph, wo = tw0 + pw;
+            const bool valid = (s < p.n) && (ho < p.Hout) && (wo < p.Wout);
+            float *yp = p.y + ((long long)s * p.Cout + co0) * plane + (long long)ho * p.Wout + wo;
+            const uint32_t d_addr = d_col0 + dbuf * N2 + lane_addr;
+            for (int c0 = 0; c0 < NT; c0 += 8) {
+                uint32_t a[8], b[8];
+                tmem_ld8(d_addr + c0, a);
+                tmem_ld8(d_addr + NT + c0, b);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int co = co0 + c0 + j;
+                        if (co < p.Cout) {
+                            float v = __uint_as_float(a[j]) + __uint_as_float(b[j]);
+                            if (p.bias) v += __ldg(p.bias + co);
+                            yp[(long long)(c0 + j) * plane] = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&d_empty[dbuf]);
+        }
+    }
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
+}
+
+// Weights -> B operand.  Output layout per (co tile, group g, tap): [k4 = 0..3][row r = 0..2NT-1][j = 0..3],
+// row r < NT holds hi(w), row r >= NT holds lo(w) of output channel co = tile*NT + (r mod NT) and input
+// channel ci = g*16 + k4*4 + j.  `flip` builds the operand of the input gradient: output channel and input
+// channel swap roles and the tap index runs backwards (filter rotated by 180 degrees).
+__global__ void conv_tc_prep_weights_kernel(const float *__restrict__ w, float *__restrict__ out, int Cout, int Cin, int taps,
+                                            int NT, int groups, int co_tiles, int flip)
+{
+    const long long total = (long long)co_tiles * groups * taps * 32 * NT;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int j = e % 4, r = (e / 4) % (2 * NT), k4 = (e / (8 * NT)) % 4;
+        const long long rest = e / (32 * NT);
+        const int tap = rest % taps, g = (rest / taps) % groups, tile = rest / ((long long)taps * groups);
+        const int n_out = tile * NT + (r % NT), k_in = g * 16 + k4 * 4 + j;
+        float v = 0.f;
+        if (!flip) { if (n_out < Cout && k_in < Cin) v = w[((long long)n_out * Cin + k_in) * taps + tap]; }
+        else { if (n_out < Cin && k_in < Cout) v = w[((long long)k_in * Cin + n_out) * taps + (taps - 1 - tap)]; }
+        uint32_t hi, lo;
+        tc::split_tf32(v, hi, lo);
+        out[e] = __uint_as_float(r < NT ? hi : lo);
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+static int *status_word()
+{
+    static int *dev = nullptr;
+    if (!dev) { if (cudaMalloc(&dev, sizeof(int)) != cudaSuccess) return nullptr; cudaMemset(dev, 0, sizeof(int)); }
+    return dev;
+}
+
+// Runs the tensor-core kernel when the geometry qualifies; returns false to let the caller use the FFMA path.
+// src: [n][C_src][H_src][W_src], dst: [n][C_dst][H_dst][W_dst]; `flip` = input-gradient role (stride must be 1).
+bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
+                 int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip)
+{
+    if (gemm_path() == 1) return false;
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return false;
+    if (W_src % 4 != 0 || (((uintptr_t)src) & 15) != 0 || sh != sw || (sh != 1 && sh != 2)) return false;
+    if (Hk * Wk > 25 || n < 1) return false;
+    int TW, TH, S_T;
+    if (W_dst % 32 == 0) { TW = 32; TH = 4; S_T = 1; }
+    else if (W_dst == 16) { TW = 16; TH = 8; S_T = 1; }
+    else if (W_dst == 8 && H_dst == 8) { TW = 8; TH = 8; S_T = 2; }
+    else return false;
+    if (H_dst % TH != 0) return false;
+    const long long work = (long long)n * H_dst * W_dst * C_dst * C_src * Hk * Wk;
+    if (gemm_path() != 2 && work < (1ll << 24)) return false;  // too small to fill the machine: FFMA tiles win
+
+    ConvTcParams p;
+    p.n = n; p.Cin = C_src; p.Cout = C_dst; p.Hout = H_dst; p.Wout = W_dst;
+    p.Wk = Wk; p.taps = Hk * Wk; p.sh = sh; p.sw = sw;
+    p.TH = TH; p.TW = TW; p.S_T = S_T;
+    p.tiles_w = W_dst / TW; p.tiles_h = H_dst / TH;
+    const int tiles_s = ceil_div(n, S_T);
+    p.n_tiles = p.tiles_w * p.tiles_h * tiles_s;
+    p.groups = ceil_div(C_src, 16);
+    // the TMA start column must be a multiple of 4 floats (16 bytes): round down and remember the offset
+    const int first = -padL;
+    const int aligned = (first >= 0) ? (first / 4) * 4 : -(((-first) + 3) / 4) * 4;
+    p.xoff = first - aligned; p.x_base = aligned; p.y_base = -padU;
+    p.PH = (TH - 1) * sh + Hk;
+    p.PWB = ((p.xoff + (TW - 1) * sw + Wk) + 3) & ~3;
+    if (p.PWB > 256 || p.PH > 256) return false;
+    const size_t patch_floats = (((size_t)S_T * 16 * p.PH * p.PWB) + 31) & ~(size_t)31;
+    // output-channel slice per CTA: the largest of 64/32/16 whose weights fit beside the patch ring
+    const int cpad = ((C_dst + 15) / 16) * 16;
+    int NT = cpad >= 64 ? 64 : (cpad >= 32 ? 32 : 16);
+    size_t smem = 0;
+    for (;; NT /= 2) {
+        const size_t b_floats = (((size_t)p.groups * p.taps * 32 * NT) + 31) & ~(size_t)31;
+        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * AS + 4) * 8 + 16 + 128;
+        if (smem <= 220 * 1024 || NT == 16) break;
+    }
+    if (smem > 220 * 1024) return false;
+    p.NT = NT;
+    const int co_tiles = ceil_div(C_dst, NT);
+
+    CUtensorMap tmap;
+    cuuint64_t gdim[4] = {(cuuint64_t)W_src, (cuuint64_t)H_src, (cuuint64_t)C_src, (cuuint64_t)n};
+    cuuint64_t gstr[3] = {(cuuint64_t)W_src * 4, (cuuint64_t)W_src * H_src * 4, (cuuint64_t)W_src * H_src * C_src * 4};
+    cuuint32_t box[4] = {(cuuint32_t)p.PWB, (cuuint32_t)p.PH, 16u, (cuuint32_t)S_T};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)src, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+
+    const size_t bprep_floats = (size_t)co_tiles * p.groups * p.taps * 32 * NT;
+    float *bprep = sc.scratch<float>(bprep_floats);
+    int *status = status_word();
+    if (!bprep || !status) return false;
+    {
+        int blocks = (int)std::min<size_t>((bprep_floats + 255) / 256, (size_t)sm_count() * 4);
+        TL_LAUNCH(conv_tc_prep_weights_kernel, blocks, 256, 0, w, bprep, Cout_w, Cin_w, p.taps, NT, p.groups, co_tiles, flip ? 1 : 0);
+    }
+    p.bprep = bprep; p.bias = bias; p.y = dst; p.status = status;
+    static bool attr_set = false;
+    if (!attr_set) { cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; }
+    int ctas = sm_count() / co_tiles;
+    if (ctas < 1) ctas = 1;
+    if (ctas > p.n_tiles) ctas = p.n_tiles;
+    dim3 grid(ctas, co_tiles);
+    TL_LAUNCH(conv_tc_kernel, grid, TC_THREADS, smem, tmap, p);
+    return true;
+}
+
+// Non-zero after a kernel gave up on a bounded wait (which wait is encoded in the value).
+int conv_tc_status()
+{
+    int *dev = status_word();
+    int h = 0;
+    if (dev && cudaMemcpy(&h, dev, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess) return h;
+    return -1;
+}
+
+} // namespace tl

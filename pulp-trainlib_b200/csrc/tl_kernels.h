@@ -37,9 +37,14 @@ struct ConvGeom {
     bool depthwise;        // Cout == Cin, one filter per channel
     bool hwc;              // activations HWC, weights [Cout][Hk][Wk][Cin]
 };
-template <class T> void conv_fw(const ConvGeom &g, const T *x, const T *w, const T *bias, T *y);
+template <class T> void conv_fw(Scope &sc, const ConvGeom &g, const T *x, const T *w, const T *bias, T *y);
 template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const T *dy, T *dw, T *dbias);
-template <class T> void conv_ig(const ConvGeom &g, const T *dy, const T *w, T *dx);
+template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx);
+// tensor-core implicit GEMM (tl_conv_tc.cu); false = geometry does not qualify, use the FFMA kernels
+bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
+                 int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip);
+int conv_tc_status();
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
                                int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
 template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk, int Wk, int hwc);

@@ -1,6 +1,7 @@
 // Runtime of libtrainlib_b200: device context, error state, staging arena, memory modes,
 // streams mode, timers and the PMSIS stand-in (pi_cl_team_fork & friends).
 #include "tl_common.h"
+namespace tl { int conv_tc_status(); }
 #include "../../include/pmsis.h"
 #include <cstdarg>
 #include <cstring>
@@ -318,6 +319,7 @@ const char *trainlib_profile_entry(int i, long long *launches, double *total_ms)
     if (total_ms) *total_ms = g_prof[i].ms;
     return g_prof[i].name;
 }
+int trainlib_tc_status(void) { return ready() ? conv_tc_status() : -1; }
 void trainlib_set_gemm_path(int p) { g.gemm_path = (p >= 0 && p <= 2) ? p : 0; }
 int trainlib_gemm_path(void) { return g.gemm_path; }
 

@@ -129,6 +129,38 @@ def test_conv2d_sweep(run, oracle, g, half):
     assert_close(got["dx"].astype(F), oracle.conv2d_ig(dy, w, g), tol, "ig")
 
 
+TC_CASES = [(geom(16, 32, 32, 16, 3, pad=1), 2), (geom(16, 32, 32, 32, 3, stride=2, pad=1), 3), (geom(32, 16, 16, 32, 3, pad=1), 1),
+            (geom(32, 16, 16, 64, 3, stride=2, pad=1), 2), (geom(64, 8, 8, 64, 3, pad=1), 3), (geom(16, 32, 32, 32, 1, stride=2), 2),
+            (geom(3, 32, 32, 16, 3, pad=1), 2), (geom(20, 64, 64, 40, 3, pad=1), 1), (geom(16, 32, 32, 16, 5, pad=2), 1)]
+
+
+@pytest.mark.parametrize("g,n", TC_CASES, ids=lambda v: str(v) if isinstance(v, int) else "c%d_%d_o%d_k%d_s%d" % (v["Cin"], v["Hin"], v["Cout"], v["Hk"], v["sh"]))
+def test_conv2d_tensor_core_path(pkg, gpulib, oracle, g, n):
+    """tcgen05 implicit-GEMM kernels (3xTF32) forced on, n streams per launch, against the fp32 oracle"""
+    rng = seeded(g["Cin"] + 7 * g["Cout"] + n)
+    Ho, Wo = out_hw(g)
+    xs = rng.uniform(-1, 1, (n, g["Cin"], g["Hin"], g["Win"])).astype(F); w = rng.uniform(-1, 1, (g["Cout"], g["Cin"], g["Hk"], g["Wk"])).astype(F)
+    dys = rng.standard_normal((n, g["Cout"], Ho, Wo)).astype(F)
+    gpulib.trainlib_set_streams(n); gpulib.trainlib_set_gemm_path(2)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        X, W_, dY = r.t(xs), r.t(w), r.t(dys)
+        Y, dX, dW, one = r.zeros(n, g["Cout"], Ho, Wo), r.zeros(*xs.shape), r.zeros(*w.shape), r.zeros(1)
+        args = r.args("Conv2D_args", input=r.blob(X, dX, C=g["Cin"], H=g["Hin"], W=g["Win"]), coeff=r.blob(W_, dW, C=g["Cin"], H=g["Hk"], W=g["Wk"], dim=w.size),
+                      bias=r.blob(one, one), output=r.blob(Y, dY, C=g["Cout"], H=Ho, W=Wo), Lpad=g["padL"], Rpad=g["padR"], Upad=g["padU"], Dpad=g["padD"],
+                      stride_h=g["sh"], stride_w=g["sw"], i2c_buffer=one, bt_buffer=one, USE_BIASES=0, USE_IM2COL=1, HWC=0)
+        l0 = gpulib.trainlib_kernel_launches()
+        r.call("pulp_conv2d_fp32_fw_cl", args); r.call("pulp_conv2d_fp32_bw_input_grads_cl", args)
+        assert gpulib.trainlib_tc_status() == 0, "a bounded tensor-core wait gave up: id %d" % gpulib.trainlib_tc_status()
+        y, dx = Y.get(), dX.get()
+        for s in range(n):
+            assert_close(y[s], oracle.conv2d_fw(xs[s], w, None, g), FP32_TOL, "tc fw stream %d" % s)
+            assert_close(dx[s], oracle.conv2d_ig(dys[s], w, g), FP32_TOL, "tc ig stream %d" % s)
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1); gpulib.trainlib_set_gemm_path(0)
+
+
 def test_mhsa_config3(run, oracle):
     """config 3: L = E = F = 256, 4 heads of 64; x ~ N(0,1), W ~ N(0, 1/E), dy ~ N(0,1), zero biases"""
     rng = seeded(3)
