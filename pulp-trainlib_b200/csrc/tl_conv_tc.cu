@@ -19,6 +19,7 @@
 // lib/sources/pulp_im2col_fp32.c:157-232; lib/sources/pulp_matmul_fp32.c:190-262].
 #include "tl_kernels.h"
 #include "tl_tc.cuh"
+#include <cstdlib>
 
 namespace tl {
 
@@ -38,16 +39,29 @@ struct ConvTcParams {
     int *status;                // 0 = ok; set to a wait id when a bounded wait gave up
 };
 
-static constexpr int TC_THREADS = 14 * 32;
-static constexpr int PS = 3;    // raw patch ring
-static constexpr int AS = 4;    // A-operand ring in tensor memory (32 columns each)
+// One thread can start a tcgen05.mma only every ~130 cycles whatever its size (measured on B200), while an
+// MMA of this kernel (M 128 x N 32..128 x K 8) keeps the tensor pipe busy for 16..64 cycles.  Four warps
+// therefore issue MMAs side by side.  The accumulators start from zero (the epilogue clears them), so the
+// order in which the issuers' MMAs land does not matter.
+//
+// Work is dealt statically: converter group j (4 warps, one per TMEM lane quarter) converts the filter taps
+// j, j+4, j+8, ... of every channel group into its own ring of RING tensor-memory buffers, and issuer j
+// multiplies exactly those chunks.  Every mbarrier thus has one producer group and one consumer that both
+// walk the same chunk sequence, so a waiter can never be more than one phase away from the barrier (the
+// parity wait would alias otherwise).
+static constexpr int GROUPS = 4;            // converter groups = MMA issuers
+static constexpr int RING = 2;              // A buffers per group (32 TMEM columns each: 16 hi + 16 lo)
+static constexpr int FIRST_ISSUER = 2, FIRST_CONV = FIRST_ISSUER + GROUPS, FIRST_EPI = FIRST_CONV + 4 * GROUPS;
+static constexpr int TC_THREADS = (FIRST_EPI + 4) * 32;
+static constexpr int PS = 3;                // raw patch ring
+static constexpr int NA = GROUPS * RING;    // A buffers in tensor memory
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
 {
-    for (uint32_t i = 0; i < (1u << 21); i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 32) __nanosleep(64);
-        if ((i & 255) == 255 && *abort_flag) return false;
+    // each attempt may sleep in hardware for up to 20 us; 50k attempts bound the wait to about a second
+    for (uint32_t i = 0; i < 50000u; i++) {
+        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, id);
@@ -64,33 +78,35 @@ __device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parit
     return ok != 0;
 }
 
+// PLANE_B = bytes between two channels of the shared-memory patch when known at compile time (the 16 loads
+// of a tap then carry immediate offsets), 0 = take it from the parameters.
+template <int PLANE_B>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
 {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NT = p.NT, N2 = 2 * NT;
-    const int chunks = p.groups * p.taps;
     const int patch_floats = p.S_T * 16 * p.PH * p.PWB;
     const uint32_t patch_bytes = (uint32_t)patch_floats * 4u;
 
     // shared memory carve-up
     float *Bs = reinterpret_cast<float *>(smem_raw);                                   // chunks * 32 * NT floats
-    const size_t b_floats = (size_t)chunks * 32 * NT;
+    const size_t b_floats = (size_t)p.groups * p.taps * 32 * NT;
     float *patch = Bs + ((b_floats + 31) & ~(size_t)31);                               // PS * patch_floats (128-byte aligned)
     const size_t patch_stride = ((size_t)patch_floats + 31) & ~(size_t)31;
     uint64_t *bars = reinterpret_cast<uint64_t *>(patch + PS * patch_stride);
-    uint64_t *patch_full = bars, *patch_empty = bars + PS, *a_full = bars + 2 * PS, *a_empty = bars + 2 * PS + AS;
-    uint64_t *d_full = bars + 2 * PS + 2 * AS, *d_empty = d_full + 2;
+    uint64_t *patch_full = bars, *patch_empty = bars + PS, *a_full = bars + 2 * PS, *a_empty = bars + 2 * PS + NA;
+    uint64_t *d_full = bars + 2 * PS + 2 * NA, *d_empty = d_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
-    const uint32_t tmem_cols = (4 * NT + AS * 32) <= 256 ? 256u : 512u;
+    const uint32_t tmem_cols = 512u;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < PS; i++) { mbar_init(&patch_full[i], 1); mbar_init(&patch_empty[i], 8); }
-        for (int i = 0; i < AS; i++) { mbar_init(&a_full[i], 8); mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&d_full[i], 1); mbar_init(&d_empty[i], 4); }
+        for (int i = 0; i < PS; i++) { mbar_init(&patch_full[i], 1); mbar_init(&patch_empty[i], 4 * GROUPS); }
+        for (int i = 0; i < NA; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_empty[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&d_full[i], GROUPS); mbar_init(&d_empty[i], 4); }
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmap);
@@ -126,66 +142,91 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer
+        // spare warp
+    } else if (warp < FIRST_CONV) {
+        // ------------------------------------------------------------ MMA issuers
         if (lane == 0) {
+            const int me = warp - FIRST_ISSUER;
             const uint32_t idesc_2n = mma_idesc(FMT_TF32, 128, N2), idesc_n = mma_idesc(FMT_TF32, 128, NT);
             const uint32_t bs_addr = smem_u32(Bs);
             const uint32_t lbo = N2 * 16, sbo = 128;
-            uint32_t ac = 0, tcnt = 0;
-            for (int t = blockIdx.x; t < p.n_tiles && !*abort_flag; t += gridDim.x, tcnt++) {
+            const uint32_t tap_bytes = 32u * NT * 4u;
+            uint32_t k = 0, tcnt = 0;           // k = chunks of this group so far
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.n_tiles && ok && !*abort_flag; t += gridDim.x, tcnt++) {
                 const int dbuf = tcnt & 1;
-                if (!wait_or_abort(&d_empty[dbuf], ((tcnt >> 1) & 1) ^ 1, abort_flag, p.status, 2)) break;
+                if (!wait_or_abort(&d_empty[dbuf], (tcnt >> 1) & 1, abort_flag, p.status, 2)) break;
                 tc_fence_after();
                 const uint32_t d_addr = d_col0 + dbuf * N2;
-                bool ok = true;
-                for (int c = 0; c < chunks; c++, ac++) {
-                    const int abuf = ac % AS;
-                    if (!wait_or_abort(&a_full[abuf], (ac / AS) & 1, abort_flag, p.status, 3)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_addr = a_col0 + abuf * 32;
-                    const uint32_t b_chunk = bs_addr + (uint32_t)c * (32u * NT * 4u);
+                for (int g = 0; g < p.groups && ok; g++) {
+                    for (int tap = me; tap < p.taps; tap += GROUPS, k++) {
+                        const int abuf = me * RING + (k % RING);
+                        if (!wait_or_abort(&a_full[abuf], (k / RING) & 1, abort_flag, p.status, 3)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_addr = a_col0 + abuf * 32;
+                        const uint32_t b_tap = bs_addr + (uint32_t)(g * p.taps + tap) * tap_bytes;
 #pragma unroll
-                    for (int kk = 0; kk < 2; kk++) {
-                        const uint64_t bdesc = smem_desc_kmajor(b_chunk + kk * 2 * lbo, lbo, sbo);
-                        mma_tf32_ts(d_addr, a_addr + kk * 8, bdesc, idesc_2n, (c | kk) ? 1u : 0u);
-                        mma_tf32_ts(d_addr, a_addr + 16 + kk * 8, bdesc, idesc_n, 1u);
+                        for (int kk = 0; kk < 2; kk++) {
+                            const uint64_t bdesc = smem_desc_kmajor(b_tap + kk * 2 * lbo, lbo, sbo);
+                            mma_tf32_ts(d_addr, a_addr + kk * 8, bdesc, idesc_2n, 1u);
+                            mma_tf32_ts(d_addr, a_addr + 16 + kk * 8, bdesc, idesc_n, 1u);
+                        }
+                        mma_commit(&a_empty[abuf]);
                     }
-                    mma_commit(&a_empty[abuf]);
                 }
                 if (!ok) break;
-                mma_commit(&d_full[dbuf]);
+                mma_commit(&d_full[dbuf]);       // one arrival per issuer: the tile is complete when all have landed
             }
         }
-    } else if (warp < 10) {
+    } else if (warp < FIRST_EPI) {
         // ------------------------------------------------------------ converters: raw patch -> (hi, lo) -> tensor memory
-        const int cw = warp - 2;
+        // Warp (q, j): q = TMEM lane quarter (32 pixels), j = 0..3 takes the taps j, j+4, j+8, ... of every
+        // channel group, all 16 channels of the group per tap.
+        const int cw = warp - FIRST_CONV;
         const int q = warp & 3;                 // TMEM lane quarter this warp may access
-        const int h = cw >> 2;                  // which 8 of the 16 channels of a group
+        const int j = cw >> 2;                  // converter group: taps j, j+4, j+8, ... of every channel group
         const int m = q * 32 + lane;            // pixel of the tile = TMEM lane
         const int tp = p.TH * p.TW;
         const int sl = m / tp, ph = (m % tp) / p.TW, pw = m % p.TW;
-        const int plane = p.PH * p.PWB;
-        const int base_off = ((sl * 16 + h * 8) * p.PH + ph * p.sh) * p.PWB + p.xoff + pw * p.sw;
+        // all addressing below is 32-bit shared-window arithmetic, set up once per thread
+        const uint32_t plane_b = PLANE_B ? (uint32_t)PLANE_B : (uint32_t)(p.PH * p.PWB) * 4u, row_b = (uint32_t)p.PWB * 4u;
+        const uint32_t slot_b = (uint32_t)patch_stride * 4u;
+        const uint32_t base_b = smem_u32(patch) + (uint32_t)(((sl * 16) * p.PH + ph * p.sh) * p.PWB + p.xoff + pw * p.sw) * 4u;
+        const uint32_t first_tap_b = (uint32_t)((j / p.Wk) * p.PWB + (j % p.Wk)) * 4u;
+        const int first_kw = j % p.Wk;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        uint32_t pc = 0, ac = 0;
+        uint32_t pc = 0, k = 0;                 // k = chunks of this group so far (the paired issuer counts the same)
         bool ok = true;
         for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
             for (int g = 0; g < p.groups && ok; g++, pc++) {
                 const int slot = pc % PS;
                 if (!warp_wait_or_abort(&patch_full[slot], (pc / PS) & 1, abort_flag, p.status, 4, lane)) { ok = false; break; }
-                const float *src = patch + slot * patch_stride + base_off;
-                for (int tap = 0; tap < p.taps; tap++, ac++) {
-                    const int abuf = ac % AS;
-                    const int kh = tap / p.Wk, kw = tap % p.Wk;
-                    uint32_t hi[8], lo[8];
-                    const float *s2 = src + kh * p.PWB + kw;
+                // software pipeline: the raw values of the next tap are fetched while the tensor-memory
+                // stores of the current one drain
+                uint32_t tap_b = base_b + slot * slot_b + first_tap_b;
+                int kw = first_kw;
+                float raw[16];
+                if (j < p.taps) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) split_tf32(s2[j * plane], hi[j], lo[j]);
-                    if (!warp_wait_or_abort(&a_empty[abuf], ((ac / AS) & 1) ^ 1, abort_flag, p.status, 5, lane)) { ok = false; break; }
+                    for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
+                }
+                for (int tap = j; tap < p.taps; tap += GROUPS, k++) {
+                    const int abuf = j * RING + (k % RING);
+                    uint32_t hi[16], lo[16];
+#pragma unroll
+                    for (int c = 0; c < 16; c++) split_tf32_fast(raw[c], hi[c], lo[c]);
+                    if (!warp_wait_or_abort(&a_empty[abuf], ((k / RING) & 1) ^ 1, abort_flag, p.status, 5, lane)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = a_col0 + abuf * 32 + lane_addr + h * 8;
-                    tmem_st8(a_addr, hi);
-                    tmem_st8(a_addr + 16, lo);
+                    const uint32_t a_addr = a_col0 + abuf * 32 + lane_addr;
+                    tmem_st16(a_addr, hi);
+                    tmem_st16(a_addr + 16, lo);
+                    // advance (kh, kw) by GROUPS taps without dividing
+                    kw += GROUPS; tap_b += GROUPS * 4u;
+                    while (kw >= p.Wk) { kw -= p.Wk; tap_b += row_b - (uint32_t)p.Wk * 4u; }
+                    if (tap + GROUPS < p.taps) {
+#pragma unroll
+                        for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
+                    }
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
@@ -203,6 +244,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         const int sl = m / tp, ph = (m % tp) / p.TW, pw = m % p.TW;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         const long long plane = (long long)p.Hout * p.Wout;
+        const uint32_t zero8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        // both accumulator buffers start from zero; the first "d_empty" phase completes once that is done
+        for (int c0 = 0; c0 < 2 * N2; c0 += 8) tmem_st8(d_col0 + lane_addr + c0, zero8);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&d_empty[0]); mbar_arrive(&d_empty[1]); }
         uint32_t tcnt = 0;
         for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, tcnt++) {
             const int dbuf = tcnt & 1;
@@ -215,9 +263,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             const uint32_t d_addr = d_col0 + dbuf * N2 + lane_addr;
             for (int c0 = 0; c0 < NT; c0 += 8) {
                 uint32_t a[8], b[8];
-                tmem_ld8(d_addr + c0, a);
-                tmem_ld8(d_addr + NT + c0, b);
+                tmem_ld8(d_addr + c0, a);                       // A_hi*B_hi + A_lo*B_hi
+                tmem_ld8(d_addr + NT + c0, b);                  // A_hi*B_lo
                 tmem_wait_ld();
+                tmem_st8(d_addr + c0, zero8);                   // leave the accumulators cleared for the next tile
+                tmem_st8(d_addr + NT + c0, zero8);
                 if (valid) {
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
@@ -230,6 +280,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                     }
                 }
             }
+            tmem_wait_st();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&d_empty[dbuf]);
@@ -331,7 +382,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     size_t smem = 0;
     for (;; NT /= 2) {
         const size_t b_floats = (((size_t)p.groups * p.taps * 32 * NT) + 31) & ~(size_t)31;
-        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * AS + 4) * 8 + 16 + 128;
+        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * NA + 4) * 8 + 16 + 128;
         if (smem <= 220 * 1024 || NT == 16) break;
     }
     if (smem > 220 * 1024) return false;
@@ -356,13 +407,26 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
         TL_LAUNCH(conv_tc_prep_weights_kernel, blocks, 256, 0, w, bprep, Cout_w, Cin_w, p.taps, NT, p.groups, co_tiles, flip ? 1 : 0);
     }
     p.bprep = bprep; p.bias = bias; p.y = dst; p.status = status;
-    static bool attr_set = false;
-    if (!attr_set) { cudaFuncSetAttribute(conv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; }
     int ctas = sm_count() / co_tiles;
     if (ctas < 1) ctas = 1;
     if (ctas > p.n_tiles) ctas = p.n_tiles;
     dim3 grid(ctas, co_tiles);
-    TL_LAUNCH(conv_tc_kernel, grid, TC_THREADS, smem, tmap, p);
+    const int plane_b = p.PH * p.PWB * 4;
+#define TL_TC_LAUNCH(PB)                                                                                              \
+    do {                                                                                                              \
+        static bool attr_set = false;                                                                                 \
+        if (!attr_set) { cudaFuncSetAttribute(conv_tc_kernel<PB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; } \
+        TL_LAUNCH(conv_tc_kernel<PB>, grid, TC_THREADS, smem, tmap, p);                                               \
+    } while (0)
+    switch (plane_b) {                       // the patch shapes of 32x32 / 16x16 / 8x8 images with 3x3 and 1x1 filters
+    case 960: TL_TC_LAUNCH(960); break;      // 6 x 40 and 10 x 24 and 15 x 16 floats
+    case 640: TL_TC_LAUNCH(640); break;      // 10 x 16
+    case 2448: TL_TC_LAUNCH(2448); break;    // 17 x 36 (stride 2, 16 output columns)
+    case 1360: TL_TC_LAUNCH(1360); break;    // 17 x 20 (stride 2, 8 output columns)
+    case 1920: TL_TC_LAUNCH(1920); break;    // 15 x 32 (1x1 stride 2)
+    default: TL_TC_LAUNCH(0); break;
+    }
+#undef TL_TC_LAUNCH
     return true;
 }
 

@@ -161,6 +161,30 @@ def test_conv2d_tensor_core_path(pkg, gpulib, oracle, g, n):
         gpulib.trainlib_set_streams(1); gpulib.trainlib_set_gemm_path(0)
 
 
+def test_conv2d_tensor_core_many_tiles(pkg, gpulib, oracle):
+    """long persistent loops (hundreds of tiles per CTA): every barrier ring wraps many times; a few streams are checked"""
+    g = geom(16, 32, 32, 16, 3, pad=1)
+    n = 3000
+    rng = seeded(77)
+    xs = rng.uniform(-1, 1, (n, 16, 32, 32)).astype(F); w = rng.uniform(-1, 1, (16, 16, 3, 3)).astype(F)
+    gpulib.trainlib_set_streams(n)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        X, W_ = r.t(xs), r.t(w)
+        Y, one = r.zeros(n, 16, 32, 32), r.zeros(1)
+        args = r.args("Conv2D_args", input=r.blob(X, one, C=16, H=32, W=32), coeff=r.blob(W_, one, C=16, H=3, W=3, dim=w.size), bias=r.blob(one, one),
+                      output=r.blob(Y, one, C=16, H=32, W=32), Lpad=1, Rpad=1, Upad=1, Dpad=1, stride_h=1, stride_w=1, i2c_buffer=one, bt_buffer=one,
+                      USE_BIASES=0, USE_IM2COL=1, HWC=0)
+        r.call("pulp_conv2d_fp32_fw_cl", args)
+        assert gpulib.trainlib_tc_status() == 0, "a bounded tensor-core wait gave up: id %d" % gpulib.trainlib_tc_status()
+        y = Y.get()
+        for s in (0, 1, 147, 148, 1499, 2998, 2999):
+            assert_close(y[s], oracle.conv2d_fw(xs[s], w, None, g), FP32_TOL, "stream %d" % s)
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1)
+
+
 def test_mhsa_config3(run, oracle):
     """config 3: L = E = F = 256, 4 heads of 64; x ~ N(0,1), W ~ N(0, 1/E), dy ~ N(0,1), zero biases"""
     rng = seeded(3)

@@ -74,6 +74,7 @@ def test_resnet8_streams_are_independent(pkg, gpulib):
     whole = gpu_step(pkg, gpulib, net, 64, first=0)
     a = gpu_step(pkg, gpulib, net, 32, first=0)
     b = gpu_step(pkg, gpulib, net, 32, first=32)
-    assert np.array_equal(whole["logits"][:32], a["logits"]) and np.array_equal(whole["logits"][32:], b["logits"])
-    assert np.array_equal(whole["loss"][:32], a["loss"])
+    # (the kernel choice depends on the launch size, so the comparison allows rounding differences)
+    assert_close(whole["logits"][:32], a["logits"], FP32_TOL, "logits of shard a"); assert_close(whole["logits"][32:], b["logits"], FP32_TOL, "logits of shard b")
+    assert_close(whole["loss"][:32], a["loss"], FP32_TOL, "loss of shard a")
     assert_close(a["grads"] + b["grads"], whole["grads"], 2e-5, "gradient additivity over shards")
