@@ -82,6 +82,23 @@ void  trainlib_set_gemm_path(int path);
 int   trainlib_tc_status(void);
 int   trainlib_gemm_path(void);
 
+/* ---- Linear input gradient for callers that must not allocate.  No counterpart in the reference
+ * (it is a variant of pulp_linear_fp32_bw_input_grads_cl with plain arguments).
+ * dx[in] = W[out x in]^T dy[out], all three DEVICE pointers; the kernels run on `cuda_stream`
+ * (NULL = the default stream) and the call returns without synchronising.
+ * Who needs it: hosts that gave the whole device to their own memory pool, loops with a memory budget
+ * fixed at start-up, callers that cannot take the device-wide stall an allocation may cause.  The call
+ * performs no cudaMalloc/cudaFree and uses no allocating library routine; its scratch is a fixed 4 MiB
+ * array inside the library image (held by every GPU that loads the library until the process exits).
+ * Limits and rules:
+ *   - `in` may be at most 1 048 576; larger layers are refused with TL_ERR_TOO_LARGE (nothing runs);
+ *   - the first call on a device looks up the array's device address; make that first call before
+ *     starting any stream capture;
+ *   - all calls share the one array: calls that overlap on the GPU (different streams) race, serialise them;
+ *   - the array keeps the last call's partial sums; each call overwrites every entry it reads.
+ * Returns TL_OK or the error code it also latches. */
+int trainlib_linear_fp32_bw_input_grads_noalloc(const float *W, const float *dy, float *dx, int out, int in, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

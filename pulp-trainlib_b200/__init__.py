@@ -71,6 +71,8 @@ def load(path=LIB_PATH):
     lib.trainlib_set_gemm_path.argtypes = [ctypes.c_int]
     lib.trainlib_gemm_path.restype = ctypes.c_int
     lib.trainlib_tc_status.restype = ctypes.c_int
+    lib.trainlib_linear_fp32_bw_input_grads_noalloc.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    lib.trainlib_linear_fp32_bw_input_grads_noalloc.restype = ctypes.c_int
     lib.fastexp_gist.argtypes = [ctypes.c_float]; lib.fastexp_gist.restype = ctypes.c_float
     lib.q_rsqrt.argtypes = [ctypes.c_float]; lib.q_rsqrt.restype = ctypes.c_float
     if path == LIB_PATH:

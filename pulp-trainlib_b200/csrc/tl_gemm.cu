@@ -294,6 +294,61 @@ template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx
     TL_LAUNCH((linear_ig_reduce_kernel<T>), ceil_div(in, 256), 256, 0, part, dx, in, slabs);
 }
 
+} // namespace tl
+
+// ------------------------------------------------------------------ Linear input gradient without any allocation
+// Some hosts cannot let a library allocate device memory: an application that has handed the whole device to its
+// own memory pool (a cudaMalloc from here would fail or fragment it), a control loop whose memory budget is fixed
+// at start-up, or a caller that cannot afford the implicit device-wide synchronisation an allocation may cause.
+// For them the slab partials of the input-gradient kernel live in this fixed array instead of the staging arena.
+// Every GPU that loads the library carries the 4 MiB until the process exits.
+static constexpr size_t TL_NOALLOC_SCRATCH_FLOATS = (size_t)1 << 20;
+static __device__ __align__(256) float tl_noalloc_scratch[TL_NOALLOC_SCRATCH_FLOATS];
+static float *tl_noalloc_scratch_addr[64];          // per device: the array's device address (host code only has a stand-in symbol)
+
+extern "C" __attribute__((visibility("default")))
+int trainlib_linear_fp32_bw_input_grads_noalloc(const float *W, const float *dy, float *dx, int out, int in, void *cuda_stream)
+{
+    using namespace tl;
+    if (!W || !dy || !dx || out < 1 || in < 1) { set_error(TL_ERR_BAD_ARGS, "linear input gradient (no-alloc): null pointer or empty layer"); return TL_ERR_BAD_ARGS; }
+    if ((size_t)in > TL_NOALLOC_SCRATCH_FLOATS) {
+        set_error(TL_ERR_TOO_LARGE, "linear input gradient (no-alloc): in = %d exceeds the fixed scratch of %zu floats", in, TL_NOALLOC_SCRATCH_FLOATS);
+        return TL_ERR_TOO_LARGE;
+    }
+    int dev = 0;
+    if (!TL_CUDA(cudaGetDevice(&dev))) return TL_ERR_CUDA;
+    if (dev < 0 || dev >= 64) { set_error(TL_ERR_BAD_ARGS, "linear input gradient (no-alloc): device index %d", dev); return TL_ERR_BAD_ARGS; }
+    if (!tl_noalloc_scratch_addr[dev]) {
+        // once per device, with that device current: the symbol itself is not a device address
+        float *ptr = nullptr;
+        if (!TL_CUDA(cudaGetSymbolAddress((void **)&ptr, tl_noalloc_scratch))) return TL_ERR_CUDA;
+        tl_noalloc_scratch_addr[dev] = ptr;
+    }
+    float *part = tl_noalloc_scratch_addr[dev];
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // same slab plan as the allocating entry point, capped by the scratch capacity
+    const int col_blocks = ceil_div(ceil_div(in, 4), 128);
+    int slabs = ceil_div(4 * sms, col_blocks);
+    if (slabs > ceil_div(out, 8)) slabs = ceil_div(out, 8);
+    const int cap = (int)(TL_NOALLOC_SCRATCH_FLOATS / (size_t)in);
+    if (slabs > cap) slabs = cap;
+    if (slabs < 1) slabs = 1;
+    const int rows_per_slab = ceil_div(out, slabs);
+    slabs = ceil_div(out, rows_per_slab);
+    cudaStream_t st = (cudaStream_t)cuda_stream;
+    // every partial that the second kernel reads is written by the first one of the same call: nothing needs clearing
+    linear_ig_partial_kernel<float><<<dim3(col_blocks, slabs), 128, 0, st>>>(W, dy, part, out, in, rows_per_slab);
+    count_launch();
+    if (!TL_CUDA(cudaGetLastError())) return TL_ERR_CUDA;
+    linear_ig_reduce_kernel<float><<<ceil_div(in, 256), 256, 0, st>>>(part, dx, in, slabs);
+    count_launch();
+    if (!TL_CUDA(cudaGetLastError())) return TL_ERR_CUDA;
+    return TL_OK;
+}
+
+namespace tl {
+
 #define INST(T)                                                                                             \
     template void gemm<T>(const GemmDesc<T> &);                                                             \
     template void mm_contract<T>(const T *, const T *, T *, int, int, int, int, bool);                      \
