@@ -429,6 +429,138 @@ conv_wg_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict_
     }
 }
 
+// 3x3 weight gradient, register-tiled.  One warp covers the whole 16 (co) x 16 (ci) channel tile: lane =
+// (co block of 4) x (ci block of 2), so a thread owns 4 x 2 x 9 = 72 accumulators.  The 8 warps of a CTA each take
+// rows of the pixel tile; along a row the 3x3 input window of the two input channels slides through registers
+// (3 new shared-memory loads per channel and pixel), so a pixel costs 10 loads for 72 FMAs.  At the end the
+// warps add their accumulators into shared memory in warp order, and the CTA writes one partial.
+template <class T, int S>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
+                          int TH, int TW, int S_T, int tiles_w, int tiles_h, int ci_tiles)
+{
+    extern __shared__ __align__(16) float smem[];
+    const int PH = (TH - 1) * S + 3, PW = (TW - 1) * S + 3;
+    const int PWp = PW | 1;
+    const int PLANE = (PH * PWp) | 1;
+    const int TP = TH * TW, DYP = S_T * TP + 1;
+    float *xs = smem;                               // [S_T][16 ci][PLANE]
+    float *dys = smem + S_T * 16 * PLANE;           // [16 co][S_T * TP + 1]
+    float *accs = dys + 16 * DYP;                   // [16 co][16 ci][9] cross-warp sum
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cob = lane >> 3, cib = lane & 7;      // 4 co blocks of 4, 8 ci blocks of 2
+    const int ci0 = (blockIdx.x % ci_tiles) * 16, co0 = (blockIdx.x / ci_tiles) * 16;
+    const int group = blockIdx.y, groups = gridDim.y;
+
+    float acc[4][2][9];
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+#pragma unroll
+            for (int t = 0; t < 9; t++) acc[c][i][t] = 0.f;
+
+    const long long in_plane = (long long)g.Hin * g.Win, out_plane = (long long)g.Hout * g.Wout;
+    const int s_tiles = (g.n + S_T - 1) / S_T;
+    const long long items = (long long)s_tiles * tiles_h * tiles_w;
+    const long long per = (items + groups - 1) / groups;
+    const long long it_begin = (long long)group * per, it_end = min(items, it_begin + per);
+
+    for (long long it = it_begin; it < it_end; it++) {
+        const int s0 = (int)(it / (tiles_h * tiles_w)) * S_T;
+        const int trem = (int)(it % (tiles_h * tiles_w));
+        const int th0 = (trem / tiles_w) * TH, tw0 = (trem % tiles_w) * TW;
+        const int h_in0 = th0 * S - g.padU, w_in0 = tw0 * S - g.padL;
+        for (int e = tid; e < S_T * 16 * PH * PW; e += CONV_THREADS) {
+            int c = e % PW, r = (e / PW) % PH, ci = (e / (PW * PH)) % 16, sl = e / (PW * PH * 16);
+            int hi = h_in0 + r, wi = w_in0 + c;
+            float v = 0.f;
+            if (s0 + sl < g.n && ci0 + ci < g.Cin && hi >= 0 && hi < g.Hin && wi >= 0 && wi < g.Win)
+                v = ld(x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)hi * g.Win + wi);
+            xs[(sl * 16 + ci) * PLANE + r * PWp + c] = v;
+        }
+        for (int e = tid; e < 16 * S_T * TP; e += CONV_THREADS) {
+            int p = e % TP, sl = (e / TP) % S_T, co = e / (TP * S_T);
+            int ho = th0 + p / TW, wo = tw0 + p % TW;
+            float v = 0.f;
+            if (s0 + sl < g.n && co0 + co < g.Cout && ho < g.Hout && wo < g.Wout)
+                v = ld(dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)ho * g.Wout + wo);
+            dys[co * DYP + sl * TP + p] = v;
+        }
+        __syncthreads();
+        // rows of the item: (stream, tile row); warp w takes rows w, w+8, ...
+        for (int row = warp; row < S_T * TH; row += CONV_THREADS / 32) {
+            const int sl = row / TH, ph = row % TH;
+            const float *xa = xs + (sl * 16 + cib * 2) * PLANE + (ph * S) * PWp;     // ci = cib*2, window row 0
+            const float *xb = xa + PLANE;                                            // ci = cib*2 + 1
+            const float *dp = dys + (cob * 4) * DYP + sl * TP + ph * TW;
+            if (S == 1) {
+                // sliding window: w[ci][kh][k] holds column (pw + k) of the three window rows
+                float w[2][3][3];
+#pragma unroll
+                for (int kh = 0; kh < 3; kh++) { w[0][kh][1] = xa[kh * PWp]; w[0][kh][2] = xa[kh * PWp + 1]; w[1][kh][1] = xb[kh * PWp]; w[1][kh][2] = xb[kh * PWp + 1]; }
+                for (int pw = 0; pw < TW; pw++) {
+#pragma unroll
+                    for (int kh = 0; kh < 3; kh++) {
+                        w[0][kh][0] = w[0][kh][1]; w[0][kh][1] = w[0][kh][2]; w[0][kh][2] = xa[kh * PWp + pw + 2];
+                        w[1][kh][0] = w[1][kh][1]; w[1][kh][1] = w[1][kh][2]; w[1][kh][2] = xb[kh * PWp + pw + 2];
+                    }
+                    float d[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) d[c] = dp[c * DYP + pw];
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int i = 0; i < 2; i++)
+#pragma unroll
+                            for (int kh = 0; kh < 3; kh++)
+#pragma unroll
+                                for (int kw = 0; kw < 3; kw++) acc[c][i][kh * 3 + kw] = fmaf(d[c], w[i][kh][kw], acc[c][i][kh * 3 + kw]);
+                }
+            } else {
+                for (int pw = 0; pw < TW; pw++) {
+                    float w[2][9];
+#pragma unroll
+                    for (int kh = 0; kh < 3; kh++)
+#pragma unroll
+                        for (int kw = 0; kw < 3; kw++) { w[0][kh * 3 + kw] = xa[kh * PWp + pw * S + kw]; w[1][kh * 3 + kw] = xb[kh * PWp + pw * S + kw]; }
+                    float d[4];
+#pragma unroll
+                    for (int c = 0; c < 4; c++) d[c] = dp[c * DYP + pw];
+#pragma unroll
+                    for (int c = 0; c < 4; c++)
+#pragma unroll
+                        for (int i = 0; i < 2; i++)
+#pragma unroll
+                            for (int t = 0; t < 9; t++) acc[c][i][t] = fmaf(d[c], w[i][t], acc[c][i][t]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    // cross-warp sum in warp order (fixed order: same result on every run)
+    for (int w = 0; w < CONV_THREADS / 32; w++) {
+        if (warp == w) {
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int i = 0; i < 2; i++)
+#pragma unroll
+                    for (int t = 0; t < 9; t++) {
+                        float *a = accs + ((cob * 4 + c) * 16 + cib * 2 + i) * 9 + t;
+                        *a = (w == 0) ? acc[c][i][t] : *a + acc[c][i][t];
+                    }
+        }
+        __syncthreads();
+    }
+    float *pp = part + (long long)group * g.Cout * g.Cin * 9;
+    for (int e = tid; e < 16 * 16 * 9; e += CONV_THREADS) {
+        int t = e % 9, ci = (e / 9) % 16, co = e / (9 * 16);
+        if (co0 + co < g.Cout && ci0 + ci < g.Cin) pp[((long long)(co0 + co) * g.Cin + ci0 + ci) * 9 + t] = accs[e];
+    }
+}
+
 template <class T>
 __global__ void reduce_partials_kernel(const float *__restrict__ part, T *__restrict__ out, long long n, int groups)
 {
@@ -487,6 +619,35 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
         TL_LAUNCH((dw_wg_kernel<T>), g.Cin * KK, 256, 0, g, x, dy, dw);
         return;
     }
+    const long long nw = (long long)g.Cout * g.Cin * KK;
+    const int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
+    if (g.Hk == 3 && g.Wk == 3 && g.sh == g.sw && (g.sh == 1 || g.sh == 2)) {
+        // about 256 pixels per item: whole rows of up to 32 pixels, several streams when the image is small
+        int TW = g.Wout < 32 ? g.Wout : 32;
+        int TH = 256 / TW; if (TH > g.Hout) TH = g.Hout; if (TH < 1) TH = 1;
+        int S_T = 256 / (TH * TW); if (S_T > g.n) S_T = g.n; if (S_T < 1) S_T = 1;
+        const int PH = (TH - 1) * g.sh + 3, PWp = ((TW - 1) * g.sw + 3) | 1, PLANE = (PH * PWp) | 1;
+        size_t smem = ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 1) + 16 * 16 * 9) * sizeof(float);
+        if (smem <= 200 * 1024) {
+            int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH);
+            long long items = (long long)ceil_div(g.n, S_T) * tiles_w * tiles_h;
+            int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
+            if (groups > items) groups = (int)items;
+            if (groups < 1) groups = 1;
+            float *part = sc.scratch<float>((size_t)groups * nw);
+            if (!part) return;
+            dim3 grid(ci_tiles * co_tiles, groups);
+            if (g.sh == 1) {
+                if (smem > 48 * 1024) cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                TL_LAUNCH((conv_wg3x3_partial_kernel<T, 1>), grid, CONV_THREADS, smem, g, x, dy, part, TH, TW, S_T, tiles_w, tiles_h, ci_tiles);
+            } else {
+                if (smem > 48 * 1024) cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                TL_LAUNCH((conv_wg3x3_partial_kernel<T, 2>), grid, CONV_THREADS, smem, g, x, dy, part, TH, TW, S_T, tiles_w, tiles_h, ci_tiles);
+            }
+            TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
+            return;
+        }
+    }
     // pixel tile: whole rows, about 256 pixels
     int TW = g.Wout < 64 ? g.Wout : 64;
     int TH = 256 / TW; if (TH < 1) TH = 1; if (TH > g.Hout) TH = g.Hout;
@@ -498,12 +659,10 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
         return;
     }
     int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH);
-    int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
     long long items = (long long)g.n * tiles_w * tiles_h;
     int groups = ceil_div(4 * sm_count(), ci_tiles * co_tiles);
     if (groups > items) groups = (int)items;
     if (groups < 1) groups = 1;
-    const long long nw = (long long)g.Cout * g.Cin * KK;
     float *part = sc.scratch<float>((size_t)groups * nw);
     if (!part) return;
     dim3 grid(ci_tiles * co_tiles, groups);

@@ -298,15 +298,21 @@ __global__ void __launch_bounds__(256) instnorm_bw_param_kernel(const T *__restr
     b = block_sum(b, red);
     if (threadIdx.x == 0) { part[2 * plane] = a / sd; part[2 * plane + 1] = b; }
 }
+// One CTA per channel: threads take the streams round-robin, then a fixed-shape tree adds the
+// per-thread sums (same result on every run).
 template <class T>
-__global__ void instnorm_param_reduce_kernel(const float *__restrict__ part, T *__restrict__ dgb, int n, int C)
+__global__ void __launch_bounds__(128) instnorm_param_reduce_kernel(const float *__restrict__ part, T *__restrict__ dgb, int n, int C)
 {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+    __shared__ float red[33];
+    const int c = blockIdx.x;
     float a = 0.f, b = 0.f;
-    for (int s = 0; s < n; s++) { a += part[2 * ((long long)s * C + c)]; b += part[2 * ((long long)s * C + c) + 1]; }
-    st(dgb + c, a);
-    st(dgb + C + c, b);
+    for (int s = threadIdx.x; s < n; s += blockDim.x) {
+        const float2 v = *reinterpret_cast<const float2 *>(part + 2 * ((long long)s * C + c));
+        a += v.x; b += v.y;
+    }
+    a = block_sum(a, red);
+    b = block_sum(b, red);
+    if (threadIdx.x == 0) { st(dgb + c, a); st(dgb + C + c, b); }
 }
 
 template <class T>
@@ -328,7 +334,7 @@ void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgb, const T *mean
     float *part = sc.scratch<float>((size_t)2 * n * C);
     if (!part) return;
     TL_LAUNCH((instnorm_bw_param_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, part, mean, stdev, D);
-    TL_LAUNCH((instnorm_param_reduce_kernel<T>), ceil_div(C, 128), 128, 0, part, dgb, n, C);
+    TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
 }
 
 // ------------------------------------------------------------------ batch norm / layer norm (forward)
