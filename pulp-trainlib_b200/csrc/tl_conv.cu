@@ -429,27 +429,32 @@ conv_wg_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict_
     }
 }
 
-// 3x3 weight gradient, register-tiled.  One warp covers the whole 16 (co) x 16 (ci) channel tile: lane =
-// (co block of 4) x (ci block of 2), so a thread owns 4 x 2 x 9 = 72 accumulators.  The 8 warps of a CTA each take
-// rows of the pixel tile; along a row the 3x3 input window of the two input channels slides through registers
-// (3 new shared-memory loads per channel and pixel), so a pixel costs 10 loads for 72 FMAs.  At the end the
-// warps add their accumulators into shared memory in warp order, and the CTA writes one partial.
-template <class T, int S>
-__global__ void __launch_bounds__(CONV_THREADS)
+// 3x3 weight gradient with left padding 1, register-tiled.  One warp covers the whole 16 (co) x 16 (ci) channel tile:
+// lane = (co block of 4) x (ci pair {b, b+8}), so a thread owns 4 x 2 x 9 = 72 accumulators.  The 8 warps of a CTA
+// each take rows of the pixel tile, whose width TW is the whole output row.  Shared memory holds input rows as
+// [4 zero columns][Win values][4 zero columns] (16-byte aligned, filled with 16-byte copies) and dY rows contiguously,
+// so four output pixels cost 4 + 6 (stride 1) or 4 + 12 (stride 2) 16-byte shared loads for 288 FMAs.  The plane
+// stride is 4 x odd floats: the 8 ci pairs of a quarter warp then touch all 32 banks exactly once per 16-byte load.
+// At the end the warps add their accumulators into shared memory in warp order and the CTA writes one partial.
+template <class T, int S, int TW>
+__global__ void __launch_bounds__(CONV_THREADS, 2)
 conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
-                          int TH, int TW, int S_T, int tiles_w, int tiles_h, int ci_tiles)
+                          int TH, int S_T, int tiles_h, int ci_tiles, int vec)
 {
     extern __shared__ __align__(16) float smem[];
-    const int PH = (TH - 1) * S + 3, PW = (TW - 1) * S + 3;
-    const int PWp = PW | 1;
-    const int PLANE = (PH * PWp) | 1;
-    const int TP = TH * TW, DYP = S_T * TP + 1;
+    constexpr int WIN = S * TW;             // input row width (host guarantees g.Win == WIN)
+    constexpr int RW = WIN + 8;             // shared-memory row: input column w sits at 4 + w
+    constexpr int W4 = WIN / 4;
+    const int PH = (TH - 1) * S + 3;
+    int P4 = PH * RW / 4; P4 |= 1;
+    const int PLANE = 4 * P4;
+    const int TP = TH * TW, DYP = S_T * TP + 4;
     float *xs = smem;                               // [S_T][16 ci][PLANE]
-    float *dys = smem + S_T * 16 * PLANE;           // [16 co][S_T * TP + 1]
+    float *dys = smem + S_T * 16 * PLANE;           // [16 co][DYP]
     float *accs = dys + 16 * DYP;                   // [16 co][16 ci][9] cross-warp sum
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cob = lane >> 3, cib = lane & 7;      // 4 co blocks of 4, 8 ci blocks of 2
+    const int cob = lane >> 3, cib = lane & 7;
     const int ci0 = (blockIdx.x % ci_tiles) * 16, co0 = (blockIdx.x / ci_tiles) * 16;
     const int group = blockIdx.y, groups = gridDim.y;
 
@@ -461,80 +466,94 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
 #pragma unroll
             for (int t = 0; t < 9; t++) acc[c][i][t] = 0.f;
 
+    // the zero columns on both sides of every row are written once; staging only touches columns 4 .. 4 + WIN
+    for (int e = tid; e < S_T * 16 * PLANE; e += CONV_THREADS) xs[e] = 0.f;
+    __syncthreads();
+
     const long long in_plane = (long long)g.Hin * g.Win, out_plane = (long long)g.Hout * g.Wout;
     const int s_tiles = (g.n + S_T - 1) / S_T;
-    const long long items = (long long)s_tiles * tiles_h * tiles_w;
+    const long long items = (long long)s_tiles * tiles_h;
     const long long per = (items + groups - 1) / groups;
     const long long it_begin = (long long)group * per, it_end = min(items, it_begin + per);
 
     for (long long it = it_begin; it < it_end; it++) {
-        const int s0 = (int)(it / (tiles_h * tiles_w)) * S_T;
-        const int trem = (int)(it % (tiles_h * tiles_w));
-        const int th0 = (trem / tiles_w) * TH, tw0 = (trem % tiles_w) * TW;
-        const int h_in0 = th0 * S - g.padU, w_in0 = tw0 * S - g.padL;
-        for (int e = tid; e < S_T * 16 * PH * PW; e += CONV_THREADS) {
-            int c = e % PW, r = (e / PW) % PH, ci = (e / (PW * PH)) % 16, sl = e / (PW * PH * 16);
-            int hi = h_in0 + r, wi = w_in0 + c;
-            float v = 0.f;
-            if (s0 + sl < g.n && ci0 + ci < g.Cin && hi >= 0 && hi < g.Hin && wi >= 0 && wi < g.Win)
-                v = ld(x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)hi * g.Win + wi);
-            xs[(sl * 16 + ci) * PLANE + r * PWp + c] = v;
-        }
-        for (int e = tid; e < 16 * S_T * TP; e += CONV_THREADS) {
-            int p = e % TP, sl = (e / TP) % S_T, co = e / (TP * S_T);
-            int ho = th0 + p / TW, wo = tw0 + p % TW;
-            float v = 0.f;
-            if (s0 + sl < g.n && co0 + co < g.Cout && ho < g.Hout && wo < g.Wout)
-                v = ld(dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)ho * g.Wout + wo);
-            dys[co * DYP + sl * TP + p] = v;
+        const int s0 = (int)(it / tiles_h) * S_T;
+        const int th0 = (int)(it % tiles_h) * TH;
+        const int h_in0 = th0 * S - g.padU;
+        if (vec) {
+            if constexpr (sizeof(T) == 4) {
+                for (int e = tid; e < S_T * 16 * PH * W4; e += CONV_THREADS) {
+                    const int c4 = e % W4, rr = e / W4;
+                    const int r = rr % PH, ci = (rr / PH) & 15, sl = rr / (PH * 16);
+                    const int hi = h_in0 + r;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (s0 + sl < g.n && ci0 + ci < g.Cin && hi >= 0 && hi < g.Hin)
+                        v = __ldg(reinterpret_cast<const float4 *>(x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)hi * WIN) + c4);
+                    *reinterpret_cast<float4 *>(xs + (sl * 16 + ci) * PLANE + r * RW + 4 + 4 * c4) = v;
+                }
+                const int TP4 = TP / 4;
+                for (int e = tid; e < 16 * S_T * TP4; e += CONV_THREADS) {
+                    const int p4 = e % TP4, sl = (e / TP4) % S_T, co = e / (TP4 * S_T);
+                    const int ho = th0 + (4 * p4) / TW;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (s0 + sl < g.n && co0 + co < g.Cout && ho < g.Hout)
+                        v = __ldg(reinterpret_cast<const float4 *>(dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)th0 * TW) + p4);
+                    *reinterpret_cast<float4 *>(dys + co * DYP + sl * TP + 4 * p4) = v;
+                }
+            }
+        } else {
+            for (int rr = warp; rr < S_T * 16 * PH; rr += CONV_THREADS / 32) {
+                const int r = rr % PH, ci = (rr / PH) & 15, sl = rr / (PH * 16);
+                const int hi = h_in0 + r;
+                const bool ok = s0 + sl < g.n && ci0 + ci < g.Cin && hi >= 0 && hi < g.Hin;
+                const T *src = x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)hi * WIN;
+                float *dst = xs + (sl * 16 + ci) * PLANE + r * RW + 4;
+                for (int c = lane; c < WIN; c += 32) dst[c] = ok ? ld(src + c) : 0.f;
+            }
+            for (int rr = warp; rr < 16 * S_T * TH; rr += CONV_THREADS / 32) {
+                const int ph = rr % TH, sl = (rr / TH) % S_T, co = rr / (TH * S_T);
+                const bool ok = s0 + sl < g.n && co0 + co < g.Cout && th0 + ph < g.Hout;
+                const T *src = dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)(th0 + ph) * TW;
+                float *dst = dys + co * DYP + sl * TP + ph * TW;
+                for (int c = lane; c < TW; c += 32) dst[c] = ok ? ld(src + c) : 0.f;
+            }
         }
         __syncthreads();
-        // rows of the item: (stream, tile row); warp w takes rows w, w+8, ...
         for (int row = warp; row < S_T * TH; row += CONV_THREADS / 32) {
             const int sl = row / TH, ph = row % TH;
-            const float *xa = xs + (sl * 16 + cib * 2) * PLANE + (ph * S) * PWp;     // ci = cib*2, window row 0
-            const float *xb = xa + PLANE;                                            // ci = cib*2 + 1
+            const float *xb = xs + (sl * 16 + cib) * PLANE + (ph * S) * RW;        // ci = cib (i = 0), + 8 planes for i = 1
             const float *dp = dys + (cob * 4) * DYP + sl * TP + ph * TW;
-            if (S == 1) {
-                // sliding window: w[ci][kh][k] holds column (pw + k) of the three window rows
-                float w[2][3][3];
 #pragma unroll
-                for (int kh = 0; kh < 3; kh++) { w[0][kh][1] = xa[kh * PWp]; w[0][kh][2] = xa[kh * PWp + 1]; w[1][kh][1] = xb[kh * PWp]; w[1][kh][2] = xb[kh * PWp + 1]; }
-                for (int pw = 0; pw < TW; pw++) {
+            for (int k = 0; k < TW / 4; k++) {
+                float4 d[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) d[c] = *reinterpret_cast<const float4 *>(dp + c * DYP + 4 * k);
+#pragma unroll
+                for (int i = 0; i < 2; i++)
 #pragma unroll
                     for (int kh = 0; kh < 3; kh++) {
-                        w[0][kh][0] = w[0][kh][1]; w[0][kh][1] = w[0][kh][2]; w[0][kh][2] = xa[kh * PWp + pw + 2];
-                        w[1][kh][0] = w[1][kh][1]; w[1][kh][1] = w[1][kh][2]; w[1][kh][2] = xb[kh * PWp + pw + 2];
+                        const float *rp = xb + i * 8 * PLANE + kh * RW;
+                        // v[m] = shared column 3 + 4*S*k + m: pixel j of this group reads v[S*j + kw]
+                        float v[4 * S + 2];
+                        v[0] = rp[4 * S * k + 3];
+                        const float4 a = *reinterpret_cast<const float4 *>(rp + 4 * S * k + 4);
+                        v[1] = a.x; v[2] = a.y; v[3] = a.z; v[4] = a.w;
+                        if (S == 1) {
+                            v[5] = rp[4 * k + 8];
+                        } else {
+                            const float4 b = *reinterpret_cast<const float4 *>(rp + 8 * k + 8);
+                            v[5] = b.x; v[6] = b.y; v[7] = b.z; v[8] = b.w; v[9] = 0.f;
+                        }
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            const float dj[4] = {d[c].x, d[c].y, d[c].z, d[c].w};
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+#pragma unroll
+                                for (int kw = 0; kw < 3; kw++)
+                                    acc[c][i][kh * 3 + kw] = fmaf(dj[j], v[S * j + kw], acc[c][i][kh * 3 + kw]);
+                        }
                     }
-                    float d[4];
-#pragma unroll
-                    for (int c = 0; c < 4; c++) d[c] = dp[c * DYP + pw];
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-#pragma unroll
-                        for (int i = 0; i < 2; i++)
-#pragma unroll
-                            for (int kh = 0; kh < 3; kh++)
-#pragma unroll
-                                for (int kw = 0; kw < 3; kw++) acc[c][i][kh * 3 + kw] = fmaf(d[c], w[i][kh][kw], acc[c][i][kh * 3 + kw]);
-                }
-            } else {
-                for (int pw = 0; pw < TW; pw++) {
-                    float w[2][9];
-#pragma unroll
-                    for (int kh = 0; kh < 3; kh++)
-#pragma unroll
-                        for (int kw = 0; kw < 3; kw++) { w[0][kh * 3 + kw] = xa[kh * PWp + pw * S + kw]; w[1][kh * 3 + kw] = xb[kh * PWp + pw * S + kw]; }
-                    float d[4];
-#pragma unroll
-                    for (int c = 0; c < 4; c++) d[c] = dp[c * DYP + pw];
-#pragma unroll
-                    for (int c = 0; c < 4; c++)
-#pragma unroll
-                        for (int i = 0; i < 2; i++)
-#pragma unroll
-                            for (int t = 0; t < 9; t++) acc[c][i][t] = fmaf(d[c], w[i][t], acc[c][i][t]);
-                }
             }
         }
         __syncthreads();
@@ -548,7 +567,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
                 for (int i = 0; i < 2; i++)
 #pragma unroll
                     for (int t = 0; t < 9; t++) {
-                        float *a = accs + ((cob * 4 + c) * 16 + cib * 2 + i) * 9 + t;
+                        float *a = accs + ((cob * 4 + c) * 16 + cib + 8 * i) * 9 + t;
                         *a = (w == 0) ? acc[c][i][t] : *a + acc[c][i][t];
                     }
         }
@@ -621,32 +640,33 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     }
     const long long nw = (long long)g.Cout * g.Cin * KK;
     const int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
-    if (g.Hk == 3 && g.Wk == 3 && g.sh == g.sw && (g.sh == 1 || g.sh == 2)) {
-        // about 256 pixels per item: whole rows of up to 32 pixels, several streams when the image is small
-        int TW = g.Wout < 32 ? g.Wout : 32;
-        int TH = 256 / TW; if (TH > g.Hout) TH = g.Hout; if (TH < 1) TH = 1;
-        int S_T = 256 / (TH * TW); if (S_T > g.n) S_T = g.n; if (S_T < 1) S_T = 1;
-        const int PH = (TH - 1) * g.sh + 3, PWp = ((TW - 1) * g.sw + 3) | 1, PLANE = (PH * PWp) | 1;
-        size_t smem = ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 1) + 16 * 16 * 9) * sizeof(float);
-        if (smem <= 200 * 1024) {
-            int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH);
-            long long items = (long long)ceil_div(g.n, S_T) * tiles_w * tiles_h;
-            int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
-            if (groups > items) groups = (int)items;
-            if (groups < 1) groups = 1;
-            float *part = sc.scratch<float>((size_t)groups * nw);
-            if (!part) return;
-            dim3 grid(ci_tiles * co_tiles, groups);
-            if (g.sh == 1) {
-                if (smem > 48 * 1024) cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                TL_LAUNCH((conv_wg3x3_partial_kernel<T, 1>), grid, CONV_THREADS, smem, g, x, dy, part, TH, TW, S_T, tiles_w, tiles_h, ci_tiles);
-            } else {
-                if (smem > 48 * 1024) cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                TL_LAUNCH((conv_wg3x3_partial_kernel<T, 2>), grid, CONV_THREADS, smem, g, x, dy, part, TH, TW, S_T, tiles_w, tiles_h, ci_tiles);
-            }
-            TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
-            return;
-        }
+    if (g.Hk == 3 && g.Wk == 3 && g.sh == g.sw && (g.sh == 1 || g.sh == 2) && g.padL == 1 && g.Win == g.sw * g.Wout &&
+        (g.Wout == 8 || g.Wout == 16 || g.Wout == 32)) {
+        // about 256 (stride 1) or 128 (stride 2) pixels per item: whole output rows, several streams when the image is small
+        const int S = g.sh, TW = g.Wout, target = S == 1 ? 256 : 128;
+        int TH = target / TW; if (TH > g.Hout) TH = g.Hout; if (TH < 1) TH = 1;
+        int S_T = target / (TH * TW); if (S_T > g.n) S_T = g.n; if (S_T < 1) S_T = 1;
+        const int PH = (TH - 1) * S + 3, RW = g.Win + 8, PLANE = 4 * ((PH * RW / 4) | 1);
+        const size_t smem = ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4) + 16 * 16 * 9) * sizeof(float);
+        const int tiles_h = ceil_div(g.Hout, TH);
+        const long long items = (long long)ceil_div(g.n, S_T) * tiles_h;
+        int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
+        if (groups > items) groups = (int)items;
+        if (groups < 1) groups = 1;
+        float *part = sc.scratch<float>((size_t)groups * nw);
+        if (!part) return;
+        const int vec = sizeof(T) == 4 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
+        dim3 grid(ci_tiles * co_tiles, groups);
+#define TL_WG3_LAUNCH(S_, TW_)                                                                                        \
+    do {                                                                                                              \
+        cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_>), grid, CONV_THREADS, smem, g, x, dy, part, TH, S_T, tiles_h, ci_tiles, vec); \
+    } while (0)
+        if (S == 1) { if (TW == 32) TL_WG3_LAUNCH(1, 32); else if (TW == 16) TL_WG3_LAUNCH(1, 16); else TL_WG3_LAUNCH(1, 8); }
+        else        { if (TW == 32) TL_WG3_LAUNCH(2, 32); else if (TW == 16) TL_WG3_LAUNCH(2, 16); else TL_WG3_LAUNCH(2, 8); }
+#undef TL_WG3_LAUNCH
+        TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
+        return;
     }
     // pixel tile: whole rows, about 256 pixels
     int TW = g.Wout < 64 ? g.Wout : 64;
