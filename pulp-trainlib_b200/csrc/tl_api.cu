@@ -449,6 +449,7 @@ template <class F> void softmax_bw_impl(void *args)
 }
 
 // ------------------------------------------------------------------ norms
+static constexpr int STEP_BOTH_GRADS = 100;   // internal: parameter and input gradients in one pass
 template <class F> void instnorm_impl(void *args, int step)
 {
     auto *a = (typename F::instnorm_t *)args; typedef typename F::T T;
@@ -469,6 +470,12 @@ template <class F> void instnorm_impl(void *args, int step)
         const T *m = sc.in(a->running_mean, ns), *v = sc.in(a->running_var, ns), *s = sc.in(a->running_stdev, ns);
         T *dx = sc.out(a->input->diff, nx);
         if (sc.ok()) instnorm_bw_input<T>(x, dy, dx, gb, m, v, s, n, C, D);
+    } else if (step == STEP_BOTH_GRADS) {
+        const T *x = sc.in(a->input->data, nx), *dy = sc.in(a->output->diff, nx), *gb = sc.in(a->coeff->data, (size_t)2 * C);
+        const T *m = sc.in(a->running_mean, ns), *v = sc.in(a->running_var, ns), *s = sc.in(a->running_stdev, ns);
+        T *dx = sc.out(a->input->diff, nx);
+        T *dgb = sc.out(a->coeff->diff, (size_t)2 * C);
+        if (sc.ok()) instnorm_bw_both<T>(sc, x, dy, dx, dgb, gb, m, v, s, n, C, D);
     } else {
         const T *x = sc.in(a->input->data, nx), *dy = sc.in(a->output->diff, nx);
         const T *m = sc.in(a->running_mean, ns), *s = sc.in(a->running_stdev, ns);
@@ -802,12 +809,14 @@ TL_EXPORT void pulp_instnorm_parallelized_fp32_bw_param_grads_cl(void *a) { inst
 TL_EXPORT void pulp_instnorm_fp32_bw_cl(void *a)
 {
     auto *c = (InstNorm_args *)a;
+    if (c->skip_wg_grad == 0 && c->skip_in_grad == 0) { instnorm_impl<F32>(a, STEP_BOTH_GRADS); return; }
     if (c->skip_wg_grad == 0) instnorm_impl<F32>(a, STEP_WGT_GRAD);
     if (c->skip_in_grad == 0) instnorm_impl<F32>(a, STEP_IN_GRAD);
 }
 TL_EXPORT void pulp_instnorm_fp16_bw_cl(void *a)
 {
     auto *c = (InstNorm_args_fp16 *)a;
+    if (c->skip_wg_grad == 0 && c->skip_in_grad == 0) { instnorm_impl<F16>(a, STEP_BOTH_GRADS); return; }
     if (c->skip_wg_grad == 0) instnorm_impl<F16>(a, STEP_WGT_GRAD);
     if (c->skip_in_grad == 0) instnorm_impl<F16>(a, STEP_IN_GRAD);
 }

@@ -200,12 +200,50 @@ template <> bool try_tc_fw<float>(Scope &sc, const ConvGeom &g, const float *x, 
 {
     return conv_tc_run(sc, x, w, bias, y, g.n, g.Cin, g.Hin, g.Win, g.Cout, g.Hout, g.Wout, g.Hk, g.Wk, g.sh, g.sw, g.padU, g.padL, g.Cout, g.Cin, false);
 }
+// dY of a strided convolution spread onto the input grid: dil[s][co][h][w] = dY[s][co][h/sh][w/sw] where both
+// divisions are exact and in range, 0 elsewhere.  One thread writes four consecutive columns (Win % 4 == 0).
+__global__ void __launch_bounds__(256) conv_dilate_dy_kernel(const float *__restrict__ dy, float *__restrict__ dil, long long planes,
+                                                            int Hout, int Wout, int Hin, int Win, int sh, int sw)
+{
+    const int W4 = Win / 4;
+    const long long total = planes * Hin * W4;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const int w4 = (int)(e % W4), h = (int)((e / W4) % Hin);
+        const long long pl = e / ((long long)W4 * Hin);
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (h % sh == 0 && h / sh < Hout) {
+            const float *row = dy + (pl * Hout + h / sh) * Wout;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int w = 4 * w4 + j;
+                if (w % sw == 0 && w / sw < Wout) v[j] = __ldg(row + w / sw);
+            }
+        }
+        *reinterpret_cast<float4 *>(dil + (pl * Hin + h) * Win + 4 * w4) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+}
+
 template <class T> static bool try_tc_ig(Scope &, const ConvGeom &, const T *, const T *, T *) { return false; }
 template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy, const float *w, float *dx)
 {
-    // stride 1 only: dX is a stride-1 convolution of dY with the rotated filters and padding k-1-pad
-    if (g.sh != 1 || g.sw != 1 || g.Hk - 1 - g.padU < 0 || g.Wk - 1 - g.padL < 0) return false;
-    return conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
+    // dX is a stride-1 convolution of dY with the rotated filters and padding k-1-pad
+    if (g.Hk - 1 - g.padU < 0 || g.Wk - 1 - g.padL < 0) return false;
+    if (g.sh == 1 && g.sw == 1)
+        return conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
+                           g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
+    // strided: spread dY onto the input grid (zeros between the samples), then the same stride-1 convolution.
+    // The tensor cores do sh*sw times the useful work, which still beats the FFMA kernel by a wide margin.
+    if (g.Win % 4 != 0 || (long long)(g.Hout - 1) * g.sh >= g.Hin || (long long)(g.Wout - 1) * g.sw >= g.Win) return false;
+    if (!conv_tc_run(sc, nullptr, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hin, g.Win, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
+                     g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true, true))
+        return false;
+    const long long planes = (long long)g.n * g.Cout;
+    float *dil = sc.scratch<float>((size_t)planes * g.Hin * g.Win);
+    if (!dil) return false;
+    const long long total = planes * g.Hin * (g.Win / 4);
+    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
+    TL_LAUNCH(conv_dilate_dy_kernel, blocks, 256, 0, dy, dil, planes, g.Hout, g.Wout, g.Hin, g.Win, g.sh, g.sw);
+    return conv_tc_run(sc, dil, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hin, g.Win, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
                        g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
 }
 
@@ -429,14 +467,14 @@ conv_wg_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict_
     }
 }
 
-// 3x3 weight gradient with left padding 1, register-tiled.  One warp covers the whole 16 (co) x 16 (ci) channel tile:
-// lane = (co block of 4) x (ci pair {b, b+8}), so a thread owns 4 x 2 x 9 = 72 accumulators.  The 8 warps of a CTA
+// Weight gradient of a 3x3 filter with left padding 1 (K = 3) or a 1x1 filter without padding (K = 1), register-tiled.  One warp covers the whole 16 (co) x 16 (ci) channel tile:
+// lane = (co block of 4) x (ci pair {b, b+8}), so a thread owns 4 x 2 x K*K accumulators (72 for 3x3).  The 8 warps of a CTA
 // each take rows of the pixel tile, whose width TW is the whole output row.  Shared memory holds input rows as
 // [4 zero columns][Win values][4 zero columns] (16-byte aligned, filled with 16-byte copies) and dY rows contiguously,
 // so four output pixels cost 4 + 6 (stride 1) or 4 + 12 (stride 2) 16-byte shared loads for 288 FMAs.  The plane
 // stride is 4 x odd floats: the 8 ci pairs of a quarter warp then touch all 32 banks exactly once per 16-byte load.
 // At the end the warps add their accumulators into shared memory in warp order and the CTA writes one partial.
-template <class T, int S, int TW>
+template <class T, int S, int TW, int K>
 __global__ void __launch_bounds__(CONV_THREADS, 2)
 conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
                           int TH, int S_T, int tiles_h, int ci_tiles, int vec)
@@ -445,26 +483,27 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
     constexpr int WIN = S * TW;             // input row width (host guarantees g.Win == WIN)
     constexpr int RW = WIN + 8;             // shared-memory row: input column w sits at 4 + w
     constexpr int W4 = WIN / 4;
-    const int PH = (TH - 1) * S + 3;
+    constexpr int KK = K * K, VOFF = (K == 1) ? 1 : 0;   // v[] below starts one column left of the first input column
+    const int PH = (TH - 1) * S + K;
     int P4 = PH * RW / 4; P4 |= 1;
     const int PLANE = 4 * P4;
     const int TP = TH * TW, DYP = S_T * TP + 4;
     float *xs = smem;                               // [S_T][16 ci][PLANE]
     float *dys = smem + S_T * 16 * PLANE;           // [16 co][DYP]
-    float *accs = dys + 16 * DYP;                   // [16 co][16 ci][9] cross-warp sum
+    float *accs = dys + 16 * DYP;                   // [16 co][16 ci][KK] cross-warp sum
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cob = lane >> 3, cib = lane & 7;
     const int ci0 = (blockIdx.x % ci_tiles) * 16, co0 = (blockIdx.x / ci_tiles) * 16;
     const int group = blockIdx.y, groups = gridDim.y;
 
-    float acc[4][2][9];
+    float acc[4][2][KK];
 #pragma unroll
     for (int c = 0; c < 4; c++)
 #pragma unroll
         for (int i = 0; i < 2; i++)
 #pragma unroll
-            for (int t = 0; t < 9; t++) acc[c][i][t] = 0.f;
+            for (int t = 0; t < KK; t++) acc[c][i][t] = 0.f;
 
     // the zero columns on both sides of every row are written once; staging only touches columns 4 .. 4 + WIN
     for (int e = tid; e < S_T * 16 * PLANE; e += CONV_THREADS) xs[e] = 0.f;
@@ -531,7 +570,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
 #pragma unroll
                 for (int i = 0; i < 2; i++)
 #pragma unroll
-                    for (int kh = 0; kh < 3; kh++) {
+                    for (int kh = 0; kh < K; kh++) {
                         const float *rp = xb + i * 8 * PLANE + kh * RW;
                         // v[m] = shared column 3 + 4*S*k + m: pixel j of this group reads v[S*j + kw]
                         float v[4 * S + 2];
@@ -550,8 +589,8 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
 #pragma unroll
                             for (int j = 0; j < 4; j++)
 #pragma unroll
-                                for (int kw = 0; kw < 3; kw++)
-                                    acc[c][i][kh * 3 + kw] = fmaf(dj[j], v[S * j + kw], acc[c][i][kh * 3 + kw]);
+                                for (int kw = 0; kw < K; kw++)
+                                    acc[c][i][kh * K + kw] = fmaf(dj[j], v[S * j + kw + VOFF], acc[c][i][kh * K + kw]);
                         }
                     }
             }
@@ -566,17 +605,17 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
 #pragma unroll
                 for (int i = 0; i < 2; i++)
 #pragma unroll
-                    for (int t = 0; t < 9; t++) {
-                        float *a = accs + ((cob * 4 + c) * 16 + cib + 8 * i) * 9 + t;
+                    for (int t = 0; t < KK; t++) {
+                        float *a = accs + ((cob * 4 + c) * 16 + cib + 8 * i) * KK + t;
                         *a = (w == 0) ? acc[c][i][t] : *a + acc[c][i][t];
                     }
         }
         __syncthreads();
     }
-    float *pp = part + (long long)group * g.Cout * g.Cin * 9;
-    for (int e = tid; e < 16 * 16 * 9; e += CONV_THREADS) {
-        int t = e % 9, ci = (e / 9) % 16, co = e / (9 * 16);
-        if (co0 + co < g.Cout && ci0 + ci < g.Cin) pp[((long long)(co0 + co) * g.Cin + ci0 + ci) * 9 + t] = accs[e];
+    float *pp = part + (long long)group * g.Cout * g.Cin * KK;
+    for (int e = tid; e < 16 * 16 * KK; e += CONV_THREADS) {
+        int t = e % KK, ci = (e / KK) % 16, co = e / (KK * 16);
+        if (co0 + co < g.Cout && ci0 + ci < g.Cin) pp[((long long)(co0 + co) * g.Cin + ci0 + ci) * KK + t] = accs[e];
     }
 }
 
@@ -640,14 +679,14 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     }
     const long long nw = (long long)g.Cout * g.Cin * KK;
     const int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
-    if (g.Hk == 3 && g.Wk == 3 && g.sh == g.sw && (g.sh == 1 || g.sh == 2) && g.padL == 1 && g.Win == g.sw * g.Wout &&
-        (g.Wout == 8 || g.Wout == 16 || g.Wout == 32)) {
+    const bool k3 = g.Hk == 3 && g.Wk == 3 && g.padL == 1, k1 = g.Hk == 1 && g.Wk == 1 && g.padL == 0 && g.padU == 0;
+    if ((k3 || k1) && g.sh == g.sw && (g.sh == 1 || g.sh == 2) && g.Win == g.sw * g.Wout && (g.Wout == 8 || g.Wout == 16 || g.Wout == 32)) {
         // about 256 (stride 1) or 128 (stride 2) pixels per item: whole output rows, several streams when the image is small
-        const int S = g.sh, TW = g.Wout, target = S == 1 ? 256 : 128;
+        const int S = g.sh, TW = g.Wout, K = g.Hk, target = S == 1 ? 256 : 128;
         int TH = target / TW; if (TH > g.Hout) TH = g.Hout; if (TH < 1) TH = 1;
         int S_T = target / (TH * TW); if (S_T > g.n) S_T = g.n; if (S_T < 1) S_T = 1;
-        const int PH = (TH - 1) * S + 3, RW = g.Win + 8, PLANE = 4 * ((PH * RW / 4) | 1);
-        const size_t smem = ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4) + 16 * 16 * 9) * sizeof(float);
+        const int PH = (TH - 1) * S + K, RW = g.Win + 8, PLANE = 4 * ((PH * RW / 4) | 1);
+        const size_t smem = ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4) + 16 * 16 * KK) * sizeof(float);
         const int tiles_h = ceil_div(g.Hout, TH);
         const long long items = (long long)ceil_div(g.n, S_T) * tiles_h;
         int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
@@ -659,8 +698,13 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
         dim3 grid(ci_tiles * co_tiles, groups);
 #define TL_WG3_LAUNCH(S_, TW_)                                                                                        \
     do {                                                                                                              \
-        cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_>), grid, CONV_THREADS, smem, g, x, dy, part, TH, S_T, tiles_h, ci_tiles, vec); \
+        if (K == 3) {                                                                                                 \
+            cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_, 3>), grid, CONV_THREADS, smem, g, x, dy, part, TH, S_T, tiles_h, ci_tiles, vec); \
+        } else {                                                                                                      \
+            cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_, 1>), grid, CONV_THREADS, smem, g, x, dy, part, TH, S_T, tiles_h, ci_tiles, vec); \
+        }                                                                                                             \
     } while (0)
         if (S == 1) { if (TW == 32) TL_WG3_LAUNCH(1, 32); else if (TW == 16) TL_WG3_LAUNCH(1, 16); else TL_WG3_LAUNCH(1, 8); }
         else        { if (TW == 32) TL_WG3_LAUNCH(2, 32); else if (TW == 16) TL_WG3_LAUNCH(2, 16); else TL_WG3_LAUNCH(2, 8); }

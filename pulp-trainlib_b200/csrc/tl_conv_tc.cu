@@ -344,7 +344,7 @@ static int *status_word()
 // src: [n][C_src][H_src][W_src], dst: [n][C_dst][H_dst][W_dst]; `flip` = input-gradient role (stride must be 1).
 bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
                  int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
-                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip)
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run)
 {
     if (gemm_path() == 1) return false;
     EncodeTiledFn enc = encode_fn();
@@ -386,6 +386,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
         if (smem <= 220 * 1024 || NT == 16) break;
     }
     if (smem > 220 * 1024) return false;
+    if (dry_run) return true;   // geometry qualifies; nothing launched
     p.NT = NT;
     const int co_tiles = ceil_div(C_dst, NT);
 
@@ -424,6 +425,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     case 2448: TL_TC_LAUNCH(2448); break;    // 17 x 36 (stride 2, 16 output columns)
     case 1360: TL_TC_LAUNCH(1360); break;    // 17 x 20 (stride 2, 8 output columns)
     case 1920: TL_TC_LAUNCH(1920); break;    // 15 x 32 (1x1 stride 2)
+    case 512: TL_TC_LAUNCH(512); break;      // 4 x 32 and 8 x 16 (1x1 stride 1)
     default: TL_TC_LAUNCH(0); break;
     }
 #undef TL_TC_LAUNCH

@@ -315,16 +315,142 @@ __global__ void __launch_bounds__(128) instnorm_param_reduce_kernel(const float 
     if (threadIdx.x == 0) { st(dgb + c, a); st(dgb + C + c, b); }
 }
 
+// fp32 planes of up to 1024 elements (a multiple of 4): one warp per plane, the plane held in registers as NV 16-byte
+// vectors per lane, so every element is read once and the reductions are warp shuffles without a CTA barrier.
+template <int NV>
+__global__ void __launch_bounds__(256) instnorm_fw_warp_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ gb,
+                                                               float *__restrict__ mean_o, float *__restrict__ var_o, float *__restrict__ std_o,
+                                                               long long planes, int C, int D, int frozen, float eps)
+{
+    const int lane = threadIdx.x & 31;
+    const long long plane = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (plane >= planes) return;
+    const int ch = (int)(plane % C), D4 = D >> 2;
+    const float4 *xp = reinterpret_cast<const float4 *>(x + plane * D);
+    float4 *yp = reinterpret_cast<float4 *>(y + plane * D);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) v[i] = (lane + 32 * i < D4) ? xp[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float mean, var, sd;
+    if (!frozen) {
+        float s = 0.f, q = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            q = fmaf(v[i].x, v[i].x, q); q = fmaf(v[i].y, v[i].y, q); q = fmaf(v[i].z, v[i].z, q); q = fmaf(v[i].w, v[i].w, q);
+        }
+        s = warp_sum(s); q = warp_sum(q);
+        const float inv = 1.f / (float)D;
+        mean = s * inv;
+        var = q * inv;
+        var = __fsub_rn(var, __fmul_rn(mean, mean));
+        var = var + eps;
+        if (var < 0.f) var = eps;
+        sd = sqrtf(var);
+        if (lane == 0) { mean_o[plane] = mean; var_o[plane] = var; std_o[plane] = sd; }
+    } else {
+        mean = mean_o[plane]; var = var_o[plane]; sd = std_o[plane];
+    }
+    const float gamma = __fdiv_rn(gb[ch], sd), beta = gb[C + ch];
+#pragma unroll
+    for (int i = 0; i < NV; i++)
+        if (lane + 32 * i < D4) {
+            float4 o;
+            o.x = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].x, mean)), beta); o.y = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].y, mean)), beta);
+            o.z = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].z, mean)), beta); o.w = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].w, mean)), beta);
+            yp[lane + 32 * i] = o;
+        }
+}
+// Backward of the same planes: both plane sums once, then dX and/or the per-plane (dgamma, dbeta) partials.
+template <int NV, bool DX, bool PART>
+__global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
+                                                               float *__restrict__ part, const float *__restrict__ gamma,
+                                                               const float *__restrict__ mean_i, const float *__restrict__ var_i,
+                                                               const float *__restrict__ std_i, long long planes, int C, int D)
+{
+    const int lane = threadIdx.x & 31;
+    const long long plane = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (plane >= planes) return;
+    const int ch = (int)(plane % C), D4 = D >> 2;
+    const float4 *xp = reinterpret_cast<const float4 *>(x + plane * D), *gp = reinterpret_cast<const float4 *>(dy + plane * D);
+    const float mean = mean_i[plane], sd = std_i[plane];
+    float4 v[NV], g[NV];
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        const bool in = lane + 32 * i < D4;
+        v[i] = in ? xp[lane + 32 * i] : make_float4(mean, mean, mean, mean);
+        g[i] = in ? gp[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float s = 0.f, p = 0.f;     // s = sum dy, p = sum (x - mean) dy
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        s += (g[i].x + g[i].y) + (g[i].z + g[i].w);
+        p = fmaf(v[i].x, g[i].x, p); p = fmaf(v[i].y, g[i].y, p); p = fmaf(v[i].z, g[i].z, p); p = fmaf(v[i].w, g[i].w, p);
+    }
+    s = warp_sum(s); p = warp_sum(p);
+    if (PART && lane == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
+    if (DX) {
+        const float var = var_i[plane], gm = gamma[ch], fD = (float)D, denom = fD * sd;
+        float4 *dp = reinterpret_cast<float4 *>(dx + plane * D);
+#pragma unroll
+        for (int i = 0; i < NV; i++)
+            if (lane + 32 * i < D4) {
+                float4 o;
+                o.x = (-s - p * (v[i].x / var) + fD * g[i].x) * gm / denom; o.y = (-s - p * (v[i].y / var) + fD * g[i].y) * gm / denom;
+                o.z = (-s - p * (v[i].z / var) + fD * g[i].z) * gm / denom; o.w = (-s - p * (v[i].w / var) + fD * g[i].w) * gm / denom;
+                dp[lane + 32 * i] = o;
+            }
+    }
+}
+static inline bool aligned16(const void *a, const void *b, const void *c) { return ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c)) & 15) == 0; }
+static inline int instnorm_nv(int D) { return (D % 4 != 0 || D > 1024) ? 0 : (D <= 128 ? 1 : (D <= 256 ? 2 : (D <= 512 ? 4 : 8))); }
+#define TL_NV_SWITCH(nv, CALL)                                                                                         \
+    do { if ((nv) == 1) { CALL(1); } else if ((nv) == 2) { CALL(2); } else if ((nv) == 4) { CALL(4); } else { CALL(8); } } while (0)
+
+static bool instnorm_fw_warp(const float *x, float *y, const float *gb, float *mean, float *var, float *stdev, int n, int C, int D, bool frozen, float eps)
+{
+    const int nv = instnorm_nv(D);
+    if (!nv || !aligned16(x, y, nullptr)) return false;
+    const long long planes = (long long)n * C;
+#define TL_CALL(NV) TL_LAUNCH((instnorm_fw_warp_kernel<NV>), (unsigned)((planes + 7) / 8), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps)
+    TL_NV_SWITCH(nv, TL_CALL);
+#undef TL_CALL
+    return true;
+}
+template <class T> static bool instnorm_fw_warp(const T *, T *, const T *, T *, T *, T *, int, int, int, bool, float) { return false; }
+// dx and/or part may be null: the kernel variant is chosen accordingly
+static bool instnorm_bw_warp(const float *x, const float *dy, float *dx, float *part, const float *gamma, const float *mean, const float *var,
+                             const float *stdev, int n, int C, int D)
+{
+    const int nv = instnorm_nv(D);
+    if (!nv || !aligned16(x, dy, dx)) return false;
+    const long long planes = (long long)n * C;
+    const unsigned blocks = (unsigned)((planes + 7) / 8);
+#define TL_CALL(NV)                                                                                                    \
+    do {                                                                                                               \
+        if (dx && part) TL_LAUNCH((instnorm_bw_warp_kernel<NV, true, true>), blocks, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);   \
+        else if (dx) TL_LAUNCH((instnorm_bw_warp_kernel<NV, true, false>), blocks, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);     \
+        else TL_LAUNCH((instnorm_bw_warp_kernel<NV, false, true>), blocks, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);             \
+    } while (0)
+    TL_NV_SWITCH(nv, TL_CALL);
+#undef TL_CALL
+    return true;
+}
+template <class T> static bool instnorm_bw_warp(const T *, const T *, T *, float *, const T *, const T *, const T *, const T *, int, int, int) { return false; }
+
 template <class T>
 void instnorm_fw(const T *x, T *y, const T *gb, T *mean, T *var, T *stdev, int n, int C, int D, bool frozen, float eps)
 {
     if (n * C <= 0) return;
+    if (instnorm_fw_warp(x, y, gb, mean, var, stdev, n, C, D, frozen, eps)) return;
     TL_LAUNCH((instnorm_fw_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, y, gb, mean, var, stdev, C, D, frozen ? 1 : 0, eps);
 }
 template <class T>
 void instnorm_bw_input(const T *x, const T *dy, T *dx, const T *gamma, const T *mean, const T *var, const T *stdev, int n, int C, int D)
 {
     if (n * C <= 0) return;
+    if (instnorm_bw_warp(x, dy, dx, (float *)nullptr, gamma, mean, var, stdev, n, C, D)) return;
     TL_LAUNCH((instnorm_bw_input_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, dx, gamma, mean, var, stdev, C, D);
 }
 template <class T>
@@ -333,8 +459,23 @@ void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgb, const T *mean
     if (n * C <= 0) return;
     float *part = sc.scratch<float>((size_t)2 * n * C);
     if (!part) return;
-    TL_LAUNCH((instnorm_bw_param_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, part, mean, stdev, D);
+    if (!instnorm_bw_warp(x, dy, (T *)nullptr, part, (const T *)nullptr, mean, (const T *)nullptr, stdev, n, C, D))
+        TL_LAUNCH((instnorm_bw_param_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, part, mean, stdev, D);
     TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
+}
+// Both gradients of one layer in one pass over x and dy (falls back to the two separate passes).
+template <class T>
+void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *dx, T *dgb, const T *gamma, const T *mean, const T *var, const T *stdev, int n, int C, int D)
+{
+    if (n * C <= 0) return;
+    float *part = sc.scratch<float>((size_t)2 * n * C);
+    if (!part) return;
+    if (instnorm_bw_warp(x, dy, dx, part, gamma, mean, var, stdev, n, C, D)) {
+        TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
+        return;
+    }
+    instnorm_bw_param<T>(sc, x, dy, dgb, mean, stdev, n, C, D);
+    instnorm_bw_input<T>(x, dy, dx, gamma, mean, var, stdev, n, C, D);
 }
 
 // ------------------------------------------------------------------ batch norm / layer norm (forward)
@@ -666,6 +807,7 @@ template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int pad
     template void instnorm_fw<T>(const T *, T *, const T *, T *, T *, T *, int, int, int, bool, float);            \
     template void instnorm_bw_input<T>(const T *, const T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void instnorm_bw_param<T>(Scope &, const T *, const T *, T *, const T *, const T *, int, int, int);   \
+    template void instnorm_bw_both<T>(Scope &, const T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void batchnorm_fw<T>(const T *, T *, const T *, const T *, int, int, int, int, float);                \
     template void layernorm_fw<T>(const T *, T *, const T *, const T *, int, int, float);                          \
     template void mse_fw<T>(const T *, const T *, T *, int, int);                                                  \

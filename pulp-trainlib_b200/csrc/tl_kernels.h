@@ -43,7 +43,7 @@ template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const
 // tensor-core implicit GEMM (tl_conv_tc.cu); false = geometry does not qualify, use the FFMA kernels
 bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
                  int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
-                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip);
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false);
 int conv_tc_status();
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
                                int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
@@ -62,6 +62,8 @@ template <class T> void instnorm_bw_input(const T *x, const T *dy, T *dx, const 
                                           const T *var, const T *stdev, int n, int C, int D);
 template <class T> void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgamma_beta, const T *mean,
                                           const T *stdev, int n, int C, int D);
+template <class T> void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *dx, T *dgamma_beta, const T *gamma, const T *mean,
+                                         const T *var, const T *stdev, int n, int C, int D);
 template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps);
 template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps);
 template <class T> void mse_fw(const T *y, const T *t, T *loss, int dim, int n);

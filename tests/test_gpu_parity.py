@@ -131,7 +131,8 @@ def test_conv2d_sweep(run, oracle, g, half):
 
 TC_CASES = [(geom(16, 32, 32, 16, 3, pad=1), 2), (geom(16, 32, 32, 32, 3, stride=2, pad=1), 3), (geom(32, 16, 16, 32, 3, pad=1), 1),
             (geom(32, 16, 16, 64, 3, stride=2, pad=1), 2), (geom(64, 8, 8, 64, 3, pad=1), 3), (geom(16, 32, 32, 32, 1, stride=2), 2),
-            (geom(3, 32, 32, 16, 3, pad=1), 2), (geom(20, 64, 64, 40, 3, pad=1), 1), (geom(16, 32, 32, 16, 5, pad=2), 1)]
+            (geom(3, 32, 32, 16, 3, pad=1), 2), (geom(20, 64, 64, 40, 3, pad=1), 1), (geom(16, 32, 32, 16, 5, pad=2), 1),
+            (geom(16, 32, 32, 16, 3, stride=2, pad=0), 2), (geom(32, 16, 16, 64, 1, stride=2), 5)]
 
 
 @pytest.mark.parametrize("g,n", TC_CASES, ids=lambda v: str(v) if isinstance(v, int) else "c%d_%d_o%d_k%d_s%d" % (v["Cin"], v["Hin"], v["Cout"], v["Hk"], v["sh"]))
