@@ -42,14 +42,21 @@ def synthetic_batch(n, first_stream=0):
     return img, lab
 
 
+def shard_streams(total, rank, world):
+    """Contiguous block of streams owned by `rank`: (first stream, count).  The first total % world ranks take one more."""
+    base, extra = divmod(total, world)
+    return rank * base + min(rank, extra), base + (1 if rank < extra else 0)
+
+
 def host_params(net, seed=0):
     p = np.zeros(net.resnet8_param_count(), F)
     net.resnet8_init_params(p.ctypes.data, seed)
     return p
 
 
-def reference_step(net_ref, n, first_stream=0, lr=LR, params=None, steps=1):
-    """Run the same C network against the reference library on the host; returns dict of results."""
+def reference_step(net_ref, n, first_stream=0, lr=LR, params=None, steps=1, allreduce=None):
+    """Run the same C network against the reference library on the host; returns dict of results.
+    `allreduce(array)` (in place) stands where the GPU arm sums the weight gradients over the ranks."""
     p = host_params(net_ref) if params is None else params.copy()
     g = np.zeros_like(p)
     ws = np.zeros(net_ref.resnet8_workspace_floats(n), F)
@@ -60,6 +67,8 @@ def reference_step(net_ref, n, first_stream=0, lr=LR, params=None, steps=1):
     for _ in range(steps):
         net_ref.resnet8_forward(img.ctypes.data, lab.ctypes.data, loss.ctypes.data)
         net_ref.resnet8_backward()
+        if allreduce is not None:
+            allreduce(g)
         grads = g.copy()
         net_ref.resnet8_update(lr)
     dt = (time.perf_counter() - t0) / steps
@@ -79,8 +88,7 @@ class ResNet8Streams(object):
         pkg, lib = self.pkg, self.lib
         net = bind_net(NET_B200)
         total = int(os.environ.get("TRAINLIB_BENCH_STREAMS", STREAMS))
-        n = total // world
-        first = rank * n
+        first, n = shard_streams(total, rank, world)
         torch = None
         if world > 1:
             import torch

@@ -488,9 +488,10 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
     int P4 = PH * RW / 4; P4 |= 1;
     const int PLANE = 4 * P4;
     const int TP = TH * TW, DYP = S_T * TP + 4;
-    float *xs = smem;                               // [S_T][16 ci][PLANE]
-    float *dys = smem + S_T * 16 * PLANE;           // [16 co][DYP]
-    float *accs = dys + 16 * DYP;                   // [16 co][16 ci][KK] cross-warp sum
+    // two stages of {input patch [S_T][16 ci][PLANE], dY tile [16 co][DYP]}: the next item is fetched with
+    // 16-byte asynchronous copies while the current one is consumed
+    const int STAGE = S_T * 16 * PLANE + 16 * DYP;
+    float *accs = smem;                             // [16 co][16 ci][KK] cross-warp sum, reuses stage 0 after the loop
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int cob = lane >> 3, cib = lane & 7;
@@ -506,7 +507,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
             for (int t = 0; t < KK; t++) acc[c][i][t] = 0.f;
 
     // the zero columns on both sides of every row are written once; staging only touches columns 4 .. 4 + WIN
-    for (int e = tid; e < S_T * 16 * PLANE; e += CONV_THREADS) xs[e] = 0.f;
+    for (int e = tid; e < 2 * STAGE; e += CONV_THREADS) smem[e] = 0.f;
     __syncthreads();
 
     const long long in_plane = (long long)g.Hin * g.Win, out_plane = (long long)g.Hout * g.Wout;
@@ -515,29 +516,36 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
     const long long per = (items + groups - 1) / groups;
     const long long it_begin = (long long)group * per, it_end = min(items, it_begin + per);
 
-    for (long long it = it_begin; it < it_end; it++) {
+    // warp-per-plane staging: a warp takes (stream, channel) planes, its lanes the 16-byte pieces of the plane
+    auto stage_item = [&](long long it, float *xs, float *dys) {
         const int s0 = (int)(it / tiles_h) * S_T;
         const int th0 = (int)(it % tiles_h) * TH;
         const int h_in0 = th0 * S - g.padU;
         if (vec) {
             if constexpr (sizeof(T) == 4) {
-                for (int e = tid; e < S_T * 16 * PH * W4; e += CONV_THREADS) {
-                    const int c4 = e % W4, rr = e / W4;
-                    const int r = rr % PH, ci = (rr / PH) & 15, sl = rr / (PH * 16);
-                    const int hi = h_in0 + r;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (s0 + sl < g.n && ci0 + ci < g.Cin && hi >= 0 && hi < g.Hin)
-                        v = __ldg(reinterpret_cast<const float4 *>(x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)hi * WIN) + c4);
-                    *reinterpret_cast<float4 *>(xs + (sl * 16 + ci) * PLANE + r * RW + 4 + 4 * c4) = v;
+                for (int pl = warp; pl < S_T * 16; pl += CONV_THREADS / 32) {
+                    const int ci = pl & 15, sl = pl >> 4;
+                    const bool pok = s0 + sl < g.n && ci0 + ci < g.Cin;
+                    const float *src = x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)h_in0 * WIN;
+                    const unsigned dst = (unsigned)__cvta_generic_to_shared(xs + pl * PLANE + 4);
+                    for (int e = lane; e < PH * W4; e += 32) {
+                        const int r = e / W4, c4 = e % W4;
+                        const bool ok = pok && h_in0 + r >= 0 && h_in0 + r < g.Hin;
+                        const float *sp = ok ? src + r * WIN + 4 * c4 : x;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (r * RW + 4 * c4) * 4), "l"(sp), "r"(ok ? 16 : 0) : "memory");
+                    }
                 }
                 const int TP4 = TP / 4;
-                for (int e = tid; e < 16 * S_T * TP4; e += CONV_THREADS) {
-                    const int p4 = e % TP4, sl = (e / TP4) % S_T, co = e / (TP4 * S_T);
-                    const int ho = th0 + (4 * p4) / TW;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (s0 + sl < g.n && co0 + co < g.Cout && ho < g.Hout)
-                        v = __ldg(reinterpret_cast<const float4 *>(dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)th0 * TW) + p4);
-                    *reinterpret_cast<float4 *>(dys + co * DYP + sl * TP + 4 * p4) = v;
+                for (int pl = warp; pl < 16 * S_T; pl += CONV_THREADS / 32) {
+                    const int sl = pl % S_T, co = pl / S_T;
+                    const bool pok = s0 + sl < g.n && co0 + co < g.Cout;
+                    const float *src = dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)th0 * TW;
+                    const unsigned dst = (unsigned)__cvta_generic_to_shared(dys + co * DYP + sl * TP);
+                    for (int e = lane; e < TP4; e += 32) {
+                        const bool ok = pok && th0 + (4 * e) / TW < g.Hout;
+                        const float *sp = ok ? src + 4 * e : dy;
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 16 * e), "l"(sp), "r"(ok ? 16 : 0) : "memory");
+                    }
                 }
             }
         } else {
@@ -557,7 +565,16 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
                 for (int c = lane; c < TW; c += 32) dst[c] = ok ? ld(src + c) : 0.f;
             }
         }
-        __syncthreads();
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    if (it_begin < it_end) stage_item(it_begin, smem, smem + S_T * 16 * PLANE);
+    int cur = 0;
+    for (long long it = it_begin; it < it_end; it++, cur ^= 1) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();        // this item has landed for every thread, and every thread is done with the other stage
+        const float *xs = smem + cur * STAGE, *dys = xs + S_T * 16 * PLANE;
+        if (it + 1 < it_end) stage_item(it + 1, smem + (cur ^ 1) * STAGE, smem + (cur ^ 1) * STAGE + S_T * 16 * PLANE);
         for (int row = warp; row < S_T * TH; row += CONV_THREADS / 32) {
             const int sl = row / TH, ph = row % TH;
             const float *xb = xs + (sl * 16 + cib) * PLANE + (ph * S) * RW;        // ci = cib (i = 0), + 8 planes for i = 1
@@ -584,19 +601,19 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
                             v[5] = b.x; v[6] = b.y; v[7] = b.z; v[8] = b.w; v[9] = 0.f;
                         }
 #pragma unroll
-                        for (int c = 0; c < 4; c++) {
-                            const float dj[4] = {d[c].x, d[c].y, d[c].z, d[c].w};
+                        for (int j = 0; j < 4; j++)
 #pragma unroll
-                            for (int j = 0; j < 4; j++)
+                            for (int kw = 0; kw < K; kw++)
 #pragma unroll
-                                for (int kw = 0; kw < K; kw++)
-                                    acc[c][i][kh * K + kw] = fmaf(dj[j], v[S * j + kw + VOFF], acc[c][i][kh * K + kw]);
-                        }
+                                for (int c = 0; c < 4; c++) {
+                                    const float dj = j == 0 ? d[c].x : (j == 1 ? d[c].y : (j == 2 ? d[c].z : d[c].w));
+                                    acc[c][i][kh * K + kw] = fmaf(dj, v[S * j + kw + VOFF], acc[c][i][kh * K + kw]);
+                                }
                     }
             }
         }
-        __syncthreads();
     }
+    __syncthreads();
     // cross-warp sum in warp order (fixed order: same result on every run)
     for (int w = 0; w < CONV_THREADS / 32; w++) {
         if (warp == w) {
@@ -686,7 +703,10 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
         int TH = target / TW; if (TH > g.Hout) TH = g.Hout; if (TH < 1) TH = 1;
         int S_T = target / (TH * TW); if (S_T > g.n) S_T = g.n; if (S_T < 1) S_T = 1;
         const int PH = (TH - 1) * S + K, RW = g.Win + 8, PLANE = 4 * ((PH * RW / 4) | 1);
-        const size_t smem = ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4) + 16 * 16 * KK) * sizeof(float);
+        // two stages must leave room for two CTAs per SM
+        while (S_T > 1 && 2 * ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4)) * sizeof(float) > 110 * 1024) S_T /= 2;
+        const size_t stage = (size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4);
+        const size_t smem = std::max<size_t>(2 * stage, (size_t)16 * 16 * KK) * sizeof(float);
         const int tiles_h = ceil_div(g.Hout, TH);
         const long long items = (long long)ceil_div(g.n, S_T) * tiles_h;
         int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
