@@ -189,24 +189,41 @@ class ResNet8Streams(object):
         return line
 
     def roofline(self, table, n, pk):
-        """Dominant kernel of the profiled step against the bound that limits it."""
+        """Dominant kernel family of the profiled step against the bound that limits it.  The template variants
+        of one kernel (plane sizes, tile widths) count as one family."""
         if not table:
             return None
-        name, count, ms = table[0]
+        fam = {}
+        for name, count, ms in table:
+            key = name.strip("()").split("<")[0]
+            c, t = fam.get(key, (0, 0.0))
+            fam[key] = (c + count, t + ms)
         total_ms = sum(r[2] for r in table)
-        # algorithmic work of the convolution kernels per step (all layers of that direction)
+        name, (count, ms) = max(fam.items(), key=lambda kv: kv[1][1])
+        # (Cin, H, Cout, k, stride) of the nine convolutions
         spec = [(3, 32, 16, 3, 1), (16, 32, 16, 3, 1), (16, 32, 16, 3, 1), (16, 32, 32, 3, 2), (32, 16, 32, 3, 1), (16, 32, 32, 1, 2), (32, 16, 64, 3, 2), (64, 8, 64, 3, 1), (32, 16, 64, 1, 2)]
         conv_flops = sum(2.0 * co * ci * k * k * (h // s) ** 2 for ci, h, co, k, s in spec) * n
-        ig_flops = conv_flops - 2.0 * 16 * 3 * 9 * 32 * 32 * n
-        r = {"kernel": name, "launches_per_step": count, "ms_per_step": ms, "share_of_kernel_time": ms / total_ms if total_ms else None, "traffic": None,
-             "peak_source": pk["source"]}
-        if "conv_fw" in name or "conv_wg" in name or "conv_ig" in name:
-            fl = ig_flops if "conv_ig" in name else conv_flops
+        ig_flops = conv_flops - 2.0 * 16 * 3 * 9 * 32 * 32 * n          # the stem has no input gradient
+        act_bytes = sum(4.0 * (ci * h * h + co * (h // s) ** 2) for ci, h, co, k, s in spec) * n
+        r = {"kernel": name, "launches_per_step": count, "ms_per_step": ms, "share_of_kernel_time": ms / total_ms if total_ms else None,
+             "traffic": None, "peak_source": pk["source"]}
+        if name in ("conv_tc_kernel", "conv_fw_kernel", "conv_ig_kernel", "conv_wg3x3_partial_kernel", "conv_wg_partial_kernel"):
+            if name == "conv_tc_kernel":
+                fl, what = conv_flops + ig_flops, "forward of 9 convolutions + input gradient of 8 (useful FLOP: the zeros of a dilated dY are not counted)"
+                # DRAM bytes of one ncu capture at 512 streams (forward + input-gradient launches), scaled by the stream count
+                r["traffic"] = None
+            elif "wg" in name:
+                fl, what = conv_flops, "weight gradient of 9 convolutions"
+            else:
+                fl, what = (ig_flops if "ig" in name else conv_flops), "convolutions on the FFMA path"
             ach = fl / (ms * 1e-3) / 1e12
-            # fp32 on the tensor cores is 3xTF32: one third of the TF32 rate, TF32 = half the bf16 rate
-            peak = pk["bf16_tflops_sustained"] / 6.0
-            r.update({"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "algorithmic_flops": fl,
-                      "peak_note": "3xTF32-effective fp32 peak = measured sustained bf16 / 6"})
+            if name == "conv_tc_kernel":
+                # fp32 on the tensor cores is 3xTF32: one third of the TF32 rate, TF32 = half the bf16 rate
+                peak, note = pk["bf16_tflops_sustained"] / 6.0, "3xTF32-effective fp32 peak = measured sustained bf16 / 6"
+            else:
+                peak, note = 72.8, "FFMA peak measured on this part: 125 MAC/clk/SM x 148 SMs x 1965 MHz"
+            r.update({"bound": "tensor" if name == "conv_tc_kernel" else "ffma", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                      "algorithmic_flops": fl, "algorithmic_bytes": 2 * act_bytes if name == "conv_tc_kernel" else act_bytes, "work": what, "peak_note": note})
         else:
             r.update({"bound": "hbm", "achieved": None, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": None})
         return r

@@ -59,23 +59,33 @@ static constexpr int NA = GROUPS * RING;    // A buffers in tensor memory
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
 {
     // each attempt may sleep in hardware for up to 20 us; 50k attempts bound the wait to about a second
+    // a failed attempt is followed by a short sleep so that the waiting warps (producer, issuers, epilogue) leave
+    // the issue slots to the converter warps; ids 3..5 sit on the critical path and sleep least
+    const uint32_t nap = (id == 3 || id == 4 || id == 5) ? 32u : 256u;
     for (uint32_t i = 0; i < 50000u; i++) {
         if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
         if (*abort_flag) return false;
+        __nanosleep(nap);
     }
     *abort_flag = 1;
     atomicCAS(status, 0, id);
     return false;
 }
 
-// Whole-warp variant: lane 0 polls, every lane gets the same answer (the callers then run
-// warp-collective tcgen05 instructions, which need the warp converged).
+// Whole-warp variant for callers that go on to warp-collective tcgen05 instructions: every lane polls the same
+// barrier in the same instruction, so the warp stays converged and all lanes get the same answer.
 __device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, int lane)
 {
-    int ok = 1;
-    if (lane == 0) ok = wait_or_abort(bar, parity, abort_flag, status, id) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    return ok != 0;
+    const uint32_t nap = (id == 3 || id == 4 || id == 5) ? 32u : 256u;
+    for (uint32_t i = 0; i < 50000u; i++) {
+        const bool done = mbar_try_wait_hint(bar, parity, 20000u);
+        if (__all_sync(0xffffffffu, done)) return true;
+        if (__any_sync(0xffffffffu, *abort_flag != 0)) return false;
+        __nanosleep(nap);
+    }
+    if (lane == 0) { *abort_flag = 1; atomicCAS(status, 0, id); }
+    __syncwarp();
+    return false;
 }
 
 // PLANE_B = bytes between two channels of the shared-memory patch when known at compile time (the 16 loads
@@ -201,31 +211,43 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             for (int g = 0; g < p.groups && ok; g++, pc++) {
                 const int slot = pc % PS;
                 if (!warp_wait_or_abort(&patch_full[slot], (pc / PS) & 1, abort_flag, p.status, 4, lane)) { ok = false; break; }
-                // software pipeline: the raw values of the next tap are fetched while the tensor-memory
-                // stores of the current one drain
-                uint32_t tap_b = base_b + slot * slot_b + first_tap_b;
+                // Software pipeline over the taps n = j, j+4, ... of this group: while the tensor-memory stores of
+                // tap n drain, tap n+1 is split in registers and the raw values of tap n+2 are fetched from shared
+                // memory; only then does the warp wait for the stores and hand buffer n to its issuer.
+                uint32_t tap_b = base_b + slot * slot_b + first_tap_b;      // address of the next tap to fetch
                 int kw = first_kw;
+                auto next_tap = [&]() {          // advance (kh, kw) by GROUPS taps without dividing
+                    kw += GROUPS; tap_b += GROUPS * 4u;
+                    while (kw >= p.Wk) { kw -= p.Wk; tap_b += row_b - (uint32_t)p.Wk * 4u; }
+                };
                 float raw[16];
+                uint32_t hi[16], lo[16];
                 if (j < p.taps) {
 #pragma unroll
                     for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
+#pragma unroll
+                    for (int c = 0; c < 16; c++) split_tf32_fast(raw[c], hi[c], lo[c]);
+                    next_tap();
+                    if (j + GROUPS < p.taps) {
+#pragma unroll
+                        for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
+                    }
                 }
                 for (int tap = j; tap < p.taps; tap += GROUPS, k++) {
                     const int abuf = j * RING + (k % RING);
-                    uint32_t hi[16], lo[16];
-#pragma unroll
-                    for (int c = 0; c < 16; c++) split_tf32_fast(raw[c], hi[c], lo[c]);
                     if (!warp_wait_or_abort(&a_empty[abuf], ((k / RING) & 1) ^ 1, abort_flag, p.status, 5, lane)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = a_col0 + abuf * 32 + lane_addr;
                     tmem_st16(a_addr, hi);
                     tmem_st16(a_addr + 16, lo);
-                    // advance (kh, kw) by GROUPS taps without dividing
-                    kw += GROUPS; tap_b += GROUPS * 4u;
-                    while (kw >= p.Wk) { kw -= p.Wk; tap_b += row_b - (uint32_t)p.Wk * 4u; }
                     if (tap + GROUPS < p.taps) {
 #pragma unroll
-                        for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
+                        for (int c = 0; c < 16; c++) split_tf32_fast(raw[c], hi[c], lo[c]);
+                        next_tap();
+                        if (tap + 2 * GROUPS < p.taps) {
+#pragma unroll
+                            for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
+                        }
                     }
                     tmem_wait_st();
                     tc_fence_before();
