@@ -44,9 +44,11 @@ struct ConvTcParams {
 // therefore issue MMAs side by side.  The accumulators start from zero (the epilogue clears them), so the
 // order in which the issuers' MMAs land does not matter.
 //
-// Work is dealt statically: converter group j (4 warps, one per TMEM lane quarter) converts the filter taps
-// j, j+4, j+8, ... of every channel group into its own ring of RING tensor-memory buffers, and issuer j
-// multiplies exactly those chunks.  Every mbarrier thus has one producer group and one consumer that both
+// Work is dealt statically: the chunks (one filter tap of one 16-channel group) are numbered in the order
+// tile, channel group, tap over the whole run of the CTA, and chunk c belongs to converter group c mod 4
+// (4 warps, one per TMEM lane quarter), which converts it into its own ring of RING tensor-memory buffers;
+// issuer j multiplies exactly the chunks of group j.  Numbering across tiles keeps the four groups level
+// when the chunks of one tile (e.g. 9) do not divide by four.  Every mbarrier thus has one producer group and one consumer that both
 // walk the same chunk sequence, so a waiter can never be more than one phase away from the barrier (the
 // parity wait would alias otherwise).
 static constexpr int GROUPS = 4;            // converter groups = MMA issuers
@@ -110,6 +112,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     uint64_t *d_full = bars + 2 * PS + 2 * NA, *d_empty = d_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    uint32_t *tap_off = tmem_slot + 2;          // byte offset of every filter tap inside a patch plane (up to 25)
 
     const uint32_t tmem_cols = 512u;
 
@@ -118,6 +121,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         for (int i = 0; i < NA; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_empty[i], 1); }
         for (int i = 0; i < 2; i++) { mbar_init(&d_full[i], GROUPS); mbar_init(&d_empty[i], 4); }
         *abort_flag = 0;
+        for (int t = 0; t < p.taps; t++) tap_off[t] = (uint32_t)((t / p.Wk) * p.PWB + (t % p.Wk)) * 4u;
         fence_barrier_init();
         tma_prefetch_desc(&tmap);
     }
@@ -162,14 +166,15 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             const uint32_t lbo = N2 * 16, sbo = 128;
             const uint32_t tap_bytes = 32u * NT * 4u;
             uint32_t k = 0, tcnt = 0;           // k = chunks of this group so far
+            uint32_t cbase = 0;                 // chunks dealt so far (all groups), mod GROUPS
             bool ok = true;
             for (int t = blockIdx.x; t < p.n_tiles && ok && !*abort_flag; t += gridDim.x, tcnt++) {
                 const int dbuf = tcnt & 1;
                 if (!wait_or_abort(&d_empty[dbuf], (tcnt >> 1) & 1, abort_flag, p.status, 2)) break;
                 tc_fence_after();
                 const uint32_t d_addr = d_col0 + dbuf * N2;
-                for (int g = 0; g < p.groups && ok; g++) {
-                    for (int tap = me; tap < p.taps; tap += GROUPS, k++) {
+                for (int g = 0; g < p.groups && ok; g++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
+                    for (int tap = (me - cbase) & (GROUPS - 1); tap < p.taps; tap += GROUPS, k++) {
                         const int abuf = me * RING + (k % RING);
                         if (!wait_or_abort(&a_full[abuf], (k / RING) & 1, abort_flag, p.status, 3)) { ok = false; break; }
                         tc_fence_after();
@@ -202,38 +207,34 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         const uint32_t plane_b = PLANE_B ? (uint32_t)PLANE_B : (uint32_t)(p.PH * p.PWB) * 4u, row_b = (uint32_t)p.PWB * 4u;
         const uint32_t slot_b = (uint32_t)patch_stride * 4u;
         const uint32_t base_b = smem_u32(patch) + (uint32_t)(((sl * 16) * p.PH + ph * p.sh) * p.PWB + p.xoff + pw * p.sw) * 4u;
-        const uint32_t first_tap_b = (uint32_t)((j / p.Wk) * p.PWB + (j % p.Wk)) * 4u;
-        const int first_kw = j % p.Wk;
+        uint32_t cbase = 0;                     // chunks dealt so far (all groups), mod GROUPS
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         uint32_t pc = 0, k = 0;                 // k = chunks of this group so far (the paired issuer counts the same)
         bool ok = true;
         for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
-            for (int g = 0; g < p.groups && ok; g++, pc++) {
+            for (int g = 0; g < p.groups && ok; g++, pc++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
                 const int slot = pc % PS;
                 if (!warp_wait_or_abort(&patch_full[slot], (pc / PS) & 1, abort_flag, p.status, 4, lane)) { ok = false; break; }
-                // Software pipeline over the taps n = j, j+4, ... of this group: while the tensor-memory stores of
-                // tap n drain, tap n+1 is split in registers and the raw values of tap n+2 are fetched from shared
-                // memory; only then does the warp wait for the stores and hand buffer n to its issuer.
-                uint32_t tap_b = base_b + slot * slot_b + first_tap_b;      // address of the next tap to fetch
-                int kw = first_kw;
-                auto next_tap = [&]() {          // advance (kh, kw) by GROUPS taps without dividing
-                    kw += GROUPS; tap_b += GROUPS * 4u;
-                    while (kw >= p.Wk) { kw -= p.Wk; tap_b += row_b - (uint32_t)p.Wk * 4u; }
-                };
+                const int first = (j - cbase) & (GROUPS - 1);
+                // Software pipeline over the taps n = first, first+4, ... of this group: while the tensor-memory
+                // stores of tap n drain, tap n+1 is split in registers and the raw values of tap n+2 are fetched
+                // from shared memory; only then does the warp wait for the stores and hand buffer n to its issuer.
+                const uint32_t slot_base = base_b + slot * slot_b;
                 float raw[16];
                 uint32_t hi[16], lo[16];
-                if (j < p.taps) {
+                if (first < p.taps) {
+                    uint32_t tap_b = slot_base + tap_off[first];
 #pragma unroll
                     for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
 #pragma unroll
                     for (int c = 0; c < 16; c++) split_tf32_fast(raw[c], hi[c], lo[c]);
-                    next_tap();
-                    if (j + GROUPS < p.taps) {
+                    if (first + GROUPS < p.taps) {
+                        tap_b = slot_base + tap_off[first + GROUPS];
 #pragma unroll
                         for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
                     }
                 }
-                for (int tap = j; tap < p.taps; tap += GROUPS, k++) {
+                for (int tap = first; tap < p.taps; tap += GROUPS, k++) {
                     const int abuf = j * RING + (k % RING);
                     if (!warp_wait_or_abort(&a_empty[abuf], ((k / RING) & 1) ^ 1, abort_flag, p.status, 5, lane)) { ok = false; break; }
                     tc_fence_after();
@@ -243,8 +244,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                     if (tap + GROUPS < p.taps) {
 #pragma unroll
                         for (int c = 0; c < 16; c++) split_tf32_fast(raw[c], hi[c], lo[c]);
-                        next_tap();
                         if (tap + 2 * GROUPS < p.taps) {
+                            const uint32_t tap_b = slot_base + tap_off[tap + 2 * GROUPS];
 #pragma unroll
                             for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
                         }
@@ -404,7 +405,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     size_t smem = 0;
     for (;; NT /= 2) {
         const size_t b_floats = (((size_t)p.groups * p.taps * 32 * NT) + 31) & ~(size_t)31;
-        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * NA + 4) * 8 + 16 + 128;
+        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * NA + 4) * 8 + 16 + 112 + 128;
         if (smem <= 220 * 1024 || NT == 16) break;
     }
     if (smem > 220 * 1024) return false;

@@ -207,4 +207,12 @@ __device__ __forceinline__ void split_tf32_fast(float x, uint32_t &hi, uint32_t 
     lo = __float_as_uint(x - __uint_as_float(hi));
 }
 
+// Split that leaves the rounding of the big part to the tensor core: kind::tf32 reads the top 19 bits of an
+// fp32 operand, i.e. it uses trunc(x) when handed x itself, so only lo = x - trunc(x) has to be computed (exact
+// in fp32, same sign as x, below 2^-10 |x|).
+__device__ __forceinline__ uint32_t split_tf32_lo_of_trunc(float x)
+{
+    return __float_as_uint(x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u));
+}
+
 } } // namespace tl::tc
