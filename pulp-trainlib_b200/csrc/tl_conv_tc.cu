@@ -33,6 +33,7 @@ struct ConvTcParams {
     int PH, PWB, xoff;          // patch rows, patch row pitch in floats, first used column
     int x_base, y_base;         // input coordinate of patch column 0 / row 0 for the tile at the origin
     int NT;                     // output channels per CTA (16, 32 or 64); blockIdx.y picks the slice
+    int ring;                   // A buffers per converter group in use (2 or 3: 4*NT + 128*ring <= 512 TMEM columns)
     const float *bprep;         // [Cout tiles][groups][taps][4][2*NT][4]
     const float *bias;
     float *y;
@@ -52,7 +53,7 @@ struct ConvTcParams {
 // walk the same chunk sequence, so a waiter can never be more than one phase away from the barrier (the
 // parity wait would alias otherwise).
 static constexpr int GROUPS = 4;            // converter groups = MMA issuers
-static constexpr int RING = 2;              // A buffers per group (32 TMEM columns each: 16 hi + 16 lo)
+static constexpr int RING = 2;              // most A buffers per group (32 TMEM columns each: 16 hi + 16 lo); a third one bought nothing
 static constexpr int FIRST_ISSUER = 2, FIRST_CONV = FIRST_ISSUER + GROUPS, FIRST_EPI = FIRST_CONV + 4 * GROUPS;
 static constexpr int TC_THREADS = (FIRST_EPI + 4) * 32;
 static constexpr int PS = 3;                // raw patch ring
@@ -165,7 +166,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             const uint32_t bs_addr = smem_u32(Bs);
             const uint32_t lbo = N2 * 16, sbo = 128;
             const uint32_t tap_bytes = 32u * NT * 4u;
-            uint32_t k = 0, tcnt = 0;           // k = chunks of this group so far
+            uint32_t tcnt = 0;
+            int rb = 0; uint32_t rph = 0;       // ring position and phase of this group's next chunk
             uint32_t cbase = 0;                 // chunks dealt so far (all groups), mod GROUPS
             bool ok = true;
             for (int t = blockIdx.x; t < p.n_tiles && ok && !*abort_flag; t += gridDim.x, tcnt++) {
@@ -174,9 +176,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                 tc_fence_after();
                 const uint32_t d_addr = d_col0 + dbuf * N2;
                 for (int g = 0; g < p.groups && ok; g++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
-                    for (int tap = (me - cbase) & (GROUPS - 1); tap < p.taps; tap += GROUPS, k++) {
-                        const int abuf = me * RING + (k % RING);
-                        if (!wait_or_abort(&a_full[abuf], (k / RING) & 1, abort_flag, p.status, 3)) { ok = false; break; }
+                    for (int tap = (me - cbase) & (GROUPS - 1); tap < p.taps; tap += GROUPS) {
+                        const int abuf = me * p.ring + rb;
+                        if (!wait_or_abort(&a_full[abuf], rph, abort_flag, p.status, 3)) { ok = false; break; }
+                        if (++rb == p.ring) { rb = 0; rph ^= 1u; }
                         tc_fence_after();
                         const uint32_t a_addr = a_col0 + abuf * 32;
                         const uint32_t b_tap = bs_addr + (uint32_t)(g * p.taps + tap) * tap_bytes;
@@ -204,12 +207,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         const int tp = p.TH * p.TW;
         const int sl = m / tp, ph = (m % tp) / p.TW, pw = m % p.TW;
         // all addressing below is 32-bit shared-window arithmetic, set up once per thread
-        const uint32_t plane_b = PLANE_B ? (uint32_t)PLANE_B : (uint32_t)(p.PH * p.PWB) * 4u, row_b = (uint32_t)p.PWB * 4u;
+        const uint32_t plane_b = PLANE_B ? (uint32_t)PLANE_B : (uint32_t)(p.PH * p.PWB) * 4u;
         const uint32_t slot_b = (uint32_t)patch_stride * 4u;
         const uint32_t base_b = smem_u32(patch) + (uint32_t)(((sl * 16) * p.PH + ph * p.sh) * p.PWB + p.xoff + pw * p.sw) * 4u;
         uint32_t cbase = 0;                     // chunks dealt so far (all groups), mod GROUPS
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        uint32_t pc = 0, k = 0;                 // k = chunks of this group so far (the paired issuer counts the same)
+        uint32_t pc = 0;
+        int rb = 0; uint32_t rph = 0;           // ring position and phase of this group's next chunk (the paired issuer counts the same)
         bool ok = true;
         for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
             for (int g = 0; g < p.groups && ok; g++, pc++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
@@ -234,9 +238,10 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                         for (int c = 0; c < 16; c++) raw[c] = ld_shared_f32(tap_b + c * plane_b);
                     }
                 }
-                for (int tap = first; tap < p.taps; tap += GROUPS, k++) {
-                    const int abuf = j * RING + (k % RING);
-                    if (!warp_wait_or_abort(&a_empty[abuf], ((k / RING) & 1) ^ 1, abort_flag, p.status, 5, lane)) { ok = false; break; }
+                for (int tap = first; tap < p.taps; tap += GROUPS) {
+                    const int abuf = j * p.ring + rb;
+                    if (!warp_wait_or_abort(&a_empty[abuf], rph ^ 1u, abort_flag, p.status, 5, lane)) { ok = false; break; }
+                    if (++rb == p.ring) { rb = 0; rph ^= 1u; }
                     tc_fence_after();
                     const uint32_t a_addr = a_col0 + abuf * 32 + lane_addr;
                     tmem_st16(a_addr, hi);
@@ -411,6 +416,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     if (smem > 220 * 1024) return false;
     if (dry_run) return true;   // geometry qualifies; nothing launched
     p.NT = NT;
+    p.ring = (4 * NT + 32 * GROUPS * RING <= 512) ? RING : 2;
     const int co_tiles = ceil_div(C_dst, NT);
 
     CUtensorMap tmap;

@@ -66,15 +66,26 @@ def test_resnet8_matches_reference_c(pkg, gpulib, n, host_batch):
     assert_close(got["params"], ref["params"], 1e-6, "updated weights")
 
 
-def test_resnet8_streams_are_independent(pkg, gpulib):
+@pytest.mark.parametrize("path,tol_act,tol_grad", [(1, 1e-6, 2e-6), (2, FP32_TOL, 1e-3)], ids=["ffma", "tensor_core"])
+def test_resnet8_streams_are_independent(pkg, gpulib, path, tol_act, tol_grad):
     """size-independent property used at the full 4096-stream size: a stream's logits and loss do
-    not depend on which other streams share the launch, and gradients add over disjoint shards."""
+    not depend on which other streams share the launch, and gradients add over disjoint shards.
+
+    The kernel choice depends on the launch size, so the path is pinned.  The FFMA kernels sum in a fixed
+    order: shards and whole agree to rounding of the final sum.  On the tensor-core path four threads issue
+    MMAs into one accumulator and the order in which they land varies from run to run; a pre-activation within
+    rounding of zero can then switch its ReLU gate, which changes single gradient elements by their full value
+    (seen: 1 element in 4 M, 1e-4 of the largest gradient).  The looser bound still catches any mixing of
+    streams, which would be of order one."""
     import bench_nets
     net = bench_nets.bind_net(bench_nets.NET_B200)
-    whole = gpu_step(pkg, gpulib, net, 64, first=0)
-    a = gpu_step(pkg, gpulib, net, 32, first=0)
-    b = gpu_step(pkg, gpulib, net, 32, first=32)
-    # (the kernel choice depends on the launch size, so the comparison allows rounding differences)
-    assert_close(whole["logits"][:32], a["logits"], FP32_TOL, "logits of shard a"); assert_close(whole["logits"][32:], b["logits"], FP32_TOL, "logits of shard b")
-    assert_close(whole["loss"][:32], a["loss"], FP32_TOL, "loss of shard a")
-    assert_close(a["grads"] + b["grads"], whole["grads"], 2e-5, "gradient additivity over shards")
+    gpulib.trainlib_set_gemm_path(path)
+    try:
+        whole = gpu_step(pkg, gpulib, net, 64, first=0)
+        a = gpu_step(pkg, gpulib, net, 32, first=0)
+        b = gpu_step(pkg, gpulib, net, 32, first=32)
+    finally:
+        gpulib.trainlib_set_gemm_path(0)
+    assert_close(whole["logits"][:32], a["logits"], tol_act, "logits of shard a"); assert_close(whole["logits"][32:], b["logits"], tol_act, "logits of shard b")
+    assert_close(whole["loss"][:32], a["loss"], tol_act, "loss of shard a")
+    assert_close(a["grads"] + b["grads"], whole["grads"], tol_grad, "gradient additivity over shards")
