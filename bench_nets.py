@@ -210,8 +210,11 @@ class ResNet8Streams(object):
         if name in ("conv_tc_kernel", "conv_fw_kernel", "conv_ig_kernel", "conv_wg3x3_partial_kernel", "conv_wg_partial_kernel"):
             if name == "conv_tc_kernel":
                 fl, what = conv_flops + ig_flops, "forward of 9 convolutions + input gradient of 8 (useful FLOP: the zeros of a dilated dY are not counted)"
-                # DRAM bytes of one ncu capture at 512 streams (forward + input-gradient launches), scaled by the stream count
-                r["traffic"] = None
+                # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.63 MB read + 0.99 MB
+                # written inside the launch; the 33.5 MB output is still dirty in L2 when it ends), scaled by the stream
+                # count: traffic grows in proportion because every stream brings its own planes
+                r["traffic"] = (33.63e6 + 0.99e6) * n / 512.0
+                r["traffic_note"] = "per launch of the 16->16 32x32 forward convolution, ncu at 512 streams scaled by streams; algorithmic bytes of that launch: %.0f MB in + %.0f MB out" % (n * 65536e-6, n * 65536e-6)
             elif "wg" in name:
                 fl, what = conv_flops, "weight gradient of 9 convolutions"
             else:
