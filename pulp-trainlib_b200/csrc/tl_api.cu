@@ -345,6 +345,7 @@ template <class F> void linear_impl(void *args, int step)
         T *db = ub ? sc.out(a->bias->diff, (size_t)out) : nullptr;
         if (!sc.ok()) return;
         if (n == 1) linear_wg_outer<T>(dy, x, dw, out, in);
+        else if (linear_wg_streams<T>(sc, dy, x, dw, n, out, in)) { /* contraction over the streams, split into blocks */ }
         else {
             GemmDesc<T> d; d.A = dy; d.a_rs = 1; d.a_cs = out; d.B = x; d.b_rs = in; d.C = dw; d.c_rs = in; d.N = out; d.K = n; d.M = in;
             gemm<T>(d);

@@ -202,25 +202,69 @@ template <> bool try_tc_fw<float>(Scope &sc, const ConvGeom &g, const float *x, 
 }
 // dY of a strided convolution spread onto the input grid: dil[s][co][h][w] = dY[s][co][h/sh][w/sw] where both
 // divisions are exact and in range, 0 elsewhere.  One thread writes four consecutive columns (Win % 4 == 0).
-__global__ void __launch_bounds__(256) conv_dilate_dy_kernel(const float *__restrict__ dy, float *__restrict__ dil, long long planes,
+__global__ void __launch_bounds__(256) conv_dilate_dy_kernel(const float *__restrict__ dy, float *__restrict__ dil, unsigned total4,
                                                             int Hout, int Wout, int Hin, int Win, int sh, int sw)
 {
-    const int W4 = Win / 4;
-    const long long total = planes * Hin * W4;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
-        const int w4 = (int)(e % W4), h = (int)((e / W4) % Hin);
-        const long long pl = e / ((long long)W4 * Hin);
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (h % sh == 0 && h / sh < Hout) {
-            const float *row = dy + (pl * Hout + h / sh) * Wout;
+    // 32-bit index arithmetic throughout (the host checks the element count)
+    const unsigned W4 = (unsigned)Win / 4u;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < total4; e += gridDim.x * blockDim.x) {
+        const unsigned w4 = e % W4, row = e / W4;       // row = plane * Hin + h
+        const unsigned h = row % (unsigned)Hin, pl = row / (unsigned)Hin;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        const unsigned ho = h / (unsigned)sh;
+        if (ho * (unsigned)sh == h && ho < (unsigned)Hout) {
+            const float *src = dy + ((size_t)pl * Hout + ho) * Wout;
+            if (sw == 2) {
+                const unsigned wo = 2u * w4;            // columns 4*w4 and 4*w4 + 2 carry samples wo and wo + 1
+                if (wo < (unsigned)Wout) v.x = __ldg(src + wo);
+                if (wo + 1 < (unsigned)Wout) v.z = __ldg(src + wo + 1);
+            } else {
+                float t[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const int w = 4 * w4 + j;
-                if (w % sw == 0 && w / sw < Wout) v[j] = __ldg(row + w / sw);
+                for (int j = 0; j < 4; j++) {
+                    const unsigned w = 4u * w4 + j, wo = w / (unsigned)sw;
+                    if (wo * (unsigned)sw == w && wo < (unsigned)Wout) t[j] = __ldg(src + wo);
+                }
+                v = make_float4(t[0], t[1], t[2], t[3]);
             }
         }
-        *reinterpret_cast<float4 *>(dil + (pl * Hin + h) * Win + 4 * w4) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4 *>(dil + (size_t)e * 4) = v;
     }
+}
+
+// Input gradient of a 1x1 convolution with stride s and no padding: dX[ci][h*s][w*s] = sum_co W[co][ci] dY[co][h][w],
+// zero at every other position.  One CTA per (stream, tile of dY pixels): the weights and the dY tile sit in shared
+// memory, a thread owns one pixel and walks the input channels; a warp then writes whole output rows (the sample
+// rows with zeros between the samples, and the s-1 all-zero rows below each).
+template <int PX>
+__global__ void __launch_bounds__(PX) conv1x1_strided_ig_kernel(ConvGeom g, const float *__restrict__ dy, const float *__restrict__ w, float *__restrict__ dx)
+{
+    extern __shared__ __align__(16) float sm1[];
+    float *ws = sm1;                                 // [Cout][Cin]
+    float *dys = sm1 + g.Cout * g.Cin;               // [Cout][PX]
+    const int opix = g.Hout * g.Wout, tiles = (opix + PX - 1) / PX;
+    const int s = blockIdx.x / tiles, p0 = (blockIdx.x % tiles) * PX;
+    for (int e = threadIdx.x; e < g.Cout * g.Cin; e += PX) ws[e] = w[e];
+    const float *dyp = dy + (size_t)s * g.Cout * opix;
+    for (int e = threadIdx.x; e < g.Cout * PX; e += PX) {
+        const int co = e / PX, p = e % PX;
+        dys[e] = (p0 + p < opix) ? dyp[(size_t)co * opix + p0 + p] : 0.f;
+    }
+    __syncthreads();
+    const int p = p0 + threadIdx.x;
+    const bool live = p < opix;
+    const int ho = live ? p / g.Wout : 0, wo = live ? p % g.Wout : 0;
+    float *dxs = dx + (size_t)s * g.Cin * g.Hin * g.Win;
+    for (int ci = 0; ci < g.Cin; ci++) {
+        float acc = 0.f;
+        for (int co = 0; co < g.Cout; co++) acc = fmaf(ws[co * g.Cin + ci], dys[co * PX + threadIdx.x], acc);
+        if (live) dxs[((size_t)ci * g.Hin + (size_t)ho * g.sh) * g.Win + (size_t)wo * g.sw] = acc;
+    }
+}
+// zero fill of dX before the scattered samples are written (16-byte stores)
+__global__ void __launch_bounds__(256) zero_f4_kernel(float4 *__restrict__ p, size_t n4)
+{
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n4; e += (size_t)gridDim.x * blockDim.x) p[e] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
 template <class T> static bool try_tc_ig(Scope &, const ConvGeom &, const T *, const T *, T *) { return false; }
@@ -231,6 +275,25 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
     if (g.sh == 1 && g.sw == 1)
         return conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
                            g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
+    if (g.Hk == 1 && g.Wk == 1 && g.padU == 0 && g.padL == 0 && gemm_path() != 1 && (((uintptr_t)dx) & 15) == 0 && (g.Hin * g.Win) % 4 == 0 &&
+        (long long)(g.Hout - 1) * g.sh < g.Hin && (long long)(g.Wout - 1) * g.sw < g.Win) {
+        // 1x1 strided: a small per-pixel matrix product scattered onto a zeroed dX; bandwidth-bound, no tensor cores
+        const int opix = g.Hout * g.Wout, PX = opix >= 256 ? 256 : 64;
+        const size_t smem = ((size_t)g.Cout * g.Cin + (size_t)g.Cout * PX) * sizeof(float);
+        if (smem <= 160 * 1024) {
+            const size_t n4 = (size_t)g.n * g.Cin * g.Hin * g.Win / 4;
+            TL_LAUNCH(zero_f4_kernel, (unsigned)std::min<size_t>((n4 + 255) / 256, (size_t)sm_count() * 32), 256, 0, reinterpret_cast<float4 *>(dx), n4);
+            const unsigned grid = (unsigned)g.n * (unsigned)((opix + PX - 1) / PX);
+            if (PX == 256) {
+                if (smem > 48 * 1024) cudaFuncSetAttribute(conv1x1_strided_ig_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                TL_LAUNCH(conv1x1_strided_ig_kernel<256>, grid, 256, smem, g, dy, w, dx);
+            } else {
+                if (smem > 48 * 1024) cudaFuncSetAttribute(conv1x1_strided_ig_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                TL_LAUNCH(conv1x1_strided_ig_kernel<64>, grid, 64, smem, g, dy, w, dx);
+            }
+            return true;
+        }
+    }
     // strided: spread dY onto the input grid (zeros between the samples), then the same stride-1 convolution.
     // The tensor cores do sh*sw times the useful work, which still beats the FFMA kernel by a wide margin.
     if (g.Win % 4 != 0 || (long long)(g.Hout - 1) * g.sh >= g.Hin || (long long)(g.Wout - 1) * g.sw >= g.Win) return false;
@@ -238,11 +301,12 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
                      g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true, true))
         return false;
     const long long planes = (long long)g.n * g.Cout;
+    const long long total = planes * g.Hin * (g.Win / 4);
+    if (total >= (1ll << 31)) return false;
     float *dil = sc.scratch<float>((size_t)planes * g.Hin * g.Win);
     if (!dil) return false;
-    const long long total = planes * g.Hin * (g.Win / 4);
-    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 16);
-    TL_LAUNCH(conv_dilate_dy_kernel, blocks, 256, 0, dy, dil, planes, g.Hout, g.Wout, g.Hin, g.Win, g.sh, g.sw);
+    const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 32);
+    TL_LAUNCH(conv_dilate_dy_kernel, blocks, 256, 0, dy, dil, (unsigned)total, g.Hout, g.Wout, g.Hin, g.Win, g.sh, g.sw);
     return conv_tc_run(sc, dil, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hin, g.Win, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
                        g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
 }

@@ -211,6 +211,43 @@ __global__ void __launch_bounds__(256) linear_wg_kernel(const T *__restrict__ dy
     }
 }
 
+// Streams mode: dW[o][i] = sum over streams of dy[s][o] * x[s][i].  The contraction runs over the streams, so the
+// streams are cut into blocks of 32: CTA b sums its block into partial b (thread = one dW element, x read
+// coalesced, dy broadcast), a second launch adds the partials in block order (fixed order, no atomics).
+template <class T>
+__global__ void __launch_bounds__(256) linear_wg_streams_partial_kernel(const T *__restrict__ dy, const T *__restrict__ x, float *__restrict__ part,
+                                                                        int n, int out, int in, int per)
+{
+    const int s0 = blockIdx.y * per, s1 = min(n, s0 + per);
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= out * in) return;
+    const int o = e / in, i = e % in;
+    float acc = 0.f;
+    for (int s = s0; s < s1; s++) acc = fmaf(ld(dy + (long long)s * out + o), ld(x + (long long)s * in + i), acc);
+    part[(long long)blockIdx.y * out * in + e] = acc;
+}
+template <class T>
+__global__ void linear_wg_streams_reduce_kernel(const float *__restrict__ part, T *__restrict__ dW, int count, int blocks)
+{
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= count) return;
+    float acc = 0.f;
+    for (int b = 0; b < blocks; b++) acc += part[(long long)b * count + e];
+    st(dW + e, acc);
+}
+template <class T> bool linear_wg_streams(Scope &sc, const T *dy, const T *x, T *dW, int n, int out, int in)
+{
+    // worth it when the layer is small against the stream count; large layers keep the GEMM tiles
+    if ((long long)out * in > 16384 || n < 64) return false;
+    const int per = 32, blocks = ceil_div(n, per), count = out * in;
+    float *part = sc.scratch<float>((size_t)blocks * count);
+    if (!part) return false;
+    dim3 grid(ceil_div(count, 256), blocks);
+    TL_LAUNCH((linear_wg_streams_partial_kernel<T>), grid, 256, 0, dy, x, part, n, out, in, per);
+    TL_LAUNCH((linear_wg_streams_reduce_kernel<T>), ceil_div(count, 256), 256, 0, part, dW, count, blocks);
+    return true;
+}
+
 template <class T> void linear_wg_outer(const T *dy, const T *x, T *dW, int out, int in)
 {
     long long work = ((long long)out * in) / (16 / sizeof(T)) + 1;
@@ -354,6 +391,7 @@ namespace tl {
     template void mm_contract<T>(const T *, const T *, T *, int, int, int, int, bool);                      \
     template void linear_fw_gemv<T>(const T *, const T *, const T *, T *, int, int);                        \
     template void linear_wg_outer<T>(const T *, const T *, T *, int, int);                                  \
+    template bool linear_wg_streams<T>(Scope &, const T *, const T *, T *, int, int, int);                  \
     template void linear_ig_gemv<T>(Scope &, const T *, const T *, T *, int, int);
 INST(float)
 INST(__half)

@@ -27,6 +27,7 @@ template <class T> void mm_contract(const T *A, const T *B, T *C, int N, int K, 
 // Batch-1 Linear kernels (HBM-bound): y = W x (+b), dW = dy (x) x, dx = W^T dy.
 template <class T> void linear_fw_gemv(const T *W, const T *x, const T *bias, T *y, int out, int in);
 template <class T> void linear_wg_outer(const T *dy, const T *x, T *dW, int out, int in);
+template <class T> bool linear_wg_streams(Scope &sc, const T *dy, const T *x, T *dW, int n, int out, int in);
 template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx, int out, int in);
 
 // ---------------------------------------------------------------- convolution
