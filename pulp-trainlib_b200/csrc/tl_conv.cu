@@ -538,23 +538,29 @@ conv_wg_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict_
 // so four output pixels cost 4 + 6 (stride 1) or 4 + 12 (stride 2) 16-byte shared loads for 288 FMAs.  The plane
 // stride is 4 x odd floats: the 8 ci pairs of a quarter warp then touch all 32 banks exactly once per 16-byte load.
 // At the end the warps add their accumulators into shared memory in warp order and the CTA writes one partial.
-template <class T, int S, int TW, int K>
+// TH (rows per item) and S_T (streams per item) are template parameters as well, so every shared-memory offset in
+// the inner loop is an immediate.
+template <int S, int TW, int K, int TH, int S_T> struct WgShape {
+    static constexpr int WIN = S * TW;             // input row width (host guarantees g.Win == WIN)
+    static constexpr int RW = WIN + 8;             // shared-memory row: input column w sits at 4 + w
+    static constexpr int W4 = WIN / 4;
+    static constexpr int KK = K * K, VOFF = (K == 1) ? 1 : 0;   // v[] starts one column left of the first input column
+    static constexpr int PH = (TH - 1) * S + K;
+    static constexpr int PLANE = 4 * ((PH * RW / 4) | 1);
+    static constexpr int TP = TH * TW, DYP = S_T * TP + 4, TP4 = TP / 4;
+    static constexpr int STAGE = S_T * 16 * PLANE + 16 * DYP;
+};
+template <class T, int S, int TW, int K, int TH, int S_T>
 __global__ void __launch_bounds__(CONV_THREADS, 2)
 conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
-                          int TH, int S_T, int tiles_h, int ci_tiles, int vec)
+                          int tiles_h, int ci_tiles, int vec, int nstage)
 {
     extern __shared__ __align__(16) float smem[];
-    constexpr int WIN = S * TW;             // input row width (host guarantees g.Win == WIN)
-    constexpr int RW = WIN + 8;             // shared-memory row: input column w sits at 4 + w
-    constexpr int W4 = WIN / 4;
-    constexpr int KK = K * K, VOFF = (K == 1) ? 1 : 0;   // v[] below starts one column left of the first input column
-    const int PH = (TH - 1) * S + K;
-    int P4 = PH * RW / 4; P4 |= 1;
-    const int PLANE = 4 * P4;
-    const int TP = TH * TW, DYP = S_T * TP + 4;
-    // two stages of {input patch [S_T][16 ci][PLANE], dY tile [16 co][DYP]}: the next item is fetched with
+    typedef WgShape<S, TW, K, TH, S_T> WS;
+    constexpr int WIN = WS::WIN, RW = WS::RW, W4 = WS::W4, KK = WS::KK, VOFF = WS::VOFF, PH = WS::PH, PLANE = WS::PLANE;
+    constexpr int TP = WS::TP, DYP = WS::DYP, STAGE = WS::STAGE;
+    // nstage stages of {input patch [S_T][16 ci][PLANE], dY tile [16 co][DYP]}: the next items are fetched with
     // 16-byte asynchronous copies while the current one is consumed
-    const int STAGE = S_T * 16 * PLANE + 16 * DYP;
     float *accs = smem;                             // [16 co][16 ci][KK] cross-warp sum, reuses stage 0 after the loop
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -571,7 +577,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
             for (int t = 0; t < KK; t++) acc[c][i][t] = 0.f;
 
     // the zero columns on both sides of every row are written once; staging only touches columns 4 .. 4 + WIN
-    for (int e = tid; e < 2 * STAGE; e += CONV_THREADS) smem[e] = 0.f;
+    for (int e = tid; e < nstage * STAGE; e += CONV_THREADS) smem[e] = 0.f;
     __syncthreads();
 
     const long long in_plane = (long long)g.Hin * g.Win, out_plane = (long long)g.Hout * g.Wout;
@@ -587,11 +593,13 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
         const int h_in0 = th0 * S - g.padU;
         if (vec) {
             if constexpr (sizeof(T) == 4) {
+#pragma unroll 1
                 for (int pl = warp; pl < S_T * 16; pl += CONV_THREADS / 32) {
                     const int ci = pl & 15, sl = pl >> 4;
                     const bool pok = s0 + sl < g.n && ci0 + ci < g.Cin;
                     const float *src = x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)h_in0 * WIN;
                     const unsigned dst = (unsigned)__cvta_generic_to_shared(xs + pl * PLANE + 4);
+#pragma unroll 1
                     for (int e = lane; e < PH * W4; e += 32) {
                         const int r = e / W4, c4 = e % W4;
                         const bool ok = pok && h_in0 + r >= 0 && h_in0 + r < g.Hin;
@@ -599,13 +607,14 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (r * RW + 4 * c4) * 4), "l"(sp), "r"(ok ? 16 : 0) : "memory");
                     }
                 }
-                const int TP4 = TP / 4;
+#pragma unroll 1
                 for (int pl = warp; pl < 16 * S_T; pl += CONV_THREADS / 32) {
                     const int sl = pl % S_T, co = pl / S_T;
                     const bool pok = s0 + sl < g.n && co0 + co < g.Cout;
                     const float *src = dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)th0 * TW;
                     const unsigned dst = (unsigned)__cvta_generic_to_shared(dys + co * DYP + sl * TP);
-                    for (int e = lane; e < TP4; e += 32) {
+#pragma unroll 1
+                    for (int e = lane; e < WS::TP4; e += 32) {
                         const bool ok = pok && th0 + (4 * e) / TW < g.Hout;
                         const float *sp = ok ? src + 4 * e : dy;
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 16 * e), "l"(sp), "r"(ok ? 16 : 0) : "memory");
@@ -632,14 +641,24 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    if (it_begin < it_end) stage_item(it_begin, smem, smem + S_T * 16 * PLANE);
+    // nstage = 2 or 3 shared-memory stages: items it+1 .. it+nstage-1 are in flight while item it is consumed.
+    // One commit group per loop step, empty once the items run out, so the group count stays in step.
+    auto stage_or_skip = [&](long long it, int stg) {
+        if (it < it_end) stage_item(it, smem + stg * STAGE, smem + stg * STAGE + S_T * 16 * PLANE);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int a = 0; a < nstage - 1; a++) stage_or_skip(it_begin + a, a);
     int cur = 0;
-    for (long long it = it_begin; it < it_end; it++, cur ^= 1) {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();        // this item has landed for every thread, and every thread is done with the other stage
+    for (long long it = it_begin; it < it_end; it++, cur = (cur + 1 == nstage) ? 0 : cur + 1) {
+        if (nstage == 3) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();        // this item has landed for every thread, and every thread is done with the stage refilled next
         const float *xs = smem + cur * STAGE, *dys = xs + S_T * 16 * PLANE;
-        if (it + 1 < it_end) stage_item(it + 1, smem + (cur ^ 1) * STAGE, smem + (cur ^ 1) * STAGE + S_T * 16 * PLANE);
-        for (int row = warp; row < S_T * TH; row += CONV_THREADS / 32) {
+        stage_or_skip(it + nstage - 1, (cur + nstage - 1) % nstage);
+#pragma unroll
+        for (int rr = 0; rr < (S_T * TH + CONV_THREADS / 32 - 1) / (CONV_THREADS / 32); rr++) {
+            const int row = warp + rr * (CONV_THREADS / 32);
+            if (row >= S_T * TH) break;
             const int sl = row / TH, ph = row % TH;
             const float *xb = xs + (sl * 16 + cib) * PLANE + (ph * S) * RW;        // ci = cib (i = 0), + 8 planes for i = 1
             const float *dp = dys + (cob * 4) * DYP + sl * TP + ph * TW;
@@ -762,39 +781,38 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     const int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
     const bool k3 = g.Hk == 3 && g.Wk == 3 && g.padL == 1, k1 = g.Hk == 1 && g.Wk == 1 && g.padL == 0 && g.padU == 0;
     if ((k3 || k1) && g.sh == g.sw && (g.sh == 1 || g.sh == 2) && g.Win == g.sw * g.Wout && (g.Wout == 8 || g.Wout == 16 || g.Wout == 32)) {
-        // about 256 (stride 1) or 128 (stride 2) pixels per item: whole output rows, several streams when the image is small
-        const int S = g.sh, TW = g.Wout, K = g.Hk, target = S == 1 ? 256 : 128;
-        int TH = target / TW; if (TH > g.Hout) TH = g.Hout; if (TH < 1) TH = 1;
-        int S_T = target / (TH * TW); if (S_T > g.n) S_T = g.n; if (S_T < 1) S_T = 1;
-        const int PH = (TH - 1) * S + K, RW = g.Win + 8, PLANE = 4 * ((PH * RW / 4) | 1);
-        // two stages must leave room for two CTAs per SM
-        while (S_T > 1 && 2 * ((size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4)) * sizeof(float) > 110 * 1024) S_T /= 2;
-        const size_t stage = (size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4);
-        const size_t smem = std::max<size_t>(2 * stage, (size_t)16 * 16 * KK) * sizeof(float);
-        const int tiles_h = ceil_div(g.Hout, TH);
-        const long long items = (long long)ceil_div(g.n, S_T) * tiles_h;
-        int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
-        if (groups > items) groups = (int)items;
-        if (groups < 1) groups = 1;
-        float *part = sc.scratch<float>((size_t)groups * nw);
-        if (!part) return;
-        const int vec = sizeof(T) == 4 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
-        dim3 grid(ci_tiles * co_tiles, groups);
-#define TL_WG3_LAUNCH(S_, TW_)                                                                                        \
+        // about 256 (stride 1) or 128 (stride 2) pixels per item: whole output rows, two streams for 8-pixel rows.
+        // The item shape is part of the kernel type: (TW, TH, S_T) = (32, 8, 1), (16, 16, 1), (8, 8, 2) for stride 1
+        // and (16, 8, 1), (8, 8, 2) for stride 2; images with fewer rows use the generic kernel below.
+        const int S = g.sh, TW = g.Wout, K = g.Hk;
+        const int TH = TW == 8 ? 8 : (S == 1 ? 256 : 128) / TW, S_T = TW == 8 ? 2 : 1;
+        if (g.Hout >= TH && !(S == 2 && TW == 32)) {     // (64-wide inputs with stride 2 take the generic kernel)
+            const int PH = (TH - 1) * S + K, RW = g.Win + 8, PLANE = 4 * ((PH * RW / 4) | 1);
+            const size_t stage = (size_t)S_T * 16 * PLANE + (size_t)16 * (S_T * TH * TW + 4);
+            const int nstage = (3 * stage * sizeof(float) <= 110 * 1024) ? 3 : 2;
+            const size_t smem = std::max<size_t>(nstage * stage, (size_t)16 * 16 * KK) * sizeof(float);
+            const int tiles_h = ceil_div(g.Hout, TH);
+            const long long items = (long long)ceil_div(g.n, S_T) * tiles_h;
+            int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
+            if (groups > items) groups = (int)items;
+            if (groups < 1) groups = 1;
+            float *part = sc.scratch<float>((size_t)groups * nw);
+            if (!part) return;
+            const int vec = sizeof(T) == 4 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
+            dim3 grid(ci_tiles * co_tiles, groups);
+#define TL_WG3_LAUNCH2(S_, TW_, K_, TH_, ST_)                                                                         \
     do {                                                                                                              \
-        if (K == 3) {                                                                                                 \
-            cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_, 3>), grid, CONV_THREADS, smem, g, x, dy, part, TH, S_T, tiles_h, ci_tiles, vec); \
-        } else {                                                                                                      \
-            cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_, 1>), grid, CONV_THREADS, smem, g, x, dy, part, TH, S_T, tiles_h, ci_tiles, vec); \
-        }                                                                                                             \
+        cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, S_, TW_, K_, TH_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_, K_, TH_, ST_>), grid, CONV_THREADS, smem, g, x, dy, part, tiles_h, ci_tiles, vec, nstage); \
     } while (0)
-        if (S == 1) { if (TW == 32) TL_WG3_LAUNCH(1, 32); else if (TW == 16) TL_WG3_LAUNCH(1, 16); else TL_WG3_LAUNCH(1, 8); }
-        else        { if (TW == 32) TL_WG3_LAUNCH(2, 32); else if (TW == 16) TL_WG3_LAUNCH(2, 16); else TL_WG3_LAUNCH(2, 8); }
+#define TL_WG3_LAUNCH(S_, TW_, TH_, ST_) do { if (K == 3) TL_WG3_LAUNCH2(S_, TW_, 3, TH_, ST_); else TL_WG3_LAUNCH2(S_, TW_, 1, TH_, ST_); } while (0)
+            if (S == 1) { if (TW == 32) TL_WG3_LAUNCH(1, 32, 8, 1); else if (TW == 16) TL_WG3_LAUNCH(1, 16, 16, 1); else TL_WG3_LAUNCH(1, 8, 8, 2); }
+            else        { if (TW == 16) TL_WG3_LAUNCH(2, 16, 8, 1); else TL_WG3_LAUNCH(2, 8, 8, 2); }
 #undef TL_WG3_LAUNCH
-        TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
-        return;
+#undef TL_WG3_LAUNCH2
+            TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
+            return;
+        }
     }
     // pixel tile: whole rows, about 256 pixels
     int TW = g.Wout < 64 ? g.Wout : 64;
