@@ -157,6 +157,71 @@ class LinearSweep(object):
                 "peak_source": pk["source"], "kernel": "linear_fw/wg/ig (whole step)", "algorithmic_bytes": self.bytes}
 
 
+class MmSweep(object):
+    """`mm` / `mm_fp16` (C = A B, matMul_args) on square shapes: the tensor-core GEMM of the matmul family against
+    the tensor roofline.  Not one of the numbered configs; `--config mm`."""
+    SHAPES = [1024, 2048, 4096]
+    name = "mm_square_1024_2048_4096"
+
+    def __init__(self, pkg, lib, half):
+        self.pkg, self.lib, self.half = pkg, lib, half
+        self.dt = np.float16 if half else np.float32
+        self.es = 2 if half else 4
+        self.flops = sum(2.0 * n ** 3 for n in self.SHAPES)
+        self.keep = pkg.Keep()
+        self.fn = "mm_fp16" if half else "mm"
+
+    def _args(self, A, B, C, n):
+        return self.pkg.make_args(self.keep, "matMul_args" + ("_fp16" if self.half else ""), A=A, B=B, C=C, N=n, K=n, M=n, trans_B=0, USE_BIASES=0)
+
+    def _inputs(self, rng, n):
+        return (rng.standard_normal((n, n)) / np.sqrt(n)).astype(self.dt), rng.standard_normal((n, n)).astype(self.dt)
+
+    def setup_device(self):
+        rng = np.random.default_rng(3)
+        self.dev, self.args_dev = [], []
+        for n in self.SHAPES:
+            A, B = self._inputs(rng, n)
+            bufs = [self.pkg.DeviceBuffer(self.lib, A), self.pkg.DeviceBuffer(self.lib, B), self.pkg.DeviceBuffer(self.lib, nbytes=n * n * self.es)]
+            self.dev.append(bufs)
+            self.args_dev.append(self._args(*[b.ptr for b in bufs], n))
+        self.flush = self.pkg.DeviceBuffer(self.lib, nbytes=256 << 20)
+
+    def l2_flush(self):
+        self.lib.trainlib_memset(self.flush.ptr, 1, self.flush.nbytes)
+
+    def step_device(self):
+        for a in self.args_dev:
+            getattr(self.lib, self.fn)(ctypes.byref(a))
+
+    def setup_host(self, lib):
+        rng = np.random.default_rng(3)
+        self.host, self.args_host = [], []
+        for n in self.SHAPES:
+            A, B = self._inputs(rng, n)
+            arrs = [A, B, np.zeros((n, n), self.dt)]
+            if hasattr(lib, "trainlib_malloc_host"):
+                arrs = [pinned_like(self.pkg, lib, a) for a in arrs]
+            self.host.append(arrs)
+            self.args_host.append(self._args(*arrs, n))
+        self.h2d = sum(3.0 * n * n * self.es for n in self.SHAPES)
+        self.d2h = sum(1.0 * n * n * self.es for n in self.SHAPES)
+
+    def step_host(self, lib):
+        for a in self.args_host:
+            getattr(lib, self.fn)(ctypes.byref(a))
+
+    def metric(self, ms):
+        return {"metric": "mm_tflops", "unit": "TFLOP/s", "value": self.flops / (ms * 1e-3) / 1e12}
+
+    def roofline(self, ms, pk):
+        tf = self.flops / (ms * 1e-3) / 1e12
+        peak = pk["bf16_tflops_sustained"] if self.half else pk["bf16_tflops_sustained"] / 6.0
+        return {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None, "peak_source": pk["source"],
+                "kernel": "gemm_tc_kernel", "algorithmic_flops": self.flops,
+                "peak_note": "measured sustained bf16 (fp16 operands)" if self.half else "3xTF32-effective fp32 peak = measured sustained bf16 / 6"}
+
+
 _pinned = []
 
 
@@ -174,6 +239,8 @@ def pinned_like(pkg, lib, a):
 def make_workload(cfg, pkg, lib, dtype):
     if cfg == "c2":
         return LinearSweep(pkg, lib, dtype == "fp16")
+    if cfg == "mm":
+        return MmSweep(pkg, lib, dtype == "fp16")
     if cfg == "c5":
         from bench_nets import ResNet8Streams
         return ResNet8Streams(pkg, lib)

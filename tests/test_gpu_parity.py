@@ -88,6 +88,32 @@ def test_mm_config_shapes(run, oracle, N, K, M):
     assert_close(r.mm(A, B, N, K, M, 0, fn="mm_add", C0=C0), want + C0, FP32_TOL, "mm_add")
 
 
+@pytest.mark.parametrize("half", [False, True], ids=["fp32_3xtf32", "fp16"])
+@pytest.mark.parametrize("N,K,M", [(128, 64, 128), (130, 70, 67), (1, 1, 1), (257, 33, 129), (64, 512, 200), (384, 256, 256), (5, 1000, 3)])
+def test_mm_tensor_core_path(pkg, gpulib, run, oracle, N, K, M, half):
+    """tcgen05 GEMM forced on for every shape (tails in all three dimensions, both B layouts, accumulate form)"""
+    rng = seeded(7 * N + 3 * K + M + (1 if half else 0))
+    A = rng.standard_normal((N, K)).astype(F); B = rng.standard_normal((K, M)).astype(F)
+    C0 = rng.standard_normal((N, M)).astype(F)
+    if half:
+        A, B, C0 = [a.astype(np.float16).astype(F) for a in (A, B, C0)]
+    Bt = np.ascontiguousarray(B.T)
+    tol = FP16_TOL if half else FP32_TOL
+    want = oracle.mm(A, B, N, K, M, 0)
+    gpulib.trainlib_set_gemm_path(2)
+    try:
+        r = run(device=True, half=half)
+        l0 = gpulib.trainlib_kernel_launches()
+        assert_close(r.mm(A, B, N, K, M, 0).astype(F), want, tol, "mm")
+        assert gpulib.trainlib_kernel_launches() == l0 + 1
+        assert_close(r.mm(A, Bt, N, K, M, 1).astype(F), want, tol, "mm trans_B")
+        if not half:
+            assert_close(r.mm(A, B, N, K, M, 0, fn="mm_add", C0=C0), want + C0, tol, "mm_add")
+        assert gpulib.trainlib_tc_status() == 0, "a bounded tensor-core wait gave up: id %d" % gpulib.trainlib_tc_status()
+    finally:
+        gpulib.trainlib_set_gemm_path(0)
+
+
 @pytest.mark.parametrize("inn,out", [(256, 256), (1024, 1024), (4096, 1024), (1024, 4096), (1000, 37)])
 @pytest.mark.parametrize("half", [False, True])
 def test_linear_config2(run, oracle, inn, out, half):
