@@ -75,7 +75,8 @@ int         trainlib_profile_entries(void);
 const char *trainlib_profile_entry(int i, long long *launches, double *total_ms);
 
 /* ---- GEMM path selection for diagnostics and profiling.
- * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force tcgen05 tensor-core tiles. */
+ * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force the tcgen05 kernels whose operands are staged by threads
+ * (convolutions: the tensor-core kernel at every size), 3 = force the TMA-fed tcgen05 GEMM for the mm family. */
 void  trainlib_set_gemm_path(int path);
 /* 0 while every tensor-core kernel so far finished normally; otherwise the id of the bounded
  * device-side wait that gave up (the kernel then returned early and its output is invalid). */

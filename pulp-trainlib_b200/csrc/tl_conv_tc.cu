@@ -369,6 +369,7 @@ static int *status_word()
 }
 // shared with the tensor-core GEMM (tl_gemm_tc.cu): one status word for every bounded wait of the library
 int *tc_status_word() { return status_word(); }
+void *tc_encode_tiled_fn() { return (void *)encode_fn(); }
 
 // Runs the tensor-core kernel when the geometry qualifies; returns false to let the caller use the FFMA path.
 // src: [n][C_src][H_src][W_src], dst: [n][C_dst][H_dst][W_dst]; `flip` = input-gradient role (stride must be 1).

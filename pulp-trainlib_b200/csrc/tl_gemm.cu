@@ -90,11 +90,14 @@ gemm_ffma_kernel(GemmDesc<T> d)
 
 // Tensor-core path (tl_gemm_tc.cu); returns false when the shape/layout does not qualify.
 template <class T> bool gemm_tensor_core(const GemmDesc<T> &d);
+template <class T> bool gemm_tensor_core_tma(const GemmDesc<T> &d);
 
 template <class T> void gemm(const GemmDesc<T> &d)
 {
     if (d.N <= 0 || d.M <= 0 || d.batch <= 0) return;
-    if (gemm_path() != 1 && gemm_tensor_core<T>(d)) return;
+    // 0 auto, 1 FFMA only, 2 staged tensor-core kernel forced, 3 TMA tensor-core kernel forced
+    if (gemm_path() != 1 && gemm_path() != 2 && gemm_tensor_core_tma<T>(d)) return;
+    if (gemm_path() != 1 && gemm_path() != 3 && gemm_tensor_core<T>(d)) return;
     long long tiles64 = (long long)ceil_div(d.N, 64) * ceil_div(d.M, 64) * d.batch;
     if (tiles64 >= sm_count() || (d.N > 32 && d.M > 32 && tiles64 * 4 >= 2 * sm_count())) {
         dim3 grid(ceil_div(d.M, 64), ceil_div(d.N, 64), d.batch);
