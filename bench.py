@@ -214,11 +214,26 @@ class MmSweep(object):
     def metric(self, ms):
         return {"metric": "mm_tflops", "unit": "TFLOP/s", "value": self.flops / (ms * 1e-3) / 1e12}
 
+    def per_shape(self, reps=5):
+        """device time of each shape alone (inputs resident, `reps` launches back to back after one warm-up)"""
+        out = []
+        for n, a in zip(self.SHAPES, self.args_dev):
+            getattr(self.lib, self.fn)(ctypes.byref(a))
+            self.lib.trainlib_synchronize()
+            self.lib.trainlib_timer_start()
+            for _ in range(reps):
+                getattr(self.lib, self.fn)(ctypes.byref(a))
+            ms = self.lib.trainlib_timer_stop_ms() / reps
+            out.append({"n": n, "ms": ms, "tflops": 2.0 * n ** 3 / (ms * 1e-3) / 1e12})
+        return out
+
     def roofline(self, ms, pk):
-        tf = self.flops / (ms * 1e-3) / 1e12
+        shapes = self.per_shape()
+        big = shapes[-1]
         peak = pk["bf16_tflops_sustained"] if self.half else pk["bf16_tflops_sustained"] / 6.0
-        return {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None, "peak_source": pk["source"],
-                "kernel": "gemm_tc_kernel", "algorithmic_flops": self.flops,
+        return {"bound": "tensor", "achieved": big["tflops"], "peak": peak, "unit": "TFLOP/s", "frac": big["tflops"] / peak, "traffic": None,
+                "peak_source": pk["source"], "kernel": "gemm_tma_kernel + pack_kmajor_kernel, %d^3" % big["n"], "algorithmic_flops": 2.0 * big["n"] ** 3,
+                "per_shape": shapes, "sweep_tflops": self.flops / (ms * 1e-3) / 1e12,
                 "peak_note": "measured sustained bf16 (fp16 operands)" if self.half else "3xTF32-effective fp32 peak = measured sustained bf16 / 6"}
 
 
