@@ -52,6 +52,12 @@ void  trainlib_free_host(void *host_ptr);
 int   trainlib_memcpy_h2d(void *dev, const void *host, size_t bytes);
 int   trainlib_memcpy_d2h(void *host, const void *dev, size_t bytes);
 int   trainlib_memset(void *dev, int byte, size_t bytes);
+/* Upload that overlaps the kernels already queued: for an input that the caller keeps in two device buffers
+ * (slot 0 / 1, alternating).  The copy runs on a second stream after the work marked with
+ * trainlib_mark_consumed(slot) has finished; everything queued on the library's stream after this call sees the
+ * new data.  `host` should be pinned (trainlib_malloc_host), otherwise the copy is synchronous. */
+int   trainlib_memcpy_h2d_overlapped(void *dev, const void *host, size_t bytes, int slot);
+int   trainlib_mark_consumed(int slot);      /* "all work queued so far is the last reader of buffer `slot`" */
 
 /* ---- streams mode.  With n > 1, every activation blob (input, output, and their
  * diffs) holds n independent batch-1 tensors back to back ([n][blob.dim]); weight

@@ -285,6 +285,37 @@ int trainlib_memcpy_d2h(void *host, const void *dev, size_t bytes)
     if (!TL_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, g.cur_stream))) return g.err;
     return TL_CUDA(cudaStreamSynchronize(g.cur_stream)) ? TL_OK : g.err;
 }
+// Overlapped upload for double-buffered inputs.  The copy runs on a second stream: it first waits until the work
+// that last read buffer `slot` (marked with trainlib_mark_consumed) has finished, and the library's stream waits for
+// the copy, so kernels queued afterwards see the new data while kernels queued before keep running beside the copy.
+static cudaStream_t g_copy_stream = nullptr;
+static cudaEvent_t g_consumed[2] = {nullptr, nullptr}, g_uploaded = nullptr;
+static bool g_consumed_set[2] = {false, false};
+static bool overlap_ready()
+{
+    if (g_copy_stream) return true;
+    if (!TL_CUDA(cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking))) return false;
+    for (int i = 0; i < 2; i++) if (!TL_CUDA(cudaEventCreateWithFlags(&g_consumed[i], cudaEventDisableTiming))) return false;
+    return TL_CUDA(cudaEventCreateWithFlags(&g_uploaded, cudaEventDisableTiming));
+}
+int trainlib_memcpy_h2d_overlapped(void *dev, const void *host, size_t bytes, int slot)
+{
+    if (!ready()) return g.err;
+    if (slot < 0 || slot > 1) { set_error(TL_ERR_BAD_ARGS, "trainlib_memcpy_h2d_overlapped: slot %d", slot); return TL_ERR_BAD_ARGS; }
+    if (!overlap_ready()) return g.err;
+    if (g_consumed_set[slot] && !TL_CUDA(cudaStreamWaitEvent(g_copy_stream, g_consumed[slot], 0))) return g.err;
+    if (!TL_CUDA(cudaMemcpyAsync(dev, host, bytes, cudaMemcpyHostToDevice, g_copy_stream))) return g.err;
+    if (!TL_CUDA(cudaEventRecord(g_uploaded, g_copy_stream))) return g.err;
+    return TL_CUDA(cudaStreamWaitEvent(g.cur_stream, g_uploaded, 0)) ? TL_OK : g.err;
+}
+int trainlib_mark_consumed(int slot)
+{
+    if (!ready()) return g.err;
+    if (slot < 0 || slot > 1) { set_error(TL_ERR_BAD_ARGS, "trainlib_mark_consumed: slot %d", slot); return TL_ERR_BAD_ARGS; }
+    if (!overlap_ready()) return g.err;
+    g_consumed_set[slot] = true;
+    return TL_CUDA(cudaEventRecord(g_consumed[slot], g.cur_stream)) ? TL_OK : g.err;
+}
 int trainlib_memset(void *dev, int byte, size_t bytes)
 {
     if (!ready()) return g.err;

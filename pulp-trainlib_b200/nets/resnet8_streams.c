@@ -186,6 +186,8 @@ static size_t p_off[2 * N_CONV + 8], p_cnt[2 * N_CONV + 8];
 static int p_n;
 static float *g_params, *g_grads;
 static float *g_img, *g_lab, *g_loss;                  /* resident copies used by resnet8_forward_host */
+static float *g_img2, *g_lab2;                         /* second copy: uploads alternate between the two */
+static int g_host_slot = -1;                           /* copy read by the step in flight (-1: caller-owned device batch) */
 
 static size_t conv_w_count(int i) { return (size_t)SPEC[i].cout * SPEC[i].cin * SPEC[i].k * SPEC[i].k; }
 
@@ -224,7 +226,7 @@ size_t resnet8_workspace_floats(int n)
     per += 2 * (act_floats(C2) + act_floats(C4) + act_floats(C6));             /* residual sums */
     per += act_floats(C2) + act_floats(C4);                                     /* shortcut input-gradient temporaries */
     per += 2 * 64 + 2 * RESNET8_CLASSES;                                        /* pooled features, logits */
-    per += RESNET8_IMAGE_FLOATS + RESNET8_CLASSES + 1;                          /* resident copy of a host batch: images, labels, losses */
+    per += 2 * (RESNET8_IMAGE_FLOATS + RESNET8_CLASSES) + 1;                    /* two resident copies of a host batch (images, labels), losses */
     return per * (size_t)n + 64;
 }
 
@@ -301,6 +303,7 @@ int resnet8_bind(int n, float *params, float *grads, float *ws)
     { float *d = take(&ws, N * 64), *g = take(&ws, N * 64); mkblob(&b_gap, d, g, 64, 1, 1); }
     { float *d = take(&ws, N * RESNET8_CLASSES), *g = take(&ws, N * RESNET8_CLASSES); mkblob(&b_z, d, g, 1, 1, RESNET8_CLASSES); }
     g_img = take(&ws, N * RESNET8_IMAGE_FLOATS); g_lab = take(&ws, N * RESNET8_CLASSES); g_loss = take(&ws, N);
+    g_img2 = take(&ws, N * RESNET8_IMAGE_FLOATS); g_lab2 = take(&ws, N * RESNET8_CLASSES);
 
     /* conv wiring: input blob of every conv */
     struct blob *conv_in[N_CONV] = {&b_x, &b_norm[0], &b_norm[1], &b_sum[0], &b_norm[3], &b_sum[0], &b_sum[1], &b_norm[5], &b_sum[1]};
@@ -360,10 +363,17 @@ void resnet8_forward_host(const float *host_images, const float *host_labels, fl
 #ifdef NET_REFERENCE
     resnet8_forward(host_images, host_labels, host_loss);
 #else
-    trainlib_memcpy_h2d(g_img, host_images, sizeof(float) * (size_t)g_n * RESNET8_IMAGE_FLOATS);
-    trainlib_memcpy_h2d(g_lab, host_labels, sizeof(float) * (size_t)g_n * RESNET8_CLASSES);
-    resnet8_forward(g_img, g_lab, g_loss);
+    /* two resident copies of the batch, used in turn: the upload of this step runs beside the backward pass and the
+       update of the previous step, which are still queued when this function is entered */
+    static int slot = 0;
+    float *img = slot ? g_img2 : g_img, *lab = slot ? g_lab2 : g_lab;
+    g_host_slot = slot;
+    trainlib_memcpy_h2d_overlapped(img, host_images, sizeof(float) * (size_t)g_n * RESNET8_IMAGE_FLOATS, slot);
+    trainlib_memcpy_h2d_overlapped(lab, host_labels, sizeof(float) * (size_t)g_n * RESNET8_CLASSES, slot);
+    resnet8_forward(img, lab, g_loss);
+    trainlib_mark_consumed(slot);                  /* resnet8_backward marks it again: it reads the images and labels too */
     trainlib_memcpy_d2h(host_loss, g_loss, sizeof(float) * (size_t)g_n);
+    slot ^= 1;
 #endif
 }
 
@@ -396,6 +406,9 @@ void resnet8_backward(void)
     stage_bw(C3, 3, C4, 4, P2, 1);
     stage_bw(C1, 1, C2, 2, -1, 0);
     relu_bw(&a_relu_n[0]); norm_bw(&a_norm[0]); conv_bw(C0);
+#ifndef NET_REFERENCE
+    if (g_host_slot >= 0) { trainlib_mark_consumed(g_host_slot); g_host_slot = -1; }   /* last reader of that batch copy */
+#endif
 }
 
 void resnet8_update(float lr)
