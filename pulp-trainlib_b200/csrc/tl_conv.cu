@@ -719,14 +719,25 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
     }
 }
 
+// out[i] = sum over groups of part[g][i], always added in the same order: 32 consecutive weights x 32 slices of the
+// groups per CTA (slice s adds groups s, s+32, ...; the slices are then added in slice order by one thread per weight).
 template <class T>
-__global__ void reduce_partials_kernel(const float *__restrict__ part, T *__restrict__ out, long long n, int groups)
+__global__ void __launch_bounds__(1024) reduce_partials_kernel(const float *__restrict__ part, T *__restrict__ out, long long n, int groups)
 {
-    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
+    __shared__ float sm[32][33];
+    const int wx = threadIdx.x & 31, sl = threadIdx.x >> 5;
+    const long long i = (long long)blockIdx.x * 32 + wx;
     float s = 0.f;
-    for (int gidx = 0; gidx < groups; gidx++) s += part[(long long)gidx * n + i];
-    st(out + i, s);
+    if (i < n)
+        for (int gidx = sl; gidx < groups; gidx += 32) s += part[(long long)gidx * n + i];
+    sm[sl][wx] = s;
+    __syncthreads();
+    if (sl == 0 && i < n) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; k++) t += sm[k][wx];
+        st(out + i, t);
+    }
 }
 
 // Fallback for filter windows above 5x5: one CTA per weight, block-wide reduction.
@@ -810,7 +821,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
             else        { if (TW == 16) TL_WG3_LAUNCH(2, 16, 8, 1); else TL_WG3_LAUNCH(2, 8, 8, 2); }
 #undef TL_WG3_LAUNCH
 #undef TL_WG3_LAUNCH2
-            TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
+            TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
             return;
         }
     }
@@ -842,7 +853,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     else if (g.Hk == 3) TL_WG_LAUNCH(3, 3);
     else TL_WG_LAUNCH(5, 5);
 #undef TL_WG_LAUNCH
-    TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 256), 256, 0, part, dw, nw, groups);
+    TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
 }
 
 // ------------------------------------------------------------------ explicit im2row / im2col / blocktranspose
