@@ -86,6 +86,7 @@ class LinearSweep(object):
     """config 2: Linear FW + WG + IG at batch 1 over (in,out) in {(256,256),(1024,1024),(4096,1024),(1024,4096)}."""
     SHAPES = [(256, 256), (1024, 1024), (4096, 1024), (1024, 4096)]
     name = "c2_linear_sweep_fw_wg_ig_batch1"
+    use_graph = True
 
     def __init__(self, pkg, lib, half):
         self.pkg, self.lib, self.half = pkg, lib, half
@@ -254,6 +255,12 @@ def pinned_like(pkg, lib, a):
 def make_workload(cfg, pkg, lib, dtype):
     if cfg == "c2":
         return LinearSweep(pkg, lib, dtype == "fp16")
+    if cfg == "c1":
+        from bench_layers import ConvStep
+        return ConvStep(pkg, lib)
+    if cfg == "c3":
+        from bench_layers import MhsaStep
+        return MhsaStep(pkg, lib)
     if cfg == "mm":
         return MmSweep(pkg, lib, dtype == "fp16")
     if cfg == "c5":
@@ -305,6 +312,7 @@ def main():
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "fp16"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="time the plain entry-point calls instead of a CUDA-graph replay (single-layer configs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     pkg = load_pkg()
@@ -340,13 +348,25 @@ def run_single(args, pkg, lib, wl):
     for _ in range(args.warmup):
         wl.step_device()
     lib.trainlib_synchronize(); pkg.check(lib)
+    # the resident step is recorded once into a CUDA graph (the same entry-point calls, device pointers) and replayed:
+    # at these sizes the calls are bound by launch latency, which the replay removes
+    graph = None
+    if getattr(wl, "use_graph", False) and not args.no_graph:
+        lib.trainlib_graph_begin(); wl.step_device(); graph = lib.trainlib_graph_end()
+        pkg.check(lib)
+        for _ in range(2):
+            lib.trainlib_graph_launch(graph)
+        lib.trainlib_synchronize(); pkg.check(lib)
     sampler = ClockSampler(lib.trainlib_device()); sampler.start()
     launches0 = lib.trainlib_kernel_launches()
     ms = []
     for _ in range(args.steps):
         wl.l2_flush()
         lib.trainlib_timer_start()
-        wl.step_device()
+        if graph:
+            lib.trainlib_graph_launch(graph)
+        else:
+            wl.step_device()
         ms.append(lib.trainlib_timer_stop_ms())
     launches = lib.trainlib_kernel_launches() - launches0
     clocks = sampler.stop()
@@ -358,7 +378,8 @@ def run_single(args, pkg, lib, wl):
     m = wl.metric(ms_step); e = wl.metric(e2e_ms)
     line = {"metric": m["metric"], "value": m["value"], "unit": m["unit"], "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16" if args.dtype == "fp16" else "f32",
-            "data": "synthetic", "config": {"workload": wl.name, "l2": "flushed between timed steps (256 MiB memset)"},
+            "data": "synthetic", "config": {"workload": wl.name, "l2": "flushed between timed steps (256 MiB memset)",
+                                            "replay": "CUDA graph of the entry-point calls of one step" if graph else "entry-point calls"},
             "roofline": wl.roofline(ms_step, pk), "gpu_launches": int(launches), "clocks": clocks,
             "e2e": {"value": e["value"], "unit": e["unit"], "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h), "ms_per_step": e2e_ms}}
     if not args.no_cpu_baseline and os.path.exists(REF_MT):

@@ -80,6 +80,16 @@ void        trainlib_profile(int on);          /* 1 = clear and start, 0 = stop 
 int         trainlib_profile_entries(void);
 const char *trainlib_profile_entry(int i, long long *launches, double *total_ms);
 
+/* ---- CUDA graphs.  Entry-point calls made between begin and end are recorded instead of executed (device pointers
+ * only: a host pointer would need a synchronous copy); the handle replays them with one launch on the library's
+ * stream.  The recorded launches keep the addresses they saw, including library scratch: run the same calls once
+ * before capturing so that the scratch arena has its final size; it is never shrunk or moved afterwards.
+ * trainlib_kernel_launches() advances by the number of recorded kernels on every replay. */
+int   trainlib_graph_begin(void);
+void *trainlib_graph_end(void);               /* NULL on failure (see trainlib_last_error) */
+int   trainlib_graph_launch(void *graph);
+void  trainlib_graph_destroy(void *graph);
+
 /* ---- GEMM path selection for diagnostics and profiling.
  * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force the tcgen05 kernels whose operands are staged by threads
  * (convolutions: the tensor-core kernel at every size), 3 = force the TMA-fed tcgen05 GEMM for the mm family. */

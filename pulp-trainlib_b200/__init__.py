@@ -68,6 +68,12 @@ def load(path=LIB_PATH):
     lib.trainlib_profile_entries.restype = ctypes.c_int
     lib.trainlib_profile_entry.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_double)]
     lib.trainlib_profile_entry.restype = ctypes.c_char_p
+    lib.trainlib_graph_begin.restype = ctypes.c_int
+    lib.trainlib_graph_end.restype = ctypes.c_void_p
+    lib.trainlib_graph_launch.argtypes = [ctypes.c_void_p]; lib.trainlib_graph_launch.restype = ctypes.c_int
+    lib.trainlib_graph_destroy.argtypes = [ctypes.c_void_p]
+    lib.trainlib_memcpy_h2d_overlapped.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]; lib.trainlib_memcpy_h2d_overlapped.restype = ctypes.c_int
+    lib.trainlib_mark_consumed.argtypes = [ctypes.c_int]; lib.trainlib_mark_consumed.restype = ctypes.c_int
     lib.trainlib_set_gemm_path.argtypes = [ctypes.c_int]
     lib.trainlib_gemm_path.restype = ctypes.c_int
     lib.trainlib_tc_status.restype = ctypes.c_int

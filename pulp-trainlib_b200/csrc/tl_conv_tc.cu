@@ -389,7 +389,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     else return false;
     if (H_dst % TH != 0) return false;
     const long long work = (long long)n * H_dst * W_dst * C_dst * C_src * Hk * Wk;
-    if (gemm_path() != 2 && work < (1ll << 24)) return false;  // too small to fill the machine: FFMA tiles win
+    if (gemm_path() != 2 && work < (1ll << 21)) return false;  // below about 2 M multiply-adds the FFMA tiles finish before the tensor-core prologue does
 
     ConvTcParams p;
     p.n = n; p.Cin = C_src; p.Cout = C_dst; p.Hout = H_dst; p.Wout = W_dst;

@@ -18,8 +18,12 @@ gemm_ffma_kernel(GemmDesc<T> d)
 {
     constexpr int BK = 16;
     constexpr int NT = (BM / TM) * (BN / TN);
-    __shared__ __align__(16) float As[BK][BM + 4];
-    __shared__ __align__(16) float Bs[BK][BN + 4];
+    constexpr int AE = BM * BK / NT, BE = BN * BK / NT;      // elements of the A / B tile each thread moves
+    static_assert(BM * BK % NT == 0 && BN * BK % NT == 0, "tile must divide over the threads");
+    // two shared-memory stages: the global loads of tile t+1 are issued before tile t is multiplied and stored
+    // afterwards, so their latency hides behind the FMAs and one barrier per K step is enough
+    __shared__ __align__(16) float As[2][BK][BM + 4];
+    __shared__ __align__(16) float Bs[2][BK][BN + 4];
 
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN), ty = tid / (BN / TN);
@@ -37,36 +41,60 @@ gemm_ffma_kernel(GemmDesc<T> d)
 
     const bool a_k_contig = (d.a_cs == 1);
     const bool b_k_contig = (d.b_rs == 1);
-
-    for (int k0 = 0; k0 < d.K; k0 += BK) {
-        // A tile: BM x BK elements
-        for (int e = tid; e < BM * BK; e += NT) {
+    float ra[AE], rb[BE];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int q = 0; q < AE; q++) {
+            const int e = tid + q * NT;
             int i, k;
             if (a_k_contig) { i = e / BK; k = e % BK; } else { k = e / BM; i = e % BM; }
-            float v = 0.f;
-            if (i0 + i < d.N && k0 + k < d.K) v = ld(A + (long long)(i0 + i) * d.a_rs + (long long)(k0 + k) * d.a_cs);
-            As[k][i] = v;
+            ra[q] = (i0 + i < d.N && k0 + k < d.K) ? ld(A + (long long)(i0 + i) * d.a_rs + (long long)(k0 + k) * d.a_cs) : 0.f;
         }
-        for (int e = tid; e < BN * BK; e += NT) {
+#pragma unroll
+        for (int q = 0; q < BE; q++) {
+            const int e = tid + q * NT;
             int j, k;
             if (b_k_contig) { j = e / BK; k = e % BK; } else { k = e / BN; j = e % BN; }
-            float v = 0.f;
-            if (j0 + j < d.M && k0 + k < d.K) v = ld(B + (long long)(k0 + k) * d.b_rs + (long long)(j0 + j) * d.b_cs);
-            Bs[k][j] = v;
+            rb[q] = (j0 + j < d.M && k0 + k < d.K) ? ld(B + (long long)(k0 + k) * d.b_rs + (long long)(j0 + j) * d.b_cs) : 0.f;
         }
-        __syncthreads();
+    };
+    auto stash = [&](int stage) {
+#pragma unroll
+        for (int q = 0; q < AE; q++) {
+            const int e = tid + q * NT;
+            int i, k;
+            if (a_k_contig) { i = e / BK; k = e % BK; } else { k = e / BM; i = e % BM; }
+            As[stage][k][i] = ra[q];
+        }
+#pragma unroll
+        for (int q = 0; q < BE; q++) {
+            const int e = tid + q * NT;
+            int j, k;
+            if (b_k_contig) { j = e / BK; k = e % BK; } else { k = e / BN; j = e % BN; }
+            Bs[stage][k][j] = rb[q];
+        }
+    };
+
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    int cur = 0;
+    for (int k0 = 0; k0 < d.K; k0 += BK, cur ^= 1) {
+        const bool more = k0 + BK < d.K;
+        if (more) fetch(k0 + BK);
 #pragma unroll
         for (int k = 0; k < BK; k++) {
             float a[TM], bb[TN];
 #pragma unroll
-            for (int r = 0; r < TM; r++) a[r] = As[k][ty * TM + r];
+            for (int r = 0; r < TM; r++) a[r] = As[cur][k][ty * TM + r];
 #pragma unroll
-            for (int c = 0; c < TN; c++) bb[c] = Bs[k][tx * TN + c];
+            for (int c = 0; c < TN; c++) bb[c] = Bs[cur][k][tx * TN + c];
 #pragma unroll
             for (int r = 0; r < TM; r++)
 #pragma unroll
                 for (int c = 0; c < TN; c++) acc[r][c] = fmaf(a[r], bb[c], acc[r][c]);
         }
+        if (more) stash(cur ^ 1);
         __syncthreads();
     }
 

@@ -25,6 +25,7 @@ struct Context {
     long long launches = 0;
     std::vector<Chunk> chunks;     // staging arena; normally exactly one chunk
     int scope_depth = 0;
+    bool arena_pinned = false;     // a captured graph holds arena addresses: never free or merge chunks again
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     int err = TL_OK;
     char err_msg[512] = {0};
@@ -160,7 +161,7 @@ static void arena_release(size_t mark)
     size_t idx = mark >> 48, off = mark & (((size_t)1 << 48) - 1);
     if (g.scope_depth == 0) {
         // top level: merge a fragmented arena into one chunk of the total size
-        if (g.chunks.size() > 1) {
+        if (g.chunks.size() > 1 && !g.arena_pinned) {
             size_t total = 0;
             cudaStreamSynchronize(g.cur_stream);
             for (auto &c : g.chunks) { total += c.cap; cudaFree(c.base); }
@@ -168,7 +169,7 @@ static void arena_release(size_t mark)
             char *base = nullptr;
             if (TL_CUDA(cudaMalloc(&base, total))) g.chunks.push_back({base, total, 0});
         } else {
-            g.chunks[0].off = 0;
+            for (auto &c : g.chunks) c.off = 0;
         }
         return;
     }
@@ -336,6 +337,48 @@ double trainlib_timer_stop_ms(void)
     return (double)ms;
 }
 long long trainlib_kernel_launches(void) { return g.launches; }
+
+// ---- CUDA graphs: capture the entry-point calls queued between begin and end, replay them with one launch
+struct TlGraph { cudaGraphExec_t exec; cudaGraph_t graph; long long kernels; };
+static long long g_capture_launches0 = 0;
+static bool g_capturing = false;
+int trainlib_graph_begin(void)
+{
+    if (!ready()) return g.err;
+    if (g_capturing) { set_error(TL_ERR_BAD_ARGS, "trainlib_graph_begin: a capture is already open"); return TL_ERR_BAD_ARGS; }
+    if (!TL_CUDA(cudaStreamBeginCapture(g.cur_stream, cudaStreamCaptureModeRelaxed))) return g.err;
+    g_capturing = true; g_capture_launches0 = g.launches;
+    g.arena_pinned = true;
+    return TL_OK;
+}
+void *trainlib_graph_end(void)
+{
+    if (!ready() || !g_capturing) return nullptr;
+    g_capturing = false;
+    cudaGraph_t graph = nullptr;
+    if (!TL_CUDA(cudaStreamEndCapture(g.cur_stream, &graph)) || !graph) return nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (!TL_CUDA(cudaGraphInstantiate(&exec, graph, 0))) { cudaGraphDestroy(graph); return nullptr; }
+    TlGraph *t = new TlGraph{exec, graph, g.launches - g_capture_launches0};
+    g.launches = g_capture_launches0;        // nothing ran during the capture
+    return t;
+}
+int trainlib_graph_launch(void *handle)
+{
+    if (!ready()) return g.err;
+    TlGraph *t = (TlGraph *)handle;
+    if (!t) { set_error(TL_ERR_BAD_ARGS, "trainlib_graph_launch: null graph"); return TL_ERR_BAD_ARGS; }
+    if (!TL_CUDA(cudaGraphLaunch(t->exec, g.cur_stream))) return g.err;
+    g.launches += t->kernels;
+    return TL_OK;
+}
+void trainlib_graph_destroy(void *handle)
+{
+    TlGraph *t = (TlGraph *)handle;
+    if (!t) return;
+    cudaGraphExecDestroy(t->exec); cudaGraphDestroy(t->graph);
+    delete t;
+}
 void trainlib_profile(int on)
 {
     if (!ready()) return;

@@ -28,6 +28,12 @@ class Tens(object):
             return self.dev.download(self.host.dtype, self.host.shape)
         return self.host
 
+    def set(self, array):
+        """overwrite the tensor in place (same address: recorded graphs keep pointing at it)"""
+        self.host[...] = np.asarray(array, dtype=self.host.dtype).reshape(self.host.shape)
+        if self.dev is not None:
+            self.dev.upload(self.host)
+
     def free(self):
         if self.dev is not None:
             self.dev.free()
