@@ -159,11 +159,23 @@ template <> __device__ __forceinline__ float dot_row<float, 4>(const float *__re
     float s = 0.f;
     int n4 = ((((uintptr_t)w | (uintptr_t)x) & 15) == 0) ? n / 4 : 0;
     const float4 *w4 = (const float4 *)w, *x4 = (const float4 *)x;
-    for (int i = lane; i < n4; i += 32) {
+    // four 16-byte loads in flight per lane, one accumulator each
+    float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int i = lane;
+    for (; i + 96 < n4; i += 128) {
+        const float4 a0 = __ldcs(w4 + i), a1 = __ldcs(w4 + i + 32), a2 = __ldcs(w4 + i + 64), a3 = __ldcs(w4 + i + 96);
+        const float4 b0 = __ldg(x4 + i), b1 = __ldg(x4 + i + 32), b2 = __ldg(x4 + i + 64), b3 = __ldg(x4 + i + 96);
+        s = fmaf(a0.x, b0.x, s); s = fmaf(a0.y, b0.y, s); s = fmaf(a0.z, b0.z, s); s = fmaf(a0.w, b0.w, s);
+        s1 = fmaf(a1.x, b1.x, s1); s1 = fmaf(a1.y, b1.y, s1); s1 = fmaf(a1.z, b1.z, s1); s1 = fmaf(a1.w, b1.w, s1);
+        s2 = fmaf(a2.x, b2.x, s2); s2 = fmaf(a2.y, b2.y, s2); s2 = fmaf(a2.z, b2.z, s2); s2 = fmaf(a2.w, b2.w, s2);
+        s3 = fmaf(a3.x, b3.x, s3); s3 = fmaf(a3.y, b3.y, s3); s3 = fmaf(a3.z, b3.z, s3); s3 = fmaf(a3.w, b3.w, s3);
+    }
+    for (; i < n4; i += 32) {
         float4 a = __ldcs(w4 + i), b = __ldg(x4 + i);
         s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
     }
-    for (int i = n4 * 4 + lane; i < n; i += 32) s = fmaf(w[i], x[i], s);
+    s = (s + s1) + (s2 + s3);
+    for (int t = n4 * 4 + lane; t < n; t += 32) s = fmaf(w[t], x[t], s);
     return s;
 }
 template <> __device__ __forceinline__ float dot_row<__half, 8>(const __half *__restrict__ w, const __half *__restrict__ x, int n, int lane)
@@ -186,25 +198,47 @@ template <> __device__ __forceinline__ float dot_row<__half, 8>(const __half *__
 
 template <class T, int VEC>
 __global__ void __launch_bounds__(256) linear_fw_kernel(const T *__restrict__ W, const T *__restrict__ x,
-                                                        const T *__restrict__ bias, T *__restrict__ y, int out, int in)
+                                                        const T *__restrict__ bias, T *__restrict__ y, int out, int in, int parts)
 {
-    const int lane = threadIdx.x & 31;
-    const int warps_per_block = blockDim.x >> 5;
-    for (int o = blockIdx.x * warps_per_block + (threadIdx.x >> 5); o < out; o += gridDim.x * warps_per_block) {
-        float s = dot_row<T, VEC>(W + (long long)o * in, x, in, lane);
+    // a row is cut into `parts` segments (a multiple of 128 elements each), one warp per segment, so that layers with
+    // few rows still put enough loads in flight; the segment sums of a row are added in segment order
+    __shared__ float seg[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rows_per_block = 8 / parts;
+    const int r = warp / parts, p = warp % parts;
+    int seg_len = ((in + parts - 1) / parts + 127) & ~127;
+    const int i0 = p * seg_len, len = max(0, min(in - i0, seg_len));
+    for (int ob = blockIdx.x * rows_per_block; ob < out; ob += gridDim.x * rows_per_block) {
+        const int o = ob + r;
+        float s = 0.f;
+        if (o < out && len > 0) s = dot_row<T, VEC>(W + (long long)o * in + i0, x + i0, len, lane);
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-        if (lane == 0) st(y + o, bias ? s + ld(bias + o) : s);
+        if (parts == 1) {
+            if (lane == 0 && o < out) st(y + o, bias ? s + ld(bias + o) : s);
+        } else {
+            if (lane == 0) seg[warp] = s;
+            __syncthreads();
+            if (lane == 0 && p == 0 && o < out) {
+                float t = 0.f;
+                for (int q = 0; q < parts; q++) t += seg[r * parts + q];
+                st(y + o, bias ? t + ld(bias + o) : t);
+            }
+            __syncthreads();
+        }
     }
 }
 
 template <class T> void linear_fw_gemv(const T *W, const T *x, const T *bias, T *y, int out, int in)
 {
-    int blocks = ceil_div(out, 8);
+    // aim at >= 8 warps per SM: split rows while that leaves segments of at least 512 elements
+    int parts = 1;
+    while (parts < 8 && (long long)out * parts < (long long)sm_count() * 8 * 4 && in / (parts * 2) >= 512) parts *= 2;
+    const int rows_per_block = 8 / parts;
+    int blocks = ceil_div(out, rows_per_block);
     int cap = sm_count() * 8;
     if (blocks > cap) blocks = cap;
-    if (sizeof(T) == 4) TL_LAUNCH((linear_fw_kernel<T, sizeof(T) == 4 ? 4 : 8>), blocks, 256, 0, W, x, bias, y, out, in);
-    else TL_LAUNCH((linear_fw_kernel<T, sizeof(T) == 4 ? 4 : 8>), blocks, 256, 0, W, x, bias, y, out, in);
+    TL_LAUNCH((linear_fw_kernel<T, sizeof(T) == 4 ? 4 : 8>), blocks, 256, 0, W, x, bias, y, out, in, parts);
 }
 
 // dW[o][i] = dy[o] * x[i]: a pure 16-byte-store stream over the out x in matrix.
@@ -307,6 +341,7 @@ __global__ void __launch_bounds__(128) linear_ig_partial_kernel(const T *__restr
     for (int q = 0; q < V; q++) acc[q] = 0.f;
     const bool vec_ok = (in % V == 0) && (((uintptr_t)W & 15) == 0);
     if (vec_ok) {
+#pragma unroll 8
         for (int o = o_begin; o < o_end; o++) {
             float g = ld(dy + o);
             if (sizeof(T) == 4) {
@@ -336,14 +371,25 @@ __global__ void __launch_bounds__(128) linear_ig_partial_kernel(const T *__restr
         if (col0 + q < in) part[(long long)slab * in + col0 + q] = acc[q];
 }
 
+// dx[i] = sum over slabs of part[slab][i], in a fixed order: 32 columns x 32 slices of the slabs per CTA
+// (slice s adds slabs s, s+32, ...; one thread per column then adds the 32 slice sums in slice order).
 template <class T>
-__global__ void linear_ig_reduce_kernel(const float *__restrict__ part, T *__restrict__ dx, int in, int slabs)
+__global__ void __launch_bounds__(1024) linear_ig_reduce_kernel(const float *__restrict__ part, T *__restrict__ dx, int in, int slabs)
 {
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= in) return;
+    __shared__ float sm[32][33];
+    const int cx = threadIdx.x & 31, sl = threadIdx.x >> 5;
+    const int i = blockIdx.x * 32 + cx;
     float s = 0.f;
-    for (int b = 0; b < slabs; b++) s += part[(long long)b * in + i];
-    st(dx + i, s);
+    if (i < in)
+        for (int b = sl; b < slabs; b += 32) s += part[(long long)b * in + i];
+    sm[sl][cx] = s;
+    __syncthreads();
+    if (sl == 0 && i < in) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 32; k++) t += sm[k][cx];
+        st(dx + i, t);
+    }
 }
 
 template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx, int out, int in)
@@ -359,7 +405,7 @@ template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx
     float *part = sc.scratch<float>((size_t)slabs * in);
     if (!part) return;
     TL_LAUNCH((linear_ig_partial_kernel<T>), dim3(col_blocks, slabs), 128, 0, W, dy, part, out, in, rows_per_slab);
-    TL_LAUNCH((linear_ig_reduce_kernel<T>), ceil_div(in, 256), 256, 0, part, dx, in, slabs);
+    TL_LAUNCH((linear_ig_reduce_kernel<T>), ceil_div(in, 32), 1024, 0, part, dx, in, slabs);
 }
 
 } // namespace tl
@@ -409,7 +455,7 @@ int trainlib_linear_fp32_bw_input_grads_noalloc(const float *W, const float *dy,
     linear_ig_partial_kernel<float><<<dim3(col_blocks, slabs), 128, 0, st>>>(W, dy, part, out, in, rows_per_slab);
     count_launch();
     if (!TL_CUDA(cudaGetLastError())) return TL_ERR_CUDA;
-    linear_ig_reduce_kernel<float><<<ceil_div(in, 256), 256, 0, st>>>(part, dx, in, slabs);
+    linear_ig_reduce_kernel<float><<<ceil_div(in, 32), 1024, 0, st>>>(part, dx, in, slabs);
     count_launch();
     if (!TL_CUDA(cudaGetLastError())) return TL_ERR_CUDA;
     return TL_OK;
