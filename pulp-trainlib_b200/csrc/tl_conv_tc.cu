@@ -34,7 +34,8 @@ struct ConvTcParams {
     int x_base, y_base;         // input coordinate of patch column 0 / row 0 for the tile at the origin
     int NT;                     // output channels per CTA (16, 32 or 64); blockIdx.y picks the slice
     int ring;                   // A buffers per converter group in use (2 or 3: 4*NT + 128*ring <= 512 TMEM columns)
-    const float *bprep;         // [Cout tiles][groups][taps][4][2*NT][4]
+    const float *w;             // filters [Cout_w][Cin_w][taps]; every CTA builds its B operand from them in its prologue
+    int Cout_w, Cin_w, flip;    // flip = input-gradient role: channels swap roles and the taps run backwards
     const float *bias;
     float *y;
     int *status;                // 0 = ok; set to a wait id when a bounded wait gave up
@@ -127,11 +128,26 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         tma_prefetch_desc(&tmap);
     }
     if (warp == 0) { tmem_alloc(tmem_slot, tmem_cols); tmem_relinquish(); }
-    // prepared weights of this CTA's output-channel slice -> shared memory (read by the tensor cores)
+    // B operand of this CTA's output-channel slice, built from the filters straight into shared memory:
+    // layout per (group g, tap): [k4 = 0..3][row r = 0..2NT-1][j = 0..3]; row r < NT holds hi(w), row r >= NT lo(w) of
+    // output channel co = slice*NT + (r mod NT) and input channel ci = g*16 + k4*4 + j.
     {
-        const float4 *src = reinterpret_cast<const float4 *>(p.bprep + (size_t)blockIdx.y * b_floats);
-        float4 *dst = reinterpret_cast<float4 *>(Bs);
-        for (size_t i = threadIdx.x; i < b_floats / 4; i += TC_THREADS) dst[i] = __ldg(src + i);
+        const int half = (int)(b_floats / 2);                  // one (hi, lo) pair per filter value
+        const int nt_shift = 31 - __clz(NT);                   // NT is 16, 32 or 64
+        for (int e = threadIdx.x; e < half; e += TC_THREADS) {
+            const int j = e & 3, rn = (e >> 2) & (NT - 1), k4 = (e >> (2 + nt_shift)) & 3;
+            const int rest = e >> (4 + nt_shift);
+            const int tap = rest % p.taps, g = rest / p.taps;
+            const int n_out = blockIdx.y * NT + rn, k_in = g * 16 + k4 * 4 + j;
+            float v = 0.f;
+            if (!p.flip) { if (n_out < p.Cout_w && k_in < p.Cin_w) v = __ldg(p.w + ((long long)n_out * p.Cin_w + k_in) * p.taps + tap); }
+            else { if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.taps + (p.taps - 1 - tap)); }
+            uint32_t hi, lo;
+            split_tf32(v, hi, lo);
+            const int base = ((rest * 4 + k4) * 2 * NT) * 4 + j;
+            Bs[base + rn * 4] = __uint_as_float(hi);
+            Bs[base + (NT + rn) * 4] = __uint_as_float(lo);
+        }
         fence_proxy_async();
     }
     tc_fence_before();
@@ -320,28 +336,6 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     if (warp == 0) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
 }
 
-// Weights -> B operand.  Output layout per (co tile, group g, tap): [k4 = 0..3][row r = 0..2NT-1][j = 0..3],
-// row r < NT holds hi(w), row r >= NT holds lo(w) of output channel co = tile*NT + (r mod NT) and input
-// channel ci = g*16 + k4*4 + j.  `flip` builds the operand of the input gradient: output channel and input
-// channel swap roles and the tap index runs backwards (filter rotated by 180 degrees).
-__global__ void conv_tc_prep_weights_kernel(const float *__restrict__ w, float *__restrict__ out, int Cout, int Cin, int taps,
-                                            int NT, int groups, int co_tiles, int flip)
-{
-    const long long total = (long long)co_tiles * groups * taps * 32 * NT;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
-        const int j = e % 4, r = (e / 4) % (2 * NT), k4 = (e / (8 * NT)) % 4;
-        const long long rest = e / (32 * NT);
-        const int tap = rest % taps, g = (rest / taps) % groups, tile = rest / ((long long)taps * groups);
-        const int n_out = tile * NT + (r % NT), k_in = g * 16 + k4 * 4 + j;
-        float v = 0.f;
-        if (!flip) { if (n_out < Cout && k_in < Cin) v = w[((long long)n_out * Cin + k_in) * taps + tap]; }
-        else { if (n_out < Cin && k_in < Cout) v = w[((long long)k_in * Cin + n_out) * taps + (taps - 1 - tap)]; }
-        uint32_t hi, lo;
-        tc::split_tf32(v, hi, lo);
-        out[e] = __uint_as_float(r < NT ? hi : lo);
-    }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -431,15 +425,10 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
 
-    const size_t bprep_floats = (size_t)co_tiles * p.groups * p.taps * 32 * NT;
-    float *bprep = sc.scratch<float>(bprep_floats);
     int *status = status_word();
-    if (!bprep || !status) return false;
-    {
-        int blocks = (int)std::min<size_t>((bprep_floats + 255) / 256, (size_t)sm_count() * 4);
-        TL_LAUNCH(conv_tc_prep_weights_kernel, blocks, 256, 0, w, bprep, Cout_w, Cin_w, p.taps, NT, p.groups, co_tiles, flip ? 1 : 0);
-    }
-    p.bprep = bprep; p.bias = bias; p.y = dst; p.status = status;
+    if (!status) return false;
+    p.w = w; p.Cout_w = Cout_w; p.Cin_w = Cin_w; p.flip = flip ? 1 : 0;
+    p.bias = bias; p.y = dst; p.status = status;
     int ctas = sm_count() / co_tiles;
     if (ctas < 1) ctas = 1;
     if (ctas > p.n_tiles) ctas = p.n_tiles;
