@@ -107,9 +107,14 @@ class ResNet8Streams(object):
         d_loss = pkg.DeviceBuffer(lib, nbytes=4 * n)
         assert net.resnet8_bind(n, d_params, d_grads, ws.ptr) == 0
 
+        graph = [None]
+
         def step():
-            net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr)
-            net.resnet8_backward()
+            if graph[0]:
+                lib.trainlib_graph_launch(graph[0])      # forward + backward, recorded once below
+            else:
+                net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr)
+                net.resnet8_backward()
             if torch is not None:
                 dist.all_reduce(t_grads)
             net.resnet8_update(LR)
@@ -119,10 +124,17 @@ class ResNet8Streams(object):
             if torch is not None:
                 torch.cuda.synchronize(); dist.barrier()
 
+        sampler = ClockSampler(lib.trainlib_device()); sampler.start()       # sampled from the warm-up on: the GPU is under the same load
         for _ in range(args.warmup):
             step()
         sync(); pkg.check(lib)
-        sampler = ClockSampler(lib.trainlib_device()); sampler.start()
+        if not getattr(args, "no_graph", False):
+            # the forward and backward pass of one step as a CUDA graph of the very same entry-point calls
+            lib.trainlib_graph_begin()
+            net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr); net.resnet8_backward()
+            graph[0] = lib.trainlib_graph_end()
+            pkg.check(lib)
+            step(); sync(); pkg.check(lib)
         l0 = lib.trainlib_kernel_launches()
         sync()
         lib.trainlib_timer_start()
@@ -178,7 +190,8 @@ class ResNet8Streams(object):
                 "data": "synthetic", "tflops": flops_step / (ms_step * 1e-3) / 1e12,
                 "config": {"workload": self.name, "streams_total": total, "streams_per_gpu": n, "lr": LR,
                            "l2": "per-step working set (%.1f GB) exceeds L2; no flush needed" % (4e-9 * net.resnet8_workspace_floats(n)),
-                           "parallelism": "streams sharded over %d rank(s); one NCCL all-reduce of %d gradient floats per step" % (world, P)},
+                           "parallelism": "streams sharded over %d rank(s); one NCCL all-reduce of %d gradient floats per step" % (world, P),
+                           "replay": "forward + backward replayed as a CUDA graph of the entry-point calls" if graph[0] else "entry-point calls"},
                 "gpu_launches": int(launches), "clocks": clocks, "mean_loss": float(loss_host.mean()),
                 "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n)},

@@ -80,6 +80,22 @@ void        trainlib_profile(int on);          /* 1 = clear and start, 0 = stop 
 int         trainlib_profile_entries(void);
 const char *trainlib_profile_entry(int i, long long *launches, double *total_ms);
 
+/* ---- layer norm and GELU beyond the reference, which has an fp32 layer-norm forward and GELU forwards only
+ * [ref: lib/include/pulp_layernorm_fp32.h:26-34, lib/sources/pulp_act_fp32.c:714].  The first seven fields are
+ * those of LayerNorm_args_fp32, so the same object also serves pulp_layerNorm_fp32_fw_cl.  Pointers are float * for
+ * the fp32 entry points and fp16 * for the fp16 ones; eps points at one value of that type.  Backward: derivative of
+ * the reference's forward formula; dx, dweight, dbias are written (not accumulated).  GELU backward: derivative of
+ * the reference's rational tanh approximation, input.diff = output.diff * gelu'(input.data). */
+struct trainlib_layernorm_args {
+    void *x; void *weight; void *bias; void *output; void *eps; int size; int step_size;
+    void *dy; void *dx; void *dweight; void *dbias;
+};
+void  trainlib_layernorm_fp16_fw_cl(void *trainlib_layernorm_args);
+void  trainlib_layernorm_fp32_bw_cl(void *trainlib_layernorm_args);
+void  trainlib_layernorm_fp16_bw_cl(void *trainlib_layernorm_args);
+void  trainlib_gelu_fp32_bw_cl(void *act_args);
+void  trainlib_gelu_fp16_bw_cl(void *act_args_fp16);
+
 /* ---- CUDA graphs.  Entry-point calls made between begin and end are recorded instead of executed (device pointers
  * only: a host pointer would need a synchronous copy); the handle replays them with one launch on the library's
  * stream.  The recorded launches keep the addresses they saw, including library scratch: run the same calls once

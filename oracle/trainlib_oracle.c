@@ -496,6 +496,28 @@ void orc_layernorm_fw(const float *x, float *y, const float *w, const float *b, 
     }
 }
 
+/* Backward of the layer norm above.  The reference has no backward for it ("parity unpinned"): this differentiates
+ * the forward formula [ref: lib/sources/pulp_layernorm_fp32.c:60-77]; tests pin it against PyTorch autograd. */
+void orc_layernorm_bw(const float *x, const float *w, const float *dy, float *dx, float *dw, float *db, int rows, int width, float eps)
+{
+    for (int j = 0; j < width; j++) { dw[j] = 0.0f; db[j] = 0.0f; }
+    for (int i = 0; i < rows; i++) {
+        const float *xr = x + (long)i * width, *gr = dy + (long)i * width;
+        float s1 = 0.0f, s2 = 0.0f;
+        for (int j = 0; j < width; j++) { s1 += xr[j]; s2 += xr[j] * xr[j]; }
+        float mean = s1 / width;
+        float sv = (float)sqrt(((s2 - 2 * s1 * mean) / width) + (mean * mean) + eps);
+        float a = 0.0f, b = 0.0f;
+        for (int j = 0; j < width; j++) { float g = w[j] * gr[j], xh = (xr[j] - mean) / sv; a += g; b += g * xh; }
+        a /= width; b /= width;
+        for (int j = 0; j < width; j++) {
+            float g = w[j] * gr[j], xh = (xr[j] - mean) / sv;
+            dx[(long)i * width + j] = (g - a - xh * b) / sv;
+            dw[j] += gr[j] * xh; db[j] += gr[j];
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ losses */
 
 /* [ref: lib/sources/pulp_losses_fp32.c:214-275] */

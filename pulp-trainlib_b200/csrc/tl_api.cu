@@ -851,6 +851,41 @@ TL_EXPORT void pulp_layerNorm_fp32_fw_cl(void *args)
     layernorm_fw<float>(x, y, w, b, a->size / a->step_size, a->step_size, eps_h);
 }
 
+// layer norm for fp16 and the backward passes (extensions: the reference stops at the fp32 forward)
+template <class T> static bool layernorm_eps(Scope &sc, void *eps_ptr, float &eps_h)
+{
+    const T *eps = sc.in((T *)eps_ptr, 1);
+    if (!sc.ok()) return false;
+    T h;
+    if (is_device_pointer(eps_ptr)) { if (trainlib_memcpy_d2h(&h, eps, sizeof(T)) != TL_OK) return false; } else h = *(T *)eps_ptr;
+    eps_h = (float)h;
+    return true;
+}
+template <class T> static void layernorm_ext(void *args, bool backward)
+{
+    auto *a = (trainlib_layernorm_args *)args;
+    TL_REQUIRE(a && a->size > 0 && a->step_size > 0 && a->size % a->step_size == 0 && a->eps, "trainlib_layernorm: size=%d step_size=%d", a ? a->size : 0, a ? a->step_size : 0);
+    const int rows = a->size / a->step_size, width = a->step_size;
+    Scope sc;
+    float eps_h = 0.f;
+    if (!layernorm_eps<T>(sc, a->eps, eps_h)) return;
+    const T *x = sc.in((T *)a->x, (size_t)a->size), *w = sc.in((T *)a->weight, (size_t)width);
+    if (!backward) {
+        const T *b = sc.in((T *)a->bias, (size_t)width);
+        T *y = sc.out((T *)a->output, (size_t)a->size);
+        if (sc.ok()) layernorm_fw<T>(x, y, w, b, rows, width, eps_h);
+    } else {
+        const T *dy = sc.in((T *)a->dy, (size_t)a->size);
+        T *dx = sc.out((T *)a->dx, (size_t)a->size), *dw = sc.out((T *)a->dweight, (size_t)width), *db = sc.out((T *)a->dbias, (size_t)width);
+        if (sc.ok()) layernorm_bw<T>(sc, x, w, dy, dx, dw, db, rows, width, eps_h);
+    }
+}
+TL_EXPORT void trainlib_layernorm_fp16_fw_cl(void *a) { layernorm_ext<__half>(a, false); }
+TL_EXPORT void trainlib_layernorm_fp32_bw_cl(void *a) { layernorm_ext<float>(a, true); }
+TL_EXPORT void trainlib_layernorm_fp16_bw_cl(void *a) { layernorm_ext<__half>(a, true); }
+TL_EXPORT void trainlib_gelu_fp32_bw_cl(void *a) { ACTB32(ACT_GELU); }
+TL_EXPORT void trainlib_gelu_fp16_bw_cl(void *a) { ACTB16(ACT_GELU); }
+
 TL_PAIR(pulp_MSELoss, pulp_MSELoss_fp16, loss_impl<F32>(a, 0, 0), loss_impl<F16>(a, 0, 0))
 TL_PAIR(pulp_MSELoss_backward, pulp_MSELoss_backward_fp16, loss_impl<F32>(a, 0, 1), loss_impl<F16>(a, 0, 1))
 TL_PAIR(pulp_CrossEntropyLoss, pulp_CrossEntropyLoss_fp16, loss_impl<F32>(a, 1, 0), loss_impl<F16>(a, 1, 0))

@@ -528,6 +528,62 @@ __global__ void __launch_bounds__(128) layernorm_fw_kernel(const T *__restrict__
     for (int j = threadIdx.x; j < width; j += blockDim.x)
         st(yp + j, __fadd_rn(__fmul_rn(__fdiv_rn(__fsub_rn(ld(xp + j), mean), sv), ld(w + j)), ld(b + j)));
 }
+// Backward of the layer norm above (the reference has no backward; derived from its forward formula):
+// xhat = (x - mean) / sv, g = w * dy;  dx = (g - mean_j(g) - xhat * mean_j(g * xhat)) / sv per row;
+// dw[j] = sum_rows dy * xhat, db[j] = sum_rows dy.  Kernel 1: one CTA per row writes dx and the row's (mean, 1/sv);
+// kernel 2: one thread per column adds over the rows in row order.
+template <class T>
+__global__ void __launch_bounds__(128) layernorm_bw_rows_kernel(const T *__restrict__ x, const T *__restrict__ w, const T *__restrict__ dy,
+                                                                T *__restrict__ dx, float2 *__restrict__ stats, int width, float eps)
+{
+    __shared__ float red[33];
+    const long long row = blockIdx.x;
+    const T *xp = x + row * width, *gp = dy + row * width;
+    float s1 = 0.f, s2 = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) { float t = ld(xp + j); s1 += t; s2 = fmaf(t, t, s2); }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    const float mean = s1 / (float)width;
+    const float sv = sqrtf(__fadd_rn(__fadd_rn(__fdiv_rn(__fsub_rn(s2, __fmul_rn(__fmul_rn(2.f, s1), mean)), (float)width), __fmul_rn(mean, mean)), eps));
+    const float inv = 1.f / sv;
+    float a = 0.f, b = 0.f;     // sum g, sum g * xhat
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float g = ld(w + j) * ld(gp + j), xh = (ld(xp + j) - mean) * inv;
+        a += g; b = fmaf(g, xh, b);
+    }
+    a = block_sum(a, red);
+    b = block_sum(b, red);
+    const float ma = a / (float)width, mb = b / (float)width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float g = ld(w + j) * ld(gp + j), xh = (ld(xp + j) - mean) * inv;
+        st(dx + row * width + j, (g - ma - xh * mb) * inv);
+    }
+    if (threadIdx.x == 0) stats[row] = make_float2(mean, inv);
+}
+template <class T>
+__global__ void __launch_bounds__(128) layernorm_bw_cols_kernel(const T *__restrict__ x, const T *__restrict__ dy, const float2 *__restrict__ stats,
+                                                                T *__restrict__ dw, T *__restrict__ db, int rows, int width)
+{
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= width) return;
+    float a = 0.f, b = 0.f;
+    for (int r = 0; r < rows; r++) {
+        const float2 st2 = stats[r];
+        const float g = ld(dy + (long long)r * width + j);
+        a = fmaf(g, (ld(x + (long long)r * width + j) - st2.x) * st2.y, a);
+        b += g;
+    }
+    st(dw + j, a); st(db + j, b);
+}
+template <class T> void layernorm_bw(Scope &sc, const T *x, const T *w, const T *dy, T *dx, T *dw, T *db, int rows, int width, float eps)
+{
+    if (rows <= 0) return;
+    float2 *stats = sc.scratch<float2>((size_t)rows);
+    if (!stats) return;
+    TL_LAUNCH((layernorm_bw_rows_kernel<T>), rows, 128, 0, x, w, dy, dx, stats, width, eps);
+    TL_LAUNCH((layernorm_bw_cols_kernel<T>), ceil_div(width, 128), 128, 0, x, dy, stats, dw, db, rows, width);
+}
+
 template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps)
 {
     if (rows <= 0) return;
@@ -810,6 +866,7 @@ template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int pad
     template void instnorm_bw_both<T>(Scope &, const T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void batchnorm_fw<T>(const T *, T *, const T *, const T *, int, int, int, int, float);                \
     template void layernorm_fw<T>(const T *, T *, const T *, const T *, int, int, float);                          \
+    template void layernorm_bw<T>(Scope &, const T *, const T *, const T *, T *, T *, T *, int, int, float);      \
     template void mse_fw<T>(const T *, const T *, T *, int, int);                                                  \
     template void mse_bw<T>(const T *, const T *, T *, int, int);                                                  \
     template void ce_fw<T>(const T *, const T *, T *, int, int);                                                   \

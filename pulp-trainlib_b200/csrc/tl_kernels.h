@@ -67,6 +67,7 @@ template <class T> void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *
                                          const T *var, const T *stdev, int n, int C, int D);
 template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps);
 template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps);
+template <class T> void layernorm_bw(Scope &sc, const T *x, const T *w, const T *dy, T *dx, T *dw, T *db, int rows, int width, float eps);
 template <class T> void mse_fw(const T *y, const T *t, T *loss, int dim, int n);
 template <class T> void mse_bw(const T *y, const T *t, T *dy, int dim, int n);
 template <class T> void ce_fw(const T *z, const T *t, T *loss, int dim, int n);

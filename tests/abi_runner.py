@@ -253,6 +253,33 @@ class AbiRunner(object):
         self.call("pulp_layerNorm_fp32_fw_cl", args)     # the reference worker runs as core 0 of 1
         return Y.get().copy()
 
+    def layernorm_ext(self, x, w, b, dy, rows, width, eps):
+        """layer norm through the library's own struct (fp16 forward and both backward passes are not in the reference)"""
+        import ctypes
+
+        class LnArgs(ctypes.Structure):
+            _fields_ = [(n, ctypes.c_void_p) for n in ("x", "weight", "bias", "output", "eps")] + [("size", ctypes.c_int), ("step_size", ctypes.c_int)] + \
+                       [(n, ctypes.c_void_p) for n in ("dy", "dx", "dweight", "dbias")]
+        X, Y, Wt, Bt, dY = self.t(x), self.zeros(*x.shape), self.t(w), self.t(b), self.t(dy)
+        dX, dW, dB, E = self.zeros(*x.shape), self.zeros(width), self.zeros(width), self.t(np.array([eps]))
+        a = LnArgs()
+        for n, t in (("x", X), ("weight", Wt), ("bias", Bt), ("output", Y), ("eps", E), ("dy", dY), ("dx", dX), ("dweight", dW), ("dbias", dB)):
+            setattr(a, n, t.arg if isinstance(t.arg, int) else t.arg.ctypes.data)
+        a.size, a.step_size = rows * width, width
+        self.keep.hold(a)
+        getattr(self.lib, "trainlib_layernorm_fp16_fw_cl" if self.half else "pulp_layerNorm_fp32_fw_cl")(ctypes.byref(a))
+        getattr(self.lib, "trainlib_layernorm_fp16_bw_cl" if self.half else "trainlib_layernorm_fp32_bw_cl")(ctypes.byref(a))
+        self.pkg.check(self.lib)
+        return dict(y=Y.get().copy(), dx=dX.get().copy(), dw=dW.get().copy(), db=dB.get().copy())
+
+    def gelu_bw(self, x, dy):
+        import ctypes
+        X, dX, Y, dY = self.t(x), self.zeros(*x.shape), self.zeros(*x.shape), self.t(dy)
+        args = self.args(self.sname("act_args"), input=self.blob(X, dX, dim=x.size, W=x.size), output=self.blob(Y, dY, dim=x.size, W=x.size), H=1, W=x.size)
+        getattr(self.lib, "trainlib_gelu_fp16_bw_cl" if self.half else "trainlib_gelu_fp32_bw_cl")(ctypes.byref(args))
+        self.pkg.check(self.lib)
+        return dX.get().copy()
+
     def loss(self, kind, y, t):
         """kind: MSELoss | CrossEntropyLoss"""
         Y, dY, T = self.t(y), self.zeros(*y.shape), self.t(t)

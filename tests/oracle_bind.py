@@ -160,6 +160,11 @@ class Oracle(object):
         self.lib.orc_layernorm_fw(_p(_ptr(x)), _p(_ptr(y)), _p(_ptr(w)), _p(_ptr(b)), _i(rows), _i(width), _f(eps))
         return y
 
+    def layernorm_bw(self, x, w, dy, rows, width, eps):
+        dx = np.zeros_like(x); dw = np.zeros(width, np.float32); db = np.zeros(width, np.float32)
+        self.lib.orc_layernorm_bw(_p(_ptr(x)), _p(_ptr(w)), _p(_ptr(dy)), _p(_ptr(dx)), _p(_ptr(dw)), _p(_ptr(db)), _i(rows), _i(width), _f(eps))
+        return dx, dw, db
+
     def mse(self, y, t):
         dy = np.zeros_like(y)
         loss = self.lib.orc_mse_fw(_p(_ptr(y)), _p(_ptr(t)), _i(y.size))

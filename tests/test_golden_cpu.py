@@ -45,3 +45,34 @@ def test_oracle_matches_torch_golden_model(oracle):
     r = oracle.mhsa(z["in_x"], z["in_wq"], z["in_wk"], z["in_wv"], z["in_bq"], z["in_bk"], z["in_bv"], z["in_wo"], z["in_dy"], L, E, F, heads)
     for k in ("y", "dx", "dwq", "dwk", "dwv", "dwo"):
         assert_close(r[k], z["out_" + k], 1e-5, "mhsa torch gm %s" % k)
+
+
+def test_oracle_layernorm_and_gelu_backward_match_autograd(oracle):
+    """the reference has no backward for layer norm and GELU: the oracle's derivatives of the reference's forward
+    formulas are pinned against PyTorch autograd of the same formulas in float64"""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(11)
+    rows, width, eps = 12, 40, 1e-5
+    x = rng.standard_normal((rows, width)).astype(np.float32); w = rng.standard_normal(width).astype(np.float32)
+    b = rng.standard_normal(width).astype(np.float32); dy = rng.standard_normal((rows, width)).astype(np.float32)
+    tx = torch.tensor(x, dtype=torch.float64, requires_grad=True); tw = torch.tensor(w, dtype=torch.float64, requires_grad=True)
+    tb = torch.tensor(b, dtype=torch.float64, requires_grad=True)
+    s1 = tx.sum(1, keepdim=True); s2 = (tx * tx).sum(1, keepdim=True); mean = s1 / width
+    sv = torch.sqrt((s2 - 2 * s1 * mean) / width + mean * mean + eps)         # the reference's variance formula
+    y = (tx - mean) / sv * tw + tb
+    y.backward(torch.tensor(dy, dtype=torch.float64))
+    assert np.abs(oracle.layernorm_fw(x, w, b, rows, width, eps) - y.detach().numpy()).max() <= 1e-5
+    dx, dw, db = oracle.layernorm_bw(x, w, dy, rows, width, eps)
+    for got, want in ((dx, tx.grad), (dw, tw.grad), (db, tb.grad)):
+        want = want.numpy()
+        assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    # GELU: 0.5 x (1 + clamp(pade_tanh(0.7978 (x + 0.044715 x^3))))
+    xg = np.linspace(-6, 6, 4001).astype(np.float32); dyg = rng.standard_normal(xg.size).astype(np.float32)
+    t = torch.tensor(xg, dtype=torch.float64, requires_grad=True)
+    u = (t * t * t * 0.044715 + t) * 0.7978; u2 = u * u
+    th = ((((u2 + 378.0) * u2 + 17325.0) * u2 + 135135.0) * u) / (((28.0 * u2 + 3150.0) * u2 + 62370.0) * u2 + 135135.0)
+    g = 0.5 * t * (1 + torch.clamp(th, -1.0, 1.0))
+    g.backward(torch.tensor(dyg, dtype=torch.float64))
+    assert np.abs(oracle.act_fw(3, xg) - g.detach().numpy()).max() <= 1e-5
+    got = oracle.act_bw(3, xg, oracle.act_fw(3, xg), dyg)
+    assert np.abs(got - t.grad.numpy()).max() <= 1e-4 * np.abs(t.grad.numpy()).max()

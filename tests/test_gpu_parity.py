@@ -393,3 +393,34 @@ def test_cuda_graph_replay_matches_direct_calls(pkg, gpulib, run, oracle):
     assert_close(Y.get(), oracle.conv2d_fw(x2, w, None, g), FP32_TOL, "graph fw")
     assert_close(dW.get(), oracle.conv2d_wg(x2, dy2, g)[0], FP32_TOL, "graph wg")
     gpulib.trainlib_graph_destroy(graph)
+
+
+@pytest.mark.parametrize("half", [False, True], ids=["fp32", "fp16"])
+@pytest.mark.parametrize("rows,width", [(128, 128), (128, 512), (7, 33)])
+def test_layernorm_forward_backward_extension(run, oracle, rows, width, half):
+    """layer norm forward (fp16 twin) and backward, which the reference lacks, against the oracle's derivative of the reference formula"""
+    rng = seeded(rows + width)
+    x = rng.standard_normal((rows, width)).astype(F); w = rng.standard_normal(width).astype(F); b = rng.standard_normal(width).astype(F)
+    dy = rng.standard_normal((rows, width)).astype(F)
+    if half:
+        x, w, b, dy = [a.astype(np.float16).astype(F) for a in (x, w, b, dy)]
+    eps = 1e-3 if half else 1e-5
+    if half:
+        eps = float(np.float16(eps))
+    got = run(device=True, half=half).layernorm_ext(x, w, b, dy, rows, width, eps)
+    tol = FP16_TOL if half else FP32_TOL
+    assert_close(got["y"].astype(F), oracle.layernorm_fw(x, w, b, rows, width, eps), tol, "layernorm y")
+    dx, dw, db = oracle.layernorm_bw(x, w, dy, rows, width, eps)
+    assert_close(got["dx"].astype(F), dx, tol, "layernorm dx")
+    assert_close(got["dw"].astype(F), dw, tol, "layernorm dw")
+    assert_close(got["db"].astype(F), db, tol, "layernorm db")
+
+
+@pytest.mark.parametrize("half", [False, True], ids=["fp32", "fp16"])
+def test_gelu_backward_extension(run, oracle, half):
+    rng = seeded(5)
+    x = np.concatenate([np.linspace(-6, 6, 1001), rng.standard_normal(3000)]).astype(F); dy = rng.standard_normal(x.size).astype(F)
+    if half:
+        x, dy = x.astype(np.float16).astype(F), dy.astype(np.float16).astype(F)
+    got = run(device=True, half=half).gelu_bw(x, dy)
+    assert_close(got.astype(F), oracle.act_bw(3, x, oracle.act_fw(3, x), dy), FP16_TOL if half else FP32_TOL, "gelu dx")
