@@ -261,6 +261,9 @@ def make_workload(cfg, pkg, lib, dtype):
     if cfg == "c3":
         from bench_layers import MhsaStep
         return MhsaStep(pkg, lib)
+    if cfg == "c4":
+        from bench_layers import MobileBertBlock
+        return MobileBertBlock(pkg, lib, dtype != "fp32")
     if cfg == "mm":
         return MmSweep(pkg, lib, dtype == "fp16")
     if cfg == "c5":
@@ -309,11 +312,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--config", default=os.environ.get("TRAINLIB_BENCH_CONFIG", "c5"))
-    ap.add_argument("--dtype", default="fp32", choices=["fp32", "fp16"])
+    ap.add_argument("--dtype", default=None, choices=["fp32", "fp16"], help="default: fp32, fp16 for config 4")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time the plain entry-point calls instead of a CUDA-graph replay (single-layer configs)")
     args = ap.parse_args()
+    if args.dtype is None:
+        args.dtype = "fp16" if args.config == "c4" else "fp32"
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     pkg = load_pkg()
     if args.impl == "reference":

@@ -177,3 +177,230 @@ class MhsaStep(_Layer):
                 "algorithmic_bytes": self.bytes, "us_per_step": 1e3 * ms,
                 "peak_note": "FFMA peak measured on this part (125 MAC/clk/SM); the 256^3 products stay on the FFMA tiles because their summation "
                              "order keeps the backward inside 1e-5 of the reference"}
+
+
+class _LnArgs(ctypes.Structure):
+    """struct trainlib_layernorm_args of include/trainlib_b200.h"""
+    _fields_ = [(n, ctypes.c_void_p) for n in ("x", "weight", "bias", "output", "eps")] + [("size", ctypes.c_int), ("step_size", ctypes.c_int)] + \
+               [(n, ctypes.c_void_p) for n in ("dy", "dx", "dweight", "dbias")]
+
+
+class MobileBertBlock(_Layer):
+    """config 4: MobileBERT-style encoder block at batch 1, forward + full backward + MSE loss, as a sequence of the
+    library's entry points on device-resident tensors (tokens row-major, [L x features]):
+
+        x1 = LN(X Wbi)                       bottleneck 512 -> 128
+        x2 = LN(x1 + MHSA(x1))               L = 128, E = F = 128, 4 heads of 32 (the attention entry points work on E x L)
+        x  = LN(x + GELU(x W1) W2)   x 4     feed-forward 128 -> 512 -> 128
+        Y  = LN(X + x Wbo)                   128 -> 512
+        loss = MSE(Y, target)
+
+    Linear layers are `mm` products (no biases), their backward two more products plus one transpose; weights ~ N(0, 0.02),
+    input and target ~ N(0, 1), layer-norm weights 1 + N(0, 0.02), biases N(0, 0.02).  `half` selects the fp16 twins."""
+    L, H, B, HEADS, NFFN, FF = 128, 512, 128, 4, 4, 512
+    LOSS_SCALE = 1024.0
+
+    def __init__(self, pkg, lib, half=True):
+        _Layer.__init__(self, pkg, lib)
+        self.half = half
+        self.dt = np.float16 if half else np.float32
+        self.es = 2 if half else 4
+        self.sfx = "_fp16" if half else ""
+        self.name = "c4_mobilebert_block_L128_h512_b128_4ffn_%s_fw_bw_batch1" % ("fp16" if half else "fp32")
+        L, H, B, FF = self.L, self.H, self.B, self.FF
+        macs = L * H * B + (4 * L * B * B + 2 * L * L * B) + self.NFFN * 2 * L * B * FF + L * B * H
+        self.flops = 3 * 2.0 * macs
+        self.bufs, self.fw, self.bw_flat = {}, [], []
+        self.params = []
+        self.use_graph = True
+
+    # ---------------------------------------------------------------- tensors
+    def _t(self, name, shape, init=None):
+        """device tensor + gradient; `init` = host array for the data"""
+        n = int(np.prod(shape))
+        if init is not None:
+            init = init.astype(np.float16).astype(F)          # the fp32 twin of the block starts from the same fp16-representable values
+        d = self.pkg.DeviceBuffer(self.lib, init.astype(self.dt)) if init is not None else self.pkg.DeviceBuffer(self.lib, nbytes=n * self.es)
+        g = self.pkg.DeviceBuffer(self.lib, nbytes=n * self.es)
+        if init is None:
+            d.zero()
+        g.zero()
+        self.bufs[name] = (d, g, tuple(shape))
+        return name
+
+    def d(self, n): return self.bufs[n][0].ptr
+    def g(self, n): return self.bufs[n][1].ptr
+    def shape(self, n): return self.bufs[n][2]
+
+    def get(self, name, grad=False):
+        d, g, shape = self.bufs[name]
+        return (g if grad else d).download(self.dt, shape).astype(np.float32)
+
+    def _blob(self, n, H=1, W=None):
+        size = int(np.prod(self.shape(n)))
+        return self.pkg.make_blob(self.keep, self.d(n), self.g(n), C=1, H=H, W=W if W is not None else size, dim=size, half=self.half)
+
+    def _call(self, lst, fn, args):
+        lst.append((getattr(self.lib, fn), args))
+
+    # ---------------------------------------------------------------- layers (each appends forward and backward calls)
+    def _mm(self, lst, A, B, C, N, K, M, trans_B):
+        a = self.pkg.make_args(self.keep, "matMul_args" + self.sfx, A=A, B=B, C=C, N=N, K=K, M=M, trans_B=trans_B, USE_BIASES=0)
+        self._call(lst, "mm" + self.sfx, a)
+
+    def _transpose(self, lst, src, dst, N, M):
+        a = self.pkg.make_args(self.keep, "transp_args" + self.sfx, in_matrix=src, out_matrix=dst, N=N, M=M)
+        self._call(lst, "transpose_matrix" + self.sfx, a)
+
+    def linear(self, x, w, y):
+        L, K = self.shape(x); M = self.shape(w)[1]
+        self._mm(self.fw, self.d(x), self.d(w), self.d(y), L, K, M, 0)
+        bw = []
+        self._mm(bw, self.g(y), self.d(w), self.g(x), L, M, K, 1)                 # dX = dY W^T
+        xt = self._t(x + "_T_for_" + w, (K, L))
+        self._transpose(bw, self.d(x), self.d(xt), L, K)
+        self._mm(bw, self.d(xt), self.g(y), self.g(w), K, L, M, 0)                # dW = X^T dY
+        return bw
+
+    def layernorm(self, x, w, b, y):
+        rows, width = self.shape(x)
+        a = _LnArgs()
+        a.x, a.weight, a.bias, a.output, a.eps = self.d(x), self.d(w), self.d(b), self.d(y), self.eps_host.ctypes.data
+        a.size, a.step_size = rows * width, width
+        a.dy, a.dx, a.dweight, a.dbias = self.g(y), self.g(x), self.g(w), self.g(b)
+        self.keep.hold(a)
+        self._call(self.fw, "trainlib_layernorm_fp16_fw_cl" if self.half else "pulp_layerNorm_fp32_fw_cl", a)
+        bw = []
+        self._call(bw, "trainlib_layernorm_fp16_bw_cl" if self.half else "trainlib_layernorm_fp32_bw_cl", a)
+        return bw
+
+    def gelu(self, x, y):
+        n = int(np.prod(self.shape(x)))
+        a = self.pkg.make_args(self.keep, "act_args" + self.sfx, input=self._blob(x), output=self._blob(y), H=1, W=n)
+        self._call(self.fw, "pulp_gelu_fp16_fw_cl" if self.half else "pulp_gelu_tanh_approx_fp32_fw_cl", a)
+        bw = []
+        self._call(bw, "trainlib_gelu_fp16_bw_cl" if self.half else "trainlib_gelu_fp32_bw_cl", a)
+        return bw
+
+    def residual(self, skip, lout, out):
+        """out = skip + lout.  Backward in two parts: `copy` (lout.diff = out.diff) runs before the branch's backward, `add`
+        (skip.diff += out.diff) after the branch has written skip.diff."""
+        a = self.pkg.make_args(self.keep, "SkipConn_args" + self.sfx, skip=self._blob(skip), lout=self._blob(lout), output=self._blob(out), skip_in_grad=0)
+        r = "fp16" if self.half else "fp32"
+        self._call(self.fw, "pulp_residualconn_%s_fw" % r, a)
+        copy, add = [], []
+        self._call(copy, "pulp_residualconn_%s_bw" % r, a)
+        self._call(add, "pulp_sumnode_%s_bw" % r, a)
+        return copy, add
+
+    def mhsa(self, x, y):
+        """x, y: [L x E] row-major; the attention entry points want E x L, so both are transposed around the call"""
+        L, E = self.shape(x); Fd, h = E, self.HEADS
+        xt, yt = self._t(x + "_T", (E, L)), self._t(y + "_T", (E, L))
+        names = {}
+        for n, shp in (("q", (Fd, L)), ("k", (Fd, L)), ("v", (Fd, L)), ("att", (Fd, L)), ("sm", (h, L, L))):
+            names[n] = self._t("mhsa_" + n, shp)
+        zb = self._t("mhsa_zero_bias", (Fd,))
+        tmax = max(L * L, E * Fd, L * Fd, E * L)
+        temp, grad, maxes, sums = self._t("mhsa_temp", (tmax,)), self._t("mhsa_grad", (L * L,)), self._t("mhsa_maxes", (L,)), self._t("mhsa_sums", (L,))
+        b2 = lambda n, Hh, Ww: self.pkg.make_blob(self.keep, self.d(n), self.g(n), C=1, H=Hh, W=Ww, half=self.half)
+        bias = lambda: self.pkg.make_blob(self.keep, self.d(zb), self.g(zb), dim=Fd, W=Fd, half=self.half)
+        a = self.pkg.make_args(self.keep, "Mhsa_args" + self.sfx, input=b2(xt, L, E), n_heads=h, output=b2(yt, L, E),
+                               coeff_in_q=b2("Wq", Fd, E), coeff_in_k=b2("Wk", Fd, E), coeff_in_v=b2("Wv", Fd, E), coeff_out=b2("Wo", E, Fd),
+                               bias_in_q=bias(), bias_in_k=bias(), bias_in_v=bias(),
+                               q=b2(names["q"], L, Fd), k=b2(names["k"], L, Fd), v=b2(names["v"], L, Fd), attention_map=b2(names["att"], L, Fd),
+                               temp_buffer=self.d(temp), grad=self.d(grad), softmax_buffer=b2(names["sm"], h, L * L), maxes=self.d(maxes), sums=self.d(sums),
+                               opt_matmul_type_fw=0, opt_matmul_type_wg=0, opt_matmul_type_ig=0)
+        self._transpose(self.fw, self.d(x), self.d(xt), L, E)
+        self._call(self.fw, "pulp_mhsa_fp16_fw_cl" if self.half else "pulp_mhsa_fp32_fw_cl", a)
+        self._transpose(self.fw, self.d(yt), self.d(y), E, L)
+        bw = []
+        self._transpose(bw, self.g(y), self.g(yt), L, E)
+        zero = self.pkg.make_args(self.keep, "transp_args" + self.sfx, in_matrix=self.d("zeros_EL"), out_matrix=self.g(xt), N=1, M=E * L)
+        self._call(bw, "transpose_matrix" + self.sfx, zero)                       # the backward accumulates into input.diff: clear it (copy of zeros)
+        self._call(bw, "pulp_mhsa_fp16_bw_cl" if self.half else "pulp_mhsa_fp32_bw_cl", a)
+        self._transpose(bw, self.g(xt), self.g(x), E, L)
+        return bw
+
+    # ---------------------------------------------------------------- graph of the block
+    def setup_device(self):
+        rng = np.random.default_rng(4)
+        L, H, B, FF = self.L, self.H, self.B, self.FF
+        rnd = lambda *s: np.float32(0.02) * rng.standard_normal(s).astype(F)
+        P = lambda name, arr: (self._t(name, arr.shape, arr), self.params.append(name))[0]
+        self.eps_host = np.array([1e-3], self.dt)          # read on the host by the layer-norm entry points
+        self._t("zeros_EL", (B * L,))
+        X = self._t("X", (L, H), rng.standard_normal((L, H)).astype(F))
+        T = self._t("target", (L, H), rng.standard_normal((L, H)).astype(F))
+        P("Wbi", rnd(H, B)); P("Wbo", rnd(B, H))
+        for n in ("Wq", "Wk", "Wv", "Wo"):
+            P(n, rnd(B, B))
+        ln = lambda name, width: (P(name + "_w", 1 + rnd(width)), P(name + "_b", rnd(width)))
+        # forward calls are appended to self.fw as the layers are declared; every layer hands back its backward calls, which are
+        # put together below in reverse order (a residual's copy before its branch, its add after it)
+        t0, x1 = self._t("t0", (L, B)), self._t("x1", (L, B))
+        bw_lin_bi = self.linear(X, "Wbi", t0); w, b = ln("ln1", B); bw_ln1 = self.layernorm(t0, w, b, x1)
+        att, r1, x = self._t("att", (L, B)), self._t("r1", (L, B)), self._t("x2", (L, B))
+        bw_mhsa = self.mhsa(x1, att)
+        res1_copy, res1_add = self.residual(x1, att, r1)
+        w, b = ln("ln2", B); bw_ln2 = self.layernorm(r1, w, b, x)
+        ffn_bw = []
+        for f in range(self.NFFN):
+            P("W1_%d" % f, rnd(B, FF)); P("W2_%d" % f, rnd(FF, B))
+            h, gl, o, r, xn = [self._t("%s_%d" % (n, f), sh) for n, sh in (("h", (L, FF)), ("gelu", (L, FF)), ("o", (L, B)), ("r", (L, B)), ("xf", (L, B)))]
+            b1 = self.linear(x, "W1_%d" % f, h); bg = self.gelu(h, gl); b2 = self.linear(gl, "W2_%d" % f, o)
+            cp, ad = self.residual(x, o, r)
+            w, b = ln("lnf_%d" % f, B); bl = self.layernorm(r, w, b, xn)
+            ffn_bw.append(bl + cp + b2 + bg + b1 + ad)
+            x = xn
+        t1, r2, Y = self._t("t1", (L, H)), self._t("r2", (L, H)), self._t("Y", (L, H))
+        bw_lin_bo = self.linear(x, "Wbo", t1)
+        reso_copy, reso_add = self.residual(X, t1, r2)
+        w, b = ln("ln_out", H); bw_ln_out = self.layernorm(r2, w, b, Y)
+        self._t("loss", (1,))
+        la = self.pkg.make_args(self.keep, "loss_args" + self.sfx, output=self._blob(Y), target=self.d(T), wr_loss=self.d("loss"))
+        self._call(self.fw, "pulp_MSELoss" + self.sfx, la)
+        bw_loss = []
+        self._call(bw_loss, "pulp_MSELoss_backward" + self.sfx, la)
+        # loss scaling, as fp16 training does: dL/dY = 2 (y - t) / 65536 is about 3e-5, inside the fp16 subnormal range, and the
+        # attention gradients behind it would underflow; every gradient below is LOSS_SCALE times the true one
+        n_y = int(np.prod(self.shape(Y)))
+        sa = self.pkg.make_args(self.keep, "scalar_mul_args" + self.sfx, input=self.g(Y), scalar=self.LOSS_SCALE, dim=n_y)
+        self._call(bw_loss, "pulp_scalar_mul_%s_cl" % ("fp16" if self.half else "fp32"), sa)
+        flat = bw_loss + bw_ln_out + reso_copy + bw_lin_bo
+        for piece in reversed(ffn_bw):
+            flat += piece
+        flat += bw_ln2 + res1_copy + bw_mhsa + res1_add + bw_ln1 + bw_lin_bi + reso_add
+        self.bw_flat = flat
+        self.flush = self.pkg.DeviceBuffer(self.lib, nbytes=256 << 20)
+
+    def step_device(self):
+        for fn, a in self.fw:
+            fn(ctypes.byref(a))
+        for fn, a in self.bw_flat:
+            fn(ctypes.byref(a))
+
+    # the block has no host-pointer form here: its end-to-end number uploads the input and target and reads back the loss
+    def setup_host(self, lib):
+        if not hasattr(lib, "trainlib_malloc_host"):
+            raise SystemExit("config 4 has no reference arm: the reference has no backward for layer norm and GELU")
+        from bench import pinned_like
+        self.hX = pinned_like(self.pkg, lib, self.get("X").astype(self.dt)); self.hT = pinned_like(self.pkg, lib, self.get("target").astype(self.dt))
+        self.hloss = pinned_like(self.pkg, lib, np.zeros(1, self.dt))
+        self.h2d = self.hX.nbytes + self.hT.nbytes; self.d2h = self.hloss.nbytes
+
+    def step_host(self, lib):
+        lib.trainlib_memcpy_h2d(self.d("X"), self.hX.ctypes.data, self.hX.nbytes)
+        lib.trainlib_memcpy_h2d(self.d("target"), self.hT.ctypes.data, self.hT.nbytes)
+        self.step_device()
+        lib.trainlib_memcpy_d2h(self.hloss.ctypes.data, self.d("loss"), self.hloss.nbytes)
+
+    def metric(self, ms):
+        return {"metric": "fw_bw_tflops", "unit": "TFLOP/s", "value": self.flops / (ms * 1e-3) / 1e12}
+
+    def roofline(self, ms, pk):
+        tf = self.flops / (ms * 1e-3) / 1e12
+        peak = pk["bf16_tflops_sustained"] if self.half else pk["bf16_tflops_sustained"] / 6.0
+        return {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "traffic": None, "peak_source": pk["source"],
+                "kernel": "whole block: %d forward + %d backward entry-point calls" % (len(self.fw), len(self.bw_flat)), "algorithmic_flops": self.flops,
+                "us_per_step": 1e3 * ms, "peak_note": "products of 128 x 128..512 x 128..512: launch-latency bound, far below any roofline"}

@@ -837,30 +837,30 @@ TL_EXPORT void pulp_batch_norm_fp32_fw_cl(void *args)
     batchnorm_fw<float>(x, y, w, b, n, a->B, a->C, a->H * a->W, eps_h);
 }
 TL_EXPORT void pulp_batch_norm_parallelized_fp32_fw_cl(void *a) { pulp_batch_norm_fp32_fw_cl(a); }
+template <class T> static bool layernorm_eps(Scope &sc, void *eps_ptr, float &eps_h)
+{
+    // eps is consumed on the host: a host pointer is read in place (no staging, no synchronisation, so the call can be
+    // recorded into a CUDA graph); a device pointer costs one blocking copy
+    (void)sc;
+    T h;
+    if (is_device_pointer(eps_ptr)) { if (trainlib_memcpy_d2h(&h, eps_ptr, sizeof(T)) != TL_OK) return false; } else h = *(T *)eps_ptr;
+    eps_h = (float)h;
+    return true;
+}
 TL_EXPORT void pulp_layerNorm_fp32_fw_cl(void *args)
 {
     auto *a = (LayerNorm_args_fp32 *)args;
     TL_REQUIRE(a->size > 0 && a->step_size > 0 && a->size % a->step_size == 0 && a->eps, "pulp_layerNorm: size=%d step_size=%d", a->size, a->step_size);
     Scope sc;
     const float *x = sc.in(a->x, (size_t)a->size), *w = sc.in(a->weight, (size_t)a->step_size), *b = sc.in(a->bias, (size_t)a->step_size);
-    const float *eps = sc.in(a->eps, 1);
     float *y = sc.out(a->output, (size_t)a->size);
     if (!sc.ok()) return;
     float eps_h = 0.f;
-    if (is_device_pointer(a->eps)) { if (trainlib_memcpy_d2h(&eps_h, eps, sizeof(float)) != TL_OK) return; } else eps_h = a->eps[0];
+    if (!layernorm_eps<float>(sc, a->eps, eps_h)) return;
     layernorm_fw<float>(x, y, w, b, a->size / a->step_size, a->step_size, eps_h);
 }
 
 // layer norm for fp16 and the backward passes (extensions: the reference stops at the fp32 forward)
-template <class T> static bool layernorm_eps(Scope &sc, void *eps_ptr, float &eps_h)
-{
-    const T *eps = sc.in((T *)eps_ptr, 1);
-    if (!sc.ok()) return false;
-    T h;
-    if (is_device_pointer(eps_ptr)) { if (trainlib_memcpy_d2h(&h, eps, sizeof(T)) != TL_OK) return false; } else h = *(T *)eps_ptr;
-    eps_h = (float)h;
-    return true;
-}
 template <class T> static void layernorm_ext(void *args, bool backward)
 {
     auto *a = (trainlib_layernorm_args *)args;

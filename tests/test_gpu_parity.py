@@ -424,3 +424,28 @@ def test_gelu_backward_extension(run, oracle, half):
         x, dy = x.astype(np.float16).astype(F), dy.astype(np.float16).astype(F)
     got = run(device=True, half=half).gelu_bw(x, dy)
     assert_close(got.astype(F), oracle.act_bw(3, x, oracle.act_fw(3, x), dy), FP16_TOL if half else FP32_TOL, "gelu dx")
+
+
+def test_mobilebert_block_fp16_against_its_fp32_twin(pkg, gpulib):
+    """config 4: the block of bench_layers.MobileBertBlock (forward, full backward, MSE) in fp16 against the same call
+    sequence through the fp32 entry points on the same fp16-representable parameters and inputs.  Every primitive of the
+    sequence has its own oracle test above; this one checks the composition and the fp16 error budget (1e-2)."""
+    import bench_layers
+    runs = {}
+    for half in (False, True):
+        blk = bench_layers.MobileBertBlock(pkg, gpulib, half=half)
+        blk.setup_device()
+        blk.step_device()
+        gpulib.trainlib_synchronize(); pkg.check(gpulib)
+        runs[half] = dict(loss=blk.get("loss"), Y=blk.get("Y"), dX=blk.get("X", grad=True), dWbi=blk.get("Wbi", grad=True), dW1=blk.get("W1_0", grad=True),
+                          dW2=blk.get("W2_3", grad=True), dWq=blk.get("Wq", grad=True), dWo=blk.get("Wo", grad=True), dln=blk.get("ln2_w", grad=True), x2=blk.get("x2"))
+    assert gpulib.trainlib_tc_status() == 0
+    for k in runs[False]:
+        assert np.abs(runs[False][k]).max() > 0, "%s is all zero: the call sequence did not reach it" % k
+        assert_close(runs[True][k], runs[False][k], FP16_TOL, "block %s (fp16 vs fp32)" % k)
+    # the fp32 twin's forward against numpy for the parts that need no reference approximations: first bottleneck + layer norm
+    blk = bench_layers.MobileBertBlock(pkg, gpulib, half=False); blk.setup_device(); blk.step_device(); gpulib.trainlib_synchronize()
+    X, Wbi, w, b = blk.get("X"), blk.get("Wbi"), blk.get("ln1_w"), blk.get("ln1_b")
+    t0 = X.astype(np.float64) @ Wbi.astype(np.float64)
+    m = t0.mean(1, keepdims=True); v = ((t0 - m) ** 2).mean(1, keepdims=True)
+    assert_close(blk.get("x1"), ((t0 - m) / np.sqrt(v + 1e-3) * w + b).astype(F), 1e-4, "bottleneck + layer norm vs numpy")
