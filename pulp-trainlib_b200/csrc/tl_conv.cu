@@ -294,7 +294,37 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
             return true;
         }
     }
-    // strided: spread dY onto the input grid (zeros between the samples), then the same stride-1 convolution.
+    // strided, general filter: one launch per parity class of dX.  Pixels (sh*i + ph, sw*j + pw) only see the filter taps
+    // kh = r + sh*m with r = (ph + padU) mod sh, and those taps read dY rows i + q - m with q = (ph + padU) / sh: a dense
+    // stride-1 convolution of dY with an (m_max+1)-row window, written to every sh-th row of dX.  No zeros are multiplied.
+    if (g.sh == g.sw && g.sh >= 2 && g.sh <= 4 && gemm_path() != 1) {
+        ConvTcClass cls[16];
+        int Hc[16], Wc[16], Ah[16], Aw[16], pu[16], pl[16], ncls = 0;
+        bool ok = true;
+        for (int ph = 0; ph < g.sh && ok; ph++)
+            for (int pw = 0; pw < g.sw && ok; pw++) {
+                const int rh = (ph + g.padU) % g.sh, qh = (ph + g.padU) / g.sh, rw = (pw + g.padL) % g.sw, qw = (pw + g.padL) / g.sw;
+                if (rh >= g.Hk || rw >= g.Wk || ph >= g.Hin || pw >= g.Win) { ok = false; break; }
+                const int mh = (g.Hk - 1 - rh) / g.sh, mw = (g.Wk - 1 - rw) / g.sw;
+                if (mh - qh < 0 || mw - qw < 0) { ok = false; break; }
+                ConvTcClass &c = cls[ncls];
+                c.kstep = g.sh; c.kh_r = rh; c.kh_m = mh; c.kw_r = rw; c.kw_m = mw; c.w_Hk = g.Hk; c.w_Wk = g.Wk;
+                c.oH = g.Hin; c.oW = g.Win; c.osy = g.sh; c.osx = g.sw; c.oy0 = ph; c.ox0 = pw;
+                Hc[ncls] = (g.Hin - ph + g.sh - 1) / g.sh; Wc[ncls] = (g.Win - pw + g.sw - 1) / g.sw;
+                Ah[ncls] = mh + 1; Aw[ncls] = mw + 1; pu[ncls] = mh - qh; pl[ncls] = mw - qw;
+                ok = conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, Hc[ncls], Wc[ncls], Ah[ncls], Aw[ncls], 1, 1,
+                                 pu[ncls], pl[ncls], g.Cout, g.Cin, true, true, &c);
+                ncls++;
+            }
+        if (ok) {
+            for (int i = 0; i < ncls; i++)
+                if (!conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, Hc[i], Wc[i], Ah[i], Aw[i], 1, 1, pu[i], pl[i],
+                                 g.Cout, g.Cin, true, false, &cls[i]))
+                    return false;       // (cannot happen after the dry runs; the FFMA kernel then recomputes all of dX)
+            return true;
+        }
+    }
+    // otherwise: spread dY onto the input grid (zeros between the samples), then the same stride-1 convolution.
     // The tensor cores do sh*sw times the useful work, which still beats the FFMA kernel by a wide margin.
     if (g.Win % 4 != 0 || (long long)(g.Hout - 1) * g.sh >= g.Hin || (long long)(g.Wout - 1) * g.sw >= g.Win) return false;
     if (!conv_tc_run(sc, nullptr, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hin, g.Win, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,

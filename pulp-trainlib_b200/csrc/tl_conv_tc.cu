@@ -36,6 +36,12 @@ struct ConvTcParams {
     int ring;                   // A buffers per converter group in use (2 or 3: 4*NT + 128*ring <= 512 TMEM columns)
     const float *w;             // filters [Cout_w][Cin_w][taps]; every CTA builds its B operand from them in its prologue
     int Cout_w, Cin_w, flip;    // flip = input-gradient role: channels swap roles and the taps run backwards
+    // Output placement: output pixel (ho, wo) of the tile grid lands at (ho*osy + oy0, wo*osx + ox0) of an oH x oW plane.
+    int oH, oW, osy, osx, oy0, ox0;
+    // Strided input gradient, one parity class of dX per launch (cls = 1): the "filter" walked by the kernel is the
+    // window of dY positions that reach this class; window position (a, b) multiplies filter tap
+    // kh = kh_r + kstep*(kh_m - a), kw = kw_r + kstep*(kw_m - b) of the full w_Hk x w_Wk filter (channels swapped as for flip).
+    int cls, kstep, kh_r, kh_m, kw_r, kw_m, w_Wk, w_taps;
     const float *bias;
     float *y;
     int *status;                // 0 = ok; set to a wait id when a bounded wait gave up
@@ -140,7 +146,12 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             const int tap = rest % p.taps, g = rest / p.taps;
             const int n_out = blockIdx.y * NT + rn, k_in = g * 16 + k4 * 4 + j;
             float v = 0.f;
-            if (!p.flip) { if (n_out < p.Cout_w && k_in < p.Cin_w) v = __ldg(p.w + ((long long)n_out * p.Cin_w + k_in) * p.taps + tap); }
+            if (p.cls) {
+                const int a = tap / p.Wk, b = tap % p.Wk;
+                const int kh = p.kh_r + p.kstep * (p.kh_m - a), kw = p.kw_r + p.kstep * (p.kw_m - b);
+                if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.w_taps + kh * p.w_Wk + kw);
+            }
+            else if (!p.flip) { if (n_out < p.Cout_w && k_in < p.Cin_w) v = __ldg(p.w + ((long long)n_out * p.Cin_w + k_in) * p.taps + tap); }
             else { if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.taps + (p.taps - 1 - tap)); }
             uint32_t hi, lo;
             split_tf32(v, hi, lo);
@@ -287,7 +298,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         const int tp = p.TH * p.TW;
         const int sl = m / tp, ph = (m % tp) / p.TW, pw = m % p.TW;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        const long long plane = (long long)p.Hout * p.Wout;
+        const long long plane = (long long)p.oH * p.oW;
         const uint32_t zero8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         // both accumulator buffers start from zero; the first "d_empty" phase completes once that is done
         for (int c0 = 0; c0 < 2 * N2; c0 += 8) tmem_st8(d_col0 + lane_addr + c0, zero8);
@@ -302,8 +313,9 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             if (!warp_wait_or_abort(&d_full[dbuf], (tcnt >> 1) & 1, abort_flag, p.status, 6, lane)) break;
             tc_fence_after();
             const int s = s0 + sl, ho = th0 + ph, wo = tw0 + pw;
-            const bool valid = (s < p.n) && (ho < p.Hout) && (wo < p.Wout);
-            float *yp = p.y + ((long long)s * p.Cout + co0) * plane + (long long)ho * p.Wout + wo;
+            const int oy = ho * p.osy + p.oy0, ox = wo * p.osx + p.ox0;
+            const bool valid = (s < p.n) && (ho < p.Hout) && (wo < p.Wout) && (oy < p.oH) && (ox < p.oW);
+            float *yp = p.y + ((long long)s * p.Cout + co0) * plane + (long long)oy * p.oW + ox;
             const uint32_t d_addr = d_col0 + dbuf * N2 + lane_addr;
             for (int c0 = 0; c0 < NT; c0 += 8) {
                 uint32_t a[8], b[8];
@@ -369,7 +381,7 @@ void *tc_encode_tiled_fn() { return (void *)encode_fn(); }
 // src: [n][C_src][H_src][W_src], dst: [n][C_dst][H_dst][W_dst]; `flip` = input-gradient role (stride must be 1).
 bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
                  int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
-                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run)
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run, const ConvTcClass *cls)
 {
     if (gemm_path() == 1) return false;
     EncodeTiledFn enc = encode_fn();
@@ -428,6 +440,13 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     int *status = status_word();
     if (!status) return false;
     p.w = w; p.Cout_w = Cout_w; p.Cin_w = Cin_w; p.flip = flip ? 1 : 0;
+    p.oH = H_dst; p.oW = W_dst; p.osy = p.osx = 1; p.oy0 = p.ox0 = 0;
+    p.cls = 0; p.kstep = 1; p.kh_r = p.kh_m = p.kw_r = p.kw_m = 0; p.w_Wk = Wk; p.w_taps = Hk * Wk;
+    if (cls) {
+        p.cls = 1; p.kstep = cls->kstep; p.kh_r = cls->kh_r; p.kh_m = cls->kh_m; p.kw_r = cls->kw_r; p.kw_m = cls->kw_m;
+        p.w_Wk = cls->w_Wk; p.w_taps = cls->w_Hk * cls->w_Wk;
+        p.oH = cls->oH; p.oW = cls->oW; p.osy = cls->osy; p.osx = cls->osx; p.oy0 = cls->oy0; p.ox0 = cls->ox0;
+    }
     p.bias = bias; p.y = dst; p.status = status;
     int ctas = sm_count() / co_tiles;
     if (ctas < 1) ctas = 1;
@@ -447,6 +466,12 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     case 1360: TL_TC_LAUNCH(1360); break;    // 17 x 20 (stride 2, 8 output columns)
     case 1920: TL_TC_LAUNCH(1920); break;    // 15 x 32 (1x1 stride 2)
     case 512: TL_TC_LAUNCH(512); break;      // 4 x 32 and 8 x 16 (1x1 stride 1)
+    case 720: TL_TC_LAUNCH(720); break;      // parity classes of a strided input gradient, 16 x 16 class grid: 9 x 20,
+    case 576: TL_TC_LAUNCH(576); break;      //   9 x 16 (and 8 x 20 = 640, 8 x 16 = 512 above)
+    case 432: TL_TC_LAUNCH(432); break;      // 8 x 8 class grid: 9 x 12,
+    case 384: TL_TC_LAUNCH(384); break;      //   8 x 12,
+    case 288: TL_TC_LAUNCH(288); break;      //   9 x 8,
+    case 256: TL_TC_LAUNCH(256); break;      //   8 x 8
     default: TL_TC_LAUNCH(0); break;
     }
 #undef TL_TC_LAUNCH

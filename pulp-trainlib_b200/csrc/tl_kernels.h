@@ -42,9 +42,12 @@ template <class T> void conv_fw(Scope &sc, const ConvGeom &g, const T *x, const 
 template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const T *dy, T *dw, T *dbias);
 template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx);
 // tensor-core implicit GEMM (tl_conv_tc.cu); false = geometry does not qualify, use the FFMA kernels
+// One parity class of a strided input gradient as a stride-1 convolution over dY (see tl_conv_tc.cu)
+struct ConvTcClass { int kstep, kh_r, kh_m, kw_r, kw_m, w_Hk, w_Wk; int oH, oW, osy, osx, oy0, ox0; };
 bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
                  int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
-                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false);
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false,
+                 const ConvTcClass *cls = nullptr);
 int conv_tc_status();
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
                                int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
