@@ -50,6 +50,13 @@ def test_library_exports_every_declared_symbol(pkg):
            "pi_perf_conf", "pi_perf_reset", "pi_perf_start", "pi_perf_stop", "pi_perf_read", "pi_l2_malloc", "pi_l2_free",
            "fastexp_gist", "q_rsqrt", "verify_tensor"]
     assert not [f for f in ext if not hasattr(lib, f)]
+    # every function include/trainlib_b200.h declares (the extensions: runtime, graphs, overlapped upload, layer norm / GELU backward)
+    import re
+    hdr = open(os.path.join(ROOT, "include", "trainlib_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    declared = sorted(set(re.findall(r"\b(trainlib_\w+)\s*\(", hdr)))
+    assert len(declared) >= 40, declared
+    assert not [f for f in declared if not hasattr(lib, f)], [f for f in declared if not hasattr(lib, f)]
 
 
 def test_host_scalars_and_state(pkg):
