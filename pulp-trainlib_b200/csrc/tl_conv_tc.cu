@@ -61,8 +61,11 @@ struct ConvTcParams {
 // parity wait would alias otherwise).
 static constexpr int GROUPS = 4;            // converter groups = MMA issuers
 static constexpr int RING = 2;              // most A buffers per group (32 TMEM columns each: 16 hi + 16 lo); a third one bought nothing
-static constexpr int FIRST_ISSUER = 2, FIRST_CONV = FIRST_ISSUER + GROUPS, FIRST_EPI = FIRST_CONV + 4 * GROUPS;
-static constexpr int TC_THREADS = (FIRST_EPI + 4) * 32;
+// Warp roles, lightest first: the warp schedulers favour the oldest ready warp, and a converter warp is ready almost
+// all the time.  With the epilogue warps last in the CTA (the first layout of this kernel) they were starved: the
+// issuers spent a quarter of their time waiting for an accumulator buffer to be released.
+static constexpr int FIRST_EPI = 0, FIRST_ISSUER = 4, FIRST_CONV = FIRST_ISSUER + GROUPS, TMA_WARP = FIRST_CONV + 4 * GROUPS;
+static constexpr int TC_THREADS = (TMA_WARP + 1) * 32;
 static constexpr int PS = 3;                // raw patch ring
 static constexpr int NA = GROUPS * RING;    // A buffers in tensor memory
 
@@ -133,7 +136,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         fence_barrier_init();
         tma_prefetch_desc(&tmap);
     }
-    if (warp == 0) { tmem_alloc(tmem_slot, tmem_cols); tmem_relinquish(); }
+    if (warp == TMA_WARP) { tmem_alloc(tmem_slot, tmem_cols); tmem_relinquish(); }
     // B operand of this CTA's output-channel slice, built from the filters straight into shared memory:
     // layout per (group g, tap): [k4 = 0..3][row r = 0..2NT-1][j = 0..3]; row r < NT holds hi(w), row r >= NT lo(w) of
     // output channel co = slice*NT + (r mod NT) and input channel ci = g*16 + k4*4 + j.
@@ -169,7 +172,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     const int co0 = blockIdx.y * NT;
     const int tiles_per_stream_group = p.tiles_w * p.tiles_h;
 
-    if (warp == 0) {
+    if (warp == TMA_WARP) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t pc = 0;
@@ -183,9 +186,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                 }
             }
         }
-    } else if (warp == 1) {
-        // spare warp
-    } else if (warp < FIRST_CONV) {
+    } else if (warp >= FIRST_ISSUER && warp < FIRST_CONV) {
         // ------------------------------------------------------------ MMA issuers
         if (lane == 0) {
             const int me = warp - FIRST_ISSUER;
@@ -193,6 +194,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             const uint32_t bs_addr = smem_u32(Bs);
             const uint32_t lbo = N2 * 16, sbo = 128;
             const uint32_t tap_bytes = 32u * NT * 4u;
+            const uint64_t bdesc0 = smem_desc_kmajor(bs_addr, lbo, sbo);
             uint32_t tcnt = 0;
             int rb = 0; uint32_t rph = 0;       // ring position and phase of this group's next chunk
             uint32_t cbase = 0;                 // chunks dealt so far (all groups), mod GROUPS
@@ -209,10 +211,11 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                         if (++rb == p.ring) { rb = 0; rph ^= 1u; }
                         tc_fence_after();
                         const uint32_t a_addr = a_col0 + abuf * 32;
-                        const uint32_t b_tap = bs_addr + (uint32_t)(g * p.taps + tap) * tap_bytes;
+                        // descriptor of this tap's weights: the start-address field (bits 0..13, units of 16 bytes) moves, the rest stays
+                        const uint64_t b_tap = bdesc0 + (uint64_t)(((uint32_t)(g * p.taps + tap) * tap_bytes) >> 4);
 #pragma unroll
                         for (int kk = 0; kk < 2; kk++) {
-                            const uint64_t bdesc = smem_desc_kmajor(b_tap + kk * 2 * lbo, lbo, sbo);
+                            const uint64_t bdesc = b_tap + (uint64_t)((kk * 2 * lbo) >> 4);
                             mma_tf32_ts(d_addr, a_addr + kk * 8, bdesc, idesc_2n, 1u);
                             mma_tf32_ts(d_addr, a_addr + 16 + kk * 8, bdesc, idesc_n, 1u);
                         }
@@ -223,7 +226,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                 mma_commit(&d_full[dbuf]);       // one arrival per issuer: the tile is complete when all have landed
             }
         }
-    } else if (warp < FIRST_EPI) {
+    } else if (warp >= FIRST_CONV) {
         // ------------------------------------------------------------ converters: raw patch -> (hi, lo) -> tensor memory
         // Warp (q, j): q = TMEM lane quarter (32 pixels), j = 0..3 takes the taps j, j+4, j+8, ... of every
         // channel group, all 16 channels of the group per tap.
@@ -300,6 +303,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         const long long plane = (long long)p.oH * p.oW;
         const uint32_t zero8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const uint32_t zero16[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
         // both accumulator buffers start from zero; the first "d_empty" phase completes once that is done
         for (int c0 = 0; c0 < 2 * N2; c0 += 8) tmem_st8(d_col0 + lane_addr + c0, zero8);
         tmem_wait_st();
@@ -317,16 +321,18 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             const bool valid = (s < p.n) && (ho < p.Hout) && (wo < p.Wout) && (oy < p.oH) && (ox < p.oW);
             float *yp = p.y + ((long long)s * p.Cout + co0) * plane + (long long)oy * p.oW + ox;
             const uint32_t d_addr = d_col0 + dbuf * N2 + lane_addr;
-            for (int c0 = 0; c0 < NT; c0 += 8) {
-                uint32_t a[8], b[8];
-                tmem_ld8(d_addr + c0, a);                       // A_hi*B_hi + A_lo*B_hi
-                tmem_ld8(d_addr + NT + c0, b);                  // A_hi*B_lo
+            // 16 output channels per step: both halves of the accumulator are read with one wait, the zeros that clear them
+            // for the next tile are issued at once and drain while the results go to global memory
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                uint32_t a[16], b[16];
+                tmem_ld16(d_addr + c0, a);                      // A_hi*B_hi + A_lo*B_hi
+                tmem_ld16(d_addr + NT + c0, b);                 // A_hi*B_lo
                 tmem_wait_ld();
-                tmem_st8(d_addr + c0, zero8);                   // leave the accumulators cleared for the next tile
-                tmem_st8(d_addr + NT + c0, zero8);
+                tmem_st16(d_addr + c0, zero16);
+                tmem_st16(d_addr + NT + c0, zero16);
                 if (valid) {
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
+                    for (int j = 0; j < 16; j++) {
                         const int co = co0 + c0 + j;
                         if (co < p.Cout) {
                             float v = __uint_as_float(a[j]) + __uint_as_float(b[j]);
@@ -345,7 +351,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
+    if (warp == TMA_WARP) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
