@@ -154,12 +154,41 @@ class ResNet8Streams(object):
         from bench import pinned_like
         h_img, h_lab, h_loss = pinned_like(pkg, lib, img), pinned_like(pkg, lib, lab), pinned_like(pkg, lib, np.zeros(n, F))
 
-        def step_e2e():
-            net.resnet8_forward_host(h_img.ctypes.data, h_lab.ctypes.data, h_loss.ctypes.data)
-            net.resnet8_backward()
-            if torch is not None:
-                dist.all_reduce(t_grads)
-            net.resnet8_update(LR)
+        if graph[0]:
+            # Two device copies of the batch, used in turn; per copy one CUDA graph of forward + backward.  A step uploads the
+            # NEXT step's batch on the copy stream (trainlib_memcpy_h2d_overlapped) while its own kernels run, then reads its
+            # losses back (blocking).  Every step still moves one batch up and one loss vector down inside the timed region.
+            slots = []
+            for sidx in range(2):
+                di, dl = pkg.DeviceBuffer(lib, nbytes=img.nbytes), pkg.DeviceBuffer(lib, nbytes=lab.nbytes)
+                lib.trainlib_memcpy_h2d(di.ptr, h_img.ctypes.data, img.nbytes); lib.trainlib_memcpy_h2d(dl.ptr, h_lab.ctypes.data, lab.nbytes)
+                lib.trainlib_graph_begin()
+                net.resnet8_forward(di.ptr, dl.ptr, d_loss.ptr); net.resnet8_backward()
+                slots.append((di, dl, lib.trainlib_graph_end()))
+                pkg.check(lib)
+            state = {"i": 0}
+
+            def upload(sidx):
+                lib.trainlib_memcpy_h2d_overlapped(slots[sidx][0].ptr, h_img.ctypes.data, img.nbytes, sidx)
+                lib.trainlib_memcpy_h2d_overlapped(slots[sidx][1].ptr, h_lab.ctypes.data, lab.nbytes, sidx)
+
+            def step_e2e():
+                sidx = state["i"] & 1; state["i"] += 1
+                lib.trainlib_graph_launch(slots[sidx][2])
+                lib.trainlib_mark_consumed(sidx)
+                if torch is not None:
+                    dist.all_reduce(t_grads)
+                net.resnet8_update(LR)
+                upload(sidx ^ 1)
+                lib.trainlib_memcpy_d2h(h_loss.ctypes.data, d_loss.ptr, 4 * n)
+            upload(0)
+        else:
+            def step_e2e():
+                net.resnet8_forward_host(h_img.ctypes.data, h_lab.ctypes.data, h_loss.ctypes.data)
+                net.resnet8_backward()
+                if torch is not None:
+                    dist.all_reduce(t_grads)
+                net.resnet8_update(LR)
 
         for _ in range(2):
             step_e2e()
@@ -223,10 +252,10 @@ class ResNet8Streams(object):
         if name in ("conv_tc_kernel", "conv_fw_kernel", "conv_ig_kernel", "conv_wg3x3_partial_kernel", "conv_wg_partial_kernel"):
             if name == "conv_tc_kernel":
                 fl, what = conv_flops + ig_flops, "forward of 9 convolutions + input gradient of 8 (useful FLOP: the zeros of a dilated dY are not counted)"
-                # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.63 MB read + 0.99 MB
+                # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.62 MB read + 0.88 MB
                 # written inside the launch; the 33.5 MB output is still dirty in L2 when it ends), scaled by the stream
                 # count: traffic grows in proportion because every stream brings its own planes
-                r["traffic"] = (33.63e6 + 0.99e6) * n / 512.0
+                r["traffic"] = (33.62e6 + 0.88e6) * n / 512.0
                 r["traffic_note"] = "per launch of the 16->16 32x32 forward convolution, ncu at 512 streams scaled by streams; algorithmic bytes of that launch: %.0f MB in + %.0f MB out" % (n * 65536e-6, n * 65536e-6)
             elif "wg" in name:
                 fl, what = conv_flops, "weight gradient of 9 convolutions"
