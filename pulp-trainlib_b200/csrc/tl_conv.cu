@@ -580,7 +580,9 @@ template <int S, int TW, int K, int TH, int S_T> struct WgShape {
     static constexpr int TP = TH * TW, DYP = S_T * TP + 4, TP4 = TP / 4;
     static constexpr int STAGE = S_T * 16 * PLANE + 16 * DYP;
 };
-template <class T, int S, int TW, int K, int TH, int S_T>
+// SMALL = at most 4 input channels (a network's first layer): the 8 lanes that would hold ci pairs hold 2 pairs x 4
+// interleaved slices of the pixel row instead, and the four slice sums are added with shuffles before the cross-warp sum.
+template <class T, int S, int TW, int K, int TH, int S_T, bool SMALL = false>
 __global__ void __launch_bounds__(CONV_THREADS, 2)
 conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, float *__restrict__ part,
                           int tiles_h, int ci_tiles, int vec, int nstage)
@@ -594,7 +596,8 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
     float *accs = smem;                             // [16 co][16 ci][KK] cross-warp sum, reuses stage 0 after the loop
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int cob = lane >> 3, cib = lane & 7;
+    const int cob = lane >> 3, cib = SMALL ? (lane & 1) : (lane & 7), kphase = SMALL ? ((lane >> 1) & 3) : 0;
+    constexpr int CI_STEP = SMALL ? 2 : 8, K_STEP = SMALL ? 4 : 1;      // second channel of a lane; stride of its 4-pixel groups
     const int ci0 = (blockIdx.x % ci_tiles) * 16, co0 = (blockIdx.x / ci_tiles) * 16;
     const int group = blockIdx.y, groups = gridDim.y;
 
@@ -626,6 +629,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
 #pragma unroll 1
                 for (int pl = warp; pl < S_T * 16; pl += CONV_THREADS / 32) {
                     const int ci = pl & 15, sl = pl >> 4;
+                    if (SMALL && ci >= 4) continue;          // never read; still zero from the initial fill
                     const bool pok = s0 + sl < g.n && ci0 + ci < g.Cin;
                     const float *src = x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)h_in0 * WIN;
                     const unsigned dst = (unsigned)__cvta_generic_to_shared(xs + pl * PLANE + 4);
@@ -693,7 +697,8 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
             const float *xb = xs + (sl * 16 + cib) * PLANE + (ph * S) * RW;        // ci = cib (i = 0), + 8 planes for i = 1
             const float *dp = dys + (cob * 4) * DYP + sl * TP + ph * TW;
 #pragma unroll
-            for (int k = 0; k < TW / 4; k++) {
+            for (int k0 = 0; k0 < TW / 4; k0 += K_STEP) {
+                const int k = k0 + kphase;
                 float4 d[4];
 #pragma unroll
                 for (int c = 0; c < 4; c++) d[c] = *reinterpret_cast<const float4 *>(dp + c * DYP + 4 * k);
@@ -701,7 +706,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
                 for (int i = 0; i < 2; i++)
 #pragma unroll
                     for (int kh = 0; kh < K; kh++) {
-                        const float *rp = xb + i * 8 * PLANE + kh * RW;
+                        const float *rp = xb + i * CI_STEP * PLANE + kh * RW;
                         // v[m] = shared column 3 + 4*S*k + m: pixel j of this group reads v[S*j + kw]
                         float v[4 * S + 2];
                         v[0] = rp[4 * S * k + 3];
@@ -727,16 +732,30 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
         }
     }
     __syncthreads();
+    if (SMALL) {
+        // the four pixel slices of a (co block, ci pair) sit in lanes that differ in bits 1 and 2
+#pragma unroll
+        for (int c = 0; c < 4; c++)
+#pragma unroll
+            for (int i = 0; i < 2; i++)
+#pragma unroll
+                for (int t = 0; t < KK; t++) {
+                    float v = acc[c][i][t];
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    acc[c][i][t] = v;
+                }
+    }
     // cross-warp sum in warp order (fixed order: same result on every run)
     for (int w = 0; w < CONV_THREADS / 32; w++) {
-        if (warp == w) {
+        if (warp == w && kphase == 0) {
 #pragma unroll
             for (int c = 0; c < 4; c++)
 #pragma unroll
                 for (int i = 0; i < 2; i++)
 #pragma unroll
                     for (int t = 0; t < KK; t++) {
-                        float *a = accs + ((cob * 4 + c) * 16 + cib + 8 * i) * KK + t;
+                        float *a = accs + ((cob * 4 + c) * 16 + cib + CI_STEP * i) * KK + t;
                         *a = (w == 0) ? acc[c][i][t] : *a + acc[c][i][t];
                     }
         }
@@ -847,7 +866,12 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
         TL_LAUNCH((conv_wg3x3_partial_kernel<T, S_, TW_, K_, TH_, ST_>), grid, CONV_THREADS, smem, g, x, dy, part, tiles_h, ci_tiles, vec, nstage); \
     } while (0)
 #define TL_WG3_LAUNCH(S_, TW_, TH_, ST_) do { if (K == 3) TL_WG3_LAUNCH2(S_, TW_, 3, TH_, ST_); else TL_WG3_LAUNCH2(S_, TW_, 1, TH_, ST_); } while (0)
-            if (S == 1) { if (TW == 32) TL_WG3_LAUNCH(1, 32, 8, 1); else if (TW == 16) TL_WG3_LAUNCH(1, 16, 16, 1); else TL_WG3_LAUNCH(1, 8, 8, 2); }
+            if (S == 1 && TW == 32 && K == 3 && g.Cin <= 4) {
+                // first layer of a network: 3 or 4 input channels
+                cudaFuncSetAttribute(conv_wg3x3_partial_kernel<T, 1, 32, 3, 8, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                TL_LAUNCH((conv_wg3x3_partial_kernel<T, 1, 32, 3, 8, 1, true>), grid, CONV_THREADS, smem, g, x, dy, part, tiles_h, ci_tiles, vec, nstage);
+            }
+            else if (S == 1) { if (TW == 32) TL_WG3_LAUNCH(1, 32, 8, 1); else if (TW == 16) TL_WG3_LAUNCH(1, 16, 16, 1); else TL_WG3_LAUNCH(1, 8, 8, 2); }
             else        { if (TW == 16) TL_WG3_LAUNCH(2, 16, 8, 1); else TL_WG3_LAUNCH(2, 8, 8, 2); }
 #undef TL_WG3_LAUNCH
 #undef TL_WG3_LAUNCH2
