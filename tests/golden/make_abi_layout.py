@@ -1,7 +1,7 @@
 """Writes tests/golden/abi_layout.json: sizeof/offsetof of every hot-path argument struct as the
 REFERENCE's own headers (lib/include/*.h) lay them out on x86-64.  Needs the reference checkout:
 
-    python tests/golden/make_abi_layout.py [/root/reference]
+    python tests/golden/make_abi_layout.py [path of the reference checkout]
 """
 import json
 import os

@@ -1,6 +1,6 @@
-"""Regenerates tests/golden/*.npz.  Needs the reference checkout (default /root/reference):
+"""Regenerates tests/golden/*.npz.  Needs the reference checkout (see --ref):
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference checkout>]
 
 * every case of tests/golden_cases.py is run through the reference's own C sources
   (oracle/_ref/libpulp_ref.so, built by `make -C oracle ref`) and stored as inputs + outputs;

@@ -20,7 +20,7 @@ def ref(pkg, reflib):
 
 
 def test_scalar_bit_tricks(oracle, pkg):
-    # known answers: q_rsqrt(64) = 0x3dff910f, q_rsqrt(32) ~ 0.17673251 (SURVEY of the reference's golden model)
+    # known answers: q_rsqrt(64) = 0x3dff910f, q_rsqrt(32) ~ 0.17673251 (values of the reference's own golden model, tests/test_mhsa_fp32/utils/mhsa.py)
     assert np.float32(oracle.q_rsqrt(64.0)).view(np.uint32) == 0x3DFF910F
     assert abs(oracle.q_rsqrt(32.0) - 0.17673251) < 1e-7
     assert oracle.fastexp_gist(0.0) == np.float32(np.uint32(1064986823).view(np.float32)) or abs(oracle.fastexp_gist(0.0) - 1.0) < 0.05
