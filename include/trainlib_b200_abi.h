@@ -228,6 +228,11 @@ struct transp_args_fp16 { fp16 *in_matrix; fp16 *out_matrix; int N; int M; int *
 struct array_broadcast_sum_fp16_args {
     fp16 *op_1; fp16 *op_2; fp16 *dest; int *op_1_dims; int *op_2_dims; int op_1_dims_len; int op_2_dims_len;
 };
+/* [ref: pulp_train_utils_fp16.h:252-262] */
+struct broadcastMatMul_args_fp16 {
+    fp16 *__restrict__ A; fp16 *__restrict__ B; fp16 *__restrict__ C;
+    int *__restrict__ A_dims; int *__restrict__ B_dims; int A_dims_len; int B_dims_len;
+};
 /* [ref: pulp_train_utils_fp16.h:133-138] */
 struct layout_args_fp16 { struct blob_fp16 *tensor; fp16 *transp_buffer; int transpose_data; int transpose_grad; };
 /* [ref: pulp_train_utils_fp16.h:150-158] */
@@ -332,6 +337,7 @@ struct pool_args_fp16 { struct blob_fp16 *input; struct blob_fp16 *output; int H
 /* ---- matmul family [ref: pulp_matmul_fp32.h:52-246; sources pulp_matmul_fp32.c:190-3697].
  * All variants compute the same C = A*B (one fp32 accumulator per output, k ascending) and
  * differ only in loop unrolling on PULP; here they are one GPU GEMM.  Argument: struct matMul_args. */
+void mm_broadcast_fp32(void *broadcastMatMul_args_fp32);   /* NumPy-style batched product  [ref: pulp_matmul_fp32.c:29] */
 void mm(void *matMul_args);
 void mm_add(void *matMul_args);          /* C += A*B  [ref: pulp_matmul_fp32.c:267] */
 void mm_M(void *matMul_args);
@@ -459,6 +465,7 @@ int verify_tensor(float *tensor_out, float *tensor_ref, int size, float toleranc
 /* Same contracts on fp16 storage with fp32 accumulation. */
 
 /* [ref: pulp_matmul_fp16.h:49-136; pulp_matmul_fp16.c:191,273] argument: struct matMul_args_fp16 */
+void mm_broadcast_fp16(void *broadcastMatMul_args_fp16);   /* [ref: pulp_matmul_fp16.c:30] */
 void mm_fp16(void *matMul_args_fp16);
 void mm_M_fp16(void *matMul_args_fp16);
 /* [ref: pulp_train_utils_fp16.h:661; pulp_train_utils_fp16.c:1258] */

@@ -518,6 +518,32 @@ void orc_layernorm_bw(const float *x, const float *w, const float *dy, float *dx
     }
 }
 
+/* Batched product with NumPy broadcasting of the leading dimensions [ref: lib/sources/pulp_matmul_fp32.c:29-186]:
+ * A [..., N, K] x B [..., K, M]; leading dimensions aligned from the right, size 1 (or missing) repeats the matrix;
+ * every product is the plain mm of the reference (k ascending, one accumulator). */
+void orc_mm_broadcast(const float *A, const float *B, float *C, const int *ad, int la, const int *bd, int lb)
+{
+    int lead = (la > lb ? la : lb) - 2, N = ad[la - 2], K = ad[la - 1], M = bd[lb - 1];
+    long od[8], sa[8], sb[8], total = 1, ra = (long)N * K, rb = (long)K * M;
+    for (int d = lead - 1; d >= 0; d--) {
+        int ia = d - (lead - (la - 2)), ib = d - (lead - (lb - 2));
+        int da = ia >= 0 ? ad[ia] : 1, db = ib >= 0 ? bd[ib] : 1;
+        od[d] = da > db ? da : db; sa[d] = da == 1 ? 0 : ra; sb[d] = db == 1 ? 0 : rb;
+        ra *= da; rb *= db; total *= od[d];
+    }
+    for (long i = 0; i < total; i++) {
+        long r = i, oa = 0, ob = 0;
+        for (int d = lead - 1; d >= 0; d--) { oa += (r % od[d]) * sa[d]; ob += (r % od[d]) * sb[d]; r /= od[d]; }
+        const float *a = A + oa, *b = B + ob; float *c = C + i * (long)N * M;
+        for (int n = 0; n < N; n++)
+            for (int m = 0; m < M; m++) {
+                float t = 0.0f;
+                for (int k = 0; k < K; k++) t += a[(long)n * K + k] * b[(long)k * M + m];
+                c[(long)n * M + m] = t;
+            }
+    }
+}
+
 /* ------------------------------------------------------------------ losses */
 
 /* [ref: lib/sources/pulp_losses_fp32.c:214-275] */

@@ -35,6 +35,7 @@ void orc_instnorm_bw_input(const float *x, const float *dy, float *dx, const flo
 void orc_instnorm_bw_param(const float *x, const float *dy, float *dgb, const float *mean, const float *stdev, int C, int D);
 void orc_batchnorm_fw(const float *x, float *y, const float *w, const float *b, int B, int C, int HW, float eps);
 void orc_layernorm_fw(const float *x, float *y, const float *w, const float *b, int rows, int width, float eps);
+void orc_mm_broadcast(const float *A, const float *B, float *C, const int *a_dims, int a_len, const int *b_dims, int b_len);
 void orc_layernorm_bw(const float *x, const float *w, const float *dy, float *dx, float *dw, float *db, int rows, int width, float eps);
 float orc_mse_fw(const float *y, const float *t, int n);
 void orc_mse_bw(const float *y, const float *t, float *dy, int n);

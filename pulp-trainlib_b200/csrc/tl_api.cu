@@ -68,6 +68,66 @@ template <class F> void mm_impl(void *void_args, bool accumulate)
     mm_contract<T>(A, B, C, a->N, a->K, a->M, a->trans_B ? 1 : 0, accumulate);
 }
 
+// Batched product with NumPy broadcasting of the leading dimensions [ref: lib/sources/pulp_matmul_fp32.c:29-186]:
+// A is [..., N, K], B is [..., K, M]; the leading dimensions are aligned from the right, a dimension of size 1 (or a
+// missing one) repeats its matrix, C holds the product matrices back to back in row-major order of the broadcast
+// batch shape.  The dimension arrays are read on the host.  Consecutive output matrices whose operand offsets advance by
+// a constant step go out as one batched launch.
+template <class T, class A_t> static void mm_broadcast_impl(void *void_args)
+{
+    auto *a = (A_t *)void_args;
+    TL_REQUIRE(a && a->A_dims && a->B_dims && a->A_dims_len >= 2 && a->B_dims_len >= 2 && a->A_dims_len <= 8 && a->B_dims_len <= 8,
+               "mm_broadcast: operands need 2..8 dimensions");
+    const int la = a->A_dims_len, lb = a->B_dims_len, lead = (la > lb ? la : lb) - 2;
+    const int N = a->A_dims[la - 2], K = a->A_dims[la - 1], M = a->B_dims[lb - 1];
+    TL_REQUIRE(N > 0 && K > 0 && M > 0 && a->B_dims[lb - 2] == K, "mm_broadcast: inner dimensions %d and %d differ or are empty", K, a->B_dims[lb - 2]);
+    long long out_dim[8], sa[8], sb[8], total = 1, count_a = (long long)N * K, count_b = (long long)K * M;
+    {
+        long long run_a = (long long)N * K, run_b = (long long)K * M;
+        for (int d = lead - 1; d >= 0; d--) {              // d counts leading dimensions from the right-aligned batch shape
+            const int ia = d - (lead - (la - 2)), ib = d - (lead - (lb - 2));
+            const int da = ia >= 0 ? a->A_dims[ia] : 1, db = ib >= 0 ? a->B_dims[ib] : 1;
+            TL_REQUIRE(da > 0 && db > 0 && (da == db || da == 1 || db == 1), "mm_broadcast: batch dimensions %d and %d do not broadcast", da, db);
+            out_dim[d] = da > db ? da : db;
+            sa[d] = da == 1 ? 0 : run_a; sb[d] = db == 1 ? 0 : run_b;
+            run_a *= da; run_b *= db;
+            total *= out_dim[d];
+        }
+        count_a = run_a; count_b = run_b;
+    }
+    Scope sc;
+    const T *A = sc.in(a->A, (size_t)count_a), *B = sc.in(a->B, (size_t)count_b);
+    T *C = sc.out(a->C, (size_t)total * N * M);
+    if (!sc.ok()) return;
+    auto offsets = [&](long long i, long long &oa, long long &ob) {
+        oa = ob = 0;
+        for (int d = lead - 1; d >= 0; d--) { const long long r = i % out_dim[d]; i /= out_dim[d]; oa += r * sa[d]; ob += r * sb[d]; }
+    };
+    long long i = 0;
+    while (i < total) {
+        long long oa0, ob0, oa1 = 0, ob1 = 0;
+        offsets(i, oa0, ob0);
+        long long run = 1, da = 0, db = 0;
+        if (i + 1 < total) {
+            offsets(i + 1, oa1, ob1);
+            da = oa1 - oa0; db = ob1 - ob0;
+            run = 2;
+            while (i + run < total) {
+                long long oa, ob;
+                offsets(i + run, oa, ob);
+                if (oa - oa0 != run * da || ob - ob0 != run * db) break;
+                run++;
+            }
+        }
+        GemmDesc<T> d;
+        d.A = A + oa0; d.a_rs = K; d.B = B + ob0; d.b_rs = M; d.C = C + i * (long long)N * M; d.c_rs = M;
+        d.N = N; d.K = K; d.M = M;
+        d.batch = (int)run; d.a_bs = da; d.b_bs = db; d.c_bs = (long long)N * M;
+        gemm<T>(d);
+        i += run;
+    }
+}
+
 // Dispatcher [ref: lib/sources/pulp_train_utils_fp32.c:1330-1683]: one GEMM whatever matmul_type
 // says; bias add after the product when mm_args->USE_BIASES == 1 (t = bias_transposed).
 template <class F> void mm_manager_impl(void *void_args)
@@ -760,6 +820,8 @@ TL_EXPORT void pulp_conv_dw_fp16_bw_cl(void *a)
     if (c->skip_in_grad == 0) pulp_conv_dw_fp16_bw_input_grads_cl(a);
 }
 
+TL_EXPORT void mm_broadcast_fp32(void *a) { mm_broadcast_impl<float, broadcastMatMul_args_fp32>(a); }
+TL_EXPORT void mm_broadcast_fp16(void *a) { mm_broadcast_impl<__half, broadcastMatMul_args_fp16>(a); }
 TL_PAIR(pulp_linear_fp32_fw_cl, pulp_linear_fp16_fw_cl, linear_impl<F32>(a, STEP_FW), linear_impl<F16>(a, STEP_FW))
 TL_PAIR(pulp_linear_fp32_bw_param_grads_cl, pulp_linear_fp16_bw_param_grads_cl, linear_impl<F32>(a, STEP_WGT_GRAD), linear_impl<F16>(a, STEP_WGT_GRAD))
 TL_PAIR(pulp_linear_fp32_bw_input_grads_cl, pulp_linear_fp16_bw_input_grads_cl, linear_impl<F32>(a, STEP_IN_GRAD), linear_impl<F16>(a, STEP_IN_GRAD))

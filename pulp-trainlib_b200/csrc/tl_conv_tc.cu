@@ -66,6 +66,7 @@ static constexpr int RING = 2;              // most A buffers per group (32 TMEM
 // issuers spent a quarter of their time waiting for an accumulator buffer to be released.
 static constexpr int FIRST_EPI = 0, FIRST_ISSUER = 4, FIRST_CONV = FIRST_ISSUER + GROUPS, TMA_WARP = FIRST_CONV + 4 * GROUPS;
 static constexpr int TC_THREADS = (TMA_WARP + 1) * 32;
+static_assert(FIRST_EPI == 0 && FIRST_ISSUER == 4, "the epilogue warps are the first four: warp w reads TMEM lanes 32 * (w % 4)");
 static constexpr int PS = 3;                // raw patch ring
 static constexpr int NA = GROUPS * RING;    // A buffers in tensor memory
 

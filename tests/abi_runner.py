@@ -253,6 +253,16 @@ class AbiRunner(object):
         self.call("pulp_layerNorm_fp32_fw_cl", args)     # the reference worker runs as core 0 of 1
         return Y.get().copy()
 
+    def mm_broadcast(self, A, B):
+        a, b = self.t(A), self.t(B)
+        out_shape = np.broadcast_shapes(A.shape[:-2], B.shape[:-2]) + (A.shape[-2], B.shape[-1])
+        c = self.zeros(*out_shape)
+        ad = (ctypes.c_int * A.ndim)(*A.shape); bd = (ctypes.c_int * B.ndim)(*B.shape)
+        args = self.args("broadcastMatMul_args_fp16" if self.half else "broadcastMatMul_args_fp32", A=a, B=b, C=c,
+                         A_dims=self.keep.hold(ad), B_dims=self.keep.hold(bd), A_dims_len=A.ndim, B_dims_len=B.ndim)
+        self.call("mm_broadcast_fp16" if self.half else "mm_broadcast_fp32", args)
+        return c.get().reshape(out_shape)
+
     def layernorm_ext(self, x, w, b, dy, rows, width, eps):
         """layer norm through the library's own struct (fp16 forward and both backward passes are not in the reference)"""
         import ctypes

@@ -160,6 +160,14 @@ class Oracle(object):
         self.lib.orc_layernorm_fw(_p(_ptr(x)), _p(_ptr(y)), _p(_ptr(w)), _p(_ptr(b)), _i(rows), _i(width), _f(eps))
         return y
 
+    def mm_broadcast(self, A, B):
+        import ctypes
+        ad = (ctypes.c_int * A.ndim)(*A.shape); bd = (ctypes.c_int * B.ndim)(*B.shape)
+        out_shape = np.broadcast_shapes(A.shape[:-2], B.shape[:-2]) + (A.shape[-2], B.shape[-1])
+        C = np.zeros(out_shape, np.float32)
+        self.lib.orc_mm_broadcast(_p(_ptr(A)), _p(_ptr(B)), _p(_ptr(C)), ad, _i(A.ndim), bd, _i(B.ndim))
+        return C
+
     def layernorm_bw(self, x, w, dy, rows, width, eps):
         dx = np.zeros_like(x); dw = np.zeros(width, np.float32); db = np.zeros(width, np.float32)
         self.lib.orc_layernorm_bw(_p(_ptr(x)), _p(_ptr(w)), _p(_ptr(dy)), _p(_ptr(dx)), _p(_ptr(dw)), _p(_ptr(db)), _i(rows), _i(width), _f(eps))

@@ -449,3 +449,15 @@ def test_mobilebert_block_fp16_against_its_fp32_twin(pkg, gpulib):
     t0 = X.astype(np.float64) @ Wbi.astype(np.float64)
     m = t0.mean(1, keepdims=True); v = ((t0 - m) ** 2).mean(1, keepdims=True)
     assert_close(blk.get("x1"), ((t0 - m) / np.sqrt(v + 1e-3) * w + b).astype(F), 1e-4, "bottleneck + layer norm vs numpy")
+
+
+@pytest.mark.parametrize("half", [False, True], ids=["fp32", "fp16"])
+@pytest.mark.parametrize("sa,sb", [((3, 5, 7), (3, 7, 4)), ((2, 1, 6, 5), (3, 5, 8)), ((1, 4, 9), (2, 3, 1, 9, 2)), ((4, 64, 96), (1, 96, 80)), ((70, 33), (33, 9))])
+def test_mm_broadcast(run, oracle, sa, sb, half):
+    """NumPy-style batched product (leading dimensions broadcast) against the oracle"""
+    rng = seeded(sum(sa) * 3 + sum(sb))
+    A = rng.standard_normal(sa).astype(F); B = rng.standard_normal(sb).astype(F)
+    if half:
+        A, B = A.astype(np.float16).astype(F), B.astype(np.float16).astype(F)
+    got = run(device=True, half=half).mm_broadcast(A, B)
+    assert_close(got.astype(F), oracle.mm_broadcast(A, B), FP16_TOL if half else FP32_TOL, "mm_broadcast")

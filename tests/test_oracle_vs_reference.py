@@ -205,3 +205,20 @@ def test_index_helpers(oracle, ref):
     p = rng.standard_normal((3, 5, 6)).astype(np.float32)
     assert_exact(oracle.pad(p, 1, 1, 1, 1), ref.pad(p, 1, 1, 1, 1), "pad 1")
     assert_exact(oracle.pad(p, 2, 1, 0, 3), np.pad(p, ((0, 0), (0, 3), (2, 1))), "pad numpy")
+
+
+MMB_SHAPES = [((3, 5, 7), (3, 7, 4)), ((2, 1, 6, 5), (3, 5, 8)), ((1, 4, 9), (2, 3, 1, 9, 2)), ((4, 6, 3), (1, 3, 5))]
+
+
+@pytest.mark.parametrize("sa,sb", MMB_SHAPES)
+def test_mm_broadcast_oracle_is_numpy_matmul_and_the_reference(oracle, reflib, pkg, sa, sb):
+    """mm_broadcast: the oracle restates NumPy broadcasting; pinned against numpy.matmul and the reference's own C"""
+    from abi_runner import AbiRunner
+    rng = np.random.default_rng(sum(sa) + sum(sb))
+    A = rng.standard_normal(sa).astype(np.float32); B = rng.standard_normal(sb).astype(np.float32)
+    want = np.matmul(A.astype(np.float64), B.astype(np.float64))
+    got = oracle.mm_broadcast(A, B)
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    ref = AbiRunner(pkg, reflib, is_ref=True).mm_broadcast(A, B)
+    assert np.array_equal(ref, got), "same products in the same order: bit-identical"
