@@ -187,12 +187,29 @@ template <class A> bool conv_flags_ok(const A *a, const char *who)
         set_error(TL_ERR_BAD_ARGS, "%s: USE_IM2COL = %d", who, a->USE_IM2COL);
         return false;
     }
-    if (a->HWC != 0) {
-        if (a->HWC == 1) set_error(TL_ERR_UNSUPPORTED, "%s: HWC layout is not implemented for Conv2D", who);
-        else { printf("[%s:] Invalid data layout format (HWC or CHW)!\n", who); set_error(TL_ERR_BAD_ARGS, "%s: HWC = %d", who, a->HWC); }
+    if (a->HWC != 0 && a->HWC != 1) {
+        printf("[%s:] Invalid data layout format (HWC or CHW)!\n", who); set_error(TL_ERR_BAD_ARGS, "%s: HWC = %d", who, a->HWC);
         return false;
     }
     return true;
+}
+
+// HWC layout [ref: lib/sources/pulp_conv2d_fp32.c:115-238 (forward), :334-452 (weight gradient), :550-660 (input gradient)]:
+// activations [H][W][C], weights [Cout][Hk][Wk][Cin].  The kernels work on CHW, so HWC operands are permuted into
+// scratch on the way in and results permuted back on the way out (one pass over each tensor; the convolution itself
+// then runs on the same tensor-core / FFMA kernels as the CHW layout).
+template <class T> static const T *hwc_in(Scope &sc, const T *src, int n, int C, int H, int W)
+{
+    T *dst = sc.scratch<T>((size_t)n * C * H * W);
+    if (!dst) return nullptr;
+    const int dims[4] = {n, H, W, C}, axes[4] = {0, 3, 1, 2};
+    transpose_nd<T>(src, dst, dims, axes, 4);
+    return dst;
+}
+template <class T> static void hwc_out(const T *chw, T *dst, int n, int C, int H, int W)
+{
+    const int dims[4] = {n, C, H, W}, axes[4] = {0, 2, 3, 1};
+    transpose_nd<T>(chw, dst, dims, axes, 4);
 }
 
 template <class F> void conv2d_fw_impl(void *args)
@@ -206,6 +223,14 @@ template <class F> void conv2d_fw_impl(void *args)
     const T *b = (a->USE_BIASES == 1 && a->bias) ? sc.in(a->bias->data, (size_t)g.Cout) : nullptr;
     T *y = sc.out(a->output->data, (size_t)g.n * g.Cout * g.Hout * g.Wout);
     if (!sc.ok()) return;
+    if (a->HWC == 1) {
+        const T *xc = hwc_in<T>(sc, x, g.n, g.Cin, g.Hin, g.Win), *wc = hwc_in<T>(sc, w, g.Cout, g.Cin, g.Hk, g.Wk);
+        T *yc = sc.scratch<T>((size_t)g.n * g.Cout * g.Hout * g.Wout);
+        if (!xc || !wc || !yc) return;
+        conv_fw<T>(sc, g, xc, wc, b, yc);
+        hwc_out<T>(yc, y, g.n, g.Cout, g.Hout, g.Wout);
+        return;
+    }
     conv_fw<T>(sc, g, x, w, b, y);
 }
 template <class F> void conv2d_wg_impl(void *args)
@@ -219,6 +244,14 @@ template <class F> void conv2d_wg_impl(void *args)
     T *dw = sc.out(a->coeff->diff, (size_t)g.Cout * g.Cin * g.Hk * g.Wk);
     T *db = (a->USE_BIASES == 1 && a->bias) ? sc.out(a->bias->diff, (size_t)g.Cout) : nullptr;
     if (!sc.ok()) return;
+    if (a->HWC == 1) {
+        const T *xc = hwc_in<T>(sc, x, g.n, g.Cin, g.Hin, g.Win), *dyc = hwc_in<T>(sc, dy, g.n, g.Cout, g.Hout, g.Wout);
+        T *dwc = sc.scratch<T>((size_t)g.Cout * g.Cin * g.Hk * g.Wk);
+        if (!xc || !dyc || !dwc) return;
+        conv_wg<T>(sc, g, xc, dyc, dwc, db);
+        hwc_out<T>(dwc, dw, g.Cout, g.Cin, g.Hk, g.Wk);
+        return;
+    }
     conv_wg<T>(sc, g, x, dy, dw, db);
 }
 template <class F> void conv2d_ig_impl(void *args)
@@ -231,6 +264,14 @@ template <class F> void conv2d_ig_impl(void *args)
     const T *w = sc.in(a->coeff->data, (size_t)g.Cout * g.Cin * g.Hk * g.Wk);
     T *dx = sc.out(a->input->diff, (size_t)g.n * g.Cin * g.Hin * g.Win);
     if (!sc.ok()) return;
+    if (a->HWC == 1) {
+        const T *dyc = hwc_in<T>(sc, dy, g.n, g.Cout, g.Hout, g.Wout), *wc = hwc_in<T>(sc, w, g.Cout, g.Cin, g.Hk, g.Wk);
+        T *dxc = sc.scratch<T>((size_t)g.n * g.Cin * g.Hin * g.Win);
+        if (!dyc || !wc || !dxc) return;
+        conv_ig<T>(sc, g, dyc, wc, dxc);
+        hwc_out<T>(dxc, dx, g.n, g.Cin, g.Hin, g.Win);
+        return;
+    }
     conv_ig<T>(sc, g, dy, w, dx);
 }
 

@@ -98,7 +98,8 @@ class AbiRunner(object):
         self.call(fn if not self.half else (fn + "_fp16" if not fn.endswith("fp16") else fn), args)
         return c.get()
 
-    def conv2d(self, x, w, dy, g, use_im2col=0, bias=None, steps=("fw", "wg", "ig")):
+    def conv2d(self, x, w, dy, g, use_im2col=0, bias=None, steps=("fw", "wg", "ig"), hwc=0):
+        """hwc=1: x, dy and the results are [H][W][C], w is [Cout][Hk][Wk][Cin] (only the flat sizes matter to the structs)"""
         from oracle_bind import out_hw
         Ho, Wo = out_hw(g)
         X, W_ = self.t(x), self.t(w)
@@ -115,7 +116,7 @@ class AbiRunner(object):
         bout = self.blob(Y, dY, C=g["Cout"], H=Ho, W=Wo)
         args = self.args(self.sname("Conv2D_args"), input=bin_, coeff=bw, bias=bb, output=bout,
                          Lpad=g["padL"], Rpad=g["padR"], Upad=g["padU"], Dpad=g["padD"], stride_h=g["sh"], stride_w=g["sw"],
-                         i2c_buffer=i2c, bt_buffer=bt, skip_wg_grad=0, skip_in_grad=0, HWC=0,
+                         i2c_buffer=i2c, bt_buffer=bt, skip_wg_grad=0, skip_in_grad=0, HWC=hwc,
                          opt_matmul_type_fw=0, opt_matmul_type_wg=0, opt_matmul_type_ig=0,
                          USE_BIASES=1 if bias is not None else 0, USE_IM2COL=use_im2col, USE_DMA_IM2COL=0)
         r = {}

@@ -461,3 +461,18 @@ def test_mm_broadcast(run, oracle, sa, sb, half):
         A, B = A.astype(np.float16).astype(F), B.astype(np.float16).astype(F)
     got = run(device=True, half=half).mm_broadcast(A, B)
     assert_close(got.astype(F), oracle.mm_broadcast(A, B), FP16_TOL if half else FP32_TOL, "mm_broadcast")
+
+
+@pytest.mark.parametrize("g", [geom(5, 9, 8, 6, 3, pad=0), geom(16, 32, 32, 32, 3, pad=1), geom(8, 16, 16, 12, 3, stride=2, pad=1)],
+                         ids=lambda v: "c%d_%dx%d_o%d_s%d_p%d" % (v["Cin"], v["Hin"], v["Win"], v["Cout"], v["sh"], v["padU"]))
+def test_conv2d_hwc_layout(run, oracle, g):
+    """HWC = 1: activations [H][W][C], weights [Cout][Hk][Wk][Cin]; the same convolution as the CHW oracle on permuted operands"""
+    rng = seeded(g["Cin"] * 5 + g["Cout"])
+    Ho, Wo = out_hw(g)
+    x = rng.uniform(-1, 1, (g["Cin"], g["Hin"], g["Win"])).astype(F); w = rng.uniform(-1, 1, (g["Cout"], g["Cin"], g["Hk"], g["Wk"])).astype(F)
+    dy = rng.standard_normal((g["Cout"], Ho, Wo)).astype(F)
+    hwc = lambda a: np.ascontiguousarray(a.transpose(1, 2, 0))
+    got = run(device=True).conv2d(hwc(x), np.ascontiguousarray(w.transpose(0, 2, 3, 1)), hwc(dy), g, use_im2col=1, hwc=1)
+    assert_close(got["y"].reshape(Ho, Wo, g["Cout"]).transpose(2, 0, 1), oracle.conv2d_fw(x, w, None, g), FP32_TOL, "hwc fw")
+    assert_close(got["dw"].reshape(g["Cout"], g["Hk"], g["Wk"], g["Cin"]).transpose(0, 3, 1, 2), oracle.conv2d_wg(x, dy, g)[0], FP32_TOL, "hwc wg")
+    assert_close(got["dx"].reshape(g["Hin"], g["Win"], g["Cin"]).transpose(2, 0, 1), oracle.conv2d_ig(dy, w, g), FP32_TOL, "hwc ig")

@@ -222,3 +222,19 @@ def test_mm_broadcast_oracle_is_numpy_matmul_and_the_reference(oracle, reflib, p
     assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
     ref = AbiRunner(pkg, reflib, is_ref=True).mm_broadcast(A, B)
     assert np.array_equal(ref, got), "same products in the same order: bit-identical"
+
+
+def test_hwc_conv2d_layout_convention_of_the_reference(oracle, reflib, pkg):
+    """HWC Conv2D: activations [H][W][C], weights [Cout][Hk][Wk][Cin].  Pinned on the reference's im2col forward (no
+    padding, where that path is right): permuting its operands gives the CHW oracle's result."""
+    from abi_runner import AbiRunner
+    from golden_cases import geom
+    g = geom(5, 9, 8, 6, 3, pad=0)
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((5, 9, 8)).astype(np.float32); w = rng.standard_normal((6, 5, 3, 3)).astype(np.float32)
+    want = oracle.conv2d_fw(x, w, None, g)
+    r = AbiRunner(pkg, reflib, is_ref=True)
+    got = r.conv2d(np.ascontiguousarray(x.transpose(1, 2, 0)), np.ascontiguousarray(w.transpose(0, 2, 3, 1)), None, g, use_im2col=1, steps=("fw",), hwc=1)
+    Ho, Wo = want.shape[1:]
+    y = got["y"].reshape(-1)[:want.size].reshape(Ho, Wo, 6).transpose(2, 0, 1)
+    assert np.abs(y - want).max() <= 1e-5 * np.abs(want).max()
