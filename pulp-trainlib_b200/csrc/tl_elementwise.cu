@@ -403,6 +403,64 @@ __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__re
             }
     }
 }
+// Planes of 513..1024 elements: two warps per plane (4 sixteen-byte vectors of x and of dY per lane instead of 8), which
+// halves the registers per thread and doubles the warps in flight; the two warp sums meet in shared memory.
+template <bool DX, bool PART>
+__global__ void __launch_bounds__(256) instnorm_bw_pair_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
+                                                               float *__restrict__ part, const float *__restrict__ gamma,
+                                                               const float *__restrict__ mean_i, const float *__restrict__ var_i,
+                                                               const float *__restrict__ std_i, long long planes, int C, int D)
+{
+    __shared__ float2 sums[4][2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, slot = warp >> 1, half = warp & 1;
+    const long long plane = (long long)blockIdx.x * 4 + slot;
+    const bool live = plane < planes;
+    const int D4 = D >> 2;
+    float4 v[4], g[4];
+    float mean = 0.f, sd = 1.f;
+    if (live) {
+        mean = mean_i[plane]; sd = std_i[plane];
+        const float4 *xp = reinterpret_cast<const float4 *>(x + plane * D), *gp = reinterpret_cast<const float4 *>(dy + plane * D);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int idx = half * 128 + lane + 32 * i;
+            const bool in = idx < D4;
+            v[i] = in ? xp[idx] : make_float4(mean, mean, mean, mean);
+            g[i] = in ? gp[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) { v[i] = make_float4(0.f, 0.f, 0.f, 0.f); g[i] = v[i]; }
+    }
+    float s = 0.f, p = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        s += (g[i].x + g[i].y) + (g[i].z + g[i].w);
+        p = fmaf(v[i].x, g[i].x, p); p = fmaf(v[i].y, g[i].y, p); p = fmaf(v[i].z, g[i].z, p); p = fmaf(v[i].w, g[i].w, p);
+    }
+    s = warp_sum(s); p = warp_sum(p);
+    if (lane == 0) sums[slot][half] = make_float2(s, p);
+    __syncthreads();
+    s = sums[slot][0].x + sums[slot][1].x; p = sums[slot][0].y + sums[slot][1].y;      // same order in both warps
+    if (!live) return;
+    if (PART && lane == 0 && half == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
+    if (DX) {
+        const int ch = (int)(plane % C);
+        const float var = var_i[plane], gm = gamma[ch], fD = (float)D, denom = fD * sd;
+        float4 *dp = reinterpret_cast<float4 *>(dx + plane * D);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int idx = half * 128 + lane + 32 * i;
+            if (idx < D4) {
+                float4 o;
+                o.x = (-s - p * (v[i].x / var) + fD * g[i].x) * gm / denom; o.y = (-s - p * (v[i].y / var) + fD * g[i].y) * gm / denom;
+                o.z = (-s - p * (v[i].z / var) + fD * g[i].z) * gm / denom; o.w = (-s - p * (v[i].w / var) + fD * g[i].w) * gm / denom;
+                dp[idx] = o;
+            }
+        }
+    }
+}
 static inline bool aligned16(const void *a, const void *b, const void *c) { return ((((uintptr_t)a) | ((uintptr_t)b) | ((uintptr_t)c)) & 15) == 0; }
 static inline int instnorm_nv(int D) { return (D % 4 != 0 || D > 1024) ? 0 : (D <= 128 ? 1 : (D <= 256 ? 2 : (D <= 512 ? 4 : 8))); }
 #define TL_NV_SWITCH(nv, CALL)                                                                                         \
@@ -426,6 +484,13 @@ static bool instnorm_bw_warp(const float *x, const float *dy, float *dx, float *
     const int nv = instnorm_nv(D);
     if (!nv || !aligned16(x, dy, dx)) return false;
     const long long planes = (long long)n * C;
+    if (nv == 8) {
+        const unsigned b4 = (unsigned)((planes + 3) / 4);
+        if (dx && part) TL_LAUNCH((instnorm_bw_pair_kernel<true, true>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        else if (dx) TL_LAUNCH((instnorm_bw_pair_kernel<true, false>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        else TL_LAUNCH((instnorm_bw_pair_kernel<false, true>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        return true;
+    }
     const unsigned blocks = (unsigned)((planes + 7) / 8);
 #define TL_CALL(NV)                                                                                                    \
     do {                                                                                                               \
