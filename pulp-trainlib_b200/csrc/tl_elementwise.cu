@@ -403,6 +403,73 @@ __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__re
             }
     }
 }
+// Planes of up to 64 elements (8x8 images): half a warp per plane, one 16-byte vector per lane; the sums run over the 16 lanes
+// of a half with xor shuffles that stay inside it.
+__device__ __forceinline__ float half_warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__global__ void __launch_bounds__(256) instnorm_fw_half_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ gb,
+                                                               float *__restrict__ mean_o, float *__restrict__ var_o, float *__restrict__ std_o,
+                                                               long long planes, int C, int D, int frozen, float eps)
+{
+    const int l16 = threadIdx.x & 15;
+    const long long plane = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const bool live = plane < planes;
+    const int D4 = D >> 2;
+    const bool in = live && l16 < D4;
+    const float4 v = in ? reinterpret_cast<const float4 *>(x + plane * D)[l16] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float mean, var, sd;
+    if (!frozen) {
+        float s = (v.x + v.y) + (v.z + v.w), q = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, v.w * v.w)));
+        s = half_warp_sum(s); q = half_warp_sum(q);
+        const float inv = 1.f / (float)D;
+        mean = s * inv;
+        var = q * inv;
+        var = __fsub_rn(var, __fmul_rn(mean, mean));
+        var = var + eps;
+        if (var < 0.f) var = eps;
+        sd = sqrtf(var);
+        if (live && l16 == 0) { mean_o[plane] = mean; var_o[plane] = var; std_o[plane] = sd; }
+    } else if (live) {
+        mean = mean_o[plane]; var = var_o[plane]; sd = std_o[plane];
+    } else { mean = 0.f; var = 1.f; sd = 1.f; }
+    if (!in) return;
+    const int ch = (int)(plane % C);
+    const float gamma = __fdiv_rn(gb[ch], sd), beta = gb[C + ch];
+    float4 o;
+    o.x = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.x, mean)), beta); o.y = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.y, mean)), beta);
+    o.z = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.z, mean)), beta); o.w = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.w, mean)), beta);
+    reinterpret_cast<float4 *>(y + plane * D)[l16] = o;
+}
+template <bool DX, bool PART>
+__global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
+                                                               float *__restrict__ part, const float *__restrict__ gamma,
+                                                               const float *__restrict__ mean_i, const float *__restrict__ var_i,
+                                                               const float *__restrict__ std_i, long long planes, int C, int D)
+{
+    const int l16 = threadIdx.x & 15;
+    const long long plane = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const bool live = plane < planes;
+    const int D4 = D >> 2;
+    const bool in = live && l16 < D4;
+    const float mean = live ? mean_i[plane] : 0.f, sd = live ? std_i[plane] : 1.f;
+    float4 v = in ? reinterpret_cast<const float4 *>(x + plane * D)[l16] : make_float4(mean, mean, mean, mean);
+    const float4 g = in ? reinterpret_cast<const float4 *>(dy + plane * D)[l16] : make_float4(0.f, 0.f, 0.f, 0.f);
+    v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+    float s = (g.x + g.y) + (g.z + g.w), p = fmaf(v.x, g.x, fmaf(v.y, g.y, fmaf(v.z, g.z, v.w * g.w)));
+    s = half_warp_sum(s); p = half_warp_sum(p);
+    if (PART && live && l16 == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
+    if (DX && in) {
+        const float var = var_i[plane], gm = gamma[(int)(plane % C)], fD = (float)D, denom = fD * sd;
+        float4 o;
+        o.x = (-s - p * (v.x / var) + fD * g.x) * gm / denom; o.y = (-s - p * (v.y / var) + fD * g.y) * gm / denom;
+        o.z = (-s - p * (v.z / var) + fD * g.z) * gm / denom; o.w = (-s - p * (v.w / var) + fD * g.w) * gm / denom;
+        reinterpret_cast<float4 *>(dx + plane * D)[l16] = o;
+    }
+}
 // Planes of 513..1024 elements: two warps per plane (4 sixteen-byte vectors of x and of dY per lane instead of 8), which
 // halves the registers per thread and doubles the warps in flight; the two warp sums meet in shared memory.
 template <bool DX, bool PART>
@@ -471,6 +538,10 @@ static bool instnorm_fw_warp(const float *x, float *y, const float *gb, float *m
     const int nv = instnorm_nv(D);
     if (!nv || !aligned16(x, y, nullptr)) return false;
     const long long planes = (long long)n * C;
+    if (D <= 64) {
+        TL_LAUNCH(instnorm_fw_half_kernel, (unsigned)((planes + 15) / 16), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps);
+        return true;
+    }
 #define TL_CALL(NV) TL_LAUNCH((instnorm_fw_warp_kernel<NV>), (unsigned)((planes + 7) / 8), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps)
     TL_NV_SWITCH(nv, TL_CALL);
 #undef TL_CALL
@@ -484,6 +555,13 @@ static bool instnorm_bw_warp(const float *x, const float *dy, float *dx, float *
     const int nv = instnorm_nv(D);
     if (!nv || !aligned16(x, dy, dx)) return false;
     const long long planes = (long long)n * C;
+    if (D <= 64) {
+        const unsigned b16 = (unsigned)((planes + 15) / 16);
+        if (dx && part) TL_LAUNCH((instnorm_bw_half_kernel<true, true>), b16, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        else if (dx) TL_LAUNCH((instnorm_bw_half_kernel<true, false>), b16, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        else TL_LAUNCH((instnorm_bw_half_kernel<false, true>), b16, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        return true;
+    }
     if (nv == 8) {
         const unsigned b4 = (unsigned)((planes + 3) / 4);
         if (dx && part) TL_LAUNCH((instnorm_bw_pair_kernel<true, true>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
