@@ -255,6 +255,24 @@ __global__ void __launch_bounds__(PX) conv1x1_strided_ig_kernel(ConvGeom g, cons
     const bool live = p < opix;
     const int ho = live ? p / g.Wout : 0, wo = live ? p % g.Wout : 0;
     float *dxs = dx + (size_t)s * g.Cin * g.Hin * g.Win;
+    if ((g.Cin & 3) == 0 && ((g.Cout * g.Cin) & 3) == 0) {
+        // four input channels per pass: one shared load of dY and one 16-byte broadcast load of weights per 4 FMAs
+        for (int ci = 0; ci < g.Cin; ci += 4) {
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+            for (int co = 0; co < g.Cout; co++) {
+                const float d = dys[co * PX + threadIdx.x];
+                const float4 wv = *reinterpret_cast<const float4 *>(ws + co * g.Cin + ci);
+                a0 = fmaf(wv.x, d, a0); a1 = fmaf(wv.y, d, a1); a2 = fmaf(wv.z, d, a2); a3 = fmaf(wv.w, d, a3);
+            }
+            if (live) {
+                float *o = dxs + ((size_t)ci * g.Hin + (size_t)ho * g.sh) * g.Win + (size_t)wo * g.sw;
+                const size_t pl = (size_t)g.Hin * g.Win;
+                o[0] = a0; o[pl] = a1; o[2 * pl] = a2; o[3 * pl] = a3;
+            }
+        }
+        return;
+    }
     for (int ci = 0; ci < g.Cin; ci++) {
         float acc = 0.f;
         for (int co = 0; co < g.Cout; co++) acc = fmaf(ws[co * g.Cin + ci], dys[co * PX + threadIdx.x], acc);
