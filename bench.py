@@ -292,6 +292,9 @@ def run_reference(args, pkg):
         return
     ref = pkg.bind(ctypes.CDLL(REF_MT))
     wl = make_workload(args.config, pkg, ref, args.dtype)
+    if getattr(wl, "no_reference", None):
+        print(json.dumps({"impl": "reference", "unavailable": wl.no_reference}))
+        return
     if hasattr(wl, "run_reference"):
         line = wl.run_reference(ref, args)
     else:
@@ -387,7 +390,9 @@ def run_single(args, pkg, lib, wl):
                                             "replay": "CUDA graph of the entry-point calls of one step" if graph else "entry-point calls"},
             "roofline": wl.roofline(ms_step, pk), "gpu_launches": int(launches), "clocks": clocks,
             "e2e": {"value": e["value"], "unit": e["unit"], "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h), "ms_per_step": e2e_ms}}
-    if not args.no_cpu_baseline and os.path.exists(REF_MT):
+    if not args.no_cpu_baseline and getattr(wl, "no_reference", None):
+        line["cpu_baseline"] = {"value": None, "unit": m["unit"], "cores": 0, "kind": "reference", "sample": "none: " + wl.no_reference}
+    elif not args.no_cpu_baseline and os.path.exists(REF_MT):
         ref = pkg.bind(ctypes.CDLL(REF_MT))
         wr = make_workload(args.config, pkg, ref, args.dtype)
         cms = time_host_lib(wr, ref, 3, 1)

@@ -199,6 +199,7 @@ class MobileBertBlock(_Layer):
     input and target ~ N(0, 1), layer-norm weights 1 + N(0, 0.02), biases N(0, 0.02).  `half` selects the fp16 twins."""
     L, H, B, HEADS, NFFN, FF = 128, 512, 128, 4, 4, 512
     LOSS_SCALE = 1024.0
+    no_reference = "the reference has no backward for layer norm and GELU, so it cannot run this block's training step"
 
     def __init__(self, pkg, lib, half=True):
         _Layer.__init__(self, pkg, lib)
@@ -383,7 +384,7 @@ class MobileBertBlock(_Layer):
     # the block has no host-pointer form here: its end-to-end number uploads the input and target and reads back the loss
     def setup_host(self, lib):
         if not hasattr(lib, "trainlib_malloc_host"):
-            raise SystemExit("config 4 has no reference arm: the reference has no backward for layer norm and GELU")
+            raise SystemExit("config 4 has no reference arm: " + self.no_reference)
         from bench import pinned_like
         self.hX = pinned_like(self.pkg, lib, self.get("X").astype(self.dt)); self.hT = pinned_like(self.pkg, lib, self.get("target").astype(self.dt))
         self.hloss = pinned_like(self.pkg, lib, np.zeros(1, self.dt))
