@@ -96,6 +96,22 @@ void  trainlib_layernorm_fp16_bw_cl(void *trainlib_layernorm_args);
 void  trainlib_gelu_fp32_bw_cl(void *act_args);
 void  trainlib_gelu_fp16_bw_cl(void *act_args_fp16);
 
+/* ---- Instance norm fused with what follows it in a residual network.  No counterpart in the reference, which runs
+ * pulp_instnorm_*_fw_cl, pulp_residualconn_*_fw and pulp_relu_*_fw_cl one after the other
+ * (lib/sources/pulp_instnorm_fp32.c:33, pulp_residual_fp32.c:71, pulp_act_fp32.c:96); results are those of that sequence,
+ * bit for bit.  `norm` points at an InstNorm_args (fp32 entry points) or InstNorm_args_fp16.
+ *   fw:  norm->output->data = relu(instnorm(norm->input->data) + skip->data); `skip` (a struct blob / blob_fp16 of the
+ *        output's size) may be NULL and `relu` 0.  The running statistics are written as by the plain forward.
+ *   bw:  norm->output->diff holds the gradient behind the ReLU (relu != 0, skip == NULL only): writes norm->input->diff
+ *        and norm->coeff->diff like pulp_instnorm_*_bw_cl after pulp_relu_*_bw_cl.  norm->output->diff may be masked in
+ *        place.  With a skip connection the ReLU's gradient has two readers, so mask it once with pulp_relu_*_bw_cl on the
+ *        sum and call pulp_instnorm_*_bw_cl. */
+struct trainlib_instnorm_act_args { void *norm; void *skip; int relu; };
+void  trainlib_instnorm_act_fp32_fw_cl(void *trainlib_instnorm_act_args);
+void  trainlib_instnorm_act_fp16_fw_cl(void *trainlib_instnorm_act_args);
+void  trainlib_instnorm_act_fp32_bw_cl(void *trainlib_instnorm_act_args);
+void  trainlib_instnorm_act_fp16_bw_cl(void *trainlib_instnorm_act_args);
+
 /* ---- CUDA graphs.  Entry-point calls made between begin and end are recorded instead of executed (device pointers
  * only: a host pointer would need a synchronous copy); the handle replays them with one launch on the library's
  * stream.  The recorded launches keep the addresses they saw, including library scratch: run the same calls once

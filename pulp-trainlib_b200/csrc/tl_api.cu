@@ -586,6 +586,35 @@ template <class F> void instnorm_impl(void *args, int step)
     }
 }
 
+// Instance norm + optional skip sum + optional ReLU (extension; see the public header).
+template <class F> void instnorm_act_impl(void *args, int backward)
+{
+    auto *f = (trainlib_instnorm_act_args *)args; typedef typename F::T T;
+    TL_REQUIRE(f && f->norm, "trainlib_instnorm_act: norm=%p", f ? f->norm : nullptr);
+    auto *a = (typename F::instnorm_t *)f->norm;
+    auto *skip = (typename F::blob_t *)f->skip;
+    const int C = a->input->C, D = a->input->H * a->input->W, n = streams();
+    TL_REQUIRE(C > 0 && D > 0, "trainlib_instnorm_act: C=%d HxW=%d", C, D);
+    const size_t nx = (size_t)n * C * D, ns = (size_t)n * C;
+    Scope sc;
+    if (!backward) {
+        TL_REQUIRE(!skip || skip->dim == a->output->dim, "trainlib_instnorm_act_fw: skip dim %d, output dim %d", skip->dim, a->output->dim);
+        const bool frozen = a->freeze_running_params != 0;
+        const T *x = sc.in(a->input->data, nx), *gb = sc.in(a->coeff->data, (size_t)2 * C), *k = skip ? sc.in(skip->data, nx) : nullptr;
+        T *y = sc.out(a->output->data, nx);
+        T *m = frozen ? sc.inout(a->running_mean, ns) : sc.out(a->running_mean, ns);
+        T *v = frozen ? sc.inout(a->running_var, ns) : sc.out(a->running_var, ns);
+        T *s = frozen ? sc.inout(a->running_stdev, ns) : sc.out(a->running_stdev, ns);
+        if (sc.ok()) instnorm_act_fw<T>(x, y, k, gb, m, v, s, n, C, D, frozen, (float)EPSILON, f->relu != 0);
+        return;
+    }
+    TL_REQUIRE(f->relu != 0 && !skip, "trainlib_instnorm_act_bw: relu=%d skip=%p (mask the sum's gradient with pulp_relu_bw and call pulp_instnorm_bw)", f->relu, f->skip);
+    const T *x = sc.in(a->input->data, nx), *y = sc.in(a->output->data, nx), *gb = sc.in(a->coeff->data, (size_t)2 * C);
+    const T *m = sc.in(a->running_mean, ns), *v = sc.in(a->running_var, ns), *s = sc.in(a->running_stdev, ns);
+    T *dy = sc.inout(a->output->diff, nx), *dx = sc.out(a->input->diff, nx), *dgb = sc.out(a->coeff->diff, (size_t)2 * C);
+    if (sc.ok()) instnorm_relu_bw<T>(sc, x, y, dy, dx, dgb, gb, m, v, s, n, C, D);
+}
+
 // ------------------------------------------------------------------ losses, optimizer, residual, pooling
 template <class F> void loss_impl(void *args, int kind, int backward)
 {
@@ -907,6 +936,8 @@ TL_PAIR(pulp_softmax_fp32_bw_cl, pulp_softmax_fp16_bw_cl, softmax_bw_impl<F32>(a
 TL_PAIR(pulp_instnorm_fp32_fw_cl, pulp_instnorm_fp16_fw_cl, instnorm_impl<F32>(a, STEP_FW), instnorm_impl<F16>(a, STEP_FW))
 TL_PAIR(pulp_instnorm_fp32_bw_param_grads_cl, pulp_instnorm_fp16_bw_param_grads_cl, instnorm_impl<F32>(a, STEP_WGT_GRAD), instnorm_impl<F16>(a, STEP_WGT_GRAD))
 TL_PAIR(pulp_instnorm_fp32_bw_input_grads_cl, pulp_instnorm_fp16_bw_input_grads_cl, instnorm_impl<F32>(a, STEP_IN_GRAD), instnorm_impl<F16>(a, STEP_IN_GRAD))
+TL_PAIR(trainlib_instnorm_act_fp32_fw_cl, trainlib_instnorm_act_fp16_fw_cl, instnorm_act_impl<F32>(a, 0), instnorm_act_impl<F16>(a, 0))
+TL_PAIR(trainlib_instnorm_act_fp32_bw_cl, trainlib_instnorm_act_fp16_bw_cl, instnorm_act_impl<F32>(a, 1), instnorm_act_impl<F16>(a, 1))
 TL_EXPORT void pulp_instnorm_parallelized_fp32_fw_cl(void *a) { instnorm_impl<F32>(a, STEP_FW); }
 TL_EXPORT void pulp_instnorm_parallelized_fp32_bw_input_grads_cl(void *a) { instnorm_impl<F32>(a, STEP_IN_GRAD); }
 TL_EXPORT void pulp_instnorm_parallelized_fp32_bw_param_grads_cl(void *a) { instnorm_impl<F32>(a, STEP_WGT_GRAD); }

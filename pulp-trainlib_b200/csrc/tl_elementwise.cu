@@ -317,10 +317,13 @@ __global__ void __launch_bounds__(128) instnorm_param_reduce_kernel(const float 
 
 // fp32 planes of up to 1024 elements (a multiple of 4): one warp per plane, the plane held in registers as NV 16-byte
 // vectors per lane, so every element is read once and the reductions are warp shuffles without a CTA barrier.
-template <int NV>
+// RELU / SKIP fuse what follows the norm in a residual network into the same pass: y = relu(norm(x) + skip), each part optional,
+// with the operations (and so the bits) of the separate norm, sum and ReLU kernels.
+__device__ __forceinline__ float relu_of(float v) { return v > 0.f ? v : 0.f; }
+template <int NV, bool RELU, bool SKIP>
 __global__ void __launch_bounds__(256) instnorm_fw_warp_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ gb,
                                                                float *__restrict__ mean_o, float *__restrict__ var_o, float *__restrict__ std_o,
-                                                               long long planes, int C, int D, int frozen, float eps)
+                                                               long long planes, int C, int D, int frozen, float eps, const float *__restrict__ skip)
 {
     const int lane = threadIdx.x & 31;
     const long long plane = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -358,11 +361,19 @@ __global__ void __launch_bounds__(256) instnorm_fw_warp_kernel(const float *__re
             float4 o;
             o.x = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].x, mean)), beta); o.y = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].y, mean)), beta);
             o.z = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].z, mean)), beta); o.w = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v[i].w, mean)), beta);
+            if (SKIP) {
+                const float4 k = reinterpret_cast<const float4 *>(skip + plane * D)[lane + 32 * i];
+                o.x = __fadd_rn(k.x, o.x); o.y = __fadd_rn(k.y, o.y); o.z = __fadd_rn(k.z, o.z); o.w = __fadd_rn(k.w, o.w);
+            }
+            if (RELU) { o.x = relu_of(o.x); o.y = relu_of(o.y); o.z = relu_of(o.z); o.w = relu_of(o.w); }
             yp[lane + 32 * i] = o;
         }
 }
 // Backward of the same planes: both plane sums once, then dX and/or the per-plane (dgamma, dbeta) partials.
-template <int NV, bool DX, bool PART>
+// GATE: dy is the gradient behind a ReLU that followed the norm; the norm's output is recomputed from x with the forward's own
+// operations and dy counts only where that output is positive (gamma points at [gamma | beta] then).
+__device__ __forceinline__ float gated(float dy, float xm, float scale, float beta) { return __fadd_rn(__fmul_rn(scale, xm), beta) > 0.f ? dy : 0.f; }
+template <int NV, bool DX, bool PART, bool GATE>
 __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
                                                                float *__restrict__ part, const float *__restrict__ gamma,
                                                                const float *__restrict__ mean_i, const float *__restrict__ var_i,
@@ -382,9 +393,14 @@ __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__re
         g[i] = in ? gp[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float s = 0.f, p = 0.f;     // s = sum dy, p = sum (x - mean) dy
+    const float gsc = GATE ? __fdiv_rn(gamma[ch], sd) : 0.f, gbeta = GATE ? gamma[C + ch] : 0.f;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        if (GATE) {
+            g[i].x = gated(g[i].x, v[i].x, gsc, gbeta); g[i].y = gated(g[i].y, v[i].y, gsc, gbeta);
+            g[i].z = gated(g[i].z, v[i].z, gsc, gbeta); g[i].w = gated(g[i].w, v[i].w, gsc, gbeta);
+        }
         s += (g[i].x + g[i].y) + (g[i].z + g[i].w);
         p = fmaf(v[i].x, g[i].x, p); p = fmaf(v[i].y, g[i].y, p); p = fmaf(v[i].z, g[i].z, p); p = fmaf(v[i].w, g[i].w, p);
     }
@@ -411,9 +427,10 @@ __device__ __forceinline__ float half_warp_sum(float v)
     for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+template <bool RELU, bool SKIP>
 __global__ void __launch_bounds__(256) instnorm_fw_half_kernel(const float *__restrict__ x, float *__restrict__ y, const float *__restrict__ gb,
                                                                float *__restrict__ mean_o, float *__restrict__ var_o, float *__restrict__ std_o,
-                                                               long long planes, int C, int D, int frozen, float eps)
+                                                               long long planes, int C, int D, int frozen, float eps, const float *__restrict__ skip)
 {
     const int l16 = threadIdx.x & 15;
     const long long plane = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
@@ -442,9 +459,14 @@ __global__ void __launch_bounds__(256) instnorm_fw_half_kernel(const float *__re
     float4 o;
     o.x = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.x, mean)), beta); o.y = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.y, mean)), beta);
     o.z = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.z, mean)), beta); o.w = __fadd_rn(__fmul_rn(gamma, __fsub_rn(v.w, mean)), beta);
+    if (SKIP) {
+        const float4 k = reinterpret_cast<const float4 *>(skip + plane * D)[l16];
+        o.x = __fadd_rn(k.x, o.x); o.y = __fadd_rn(k.y, o.y); o.z = __fadd_rn(k.z, o.z); o.w = __fadd_rn(k.w, o.w);
+    }
+    if (RELU) { o.x = relu_of(o.x); o.y = relu_of(o.y); o.z = relu_of(o.z); o.w = relu_of(o.w); }
     reinterpret_cast<float4 *>(y + plane * D)[l16] = o;
 }
-template <bool DX, bool PART>
+template <bool DX, bool PART, bool GATE>
 __global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
                                                                float *__restrict__ part, const float *__restrict__ gamma,
                                                                const float *__restrict__ mean_i, const float *__restrict__ var_i,
@@ -457,8 +479,13 @@ __global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__re
     const bool in = live && l16 < D4;
     const float mean = live ? mean_i[plane] : 0.f, sd = live ? std_i[plane] : 1.f;
     float4 v = in ? reinterpret_cast<const float4 *>(x + plane * D)[l16] : make_float4(mean, mean, mean, mean);
-    const float4 g = in ? reinterpret_cast<const float4 *>(dy + plane * D)[l16] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 g = in ? reinterpret_cast<const float4 *>(dy + plane * D)[l16] : make_float4(0.f, 0.f, 0.f, 0.f);
     v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+    if (GATE && in) {
+        const int ch = (int)(plane % C);
+        const float gsc = __fdiv_rn(gamma[ch], sd), gbeta = gamma[C + ch];
+        g.x = gated(g.x, v.x, gsc, gbeta); g.y = gated(g.y, v.y, gsc, gbeta); g.z = gated(g.z, v.z, gsc, gbeta); g.w = gated(g.w, v.w, gsc, gbeta);
+    }
     float s = (g.x + g.y) + (g.z + g.w), p = fmaf(v.x, g.x, fmaf(v.y, g.y, fmaf(v.z, g.z, v.w * g.w)));
     s = half_warp_sum(s); p = half_warp_sum(p);
     if (PART && live && l16 == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
@@ -472,7 +499,7 @@ __global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__re
 }
 // Planes of 513..1024 elements: two warps per plane (4 sixteen-byte vectors of x and of dY per lane instead of 8), which
 // halves the registers per thread and doubles the warps in flight; the two warp sums meet in shared memory.
-template <bool DX, bool PART>
+template <bool DX, bool PART, bool GATE>
 __global__ void __launch_bounds__(256) instnorm_bw_pair_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
                                                                float *__restrict__ part, const float *__restrict__ gamma,
                                                                const float *__restrict__ mean_i, const float *__restrict__ var_i,
@@ -500,9 +527,15 @@ __global__ void __launch_bounds__(256) instnorm_bw_pair_kernel(const float *__re
         for (int i = 0; i < 4; i++) { v[i] = make_float4(0.f, 0.f, 0.f, 0.f); g[i] = v[i]; }
     }
     float s = 0.f, p = 0.f;
+    float gsc = 0.f, gbeta = 0.f;
+    if (GATE && live) { const int gch = (int)(plane % C); gsc = __fdiv_rn(gamma[gch], sd); gbeta = gamma[C + gch]; }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        if (GATE) {
+            g[i].x = gated(g[i].x, v[i].x, gsc, gbeta); g[i].y = gated(g[i].y, v[i].y, gsc, gbeta);
+            g[i].z = gated(g[i].z, v[i].z, gsc, gbeta); g[i].w = gated(g[i].w, v[i].w, gsc, gbeta);
+        }
         s += (g[i].x + g[i].y) + (g[i].z + g[i].w);
         p = fmaf(v[i].x, g[i].x, p); p = fmaf(v[i].y, g[i].y, p); p = fmaf(v[i].z, g[i].z, p); p = fmaf(v[i].w, g[i].w, p);
     }
@@ -533,54 +566,62 @@ static inline int instnorm_nv(int D) { return (D % 4 != 0 || D > 1024) ? 0 : (D 
 #define TL_NV_SWITCH(nv, CALL)                                                                                         \
     do { if ((nv) == 1) { CALL(1); } else if ((nv) == 2) { CALL(2); } else if ((nv) == 4) { CALL(4); } else { CALL(8); } } while (0)
 
-static bool instnorm_fw_warp(const float *x, float *y, const float *gb, float *mean, float *var, float *stdev, int n, int C, int D, bool frozen, float eps)
+template <bool RELU, bool SKIP>
+static void instnorm_fw_warp_launch(const float *x, float *y, const float *gb, float *mean, float *var, float *stdev, long long planes, int C, int D,
+                                    bool frozen, float eps, const float *skip, int nv)
 {
-    const int nv = instnorm_nv(D);
-    if (!nv || !aligned16(x, y, nullptr)) return false;
-    const long long planes = (long long)n * C;
     if (D <= 64) {
-        TL_LAUNCH(instnorm_fw_half_kernel, (unsigned)((planes + 15) / 16), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps);
-        return true;
+        TL_LAUNCH((instnorm_fw_half_kernel<RELU, SKIP>), (unsigned)((planes + 15) / 16), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps, skip);
+        return;
     }
-#define TL_CALL(NV) TL_LAUNCH((instnorm_fw_warp_kernel<NV>), (unsigned)((planes + 7) / 8), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps)
+#define TL_CALL(NV) TL_LAUNCH((instnorm_fw_warp_kernel<NV, RELU, SKIP>), (unsigned)((planes + 7) / 8), 256, 0, x, y, gb, mean, var, stdev, planes, C, D, frozen ? 1 : 0, eps, skip)
     TL_NV_SWITCH(nv, TL_CALL);
 #undef TL_CALL
+}
+static bool instnorm_fw_warp(const float *x, float *y, const float *gb, float *mean, float *var, float *stdev, int n, int C, int D, bool frozen, float eps,
+                             const float *skip = nullptr, bool relu = false)
+{
+    const int nv = instnorm_nv(D);
+    if (!nv || !aligned16(x, y, skip)) return false;
+    const long long planes = (long long)n * C;
+    if (relu && skip) instnorm_fw_warp_launch<true, true>(x, y, gb, mean, var, stdev, planes, C, D, frozen, eps, skip, nv);
+    else if (relu) instnorm_fw_warp_launch<true, false>(x, y, gb, mean, var, stdev, planes, C, D, frozen, eps, skip, nv);
+    else if (skip) instnorm_fw_warp_launch<false, true>(x, y, gb, mean, var, stdev, planes, C, D, frozen, eps, skip, nv);
+    else instnorm_fw_warp_launch<false, false>(x, y, gb, mean, var, stdev, planes, C, D, frozen, eps, skip, nv);
     return true;
 }
-template <class T> static bool instnorm_fw_warp(const T *, T *, const T *, T *, T *, T *, int, int, int, bool, float) { return false; }
+template <class T> static bool instnorm_fw_warp(const T *, T *, const T *, T *, T *, T *, int, int, int, bool, float, const T * = nullptr, bool = false) { return false; }
 // dx and/or part may be null: the kernel variant is chosen accordingly
 static bool instnorm_bw_warp(const float *x, const float *dy, float *dx, float *part, const float *gamma, const float *mean, const float *var,
-                             const float *stdev, int n, int C, int D)
+                             const float *stdev, int n, int C, int D, bool gate = false)
 {
     const int nv = instnorm_nv(D);
     if (!nv || !aligned16(x, dy, dx)) return false;
+    if (gate && !(dx && part)) return false;           // the gated form exists for the one-pass backward only
     const long long planes = (long long)n * C;
+#define TL_BW_VARIANTS(KERNEL, GRID, ...)                                                                              \
+    do {                                                                                                               \
+        if (gate) TL_LAUNCH((KERNEL<__VA_ARGS__ true, true, true>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);              \
+        else if (dx && part) TL_LAUNCH((KERNEL<__VA_ARGS__ true, true, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);  \
+        else if (dx) TL_LAUNCH((KERNEL<__VA_ARGS__ true, false, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);         \
+        else TL_LAUNCH((KERNEL<__VA_ARGS__ false, true, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);                 \
+    } while (0)
     if (D <= 64) {
-        const unsigned b16 = (unsigned)((planes + 15) / 16);
-        if (dx && part) TL_LAUNCH((instnorm_bw_half_kernel<true, true>), b16, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
-        else if (dx) TL_LAUNCH((instnorm_bw_half_kernel<true, false>), b16, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
-        else TL_LAUNCH((instnorm_bw_half_kernel<false, true>), b16, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        TL_BW_VARIANTS(instnorm_bw_half_kernel, (unsigned)((planes + 15) / 16), );
         return true;
     }
     if (nv == 8) {
-        const unsigned b4 = (unsigned)((planes + 3) / 4);
-        if (dx && part) TL_LAUNCH((instnorm_bw_pair_kernel<true, true>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
-        else if (dx) TL_LAUNCH((instnorm_bw_pair_kernel<true, false>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
-        else TL_LAUNCH((instnorm_bw_pair_kernel<false, true>), b4, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);
+        TL_BW_VARIANTS(instnorm_bw_pair_kernel, (unsigned)((planes + 3) / 4), );
         return true;
     }
     const unsigned blocks = (unsigned)((planes + 7) / 8);
-#define TL_CALL(NV)                                                                                                    \
-    do {                                                                                                               \
-        if (dx && part) TL_LAUNCH((instnorm_bw_warp_kernel<NV, true, true>), blocks, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);   \
-        else if (dx) TL_LAUNCH((instnorm_bw_warp_kernel<NV, true, false>), blocks, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);     \
-        else TL_LAUNCH((instnorm_bw_warp_kernel<NV, false, true>), blocks, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);             \
-    } while (0)
-    TL_NV_SWITCH(nv, TL_CALL);
-#undef TL_CALL
+    if (nv == 1) TL_BW_VARIANTS(instnorm_bw_warp_kernel, blocks, 1, );
+    else if (nv == 2) TL_BW_VARIANTS(instnorm_bw_warp_kernel, blocks, 2, );
+    else TL_BW_VARIANTS(instnorm_bw_warp_kernel, blocks, 4, );
+#undef TL_BW_VARIANTS
     return true;
 }
-template <class T> static bool instnorm_bw_warp(const T *, const T *, T *, float *, const T *, const T *, const T *, const T *, int, int, int) { return false; }
+template <class T> static bool instnorm_bw_warp(const T *, const T *, T *, float *, const T *, const T *, const T *, const T *, int, int, int, bool = false) { return false; }
 
 template <class T>
 void instnorm_fw(const T *x, T *y, const T *gb, T *mean, T *var, T *stdev, int n, int C, int D, bool frozen, float eps)
@@ -619,6 +660,34 @@ void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *dx, T *dgb, const T
     }
     instnorm_bw_param<T>(sc, x, dy, dgb, mean, stdev, n, C, D);
     instnorm_bw_input<T>(x, dy, dx, gamma, mean, var, stdev, n, C, D);
+}
+
+// y = relu(norm(x) + skip) with `skip` and the ReLU optional.  One pass where the plane shape has a warp kernel, otherwise the
+// norm, sum and ReLU kernels one after the other (same values either way).
+template <class T>
+void instnorm_act_fw(const T *x, T *y, const T *skip, const T *gb, T *mean, T *var, T *stdev, int n, int C, int D, bool frozen, float eps, bool relu)
+{
+    if (n * C <= 0) return;
+    if (instnorm_fw_warp(x, y, gb, mean, var, stdev, n, C, D, frozen, eps, skip, relu)) return;
+    const long long total = (long long)n * C * D;
+    instnorm_fw<T>(x, y, gb, mean, var, stdev, n, C, D, frozen, eps);
+    if (skip) add<T>(skip, y, y, total);
+    if (relu) act_fw<T>(ACT_RELU, y, y, total, 0.f);
+}
+// Backward of y = relu(norm(x)): both gradients of the norm from dL/dy.  `y` (the forward output) and `dy` are only touched
+// by the fallback, which masks dy in place.
+template <class T>
+void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, T *dx, T *dgb, const T *gb, const T *mean, const T *var, const T *stdev, int n, int C, int D)
+{
+    if (n * C <= 0) return;
+    float *part = sc.scratch<float>((size_t)2 * n * C);
+    if (!part) return;
+    if (instnorm_bw_warp(x, dy, dx, part, gb, mean, var, stdev, n, C, D, true)) {
+        TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
+        return;
+    }
+    act_bw<T>(ACT_RELU, y, (const T *)nullptr, dy, dy, (long long)n * C * D, 0.f);
+    instnorm_bw_both<T>(sc, x, dy, dx, dgb, gb, mean, var, stdev, n, C, D);
 }
 
 // ------------------------------------------------------------------ batch norm / layer norm (forward)
@@ -1007,6 +1076,8 @@ template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int pad
     template void instnorm_bw_input<T>(const T *, const T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void instnorm_bw_param<T>(Scope &, const T *, const T *, T *, const T *, const T *, int, int, int);   \
     template void instnorm_bw_both<T>(Scope &, const T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
+    template void instnorm_act_fw<T>(const T *, T *, const T *, const T *, T *, T *, T *, int, int, int, bool, float, bool);             \
+    template void instnorm_relu_bw<T>(Scope &, const T *, const T *, T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void batchnorm_fw<T>(const T *, T *, const T *, const T *, int, int, int, int, float);                \
     template void layernorm_fw<T>(const T *, T *, const T *, const T *, int, int, float);                          \
     template void layernorm_bw<T>(Scope &, const T *, const T *, const T *, T *, T *, T *, int, int, float);      \

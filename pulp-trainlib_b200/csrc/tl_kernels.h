@@ -68,6 +68,11 @@ template <class T> void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T 
                                           const T *stdev, int n, int C, int D);
 template <class T> void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *dx, T *dgamma_beta, const T *gamma, const T *mean,
                                          const T *var, const T *stdev, int n, int C, int D);
+// y = relu(norm(x) + skip) in one pass (skip may be null, relu false), and the backward of y = relu(norm(x)) from dL/dy.
+template <class T> void instnorm_act_fw(const T *x, T *y, const T *skip, const T *gamma_beta, T *mean, T *var, T *stdev,
+                                        int n, int C, int D, bool frozen, float eps, bool relu);
+template <class T> void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, T *dx, T *dgamma_beta, const T *gamma_beta, const T *mean,
+                                         const T *var, const T *stdev, int n, int C, int D);
 template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps);
 template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps);
 template <class T> void layernorm_bw(Scope &sc, const T *x, const T *w, const T *dy, T *dx, T *dw, T *db, int rows, int width, float eps);

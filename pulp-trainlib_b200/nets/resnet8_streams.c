@@ -82,6 +82,27 @@ static void norm_bw(struct InstNorm_args *a)
     pulp_instnorm_fp32_bw_cl(a);
 #endif
 }
+#ifndef NET_REFERENCE
+/* The library can run a norm, the residual sum behind it and the ReLU in one pass over the activation (same values as the
+   three calls); resnet8_set_fusion(0) goes back to the separate calls. */
+static int g_fuse = 1;
+void resnet8_set_fusion(int on) { g_fuse = on != 0; }
+static void norm_act_fw(struct InstNorm_args *a, struct blob *skip, int relu)
+{
+    struct trainlib_instnorm_act_args f; f.norm = a; f.skip = skip; f.relu = relu;
+    trainlib_instnorm_act_fp32_fw_cl(&f);
+}
+static void norm_relu_bw(struct InstNorm_args *a)
+{
+    struct trainlib_instnorm_act_args f; f.norm = a; f.skip = NULL; f.relu = 1;
+    trainlib_instnorm_act_fp32_bw_cl(&f);
+}
+#else
+enum { g_fuse = 0 };
+void resnet8_set_fusion(int on) { (void)on; }
+static void norm_act_fw(struct InstNorm_args *a, struct blob *skip, int relu) { (void)a; (void)skip; (void)relu; }
+static void norm_relu_bw(struct InstNorm_args *a) { (void)a; }
+#endif
 static void relu_fw(struct act_args *a)
 {
 #ifdef NET_REFERENCE
@@ -338,6 +359,15 @@ float *resnet8_logits(void) { return b_z.data; }
 
 static void stage(int conv_a, int norm_a, int conv_b, int norm_b, int proj, int r)
 {
+    if (g_fuse) {
+        conv_fw(&a_conv[conv_a]); norm_act_fw(&a_norm[norm_a], NULL, 1);
+        if (proj >= 0) conv_fw(&a_conv[proj]);
+        conv_fw(&a_conv[conv_b]);
+        /* the sum goes where the separate calls leave it: the norm writes relu(norm + skip) straight into the sum's blob */
+        struct InstNorm_args t = a_norm[norm_b]; t.output = a_res[r].output;
+        norm_act_fw(&t, a_res[r].skip, 1);
+        return;
+    }
     conv_fw(&a_conv[conv_a]); norm_fw(&a_norm[norm_a]); relu_fw(&a_relu_n[norm_a]);
     conv_fw(&a_conv[conv_b]); norm_fw(&a_norm[norm_b]);
     if (proj >= 0) conv_fw(&a_conv[proj]);
@@ -348,7 +378,8 @@ static void stage(int conv_a, int norm_a, int conv_b, int norm_b, int proj, int 
 void resnet8_forward(const float *images, const float *labels, float *loss)
 {
     b_x.data = (float *)images;
-    conv_fw(&a_conv[C0]); norm_fw(&a_norm[0]); relu_fw(&a_relu_n[0]);
+    conv_fw(&a_conv[C0]);
+    if (g_fuse) norm_act_fw(&a_norm[0], NULL, 1); else { norm_fw(&a_norm[0]); relu_fw(&a_relu_n[0]); }
     stage(C1, 1, C2, 2, -1, 0);
     stage(C3, 3, C4, 4, P2, 1);
     stage(C5, 5, C6, 6, P3, 2);
@@ -383,7 +414,7 @@ static void stage_bw(int conv_a, int norm_a, int conv_b, int norm_b, int proj, i
 {
     relu_bw(&a_relu_s[r]);                         /* sum.diff masked in place; norm_b and the shortcut share it */
     norm_bw(&a_norm[norm_b]); conv_bw(conv_b);
-    relu_bw(&a_relu_n[norm_a]); norm_bw(&a_norm[norm_a]);
+    if (g_fuse) norm_relu_bw(&a_norm[norm_a]); else { relu_bw(&a_relu_n[norm_a]); norm_bw(&a_norm[norm_a]); }
     conv_bw(conv_a);                               /* writes the stage input's gradient */
     if (proj >= 0) {
         struct blob *in = a_conv[proj].input; float *keep = in->diff;
@@ -405,7 +436,8 @@ void resnet8_backward(void)
     stage_bw(C5, 5, C6, 6, P3, 2);
     stage_bw(C3, 3, C4, 4, P2, 1);
     stage_bw(C1, 1, C2, 2, -1, 0);
-    relu_bw(&a_relu_n[0]); norm_bw(&a_norm[0]); conv_bw(C0);
+    if (g_fuse) norm_relu_bw(&a_norm[0]); else { relu_bw(&a_relu_n[0]); norm_bw(&a_norm[0]); }
+    conv_bw(C0);
 #ifndef NET_REFERENCE
     if (g_host_slot >= 0) { trainlib_mark_consumed(g_host_slot); g_host_slot = -1; }   /* last reader of that batch copy */
 #endif

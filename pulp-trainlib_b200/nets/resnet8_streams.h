@@ -37,6 +37,7 @@ void   resnet8_update(float lr);                  /* SGD on every parameter blob
 float *resnet8_logits(void);                      /* [n][10], inside the workspace */
 int    resnet8_param_blobs(void);                 /* number of parameter tensors */
 size_t resnet8_param_offset(int i, size_t *count);/* offset/size of parameter tensor i in the flat buffer */
+void   resnet8_set_fusion(int on);                /* 1 (default): norm + residual sum + ReLU as one library call; 0: separate calls */
 double resnet8_flops_per_stream(void);            /* FW + WG + IG multiply-add FLOPs of the convs and the Linear */
 
 #ifdef __cplusplus

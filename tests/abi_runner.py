@@ -283,6 +283,30 @@ class AbiRunner(object):
         self.pkg.check(self.lib)
         return dict(y=Y.get().copy(), dx=dX.get().copy(), dw=dW.get().copy(), db=dB.get().copy())
 
+    def instnorm_act(self, x, gb, dy, skip=None, relu=True, backward=True, n=1):
+        """the library's fused norm (+ skip sum) (+ ReLU): one forward call, one backward call; x is [n][C][H][W] when n > 1"""
+        import ctypes
+
+        class FusedArgs(ctypes.Structure):
+            _fields_ = [("norm", ctypes.c_void_p), ("skip", ctypes.c_void_p), ("relu", ctypes.c_int)]
+        C, H, W = x.shape[-3:]
+        X, dX, Y, dY = self.t(x), self.zeros(*x.shape), self.zeros(*x.shape), self.t(dy)
+        GB, dGB = self.t(gb), self.zeros(2 * C)
+        m, v, s = self.zeros(n * C), self.zeros(n * C), self.zeros(n * C)
+        norm = self.args(self.sname("InstNorm_args"), input=self.blob(X, dX, C=C, H=H, W=W), output=self.blob(Y, dY, C=C, H=H, W=W),
+                         coeff=self.blob(GB, dGB, dim=2 * C, W=2 * C), running_mean=m, running_var=v, running_stdev=s,
+                         freeze_running_params=0, skip_wg_grad=0, skip_in_grad=0)
+        f = FusedArgs(); f.norm = ctypes.addressof(norm); f.relu = 1 if relu else 0
+        if skip is not None:
+            S = self.t(skip); sb = self.blob(S, None, C=C, H=H, W=W); f.skip = ctypes.addressof(sb)
+        self.keep.hold(f)
+        getattr(self.lib, self.fname("trainlib_instnorm_act_fp32_fw_cl"))(ctypes.byref(f)); self.pkg.check(self.lib)
+        out = dict(y=Y.get().copy(), mean=m.get().copy(), std=s.get().copy())
+        if backward:
+            getattr(self.lib, self.fname("trainlib_instnorm_act_fp32_bw_cl"))(ctypes.byref(f)); self.pkg.check(self.lib)
+            out.update(dx=dX.get().copy(), dgb=dGB.get().copy())
+        return out
+
     def gelu_bw(self, x, dy):
         import ctypes
         X, dX, Y, dY = self.t(x), self.zeros(*x.shape), self.zeros(*x.shape), self.t(dy)

@@ -476,3 +476,63 @@ def test_conv2d_hwc_layout(run, oracle, g):
     assert_close(got["y"].reshape(Ho, Wo, g["Cout"]).transpose(2, 0, 1), oracle.conv2d_fw(x, w, None, g), FP32_TOL, "hwc fw")
     assert_close(got["dw"].reshape(g["Cout"], g["Hk"], g["Wk"], g["Cin"]).transpose(0, 3, 1, 2), oracle.conv2d_wg(x, dy, g)[0], FP32_TOL, "hwc wg")
     assert_close(got["dx"].reshape(g["Hin"], g["Win"], g["Cin"]).transpose(2, 0, 1), oracle.conv2d_ig(dy, w, g), FP32_TOL, "hwc ig")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("C,H,W,n", [(16, 32, 32, 3), (32, 16, 16, 2), (64, 8, 8, 5), (6, 12, 12, 2), (3, 7, 7, 1), (4, 40, 40, 1)],
+                         ids=["32x32_pair", "16x16_warp", "8x8_half", "12x12_warp1", "7x7_generic", "40x40_generic"])
+@pytest.mark.parametrize("with_skip", [False, True], ids=["relu", "skip_relu"])
+def test_instnorm_fused_with_sum_and_relu(pkg, gpulib, oracle, C, H, W, n, with_skip):
+    """trainlib_instnorm_act_*: one pass must give the bits of norm -> (+ skip) -> ReLU made of the reference's three calls, and
+    its backward those of ReLU backward -> norm backward; the three calls themselves are checked against the oracle."""
+    rng = seeded(77)
+    x = rng.standard_normal((n, C, H, W)).astype(F); gb = rng.standard_normal(2 * C).astype(F); dy = rng.standard_normal(x.shape).astype(F)
+    skip = rng.standard_normal(x.shape).astype(F) if with_skip else None
+    gpulib.trainlib_set_streams(n)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        fused = r.instnorm_act(x, gb, dy, skip=skip, relu=True, backward=not with_skip, n=n)
+        # the separate calls
+        X, dX, Y, dY, GB, dGB = r.t(x), r.zeros(*x.shape), r.zeros(*x.shape), r.t(dy), r.t(gb), r.zeros(2 * C)
+        m, v, sd = r.zeros(n * C), r.zeros(n * C), r.zeros(n * C)
+        a = r.args("InstNorm_args", input=r.blob(X, dX, C=C, H=H, W=W), output=r.blob(Y, dY, C=C, H=H, W=W), coeff=r.blob(GB, dGB, dim=2 * C, W=2 * C),
+                   running_mean=m, running_var=v, running_stdev=sd, freeze_running_params=0, skip_wg_grad=0, skip_in_grad=0)
+        r.call("pulp_instnorm_fp32_fw_cl", a)
+        y_norm = Y.get().copy()
+        want = y_norm + skip if with_skip else y_norm          # one fp32 addition per element, as pulp_residualconn_fp32_fw
+        want = np.where(want > 0, want, F(0)).astype(F)
+        assert np.array_equal(fused["y"], want), "fused forward differs from the three calls"
+        assert np.array_equal(fused["mean"], m.get()) and np.array_equal(fused["std"], sd.get())
+        for s in range(n):
+            o = oracle.instnorm(x[s], gb, dy[s])
+            ws = o["y"] + skip[s] if with_skip else o["y"]
+            assert_close(fused["y"][s], np.maximum(ws, 0), FP32_TOL, "fused forward vs oracle")
+        if not with_skip:
+            dY.set(np.where(want > 0, dy, F(0)).astype(F))      # pulp_relu_fp32_bw_cl
+            r.call("pulp_instnorm_fp32_bw_cl", a)
+            assert np.array_equal(fused["dx"], dX.get()), "fused backward dX differs from ReLU backward + norm backward"
+            assert np.array_equal(fused["dgb"], dGB.get()), "fused backward parameter gradient differs"
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1)
+
+
+@pytest.mark.gpu
+def test_instnorm_fused_fp16_and_rejections(pkg, gpulib):
+    """fp16 twin (composed from the separate kernels) and the argument checks of the backward call"""
+    rng = seeded(78)
+    C, H, W = 8, 16, 16
+    x = rng.standard_normal((C, H, W)).astype(np.float16); gb = rng.standard_normal(2 * C).astype(np.float16); dy = rng.standard_normal(x.shape).astype(np.float16)
+    r = AbiRunner(pkg, gpulib, device=True, half=True)
+    fused = r.instnorm_act(x, gb, dy, relu=True)
+    plain = r.instnorm(x, gb, dy)
+    want = np.where(plain["y"] > 0, plain["y"], np.float16(0))
+    assert np.array_equal(fused["y"], want)
+    masked = r.instnorm(x, gb, np.where(want > 0, dy, np.float16(0)).astype(np.float16))
+    assert np.array_equal(fused["dx"], masked["dx"]) and np.array_equal(fused["dgb"], masked["dgb"])
+    r.close()
+    r = AbiRunner(pkg, gpulib, device=True)
+    x32 = x.astype(F)
+    with pytest.raises(Exception):
+        r.instnorm_act(x32, gb.astype(F), dy.astype(F), skip=x32, relu=True, backward=True)    # backward with a skip is refused
+    r.close()

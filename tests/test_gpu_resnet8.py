@@ -89,3 +89,19 @@ def test_resnet8_streams_are_independent(pkg, gpulib, path, tol_act, tol_grad):
     assert_close(whole["logits"][:32], a["logits"], tol_act, "logits of shard a"); assert_close(whole["logits"][32:], b["logits"], tol_act, "logits of shard b")
     assert_close(whole["loss"][:32], a["loss"], tol_act, "loss of shard a")
     assert_close(a["grads"] + b["grads"], whole["grads"], tol_grad, "gradient additivity over shards")
+
+
+@pytest.mark.gpu
+def test_resnet8_fused_norm_calls_change_nothing(pkg, gpulib):
+    """norm + residual sum + ReLU as one library call (the default of the net) against the separate reference calls: same bits
+    on the FFMA path, whose accumulation order is fixed"""
+    import bench_nets
+    net = bench_nets.bind_net(bench_nets.NET_B200)
+    gpulib.trainlib_set_gemm_path(1)
+    try:
+        net.resnet8_set_fusion(1); fused = gpu_step(pkg, gpulib, net, 48, first=3)
+        net.resnet8_set_fusion(0); plain = gpu_step(pkg, gpulib, net, 48, first=3)
+    finally:
+        net.resnet8_set_fusion(1); gpulib.trainlib_set_gemm_path(0)
+    for k in ("logits", "loss", "grads"):
+        assert np.array_equal(fused[k], plain[k]), "%s differs between fused and separate calls" % k
