@@ -98,19 +98,29 @@ void  trainlib_gelu_fp16_bw_cl(void *act_args_fp16);
 
 /* ---- Instance norm fused with what follows it in a residual network.  No counterpart in the reference, which runs
  * pulp_instnorm_*_fw_cl, pulp_residualconn_*_fw and pulp_relu_*_fw_cl one after the other
- * (lib/sources/pulp_instnorm_fp32.c:33, pulp_residual_fp32.c:71, pulp_act_fp32.c:96); results are those of that sequence,
+ * (lib/sources/pulp_instnorm_fp32.c:27, pulp_residual_fp32.c:26, pulp_act_fp32.c:83); results are those of that sequence,
  * bit for bit.  `norm` points at an InstNorm_args (fp32 entry points) or InstNorm_args_fp16.
  *   fw:  norm->output->data = relu(instnorm(norm->input->data) + skip->data); `skip` (a struct blob / blob_fp16 of the
  *        output's size) may be NULL and `relu` 0.  The running statistics are written as by the plain forward.
  *   bw:  norm->output->diff holds the gradient behind the ReLU (relu != 0, skip == NULL only): writes norm->input->diff
  *        and norm->coeff->diff like pulp_instnorm_*_bw_cl after pulp_relu_*_bw_cl.  norm->output->diff may be masked in
  *        place.  With a skip connection the ReLU's gradient has two readers, so mask it once with pulp_relu_*_bw_cl on the
- *        sum and call pulp_instnorm_*_bw_cl. */
-struct trainlib_instnorm_act_args { void *norm; void *skip; int relu; };
+ *        sum and call pulp_instnorm_*_bw_cl.
+ *        `diff2` (backward only; NULL or an array of the output's size and type): the gradient that a second reader of the
+ *        output left, e.g. an identity shortcut; it is added to norm->output->diff first, as pulp_sumnode_*_bw would
+ *        (lib/sources/pulp_residual_fp32.c:59), without writing the sum back. */
+struct trainlib_instnorm_act_args { void *norm; void *skip; int relu; void *diff2; };
 void  trainlib_instnorm_act_fp32_fw_cl(void *trainlib_instnorm_act_args);
 void  trainlib_instnorm_act_fp16_fw_cl(void *trainlib_instnorm_act_args);
 void  trainlib_instnorm_act_fp32_bw_cl(void *trainlib_instnorm_act_args);
 void  trainlib_instnorm_act_fp16_bw_cl(void *trainlib_instnorm_act_args);
+
+/* ---- Input gradient of Conv2D added to what input->diff already holds (CHW only).  No counterpart in the reference, where a
+ * shortcut convolution writes its input gradient to a buffer of its own and pulp_sumnode_*_bw adds it to the gradient of
+ * the main branch (lib/sources/pulp_conv2d_fp32.c:454, pulp_residual_fp32.c:59); the values are those of that pair of calls.
+ * A 1x1 strided convolution adds its samples in place and touches nothing between them. */
+void  trainlib_conv2d_fp32_bw_input_grads_acc_cl(void *Conv2D_args);
+void  trainlib_conv2d_fp16_bw_input_grads_acc_cl(void *Conv2D_args_fp16);
 
 /* ---- CUDA graphs.  Entry-point calls made between begin and end are recorded instead of executed (device pointers
  * only: a host pointer would need a synchronous copy); the handle replays them with one launch on the library's

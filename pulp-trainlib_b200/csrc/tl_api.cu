@@ -254,7 +254,7 @@ template <class F> void conv2d_wg_impl(void *args)
     }
     conv_wg<T>(sc, g, x, dy, dw, db);
 }
-template <class F> void conv2d_ig_impl(void *args)
+template <class F> void conv2d_ig_impl(void *args, bool accumulate = false)
 {
     auto *a = (typename F::conv2d_t *)args; typedef typename F::T T;
     if (!conv_flags_ok(a, "pulp_conv2d_bw_input_grads_cl")) return;
@@ -262,8 +262,14 @@ template <class F> void conv2d_ig_impl(void *args)
     Scope sc;
     const T *dy = sc.in(a->output->diff, (size_t)g.n * g.Cout * g.Hout * g.Wout);
     const T *w = sc.in(a->coeff->data, (size_t)g.Cout * g.Cin * g.Hk * g.Wk);
-    T *dx = sc.out(a->input->diff, (size_t)g.n * g.Cin * g.Hin * g.Win);
+    const size_t nx = (size_t)g.n * g.Cin * g.Hin * g.Win;
+    T *dx = accumulate ? sc.inout(a->input->diff, nx) : sc.out(a->input->diff, nx);
     if (!sc.ok()) return;
+    if (accumulate) {
+        TL_REQUIRE(a->HWC == 0, "trainlib_conv2d_bw_input_grads_acc_cl: HWC=%d (CHW only)", a->HWC);
+        conv_ig_accumulate<T>(sc, g, dy, w, dx);
+        return;
+    }
     if (a->HWC == 1) {
         const T *dyc = hwc_in<T>(sc, dy, g.n, g.Cout, g.Hout, g.Wout), *wc = hwc_in<T>(sc, w, g.Cout, g.Cin, g.Hk, g.Wk);
         T *dxc = sc.scratch<T>((size_t)g.n * g.Cin * g.Hin * g.Win);
@@ -611,8 +617,9 @@ template <class F> void instnorm_act_impl(void *args, int backward)
     TL_REQUIRE(f->relu != 0 && !skip, "trainlib_instnorm_act_bw: relu=%d skip=%p (mask the sum's gradient with pulp_relu_bw and call pulp_instnorm_bw)", f->relu, f->skip);
     const T *x = sc.in(a->input->data, nx), *y = sc.in(a->output->data, nx), *gb = sc.in(a->coeff->data, (size_t)2 * C);
     const T *m = sc.in(a->running_mean, ns), *v = sc.in(a->running_var, ns), *s = sc.in(a->running_stdev, ns);
+    const T *dy2 = f->diff2 ? sc.in((const T *)f->diff2, nx) : nullptr;
     T *dy = sc.inout(a->output->diff, nx), *dx = sc.out(a->input->diff, nx), *dgb = sc.out(a->coeff->diff, (size_t)2 * C);
-    if (sc.ok()) instnorm_relu_bw<T>(sc, x, y, dy, dx, dgb, gb, m, v, s, n, C, D);
+    if (sc.ok()) instnorm_relu_bw<T>(sc, x, y, dy, dy2, dx, dgb, gb, m, v, s, n, C, D);
 }
 
 // ------------------------------------------------------------------ losses, optimizer, residual, pooling
@@ -842,6 +849,7 @@ TL_PAIR(pulp_blocktransp_fp32, pulp_blocktransp_fp16, blocktransp_impl<F32>(a), 
 TL_PAIR(pulp_conv2d_fp32_fw_cl, pulp_conv2d_fp16_fw_cl, conv2d_fw_impl<F32>(a), conv2d_fw_impl<F16>(a))
 TL_PAIR(pulp_conv2d_fp32_bw_param_grads_cl, pulp_conv2d_fp16_bw_param_grads_cl, conv2d_wg_impl<F32>(a), conv2d_wg_impl<F16>(a))
 TL_PAIR(pulp_conv2d_fp32_bw_input_grads_cl, pulp_conv2d_fp16_bw_input_grads_cl, conv2d_ig_impl<F32>(a), conv2d_ig_impl<F16>(a))
+TL_PAIR(trainlib_conv2d_fp32_bw_input_grads_acc_cl, trainlib_conv2d_fp16_bw_input_grads_acc_cl, conv2d_ig_impl<F32>(a, true), conv2d_ig_impl<F16>(a, true))
 TL_EXPORT void pulp_conv2d_fp32_bw_cl(void *a)
 {
     auto *c = (Conv2D_args *)a;

@@ -234,9 +234,10 @@ __global__ void __launch_bounds__(256) conv_dilate_dy_kernel(const float *__rest
 
 // Input gradient of a 1x1 convolution with stride s and no padding: dX[ci][h*s][w*s] = sum_co W[co][ci] dY[co][h][w],
 // zero at every other position.  One CTA per (stream, tile of dY pixels): the weights and the dY tile sit in shared
-// memory, a thread owns one pixel and walks the input channels; a warp then writes whole output rows (the sample
-// rows with zeros between the samples, and the s-1 all-zero rows below each).
-template <int PX>
+// memory, a thread owns one pixel and walks the input channels, four at a time.  dX is zeroed by a kernel of its own
+// first; with ACC the samples are added to what dX holds instead (a gradient that another branch already wrote there),
+// and the positions between the samples are not touched at all.
+template <int PX, bool ACC>
 __global__ void __launch_bounds__(PX) conv1x1_strided_ig_kernel(ConvGeom g, const float *__restrict__ dy, const float *__restrict__ w, float *__restrict__ dx)
 {
     extern __shared__ __align__(16) float sm1[];
@@ -268,7 +269,8 @@ __global__ void __launch_bounds__(PX) conv1x1_strided_ig_kernel(ConvGeom g, cons
             if (live) {
                 float *o = dxs + ((size_t)ci * g.Hin + (size_t)ho * g.sh) * g.Win + (size_t)wo * g.sw;
                 const size_t pl = (size_t)g.Hin * g.Win;
-                o[0] = a0; o[pl] = a1; o[2 * pl] = a2; o[3 * pl] = a3;
+                if (ACC) { o[0] = __fadd_rn(a0, o[0]); o[pl] = __fadd_rn(a1, o[pl]); o[2 * pl] = __fadd_rn(a2, o[2 * pl]); o[3 * pl] = __fadd_rn(a3, o[3 * pl]); }
+                else { o[0] = a0; o[pl] = a1; o[2 * pl] = a2; o[3 * pl] = a3; }
             }
         }
         return;
@@ -276,7 +278,10 @@ __global__ void __launch_bounds__(PX) conv1x1_strided_ig_kernel(ConvGeom g, cons
     for (int ci = 0; ci < g.Cin; ci++) {
         float acc = 0.f;
         for (int co = 0; co < g.Cout; co++) acc = fmaf(ws[co * g.Cin + ci], dys[co * PX + threadIdx.x], acc);
-        if (live) dxs[((size_t)ci * g.Hin + (size_t)ho * g.sh) * g.Win + (size_t)wo * g.sw] = acc;
+        if (live) {
+            float *o = dxs + ((size_t)ci * g.Hin + (size_t)ho * g.sh) * g.Win + (size_t)wo * g.sw;
+            *o = ACC ? __fadd_rn(acc, *o) : acc;
+        }
     }
 }
 // zero fill of dX before the scattered samples are written (16-byte stores)
@@ -285,6 +290,32 @@ __global__ void __launch_bounds__(256) zero_f4_kernel(float4 *__restrict__ p, si
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n4; e += (size_t)gridDim.x * blockDim.x) p[e] = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
+// 1x1, strided, unpadded: a small per-pixel matrix product scattered onto a zeroed dX (or added into dX); bandwidth-bound,
+// no tensor cores.  False when the geometry or the path selection rules it out.
+static bool try_conv1x1_ig(const ConvGeom &g, const float *dy, const float *w, float *dx, bool acc)
+{
+    if (!(g.Hk == 1 && g.Wk == 1 && g.padU == 0 && g.padL == 0 && !g.depthwise && gemm_path() != 1 && (((uintptr_t)dx) & 15) == 0 && (g.Hin * g.Win) % 4 == 0 &&
+          (g.sh > 1 || g.sw > 1) && (long long)(g.Hout - 1) * g.sh < g.Hin && (long long)(g.Wout - 1) * g.sw < g.Win))
+        return false;
+    const int opix = g.Hout * g.Wout, PX = opix >= 256 ? 256 : 64;
+    const size_t smem = ((size_t)g.Cout * g.Cin + (size_t)g.Cout * PX) * sizeof(float);
+    if (smem > 160 * 1024) return false;
+    if (!acc) {
+        const size_t n4 = (size_t)g.n * g.Cin * g.Hin * g.Win / 4;
+        TL_LAUNCH(zero_f4_kernel, (unsigned)std::min<size_t>((n4 + 255) / 256, (size_t)sm_count() * 32), 256, 0, reinterpret_cast<float4 *>(dx), n4);
+    }
+    const unsigned grid = (unsigned)g.n * (unsigned)((opix + PX - 1) / PX);
+#define TL_1X1(PXV, ACCV)                                                                                              \
+    do {                                                                                                               \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(conv1x1_strided_ig_kernel<PXV, ACCV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        TL_LAUNCH((conv1x1_strided_ig_kernel<PXV, ACCV>), grid, PXV, smem, g, dy, w, dx);                               \
+    } while (0)
+    if (PX == 256) { if (acc) TL_1X1(256, true); else TL_1X1(256, false); }
+    else { if (acc) TL_1X1(64, true); else TL_1X1(64, false); }
+#undef TL_1X1
+    return true;
+}
+template <class T> static bool try_conv1x1_ig(const ConvGeom &, const T *, const T *, T *, bool) { return false; }
 template <class T> static bool try_tc_ig(Scope &, const ConvGeom &, const T *, const T *, T *) { return false; }
 template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy, const float *w, float *dx)
 {
@@ -293,25 +324,7 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
     if (g.sh == 1 && g.sw == 1)
         return conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
                            g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
-    if (g.Hk == 1 && g.Wk == 1 && g.padU == 0 && g.padL == 0 && gemm_path() != 1 && (((uintptr_t)dx) & 15) == 0 && (g.Hin * g.Win) % 4 == 0 &&
-        (long long)(g.Hout - 1) * g.sh < g.Hin && (long long)(g.Wout - 1) * g.sw < g.Win) {
-        // 1x1 strided: a small per-pixel matrix product scattered onto a zeroed dX; bandwidth-bound, no tensor cores
-        const int opix = g.Hout * g.Wout, PX = opix >= 256 ? 256 : 64;
-        const size_t smem = ((size_t)g.Cout * g.Cin + (size_t)g.Cout * PX) * sizeof(float);
-        if (smem <= 160 * 1024) {
-            const size_t n4 = (size_t)g.n * g.Cin * g.Hin * g.Win / 4;
-            TL_LAUNCH(zero_f4_kernel, (unsigned)std::min<size_t>((n4 + 255) / 256, (size_t)sm_count() * 32), 256, 0, reinterpret_cast<float4 *>(dx), n4);
-            const unsigned grid = (unsigned)g.n * (unsigned)((opix + PX - 1) / PX);
-            if (PX == 256) {
-                if (smem > 48 * 1024) cudaFuncSetAttribute(conv1x1_strided_ig_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                TL_LAUNCH(conv1x1_strided_ig_kernel<256>, grid, 256, smem, g, dy, w, dx);
-            } else {
-                if (smem > 48 * 1024) cudaFuncSetAttribute(conv1x1_strided_ig_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-                TL_LAUNCH(conv1x1_strided_ig_kernel<64>, grid, 64, smem, g, dy, w, dx);
-            }
-            return true;
-        }
-    }
+    if (try_conv1x1_ig(g, dy, w, dx, false)) return true;
     // strided, general filter: one launch per parity class of dX.  Pixels (sh*i + ph, sw*j + pw) only see the filter taps
     // kh = r + sh*m with r = (ph + padU) mod sh, and those taps read dY rows i + q - m with q = (ph + padU) / sh: a dense
     // stride-1 convolution of dY with an (m_max+1)-row window, written to every sh-th row of dX.  No zeros are multiplied.
@@ -470,6 +483,16 @@ conv_ig_kernel(ConvGeom g, const T *__restrict__ dy, const T *__restrict__ w, T 
     }
 }
 
+// dX += input gradient: in place where a kernel can add (1x1 strided), otherwise through scratch and one sum
+template <class T> void conv_ig_accumulate(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx)
+{
+    if (try_conv1x1_ig(g, dy, w, dx, true)) return;
+    const size_t nx = (size_t)g.n * g.Cin * g.Hin * g.Win;
+    T *tmp = sc.scratch<T>(nx);
+    if (!tmp) return;
+    conv_ig<T>(sc, g, dy, w, tmp);
+    add<T>(tmp, dx, dx, (long long)nx);
+}
 template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx)
 {
     if (!g.depthwise && try_tc_ig<T>(sc, g, dy, w, dx)) return;
@@ -996,6 +1019,7 @@ template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk
     template void conv_fw<T>(Scope &, const ConvGeom &, const T *, const T *, const T *, T *);                       \
     template void conv_wg<T>(Scope &, const ConvGeom &, const T *, const T *, T *, T *);                    \
     template void conv_ig<T>(Scope &, const ConvGeom &, const T *, const T *, T *);                                  \
+    template void conv_ig_accumulate<T>(Scope &, const ConvGeom &, const T *, const T *, T *);                       \
     template void im2row<T>(const T *, T *, int, int, int, int, int, int, int, int, int, int, int, int, int, int); \
     template void blocktransp<T>(const T *, T *, int, int, int, int, int);
 INST(float)

@@ -372,12 +372,14 @@ __global__ void __launch_bounds__(256) instnorm_fw_warp_kernel(const float *__re
 // Backward of the same planes: both plane sums once, then dX and/or the per-plane (dgamma, dbeta) partials.
 // GATE: dy is the gradient behind a ReLU that followed the norm; the norm's output is recomputed from x with the forward's own
 // operations and dy counts only where that output is positive (gamma points at [gamma | beta] then).
+// dy2: a second gradient of the same output (another reader of it), added to dy first; GATE kernels only.
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w)); }
 __device__ __forceinline__ float gated(float dy, float xm, float scale, float beta) { return __fadd_rn(__fmul_rn(scale, xm), beta) > 0.f ? dy : 0.f; }
 template <int NV, bool DX, bool PART, bool GATE>
 __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
                                                                float *__restrict__ part, const float *__restrict__ gamma,
                                                                const float *__restrict__ mean_i, const float *__restrict__ var_i,
-                                                               const float *__restrict__ std_i, long long planes, int C, int D)
+                                                               const float *__restrict__ std_i, long long planes, int C, int D, const float *__restrict__ dy2)
 {
     const int lane = threadIdx.x & 31;
     const long long plane = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -391,6 +393,7 @@ __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__re
         const bool in = lane + 32 * i < D4;
         v[i] = in ? xp[lane + 32 * i] : make_float4(mean, mean, mean, mean);
         g[i] = in ? gp[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (GATE && dy2 && in) g[i] = add4(g[i], reinterpret_cast<const float4 *>(dy2 + plane * D)[lane + 32 * i]);
     }
     float s = 0.f, p = 0.f;     // s = sum dy, p = sum (x - mean) dy
     const float gsc = GATE ? __fdiv_rn(gamma[ch], sd) : 0.f, gbeta = GATE ? gamma[C + ch] : 0.f;
@@ -470,7 +473,7 @@ template <bool DX, bool PART, bool GATE>
 __global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
                                                                float *__restrict__ part, const float *__restrict__ gamma,
                                                                const float *__restrict__ mean_i, const float *__restrict__ var_i,
-                                                               const float *__restrict__ std_i, long long planes, int C, int D)
+                                                               const float *__restrict__ std_i, long long planes, int C, int D, const float *__restrict__ dy2)
 {
     const int l16 = threadIdx.x & 15;
     const long long plane = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
@@ -481,6 +484,7 @@ __global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__re
     float4 v = in ? reinterpret_cast<const float4 *>(x + plane * D)[l16] : make_float4(mean, mean, mean, mean);
     float4 g = in ? reinterpret_cast<const float4 *>(dy + plane * D)[l16] : make_float4(0.f, 0.f, 0.f, 0.f);
     v.x -= mean; v.y -= mean; v.z -= mean; v.w -= mean;
+    if (GATE && dy2 && in) g = add4(g, reinterpret_cast<const float4 *>(dy2 + plane * D)[l16]);
     if (GATE && in) {
         const int ch = (int)(plane % C);
         const float gsc = __fdiv_rn(gamma[ch], sd), gbeta = gamma[C + ch];
@@ -503,7 +507,7 @@ template <bool DX, bool PART, bool GATE>
 __global__ void __launch_bounds__(256) instnorm_bw_pair_kernel(const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ dx,
                                                                float *__restrict__ part, const float *__restrict__ gamma,
                                                                const float *__restrict__ mean_i, const float *__restrict__ var_i,
-                                                               const float *__restrict__ std_i, long long planes, int C, int D)
+                                                               const float *__restrict__ std_i, long long planes, int C, int D, const float *__restrict__ dy2)
 {
     __shared__ float2 sums[4][2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, slot = warp >> 1, half = warp & 1;
@@ -521,6 +525,7 @@ __global__ void __launch_bounds__(256) instnorm_bw_pair_kernel(const float *__re
             const bool in = idx < D4;
             v[i] = in ? xp[idx] : make_float4(mean, mean, mean, mean);
             g[i] = in ? gp[idx] : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (GATE && dy2 && in) g[i] = add4(g[i], reinterpret_cast<const float4 *>(dy2 + plane * D)[idx]);
         }
     } else {
 #pragma unroll
@@ -593,18 +598,19 @@ static bool instnorm_fw_warp(const float *x, float *y, const float *gb, float *m
 template <class T> static bool instnorm_fw_warp(const T *, T *, const T *, T *, T *, T *, int, int, int, bool, float, const T * = nullptr, bool = false) { return false; }
 // dx and/or part may be null: the kernel variant is chosen accordingly
 static bool instnorm_bw_warp(const float *x, const float *dy, float *dx, float *part, const float *gamma, const float *mean, const float *var,
-                             const float *stdev, int n, int C, int D, bool gate = false)
+                             const float *stdev, int n, int C, int D, bool gate = false, const float *dy2 = nullptr)
 {
     const int nv = instnorm_nv(D);
     if (!nv || !aligned16(x, dy, dx)) return false;
     if (gate && !(dx && part)) return false;           // the gated form exists for the one-pass backward only
+    if (dy2 && (!gate || (((uintptr_t)dy2) & 15) != 0)) return false;
     const long long planes = (long long)n * C;
 #define TL_BW_VARIANTS(KERNEL, GRID, ...)                                                                              \
     do {                                                                                                               \
-        if (gate) TL_LAUNCH((KERNEL<__VA_ARGS__ true, true, true>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);              \
-        else if (dx && part) TL_LAUNCH((KERNEL<__VA_ARGS__ true, true, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);  \
-        else if (dx) TL_LAUNCH((KERNEL<__VA_ARGS__ true, false, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);         \
-        else TL_LAUNCH((KERNEL<__VA_ARGS__ false, true, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D);                 \
+        if (gate) TL_LAUNCH((KERNEL<__VA_ARGS__ true, true, true>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D, dy2);         \
+        else if (dx && part) TL_LAUNCH((KERNEL<__VA_ARGS__ true, true, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D, dy2);  \
+        else if (dx) TL_LAUNCH((KERNEL<__VA_ARGS__ true, false, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D, dy2);    \
+        else TL_LAUNCH((KERNEL<__VA_ARGS__ false, true, false>), GRID, 256, 0, x, dy, dx, part, gamma, mean, var, stdev, planes, C, D, dy2);            \
     } while (0)
     if (D <= 64) {
         TL_BW_VARIANTS(instnorm_bw_half_kernel, (unsigned)((planes + 15) / 16), );
@@ -621,7 +627,7 @@ static bool instnorm_bw_warp(const float *x, const float *dy, float *dx, float *
 #undef TL_BW_VARIANTS
     return true;
 }
-template <class T> static bool instnorm_bw_warp(const T *, const T *, T *, float *, const T *, const T *, const T *, const T *, int, int, int, bool = false) { return false; }
+template <class T> static bool instnorm_bw_warp(const T *, const T *, T *, float *, const T *, const T *, const T *, const T *, int, int, int, bool = false, const T * = nullptr) { return false; }
 
 template <class T>
 void instnorm_fw(const T *x, T *y, const T *gb, T *mean, T *var, T *stdev, int n, int C, int D, bool frozen, float eps)
@@ -674,18 +680,20 @@ void instnorm_act_fw(const T *x, T *y, const T *skip, const T *gb, T *mean, T *v
     if (skip) add<T>(skip, y, y, total);
     if (relu) act_fw<T>(ACT_RELU, y, y, total, 0.f);
 }
-// Backward of y = relu(norm(x)): both gradients of the norm from dL/dy.  `y` (the forward output) and `dy` are only touched
-// by the fallback, which masks dy in place.
+// Backward of y = relu(norm(x)): both gradients of the norm from dL/dy (+ dy2, the gradient of a second reader of y, when
+// given).  `y` (the forward output) is only read by the fallback, which sums and masks into dy in place.
 template <class T>
-void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, T *dx, T *dgb, const T *gb, const T *mean, const T *var, const T *stdev, int n, int C, int D)
+void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, const T *dy2, T *dx, T *dgb, const T *gb, const T *mean, const T *var, const T *stdev,
+                      int n, int C, int D)
 {
     if (n * C <= 0) return;
     float *part = sc.scratch<float>((size_t)2 * n * C);
     if (!part) return;
-    if (instnorm_bw_warp(x, dy, dx, part, gb, mean, var, stdev, n, C, D, true)) {
+    if (instnorm_bw_warp(x, dy, dx, part, gb, mean, var, stdev, n, C, D, true, dy2)) {
         TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
         return;
     }
+    if (dy2) add<T>(dy2, dy, dy, (long long)n * C * D);
     act_bw<T>(ACT_RELU, y, (const T *)nullptr, dy, dy, (long long)n * C * D, 0.f);
     instnorm_bw_both<T>(sc, x, dy, dx, dgb, gb, mean, var, stdev, n, C, D);
 }
@@ -1077,7 +1085,7 @@ template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int pad
     template void instnorm_bw_param<T>(Scope &, const T *, const T *, T *, const T *, const T *, int, int, int);   \
     template void instnorm_bw_both<T>(Scope &, const T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void instnorm_act_fw<T>(const T *, T *, const T *, const T *, T *, T *, T *, int, int, int, bool, float, bool);             \
-    template void instnorm_relu_bw<T>(Scope &, const T *, const T *, T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
+    template void instnorm_relu_bw<T>(Scope &, const T *, const T *, T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void batchnorm_fw<T>(const T *, T *, const T *, const T *, int, int, int, int, float);                \
     template void layernorm_fw<T>(const T *, T *, const T *, const T *, int, int, float);                          \
     template void layernorm_bw<T>(Scope &, const T *, const T *, const T *, T *, T *, T *, int, int, float);      \

@@ -41,6 +41,7 @@ struct ConvGeom {
 template <class T> void conv_fw(Scope &sc, const ConvGeom &g, const T *x, const T *w, const T *bias, T *y);
 template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const T *dy, T *dw, T *dbias);
 template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx);
+template <class T> void conv_ig_accumulate(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx);   // dx += input gradient
 // tensor-core implicit GEMM (tl_conv_tc.cu); false = geometry does not qualify, use the FFMA kernels
 // One parity class of a strided input gradient as a stride-1 convolution over dY (see tl_conv_tc.cu)
 struct ConvTcClass { int kstep, kh_r, kh_m, kw_r, kw_m, w_Hk, w_Wk; int oH, oW, osy, osx, oy0, ox0; };
@@ -71,7 +72,7 @@ template <class T> void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *
 // y = relu(norm(x) + skip) in one pass (skip may be null, relu false), and the backward of y = relu(norm(x)) from dL/dy.
 template <class T> void instnorm_act_fw(const T *x, T *y, const T *skip, const T *gamma_beta, T *mean, T *var, T *stdev,
                                         int n, int C, int D, bool frozen, float eps, bool relu);
-template <class T> void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, T *dx, T *dgamma_beta, const T *gamma_beta, const T *mean,
+template <class T> void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, const T *dy2, T *dx, T *dgamma_beta, const T *gamma_beta, const T *mean,
                                          const T *var, const T *stdev, int n, int C, int D);
 template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps);
 template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps);

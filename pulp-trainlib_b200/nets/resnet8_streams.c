@@ -89,19 +89,21 @@ static int g_fuse = 1;
 void resnet8_set_fusion(int on) { g_fuse = on != 0; }
 static void norm_act_fw(struct InstNorm_args *a, struct blob *skip, int relu)
 {
-    struct trainlib_instnorm_act_args f; f.norm = a; f.skip = skip; f.relu = relu;
+    struct trainlib_instnorm_act_args f; f.norm = a; f.skip = skip; f.relu = relu; f.diff2 = NULL;
     trainlib_instnorm_act_fp32_fw_cl(&f);
 }
-static void norm_relu_bw(struct InstNorm_args *a)
+static void norm_relu_bw(struct InstNorm_args *a, float *diff2)
 {
-    struct trainlib_instnorm_act_args f; f.norm = a; f.skip = NULL; f.relu = 1;
+    struct trainlib_instnorm_act_args f; f.norm = a; f.skip = NULL; f.relu = 1; f.diff2 = diff2;
     trainlib_instnorm_act_fp32_bw_cl(&f);
 }
+static void conv_ig_add(struct Conv2D_args *a) { trainlib_conv2d_fp32_bw_input_grads_acc_cl(a); }
 #else
 enum { g_fuse = 0 };
 void resnet8_set_fusion(int on) { (void)on; }
 static void norm_act_fw(struct InstNorm_args *a, struct blob *skip, int relu) { (void)a; (void)skip; (void)relu; }
-static void norm_relu_bw(struct InstNorm_args *a) { (void)a; }
+static void norm_relu_bw(struct InstNorm_args *a, float *diff2) { (void)a; (void)diff2; }
+static void conv_ig_add(struct Conv2D_args *a) { (void)a; }
 #endif
 static void relu_fw(struct act_args *a)
 {
@@ -414,16 +416,19 @@ static void stage_bw(int conv_a, int norm_a, int conv_b, int norm_b, int proj, i
 {
     relu_bw(&a_relu_s[r]);                         /* sum.diff masked in place; norm_b and the shortcut share it */
     norm_bw(&a_norm[norm_b]); conv_bw(conv_b);
-    if (g_fuse) norm_relu_bw(&a_norm[norm_a]); else { relu_bw(&a_relu_n[norm_a]); norm_bw(&a_norm[norm_a]); }
+    if (g_fuse) norm_relu_bw(&a_norm[norm_a], NULL); else { relu_bw(&a_relu_n[norm_a]); norm_bw(&a_norm[norm_a]); }
     conv_bw(conv_a);                               /* writes the stage input's gradient */
-    if (proj >= 0) {
+    if (proj >= 0 && g_fuse) {
+        conv_wg(&a_conv[proj]);
+        conv_ig_add(&a_conv[proj]);                /* the shortcut's dX is added to the stage input's gradient in place */
+    } else if (proj >= 0) {
         struct blob *in = a_conv[proj].input; float *keep = in->diff;
         conv_wg(&a_conv[proj]);
         in->diff = b_tmp[r - 1].diff;              /* shortcut dX goes to a temporary ... */
         conv_ig(&a_conv[proj]);
         in->diff = keep;
         skip_call(&a_skipgrad[r], pulp_sumnode_fp32_bw);   /* ... and is added to the stage input's gradient */
-    } else {
+    } else if (!g_fuse) {                          /* fused: the stem's norm backward reads both gradients itself */
         skip_call(&a_skipgrad[0], pulp_sumnode_fp32_bw);   /* identity shortcut: norm0.diff += sum1.diff */
     }
 }
@@ -436,7 +441,7 @@ void resnet8_backward(void)
     stage_bw(C5, 5, C6, 6, P3, 2);
     stage_bw(C3, 3, C4, 4, P2, 1);
     stage_bw(C1, 1, C2, 2, -1, 0);
-    if (g_fuse) norm_relu_bw(&a_norm[0]); else { relu_bw(&a_relu_n[0]); norm_bw(&a_norm[0]); }
+    if (g_fuse) norm_relu_bw(&a_norm[0], b_sum[0].diff); else { relu_bw(&a_relu_n[0]); norm_bw(&a_norm[0]); }
     conv_bw(C0);
 #ifndef NET_REFERENCE
     if (g_host_slot >= 0) { trainlib_mark_consumed(g_host_slot); g_host_slot = -1; }   /* last reader of that batch copy */

@@ -283,12 +283,12 @@ class AbiRunner(object):
         self.pkg.check(self.lib)
         return dict(y=Y.get().copy(), dx=dX.get().copy(), dw=dW.get().copy(), db=dB.get().copy())
 
-    def instnorm_act(self, x, gb, dy, skip=None, relu=True, backward=True, n=1):
+    def instnorm_act(self, x, gb, dy, skip=None, relu=True, backward=True, n=1, diff2=None):
         """the library's fused norm (+ skip sum) (+ ReLU): one forward call, one backward call; x is [n][C][H][W] when n > 1"""
         import ctypes
 
         class FusedArgs(ctypes.Structure):
-            _fields_ = [("norm", ctypes.c_void_p), ("skip", ctypes.c_void_p), ("relu", ctypes.c_int)]
+            _fields_ = [("norm", ctypes.c_void_p), ("skip", ctypes.c_void_p), ("relu", ctypes.c_int), ("diff2", ctypes.c_void_p)]
         C, H, W = x.shape[-3:]
         X, dX, Y, dY = self.t(x), self.zeros(*x.shape), self.zeros(*x.shape), self.t(dy)
         GB, dGB = self.t(gb), self.zeros(2 * C)
@@ -299,6 +299,8 @@ class AbiRunner(object):
         f = FusedArgs(); f.norm = ctypes.addressof(norm); f.relu = 1 if relu else 0
         if skip is not None:
             S = self.t(skip); sb = self.blob(S, None, C=C, H=H, W=W); f.skip = ctypes.addressof(sb)
+        if diff2 is not None:
+            D2 = self.t(diff2); f.diff2 = D2.arg if isinstance(D2.arg, int) else D2.arg.ctypes.data
         self.keep.hold(f)
         getattr(self.lib, self.fname("trainlib_instnorm_act_fp32_fw_cl"))(ctypes.byref(f)); self.pkg.check(self.lib)
         out = dict(y=Y.get().copy(), mean=m.get().copy(), std=s.get().copy())

@@ -491,7 +491,8 @@ def test_instnorm_fused_with_sum_and_relu(pkg, gpulib, oracle, C, H, W, n, with_
     gpulib.trainlib_set_streams(n)
     try:
         r = AbiRunner(pkg, gpulib, device=True)
-        fused = r.instnorm_act(x, gb, dy, skip=skip, relu=True, backward=not with_skip, n=n)
+        dy2 = rng.standard_normal(x.shape).astype(F) if (C * H * W) % 2 == 0 else None     # a second reader's gradient on some shapes
+        fused = r.instnorm_act(x, gb, dy, skip=skip, relu=True, backward=not with_skip, n=n, diff2=None if with_skip else dy2)
         # the separate calls
         X, dX, Y, dY, GB, dGB = r.t(x), r.zeros(*x.shape), r.zeros(*x.shape), r.t(dy), r.t(gb), r.zeros(2 * C)
         m, v, sd = r.zeros(n * C), r.zeros(n * C), r.zeros(n * C)
@@ -508,7 +509,8 @@ def test_instnorm_fused_with_sum_and_relu(pkg, gpulib, oracle, C, H, W, n, with_
             ws = o["y"] + skip[s] if with_skip else o["y"]
             assert_close(fused["y"][s], np.maximum(ws, 0), FP32_TOL, "fused forward vs oracle")
         if not with_skip:
-            dY.set(np.where(want > 0, dy, F(0)).astype(F))      # pulp_relu_fp32_bw_cl
+            both = dy + dy2 if dy2 is not None else dy          # pulp_sumnode_fp32_bw
+            dY.set(np.where(want > 0, both, F(0)).astype(F))    # pulp_relu_fp32_bw_cl
             r.call("pulp_instnorm_fp32_bw_cl", a)
             assert np.array_equal(fused["dx"], dX.get()), "fused backward dX differs from ReLU backward + norm backward"
             assert np.array_equal(fused["dgb"], dGB.get()), "fused backward parameter gradient differs"
@@ -536,3 +538,36 @@ def test_instnorm_fused_fp16_and_rejections(pkg, gpulib):
     with pytest.raises(Exception):
         r.instnorm_act(x32, gb.astype(F), dy.astype(F), skip=x32, relu=True, backward=True)    # backward with a skip is refused
     r.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("g,n", [(geom(16, 32, 32, 32, 1, stride=2, pad=0), 3), (geom(32, 16, 16, 64, 1, stride=2, pad=0), 2), (geom(6, 9, 9, 4, 1, stride=2, pad=0), 2),
+                                 (geom(8, 12, 12, 8, 3, stride=1, pad=1), 2), (geom(4, 8, 8, 6, 1, stride=1, pad=0), 1)],
+                         ids=["1x1_s2_16to32", "1x1_s2_32to64", "1x1_s2_odd", "3x3_s1", "1x1_s1"])
+def test_conv2d_input_gradient_accumulate(pkg, gpulib, oracle, g, n):
+    """trainlib_conv2d_fp32_bw_input_grads_acc_cl: input.diff += dX, against the plain call into a second buffer plus one fp32 sum"""
+    rng = seeded(91)
+    Ho, Wo = out_hw(g)
+    w = rng.uniform(-1, 1, (g["Cout"], g["Cin"], g["Hk"], g["Wk"])).astype(F)
+    dy = rng.standard_normal((n, g["Cout"], Ho, Wo)).astype(F); base = rng.standard_normal((n, g["Cin"], g["Hin"], g["Win"])).astype(F)
+    gpulib.trainlib_set_streams(n)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        X, W_, dY, Y = r.zeros(*base.shape), r.t(w), r.t(dy), r.zeros(*dy.shape)
+        dX_plain, dX_acc, one = r.zeros(*base.shape), r.t(base), r.zeros(1)
+        def args(dx):
+            return r.args("Conv2D_args", input=r.blob(X, dx, C=g["Cin"], H=g["Hin"], W=g["Win"]), coeff=r.blob(W_, None, C=g["Cin"], H=g["Hk"], W=g["Wk"], dim=w.size),
+                          bias=r.blob(one, one), output=r.blob(Y, dY, C=g["Cout"], H=Ho, W=Wo), Lpad=g["padL"], Rpad=g["padR"], Upad=g["padU"], Dpad=g["padD"],
+                          stride_h=g["sh"], stride_w=g["sw"], i2c_buffer=one, bt_buffer=one, USE_BIASES=0, USE_IM2COL=0, HWC=0)
+        r.call("pulp_conv2d_fp32_bw_input_grads_cl", args(dX_plain))
+        r.call("trainlib_conv2d_fp32_bw_input_grads_acc_cl", args(dX_acc))
+        plain, acc = dX_plain.get(), dX_acc.get()
+        for s in range(n):
+            assert_close(plain[s], oracle.conv2d_ig(dy[s], w, g), FP32_TOL, "plain input gradient")
+        if g["sh"] > 1 and g["Hk"] == 1:
+            assert np.array_equal(acc, plain + base), "accumulated input gradient differs from plain + base"
+        else:
+            assert_close(acc, plain + base, FP32_TOL, "accumulated input gradient")     # tensor-core path: not run-to-run bit-stable
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1)
