@@ -894,7 +894,8 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
             const size_t smem = std::max<size_t>(nstage * stage, (size_t)16 * 16 * KK) * sizeof(float);
             const int tiles_h = ceil_div(g.Hout, TH);
             const long long items = (long long)ceil_div(g.n, S_T) * tiles_h;
-            int groups = ceil_div(2 * sm_count(), ci_tiles * co_tiles);
+            // one wave: two CTAs fit an SM, and a grid that needs a few CTAs more than the slots runs twice as long
+            int groups = (2 * sm_count()) / (ci_tiles * co_tiles);
             if (groups > items) groups = (int)items;
             if (groups < 1) groups = 1;
             float *part = sc.scratch<float>((size_t)groups * nw);
