@@ -419,15 +419,6 @@ template <class F> void dw_impl(void *args, int step)
 // ------------------------------------------------------------------ linear
 // W is [out x in]; y = W x (+ b); dW = dy (x) x, db = dy; dx = W^T dy
 // [ref: lib/sources/pulp_linear_fp32.c:25-267].  With n streams the three become GEMMs.
-template <class T> __global__ void stream_sum_kernel(const T *in, T *out, int n, int dim)
-{
-    int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= dim) return;
-    float s = 0.f;
-    for (int i = 0; i < n; i++) s += ld(in + (long long)i * dim + j);
-    st(out + j, s);
-}
-
 template <class F> void linear_impl(void *args, int step)
 {
     auto *a = (typename F::linear_t *)args; typedef typename F::T T;
@@ -457,7 +448,7 @@ template <class F> void linear_impl(void *args, int step)
             GemmDesc<T> d; d.A = dy; d.a_rs = 1; d.a_cs = out; d.B = x; d.b_rs = in; d.C = dw; d.c_rs = in; d.N = out; d.K = n; d.M = in;
             gemm<T>(d);
         }
-        if (db) TL_LAUNCH((stream_sum_kernel<T>), ceil_div(out, 128), 128, 0, dy, db, n, out);
+        if (db) column_sum<T>(sc, dy, db, n, out);
     } else {
         const T *dy = sc.in(a->output->diff, (size_t)n * out), *w = sc.in(a->coeff->data, (size_t)out * in);
         T *dx = sc.out(a->input->diff, (size_t)n * in);

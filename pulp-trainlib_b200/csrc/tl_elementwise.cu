@@ -298,22 +298,51 @@ __global__ void __launch_bounds__(256) instnorm_bw_param_kernel(const T *__restr
     b = block_sum(b, red);
     if (threadIdx.x == 0) { part[2 * plane] = a / sd; part[2 * plane + 1] = b; }
 }
-// One CTA per channel: threads take the streams round-robin, then a fixed-shape tree adds the
-// per-thread sums (same result on every run).
+// out[map(j)] = sum over the n rows of in[n][dim], always added in the same order.  First pass: the rows are cut into
+// slices; a CTA takes 32 columns of one slice, its 8 warps the rows round-robin (each warp reads 32 consecutive floats), and
+// adds the 8 sums in warp order.  Second pass: one thread per column adds the slice sums in slice order.
+// pairs > 0: the columns are (a, b) pairs per channel and the output is [all a | all b] (instance-norm parameters).
 template <class T>
-__global__ void __launch_bounds__(128) instnorm_param_reduce_kernel(const float *__restrict__ part, T *__restrict__ dgb, int n, int C)
+__global__ void __launch_bounds__(256) column_partial_kernel(const T *__restrict__ in, float *__restrict__ part, int n, int dim, int rows_per_slice)
 {
-    __shared__ float red[33];
-    const int c = blockIdx.x;
-    float a = 0.f, b = 0.f;
-    for (int s = threadIdx.x; s < n; s += blockDim.x) {
-        const float2 v = *reinterpret_cast<const float2 *>(part + 2 * ((long long)s * C + c));
-        a += v.x; b += v.y;
+    __shared__ float sm[8][33];
+    const int c = threadIdx.x & 31, r = threadIdx.x >> 5, j = blockIdx.x * 32 + c;
+    const int begin = blockIdx.y * rows_per_slice, end = min(n, begin + rows_per_slice);
+    float s = 0.f;
+    if (j < dim)
+        for (int i = begin + r; i < end; i += 8) s += ld(in + (long long)i * dim + j);
+    sm[r][c] = s;
+    __syncthreads();
+    if (r == 0 && j < dim) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += sm[k][c];
+        part[(long long)blockIdx.y * dim + j] = t;
     }
-    a = block_sum(a, red);
-    b = block_sum(b, red);
-    if (threadIdx.x == 0) { st(dgb + c, a); st(dgb + C + c, b); }
 }
+template <class T>
+__global__ void __launch_bounds__(128) column_final_kernel(const float *__restrict__ part, T *__restrict__ out, int slices, int dim, int pairs)
+{
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= dim) return;
+    float s = 0.f;
+    for (int k = 0; k < slices; k++) s += part[(long long)k * dim + j];
+    st(out + (pairs > 0 ? (j & 1) * pairs + (j >> 1) : j), s);
+}
+template <class TI, class TO>
+static bool column_sum_launch(Scope &sc, const TI *in, TO *out, int n, int dim, int pairs)
+{
+    if (n <= 0 || dim <= 0) return true;
+    const int rows_per_slice = n >= 4096 ? 64 : (n >= 256 ? 32 : 8), slices = (n + rows_per_slice - 1) / rows_per_slice;
+    float *part = sc.scratch<float>((size_t)slices * dim);
+    if (!part) return false;
+    TL_LAUNCH((column_partial_kernel<TI>), dim3((unsigned)((dim + 31) / 32), (unsigned)slices), 256, 0, in, part, n, dim, rows_per_slice);
+    TL_LAUNCH((column_final_kernel<TO>), (unsigned)((dim + 127) / 128), 128, 0, part, out, slices, dim, pairs);
+    return true;
+}
+// dgb = [sum of a | sum of b] over the streams of part[n][C] (a, b) pairs
+template <class T> static void instnorm_param_reduce(Scope &sc, const float *part, T *dgb, int n, int C) { column_sum_launch<float, T>(sc, part, dgb, n, 2 * C, C); }
+template <class T> void column_sum(Scope &sc, const T *in, T *out, int n, int dim) { column_sum_launch<T, T>(sc, in, out, n, dim, 0); }
 
 // fp32 planes of up to 1024 elements (a multiple of 4): one warp per plane, the plane held in registers as NV 16-byte
 // vectors per lane, so every element is read once and the reductions are warp shuffles without a CTA barrier.
@@ -651,7 +680,7 @@ void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgb, const T *mean
     if (!part) return;
     if (!instnorm_bw_warp(x, dy, (T *)nullptr, part, (const T *)nullptr, mean, (const T *)nullptr, stdev, n, C, D))
         TL_LAUNCH((instnorm_bw_param_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, part, mean, stdev, D);
-    TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
+    instnorm_param_reduce<T>(sc, part, dgb, n, C);
 }
 // Both gradients of one layer in one pass over x and dy (falls back to the two separate passes).
 template <class T>
@@ -661,7 +690,7 @@ void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *dx, T *dgb, const T
     float *part = sc.scratch<float>((size_t)2 * n * C);
     if (!part) return;
     if (instnorm_bw_warp(x, dy, dx, part, gamma, mean, var, stdev, n, C, D)) {
-        TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
+        instnorm_param_reduce<T>(sc, part, dgb, n, C);
         return;
     }
     instnorm_bw_param<T>(sc, x, dy, dgb, mean, stdev, n, C, D);
@@ -690,7 +719,7 @@ void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, const T *dy2, T 
     float *part = sc.scratch<float>((size_t)2 * n * C);
     if (!part) return;
     if (instnorm_bw_warp(x, dy, dx, part, gb, mean, var, stdev, n, C, D, true, dy2)) {
-        TL_LAUNCH((instnorm_param_reduce_kernel<T>), C, 128, 0, part, dgb, n, C);
+        instnorm_param_reduce<T>(sc, part, dgb, n, C);
         return;
     }
     if (dy2) add<T>(dy2, dy, dy, (long long)n * C * D);
@@ -1084,6 +1113,7 @@ template <class T> void pad2d(const T *src, T *dst, int C, int H, int W, int pad
     template void instnorm_bw_input<T>(const T *, const T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void instnorm_bw_param<T>(Scope &, const T *, const T *, T *, const T *, const T *, int, int, int);   \
     template void instnorm_bw_both<T>(Scope &, const T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
+    template void column_sum<T>(Scope &, const T *, T *, int, int);                                                \
     template void instnorm_act_fw<T>(const T *, T *, const T *, const T *, T *, T *, T *, int, int, int, bool, float, bool);             \
     template void instnorm_relu_bw<T>(Scope &, const T *, const T *, T *, const T *, T *, T *, const T *, const T *, const T *, const T *, int, int, int); \
     template void batchnorm_fw<T>(const T *, T *, const T *, const T *, int, int, int, int, float);                \

@@ -74,6 +74,7 @@ template <class T> void instnorm_act_fw(const T *x, T *y, const T *skip, const T
                                         int n, int C, int D, bool frozen, float eps, bool relu);
 template <class T> void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, const T *dy2, T *dx, T *dgamma_beta, const T *gamma_beta, const T *mean,
                                          const T *var, const T *stdev, int n, int C, int D);
+template <class T> void column_sum(Scope &sc, const T *in, T *out, int n, int dim);    // out[j] = sum_i in[i][j], fixed order
 template <class T> void batchnorm_fw(const T *x, T *y, const T *w, const T *b, int n, int B, int C, int HW, float eps);
 template <class T> void layernorm_fw(const T *x, T *y, const T *w, const T *b, int rows, int width, float eps);
 template <class T> void layernorm_bw(Scope &sc, const T *x, const T *w, const T *dy, T *dx, T *dw, T *db, int rows, int width, float eps);
