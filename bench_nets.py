@@ -225,7 +225,7 @@ class ResNet8Streams(object):
                 "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n)},
                 "roofline": self.roofline(table, n, pk),
-                "kernel_table": [{"kernel": k, "launches": c, "ms": round(ms, 4)} for k, c, ms in table[:24]]}
+                "kernel_table": [{"kernel": k, "launches": c, "ms": round(ms, 4)} for k, c, ms in table[:40]]}
         if world == 1 and not args.no_cpu_baseline and os.path.exists(NET_REF_MT):
             line["cpu_baseline"] = self.cpu_baseline()
         return line

@@ -985,13 +985,47 @@ __global__ void avgpool_bw_kernel(const T *__restrict__ dy, T *__restrict__ dx, 
         st(dx + e, s);
     }
 }
+// Global pooling of fp32 planes (one window = the whole plane, a multiple of 4 elements): a thread per plane adds the plane
+// in the reference's order from 16-byte loads; backward writes dy / count with 16-byte stores.
+__global__ void __launch_bounds__(256) avgpool_global_fw_kernel(const float *__restrict__ x, float *__restrict__ y, long long planes, int hw4, float cnt)
+{
+    const long long pl = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (pl >= planes) return;
+    const float4 *xp = reinterpret_cast<const float4 *>(x) + pl * hw4;
+    float s = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < hw4; i++) { const float4 v = xp[i]; s += v.x; s += v.y; s += v.z; s += v.w; }
+    y[pl] = __fdiv_rn(s, cnt);
+}
+__global__ void __launch_bounds__(256) avgpool_global_bw_kernel(const float *__restrict__ dy, float4 *__restrict__ dx, long long total4, int hw4, float cnt)
+{
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total4; e += (long long)gridDim.x * blockDim.x) {
+        const float v = __fdiv_rn(dy[e / hw4], cnt);
+        dx[e] = make_float4(v, v, v, v);
+    }
+}
+static bool avgpool_global(const float *x, const float *y, int H, int W, int Ho, int Wo, int Hk, int Wk)
+{
+    return Ho == 1 && Wo == 1 && Hk == H && Wk == W && (H * W) % 4 == 0 && ((((uintptr_t)x) | ((uintptr_t)y)) & 15) == 0;
+}
+template <class T> static bool avgpool_global(const T *, const T *, int, int, int, int, int, int) { return false; }
+static void avgpool_global_fw(const float *x, float *y, long long planes, int hw) { TL_LAUNCH(avgpool_global_fw_kernel, (unsigned)((planes + 255) / 256), 256, 0, x, y, planes, hw / 4, (float)hw); }
+static void avgpool_global_bw(const float *dy, float *dx, long long planes, int hw)
+{
+    const long long total4 = planes * (hw / 4);
+    TL_LAUNCH(avgpool_global_bw_kernel, grid_for(total4), 256, 0, dy, reinterpret_cast<float4 *>(dx), total4, hw / 4, (float)hw);
+}
+template <class T> static void avgpool_global_fw(const T *, T *, long long, int) {}
+template <class T> static void avgpool_global_bw(const T *, T *, long long, int) {}
 template <class T> void avgpool_fw(const T *x, T *y, int n, int C, int H, int W, int Ho, int Wo, int Hk, int Wk, int sh, int sw)
 {
+    if ((long long)n * C > 0 && avgpool_global(x, y, H, W, Ho, Wo, Hk, Wk)) { avgpool_global_fw(x, y, (long long)n * C, H * W); return; }
     long long total = (long long)n * C * Ho * Wo;
     if (total > 0) TL_LAUNCH((avgpool_fw_kernel<T>), grid_for(total), 256, 0, x, y, total, H, W, Ho, Wo, Hk, Wk, sh, sw);
 }
 template <class T> void avgpool_bw(const T *dy, T *dx, int n, int C, int H, int W, int Ho, int Wo, int Hk, int Wk, int sh, int sw)
 {
+    if ((long long)n * C > 0 && avgpool_global(dx, dx, H, W, Ho, Wo, Hk, Wk)) { avgpool_global_bw(dy, dx, (long long)n * C, H * W); return; }
     long long total = (long long)n * C * H * W;
     if (total > 0) TL_LAUNCH((avgpool_bw_kernel<T>), grid_for(total), 256, 0, dy, dx, total, H, W, Ho, Wo, Hk, Wk, sh, sw);
 }
