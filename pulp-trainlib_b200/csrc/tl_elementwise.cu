@@ -402,6 +402,9 @@ __global__ void __launch_bounds__(256) instnorm_fw_warp_kernel(const float *__re
 // GATE: dy is the gradient behind a ReLU that followed the norm; the norm's output is recomputed from x with the forward's own
 // operations and dy counts only where that output is positive (gamma points at [gamma | beta] then).
 // dy2: a second gradient of the same output (another reader of it), added to dy first; GATE kernels only.
+// dx = (D dy - sum(dy) - (x - mean) sum((x - mean) dy) / var) * gamma / (D stdev), the two per-plane quotients taken once:
+// ka = gamma / (D stdev), kb = sum((x - mean) dy) / var
+__device__ __forceinline__ float dx_of(float dy, float xm, float s, float kb, float fD, float ka) { return (fmaf(fD, dy, -s) - kb * xm) * ka; }
 __device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z), __fadd_rn(a.w, b.w)); }
 __device__ __forceinline__ float gated(float dy, float xm, float scale, float beta) { return __fadd_rn(__fmul_rn(scale, xm), beta) > 0.f ? dy : 0.f; }
 template <int NV, bool DX, bool PART, bool GATE>
@@ -439,14 +442,14 @@ __global__ void __launch_bounds__(256) instnorm_bw_warp_kernel(const float *__re
     s = warp_sum(s); p = warp_sum(p);
     if (PART && lane == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
     if (DX) {
-        const float var = var_i[plane], gm = gamma[ch], fD = (float)D, denom = fD * sd;
+        const float var = var_i[plane], gm = gamma[ch], fD = (float)D, ka = gm / (fD * sd), kb = p / var;
         float4 *dp = reinterpret_cast<float4 *>(dx + plane * D);
 #pragma unroll
         for (int i = 0; i < NV; i++)
             if (lane + 32 * i < D4) {
                 float4 o;
-                o.x = (-s - p * (v[i].x / var) + fD * g[i].x) * gm / denom; o.y = (-s - p * (v[i].y / var) + fD * g[i].y) * gm / denom;
-                o.z = (-s - p * (v[i].z / var) + fD * g[i].z) * gm / denom; o.w = (-s - p * (v[i].w / var) + fD * g[i].w) * gm / denom;
+                o.x = dx_of(g[i].x, v[i].x, s, kb, fD, ka); o.y = dx_of(g[i].y, v[i].y, s, kb, fD, ka);
+                o.z = dx_of(g[i].z, v[i].z, s, kb, fD, ka); o.w = dx_of(g[i].w, v[i].w, s, kb, fD, ka);
                 dp[lane + 32 * i] = o;
             }
     }
@@ -523,10 +526,10 @@ __global__ void __launch_bounds__(256) instnorm_bw_half_kernel(const float *__re
     s = half_warp_sum(s); p = half_warp_sum(p);
     if (PART && live && l16 == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
     if (DX && in) {
-        const float var = var_i[plane], gm = gamma[(int)(plane % C)], fD = (float)D, denom = fD * sd;
+        const float var = var_i[plane], gm = gamma[(int)(plane % C)], fD = (float)D, ka = gm / (fD * sd), kb = p / var;
         float4 o;
-        o.x = (-s - p * (v.x / var) + fD * g.x) * gm / denom; o.y = (-s - p * (v.y / var) + fD * g.y) * gm / denom;
-        o.z = (-s - p * (v.z / var) + fD * g.z) * gm / denom; o.w = (-s - p * (v.w / var) + fD * g.w) * gm / denom;
+        o.x = dx_of(g.x, v.x, s, kb, fD, ka); o.y = dx_of(g.y, v.y, s, kb, fD, ka);
+        o.z = dx_of(g.z, v.z, s, kb, fD, ka); o.w = dx_of(g.w, v.w, s, kb, fD, ka);
         reinterpret_cast<float4 *>(dx + plane * D)[l16] = o;
     }
 }
@@ -581,15 +584,15 @@ __global__ void __launch_bounds__(256) instnorm_bw_pair_kernel(const float *__re
     if (PART && lane == 0 && half == 0) { part[2 * plane] = p / sd; part[2 * plane + 1] = s; }
     if (DX) {
         const int ch = (int)(plane % C);
-        const float var = var_i[plane], gm = gamma[ch], fD = (float)D, denom = fD * sd;
+        const float var = var_i[plane], gm = gamma[ch], fD = (float)D, ka = gm / (fD * sd), kb = p / var;
         float4 *dp = reinterpret_cast<float4 *>(dx + plane * D);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int idx = half * 128 + lane + 32 * i;
             if (idx < D4) {
                 float4 o;
-                o.x = (-s - p * (v[i].x / var) + fD * g[i].x) * gm / denom; o.y = (-s - p * (v[i].y / var) + fD * g[i].y) * gm / denom;
-                o.z = (-s - p * (v[i].z / var) + fD * g[i].z) * gm / denom; o.w = (-s - p * (v[i].w / var) + fD * g[i].w) * gm / denom;
+                o.x = dx_of(g[i].x, v[i].x, s, kb, fD, ka); o.y = dx_of(g[i].y, v[i].y, s, kb, fD, ka);
+                o.z = dx_of(g[i].z, v[i].z, s, kb, fD, ka); o.w = dx_of(g[i].w, v[i].w, s, kb, fD, ka);
                 dp[idx] = o;
             }
         }
