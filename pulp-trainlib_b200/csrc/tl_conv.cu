@@ -662,38 +662,40 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
 
     // warp-per-plane staging: a warp takes (stream, channel) planes, its lanes the 16-byte pieces of the plane
     auto stage_item = [&](long long it, float *xs, float *dys) {
-        const int s0 = (int)(it / tiles_h) * S_T;
-        const int th0 = (int)(it % tiles_h) * TH;
+        const int it32 = (int)it;                  // the host keeps the item count below 2^31
+        const int s0 = (it32 / tiles_h) * S_T;
+        const int th0 = (it32 % tiles_h) * TH;
         const int h_in0 = th0 * S - g.padU;
         if (vec) {
             if constexpr (sizeof(T) == 4) {
-#pragma unroll 1
-                for (int pl = warp; pl < S_T * 16; pl += CONV_THREADS / 32) {
+                // every 16-byte piece of the item is one asynchronous copy; thread tid takes the pieces tid, tid + 256, ...  The
+                // piece -> (plane, row, column) split has compile-time divisors and 32-bit offsets from the item's base address.
+                constexpr int NGX = S_T * 16 * PH * W4, NGD = 16 * S_T * WS::TP4;
+                const float *xit = x + ((long long)s0 * g.Cin + ci0) * in_plane + (long long)h_in0 * WIN;
+                const unsigned xdst = (unsigned)__cvta_generic_to_shared(xs) + 16u;
+#pragma unroll
+                for (int k = 0; k < (NGX + CONV_THREADS - 1) / CONV_THREADS; k++) {
+                    const int e = tid + k * CONV_THREADS;
+                    if (NGX % CONV_THREADS != 0 && e >= NGX) break;
+                    const int c4 = e % W4, prow = e / W4, r = prow % PH, pl = prow / PH;
                     const int ci = pl & 15, sl = pl >> 4;
                     if (SMALL && ci >= 4) continue;          // never read; still zero from the initial fill
-                    const bool pok = s0 + sl < g.n && ci0 + ci < g.Cin;
-                    const float *src = x + ((long long)(s0 + sl) * g.Cin + ci0 + ci) * in_plane + (long long)h_in0 * WIN;
-                    const unsigned dst = (unsigned)__cvta_generic_to_shared(xs + pl * PLANE + 4);
-#pragma unroll 1
-                    for (int e = lane; e < PH * W4; e += 32) {
-                        const int r = e / W4, c4 = e % W4;
-                        const bool ok = pok && h_in0 + r >= 0 && h_in0 + r < g.Hin;
-                        const float *sp = ok ? src + r * WIN + 4 * c4 : x;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + (r * RW + 4 * c4) * 4), "l"(sp), "r"(ok ? 16 : 0) : "memory");
-                    }
+                    const bool ok = s0 + sl < g.n && ci0 + ci < g.Cin && (unsigned)(h_in0 + r) < (unsigned)g.Hin;
+                    const int goff = (sl * g.Cin + ci) * (int)in_plane + r * WIN + 4 * c4;
+                    const float *sp = ok ? xit + goff : x;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(xdst + (unsigned)(pl * PLANE + r * RW + 4 * c4) * 4u), "l"(sp), "r"(ok ? 16 : 0) : "memory");
                 }
-#pragma unroll 1
-                for (int pl = warp; pl < 16 * S_T; pl += CONV_THREADS / 32) {
-                    const int sl = pl % S_T, co = pl / S_T;
-                    const bool pok = s0 + sl < g.n && co0 + co < g.Cout;
-                    const float *src = dy + ((long long)(s0 + sl) * g.Cout + co0 + co) * out_plane + (long long)th0 * TW;
-                    const unsigned dst = (unsigned)__cvta_generic_to_shared(dys + co * DYP + sl * TP);
-#pragma unroll 1
-                    for (int e = lane; e < WS::TP4; e += 32) {
-                        const bool ok = pok && th0 + (4 * e) / TW < g.Hout;
-                        const float *sp = ok ? src + 4 * e : dy;
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst + 16 * e), "l"(sp), "r"(ok ? 16 : 0) : "memory");
-                    }
+                const float *dit = dy + ((long long)s0 * g.Cout + co0) * out_plane + (long long)th0 * TW;
+                const unsigned ddst = (unsigned)__cvta_generic_to_shared(dys);
+#pragma unroll
+                for (int k = 0; k < (NGD + CONV_THREADS - 1) / CONV_THREADS; k++) {
+                    const int e = tid + k * CONV_THREADS;
+                    if (NGD % CONV_THREADS != 0 && e >= NGD) break;
+                    const int q = e % WS::TP4, sl = (e / WS::TP4) % S_T, co = e / (WS::TP4 * S_T);
+                    const bool ok = s0 + sl < g.n && co0 + co < g.Cout && th0 + (4 * q) / TW < g.Hout;
+                    const int goff = (sl * g.Cout + co) * (int)out_plane + 4 * q;
+                    const float *sp = ok ? dit + goff : dy;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ddst + (unsigned)(co * DYP + sl * TP + 4 * q) * 4u), "l"(sp), "r"(ok ? 16 : 0) : "memory");
                 }
             }
         } else {
