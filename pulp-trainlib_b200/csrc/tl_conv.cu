@@ -680,6 +680,7 @@ conv_wg3x3_partial_kernel(ConvGeom g, const T *__restrict__ x, const T *__restri
                     const int c4 = e % W4, prow = e / W4, r = prow % PH, pl = prow / PH;
                     const int ci = pl & 15, sl = pl >> 4;
                     if (SMALL && ci >= 4) continue;          // never read; still zero from the initial fill
+                    if (K == 1 && S > 1 && r % S != 0) continue;    // a strided 1x1 filter never reads the rows between its samples
                     const bool ok = s0 + sl < g.n && ci0 + ci < g.Cin && (unsigned)(h_in0 + r) < (unsigned)g.Hin;
                     const int goff = (sl * g.Cin + ci) * (int)in_plane + r * WIN + 4 * c4;
                     const float *sp = ok ? xit + goff : x;
