@@ -34,6 +34,7 @@ struct ConvTcParams {
     int x_base, y_base;         // input coordinate of patch column 0 / row 0 for the tile at the origin
     int NT;                     // output channels per CTA (16, 32 or 64); blockIdx.y picks the slice
     int ring;                   // A buffers per converter group in use (2 or 3: 4*NT + 128*ring <= 512 TMEM columns)
+    int nd, nd_log2;            // accumulator buffers in tensor memory (2 or 4: nd*2*NT + 128*ring <= 512 columns)
     const float *w;             // filters [Cout_w][Cin_w][taps]; every CTA builds its B operand from them in its prologue
     int Cout_w, Cin_w, flip;    // flip = input-gradient role: channels swap roles and the taps run backwards
     // Output placement: output pixel (ho, wo) of the tile grid lands at (ho*osy + oy0, wo*osx + ox0) of an oH x oW plane.
@@ -69,6 +70,7 @@ static constexpr int TC_THREADS = (TMA_WARP + 1) * 32;
 static_assert(FIRST_EPI == 0 && FIRST_ISSUER == 4, "the epilogue warps are the first four: warp w reads TMEM lanes 32 * (w % 4)");
 static constexpr int PS = 3;                // raw patch ring
 static constexpr int NA = GROUPS * RING;    // A buffers in tensor memory
+static constexpr int MAX_ND = 4;            // accumulator buffers (2 when 4 would not fit the 512 columns)
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
 {
@@ -121,8 +123,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     const size_t patch_stride = ((size_t)patch_floats + 31) & ~(size_t)31;
     uint64_t *bars = reinterpret_cast<uint64_t *>(patch + PS * patch_stride);
     uint64_t *patch_full = bars, *patch_empty = bars + PS, *a_full = bars + 2 * PS, *a_empty = bars + 2 * PS + NA;
-    uint64_t *d_full = bars + 2 * PS + 2 * NA, *d_empty = d_full + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + 2);
+    uint64_t *d_full = bars + 2 * PS + 2 * NA, *d_empty = d_full + MAX_ND;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(d_empty + MAX_ND);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     uint32_t *tap_off = tmem_slot + 2;          // byte offset of every filter tap inside a patch plane (up to 25)
 
@@ -131,7 +133,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     if (threadIdx.x == 0) {
         for (int i = 0; i < PS; i++) { mbar_init(&patch_full[i], 1); mbar_init(&patch_empty[i], 4 * GROUPS); }
         for (int i = 0; i < NA; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_empty[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&d_full[i], GROUPS); mbar_init(&d_empty[i], 4); }
+        for (int i = 0; i < MAX_ND; i++) { mbar_init(&d_full[i], GROUPS); mbar_init(&d_empty[i], 4); }
         *abort_flag = 0;
         for (int t = 0; t < p.taps; t++) tap_off[t] = (uint32_t)((t / p.Wk) * p.PWB + (t % p.Wk)) * 4u;
         fence_barrier_init();
@@ -169,7 +171,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t d_col0 = tmem_base, a_col0 = tmem_base + 4 * NT;
+    const uint32_t d_col0 = tmem_base, a_col0 = tmem_base + p.nd * N2;      // nd accumulator buffers of 2 NT columns, then the A ring
     const int co0 = blockIdx.y * NT;
     const int tiles_per_stream_group = p.tiles_w * p.tiles_h;
 
@@ -201,8 +203,8 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             uint32_t cbase = 0;                 // chunks dealt so far (all groups), mod GROUPS
             bool ok = true;
             for (int t = blockIdx.x; t < p.n_tiles && ok && !*abort_flag; t += gridDim.x, tcnt++) {
-                const int dbuf = tcnt & 1;
-                if (!wait_or_abort(&d_empty[dbuf], (tcnt >> 1) & 1, abort_flag, p.status, 2)) break;
+                const int dbuf = tcnt & (p.nd - 1);
+                if (!wait_or_abort(&d_empty[dbuf], (tcnt >> p.nd_log2) & 1, abort_flag, p.status, 2)) break;
                 tc_fence_after();
                 const uint32_t d_addr = d_col0 + dbuf * N2;
                 for (int g = 0; g < p.groups && ok; g++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
@@ -305,17 +307,17 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         const long long plane = (long long)p.oH * p.oW;
         const uint32_t zero8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const uint32_t zero16[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-        // both accumulator buffers start from zero; the first "d_empty" phase completes once that is done
-        for (int c0 = 0; c0 < 2 * N2; c0 += 8) tmem_st8(d_col0 + lane_addr + c0, zero8);
+        // all accumulator buffers start from zero; the first "d_empty" phase completes once that is done
+        for (int c0 = 0; c0 < p.nd * N2; c0 += 8) tmem_st8(d_col0 + lane_addr + c0, zero8);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&d_empty[0]); mbar_arrive(&d_empty[1]); }
+        if (lane == 0) for (int i = 0; i < p.nd; i++) mbar_arrive(&d_empty[i]);
         uint32_t tcnt = 0;
         for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, tcnt++) {
-            const int dbuf = tcnt & 1;
+            const int dbuf = tcnt & (p.nd - 1);
             const int tw0 = (t % p.tiles_w) * p.TW, th0 = ((t / p.tiles_w) % p.tiles_h) * p.TH, s0 = (t / tiles_per_stream_group) * p.S_T;
-            if (!warp_wait_or_abort(&d_full[dbuf], (tcnt >> 1) & 1, abort_flag, p.status, 6, lane)) break;
+            if (!warp_wait_or_abort(&d_full[dbuf], (tcnt >> p.nd_log2) & 1, abort_flag, p.status, 6, lane)) break;
             tc_fence_after();
             const int s = s0 + sl, ho = th0 + ph, wo = tw0 + pw;
             const int oy = ho * p.osy + p.oy0, ox = wo * p.osx + p.ox0;
@@ -426,13 +428,15 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     size_t smem = 0;
     for (;; NT /= 2) {
         const size_t b_floats = (((size_t)p.groups * p.taps * 32 * NT) + 31) & ~(size_t)31;
-        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * NA + 4) * 8 + 16 + 112 + 128;
+        smem = (b_floats + PS * patch_floats) * 4 + (2 * PS + 2 * NA + 2 * MAX_ND) * 8 + 16 + 112 + 128;
         if (smem <= 220 * 1024 || NT == 16) break;
     }
     if (smem > 220 * 1024) return false;
     if (dry_run) return true;   // geometry qualifies; nothing launched
     p.NT = NT;
     p.ring = (4 * NT + 32 * GROUPS * RING <= 512) ? RING : 2;
+    p.nd = (MAX_ND * 2 * NT + 32 * GROUPS * p.ring <= 512) ? MAX_ND : 2;
+    p.nd_log2 = p.nd == 4 ? 2 : 1;
     const int co_tiles = ceil_div(C_dst, NT);
 
     CUtensorMap tmap;
