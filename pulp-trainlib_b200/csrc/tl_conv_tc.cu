@@ -72,16 +72,19 @@ static constexpr int PS = 3;                // raw patch ring
 static constexpr int NA = GROUPS * RING;    // A buffers in tensor memory
 static constexpr int MAX_ND = 4;            // accumulator buffers (2 when 4 would not fit the 512 columns)
 
+// Polling costs issue slots that the converter warps need (half of the instructions this kernel executed were failed
+// polls when every failed attempt slept 32 ns): the first attempt is bare, later ones sleep NAP_FAST / NAP_SLOW ns in
+// between, and the abort flag is only looked at every 16th attempt.
+static constexpr uint32_t NAP_FAST = 128u, NAP_SLOW = 512u;
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
 {
-    // each attempt may sleep in hardware for up to 20 us; 50k attempts bound the wait to about a second
-    // a failed attempt is followed by a short sleep so that the waiting warps (producer, issuers, epilogue) leave
-    // the issue slots to the converter warps; ids 3..5 sit on the critical path and sleep least
-    const uint32_t nap = (id == 3 || id == 4 || id == 5) ? 32u : 256u;
-    for (uint32_t i = 0; i < 50000u; i++) {
-        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
-        if (*abort_flag) return false;
+    // ids 3..5 sit on the critical path and sleep least; about a second of attempts bounds the wait
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint32_t nap = (id == 3 || id == 4 || id == 5) ? NAP_FAST : NAP_SLOW;
+    for (uint32_t i = 0; i < 4000000u; i++) {
         __nanosleep(nap);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 15u) == 15u && *abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(status, 0, id);
@@ -92,12 +95,12 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 // barrier in the same instruction, so the warp stays converged and all lanes get the same answer.
 __device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, int lane)
 {
-    const uint32_t nap = (id == 3 || id == 4 || id == 5) ? 32u : 256u;
-    for (uint32_t i = 0; i < 50000u; i++) {
-        const bool done = mbar_try_wait_hint(bar, parity, 20000u);
-        if (__all_sync(0xffffffffu, done)) return true;
-        if (__any_sync(0xffffffffu, *abort_flag != 0)) return false;
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    const uint32_t nap = (id == 3 || id == 4 || id == 5) ? NAP_FAST : NAP_SLOW;
+    for (uint32_t i = 0; i < 4000000u; i++) {
         __nanosleep(nap);
+        if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+        if ((i & 15u) == 15u && __any_sync(0xffffffffu, *abort_flag != 0)) return false;
     }
     if (lane == 0) { *abort_flag = 1; atomicCAS(status, 0, id); }
     __syncwarp();
