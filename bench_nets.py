@@ -255,7 +255,7 @@ class ResNet8Streams(object):
                 # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.62 MB read + 0.88 MB
                 # written inside the launch; the 33.5 MB output is still dirty in L2 when it ends), scaled by the stream
                 # count: traffic grows in proportion because every stream brings its own planes
-                r["traffic"] = (33.62e6 + 0.88e6) * n / 512.0
+                r["traffic"] = (33.61e6 + 0.60e6) * n / 512.0
                 r["traffic_note"] = "per launch of the 16->16 32x32 forward convolution, ncu at 512 streams scaled by streams; algorithmic bytes of that launch: %.0f MB in + %.0f MB out" % (n * 65536e-6, n * 65536e-6)
             elif "wg" in name:
                 fl, what = conv_flops, "weight gradient of 9 convolutions"
