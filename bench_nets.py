@@ -252,7 +252,7 @@ class ResNet8Streams(object):
         if name in ("conv_tc_kernel", "conv_fw_kernel", "conv_ig_kernel", "conv_wg3x3_partial_kernel", "conv_wg_partial_kernel"):
             if name == "conv_tc_kernel":
                 fl, what = conv_flops + ig_flops, "forward of 9 convolutions + input gradient of 8 (useful FLOP: the zeros of a dilated dY are not counted)"
-                # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.62 MB read + 0.88 MB
+                # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.61 MB read + 0.60 MB
                 # written inside the launch; the 33.5 MB output is still dirty in L2 when it ends), scaled by the stream
                 # count: traffic grows in proportion because every stream brings its own planes
                 r["traffic"] = (33.61e6 + 0.60e6) * n / 512.0
