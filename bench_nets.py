@@ -283,7 +283,7 @@ class ResNet8Streams(object):
         reference_step(net, n, first_stream=first, steps=steps)
         return time.perf_counter() - t0
 
-    def _reference_throughput(self, per_proc=16, steps=1):
+    def _reference_throughput(self, per_proc=128, steps=1):
         """The reference library parallelises one call over a team of 8 threads (NUM_CORES is a compile-time constant of its
         sources).  Streams are independent, so all host cores are used by running cpu_count // 8 processes side by side, each
         with its own team on its own slice of the sample; throughput = streams finished / wall time of the slowest."""
@@ -298,7 +298,7 @@ class ResNet8Streams(object):
         wall = max(times)
         return {"samples_per_s": procs * per_proc * steps / wall, "procs": procs, "cores": 8 * procs, "sample": procs * per_proc, "steps": steps, "wall_s": wall}
 
-    def cpu_baseline(self, sample=16, steps=1):
+    def cpu_baseline(self, sample=128, steps=1):
         r = self._reference_throughput(sample, steps)
         return {"value": r["samples_per_s"], "unit": "samples/s", "cores": r["cores"], "kind": "reference",
                 "sample": "%d of the %d streams (%d processes x %d streams, pthread team of 8 each), %d step(s), reference C sources" % (r["sample"], STREAMS, r["procs"], sample, steps),
@@ -308,10 +308,10 @@ class ResNet8Streams(object):
         if not os.path.exists(NET_REF_MT):
             return {"unavailable": "oracle/_ref/libresnet8_ref.so was not built (needs the reference checkout at build time)", "value": None, "unit": "samples/s"}
         steps = max(1, min(args.steps, 3))
-        r = self._reference_throughput(16, steps)
+        r = self._reference_throughput(128, steps)
         v = r["samples_per_s"]
         return {"metric": "train_step_samples_per_s", "value": v, "unit": "samples/s", "ms_per_step": 1e3 * STREAMS / v, "dtype": "f32",
                 "config": {"workload": self.name, "streams_total": STREAMS, "sample_streams": r["sample"]},
                 "cpu_baseline": {"value": v, "unit": "samples/s", "cores": r["cores"], "kind": "reference",
-                                 "sample": "%d of the %d streams per step: %d processes x 16 streams, each with the reference's pthread team of 8 "
+                                 "sample": "%d of the %d streams per step: %d processes x 128 streams, each with the reference's pthread team of 8 "
                                            "(streams are independent, so samples/s does not depend on the count)" % (r["sample"], STREAMS, r["procs"])}}
