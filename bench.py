@@ -318,6 +318,7 @@ def main():
     ap.add_argument("--dtype", default=None, choices=["fp32", "fp16"], help="default: fp32, fp16 for config 4")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fusion", action="store_true", help="config 5: issue the reference's separate calls for norm, residual sum and ReLU instead of the fused extension calls")
     ap.add_argument("--no-graph", action="store_true", help="time the plain entry-point calls instead of a CUDA-graph replay (single-layer configs)")
     args = ap.parse_args()
     if args.dtype is None:

@@ -106,6 +106,8 @@ class ResNet8Streams(object):
         d_img, d_lab = pkg.DeviceBuffer(lib, img), pkg.DeviceBuffer(lib, lab)
         d_loss = pkg.DeviceBuffer(lib, nbytes=4 * n)
         assert net.resnet8_bind(n, d_params, d_grads, ws.ptr) == 0
+        fused = not getattr(args, "no_fusion", False)
+        net.resnet8_set_fusion(1 if fused else 0)
 
         graph = [None]
 
@@ -220,7 +222,9 @@ class ResNet8Streams(object):
                 "config": {"workload": self.name, "streams_total": total, "streams_per_gpu": n, "lr": LR,
                            "l2": "per-step working set (%.1f GB) exceeds L2; no flush needed" % (4e-9 * net.resnet8_workspace_floats(n)),
                            "parallelism": "streams sharded over %d rank(s); one NCCL all-reduce of %d gradient floats per step" % (world, P),
-                           "replay": "forward + backward replayed as a CUDA graph of the entry-point calls" if graph[0] else "entry-point calls"},
+                           "replay": "forward + backward replayed as a CUDA graph of the entry-point calls" if graph[0] else "entry-point calls",
+                           "calls": "norm + residual sum + ReLU and the shortcut gradient joins as one library call each (same bits as the separate calls; --no-fusion issues the reference's separate calls)" if fused
+                                    else "the reference's separate calls for norm, residual sum, ReLU and gradient joins (--no-fusion)"},
                 "gpu_launches": int(launches), "clocks": clocks, "mean_loss": float(loss_host.mean()),
                 "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n)},
