@@ -320,6 +320,24 @@ __global__ void __launch_bounds__(256) column_partial_kernel(const T *__restrict
         part[(long long)blockIdx.y * dim + j] = t;
     }
 }
+// One pass for few rows: a single slice, the 8 warp sums go straight to the output (with the pair mapping of the second pass).
+template <class TI, class TO>
+__global__ void __launch_bounds__(256) column_direct_kernel(const TI *__restrict__ in, TO *__restrict__ out, int n, int dim, int pairs)
+{
+    __shared__ float sm[8][33];
+    const int c = threadIdx.x & 31, r = threadIdx.x >> 5, j = blockIdx.x * 32 + c;
+    float s = 0.f;
+    if (j < dim)
+        for (int i = r; i < n; i += 8) s += ld(in + (long long)i * dim + j);
+    sm[r][c] = s;
+    __syncthreads();
+    if (r == 0 && j < dim) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) t += sm[k][c];
+        st(out + (pairs > 0 ? (j & 1) * pairs + (j >> 1) : j), t);
+    }
+}
 template <class T>
 __global__ void __launch_bounds__(128) column_final_kernel(const float *__restrict__ part, T *__restrict__ out, int slices, int dim, int pairs)
 {
@@ -333,6 +351,10 @@ template <class TI, class TO>
 static bool column_sum_launch(Scope &sc, const TI *in, TO *out, int n, int dim, int pairs)
 {
     if (n <= 0 || dim <= 0) return true;
+    if (n <= 1024) {        // 128 rows per thread at most: one launch instead of two
+        TL_LAUNCH((column_direct_kernel<TI, TO>), (unsigned)((dim + 31) / 32), 256, 0, in, out, n, dim, pairs);
+        return true;
+    }
     const int rows_per_slice = n >= 4096 ? 64 : (n >= 256 ? 32 : 8), slices = (n + rows_per_slice - 1) / rows_per_slice;
     float *part = sc.scratch<float>((size_t)slices * dim);
     if (!part) return false;
