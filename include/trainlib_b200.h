@@ -134,7 +134,9 @@ void  trainlib_graph_destroy(void *graph);
 
 /* ---- GEMM path selection for diagnostics and profiling.
  * 0 = automatic, 1 = force FFMA SIMT tiles, 2 = force the tcgen05 kernels whose operands are staged by threads
- * (convolutions: the tensor-core kernel at every size), 3 = force the TMA-fed tcgen05 GEMM for the mm family. */
+ * (convolutions: the tensor-core kernel at every size), 3 = force the TMA-fed tcgen05 GEMM for the mm family,
+ * 4 = convolutions take the tensor-core kernel that builds its A operand in tensor memory also where the
+ * row-slot kernel (operands read in place from the TMA-written rows) would qualify. */
 void  trainlib_set_gemm_path(int path);
 /* 0 while every tensor-core kernel so far finished normally; otherwise the id of the bounded
  * device-side wait that gave up (the kernel then returned early and its output is invalid). */

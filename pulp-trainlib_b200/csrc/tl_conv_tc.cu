@@ -389,6 +389,10 @@ static int *status_word()
 int *tc_status_word() { return status_word(); }
 void *tc_encode_tiled_fn() { return (void *)encode_fn(); }
 
+bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst,
+                 int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
+                 int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run, const ConvTcClass *cls);
+
 // Runs the tensor-core kernel when the geometry qualifies; returns false to let the caller use the FFMA path.
 // src: [n][C_src][H_src][W_src], dst: [n][C_dst][H_dst][W_dst]; `flip` = input-gradient role (stride must be 1).
 bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
@@ -408,6 +412,10 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     if (H_dst % TH != 0) return false;
     const long long work = (long long)n * H_dst * W_dst * C_dst * C_src * Hk * Wk;
     if (gemm_path() != 2 && work < (1ll << 21)) return false;  // below about 2 M multiply-adds the FFMA tiles finish before the tensor-core prologue does
+    // width-preserving stride-1 geometries on 32 / 16 / 8-pixel rows: the kernel that splits every input element once
+    if (gemm_path() != 4 && conv_mn_run(src, w, bias, dst, n, C_src, H_src, W_src, C_dst, H_dst, W_dst, Hk, Wk, sh, sw, padU, padL,
+                                        Cout_w, Cin_w, flip, dry_run, cls))
+        return true;
 
     ConvTcParams p;
     p.n = n; p.Cin = C_src; p.Cout = C_dst; p.Hout = H_dst; p.Wout = W_dst;

@@ -394,7 +394,7 @@ const char *trainlib_profile_entry(int i, long long *launches, double *total_ms)
     return g_prof[i].name;
 }
 int trainlib_tc_status(void) { return ready() ? conv_tc_status() : -1; }
-void trainlib_set_gemm_path(int p) { g.gemm_path = (p >= 0 && p <= 3) ? p : 0; }
+void trainlib_set_gemm_path(int p) { g.gemm_path = (p >= 0 && p <= 4) ? p : 0; }
 int trainlib_gemm_path(void) { return g.gemm_path; }
 
 // -------------------------------------------------------------------- PMSIS stand-in

@@ -59,6 +59,37 @@ __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarr
 // make generic-proxy shared-memory writes visible to the async proxy (TMA, tensor cores)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// ------------------------------------------------------------------ bounded waits with a CTA-wide abort flag
+// First attempt bare, later attempts sleep `nap` ns in between; about a second of attempts bounds the wait.  On expiry
+// the thread raises the CTA's abort flag and records `id` in the global status word (first failure wins); every role
+// of the CTA then leaves its loop, tensor memory is released and the kernel returns with invalid output.
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, uint32_t nap)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < 4000000u; i++) {
+        __nanosleep(nap);
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 15u) == 15u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicCAS(status, 0, id);
+    return false;
+}
+// Whole-warp variant for callers that go on to warp-collective tcgen05 instructions: every lane polls the same
+// barrier in the same instruction, so the warp stays converged and all lanes get the same answer.
+__device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, uint32_t nap, int lane)
+{
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    for (uint32_t i = 0; i < 4000000u; i++) {
+        __nanosleep(nap);
+        if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+        if ((i & 15u) == 15u && __any_sync(0xffffffffu, *abort_flag != 0)) return false;
+    }
+    if (lane == 0) { *abort_flag = 1; atomicCAS(status, 0, id); }
+    __syncwarp();
+    return false;
+}
+
 __device__ __forceinline__ bool elect_one()
 {
     uint32_t pred;
@@ -153,6 +184,24 @@ __device__ __forceinline__ uint64_t smem_desc_kmajor_sw128(uint32_t smem_addr, u
     d |= (uint64_t)2 << 61;
     return d;
 }
+
+// Descriptor of an MN-major operand in one of the swizzled layouts TMA writes: the M (or N) index runs fastest.
+// A span of consecutive M elements is contiguous (128 / 64 / 32 bytes for layout type 2, 1 / 4 / 6), the next span
+// follows `lbo` bytes later; consecutive K sit one swizzle row apart and groups of K rows (eight; four for layout
+// type 1) are `sbo` bytes apart.  32-bit operands (kind::tf32) accept only layout type 1: 128-byte rows whose
+// 32-byte pieces are XOR-swizzled with the row number mod 4 - what TMA writes with SWIZZLE_128B_ATOM_32B.
+__device__ __forceinline__ uint64_t smem_desc_mnmajor(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)layout_type << 61;
+    return d;
+}
+constexpr uint32_t LAYOUT_SW128 = 2, LAYOUT_SW64 = 4, LAYOUT_SW32 = 6, LAYOUT_SW128_ATOM32 = 1;
+constexpr uint32_t IDESC_A_MN_MAJOR = 1u << 15, IDESC_B_MN_MAJOR = 1u << 16;   // operand majorness bits of the instruction descriptor
 
 // Instruction descriptor of tcgen05.mma kind::tf32 / kind::f16 with fp32 accumulation, both operands K-major:
 // D format fp32 (1) in bits [4,6), A format in [7,10), B format in [10,13) (0 = f16, 1 = bf16, 2 = tf32),
