@@ -22,9 +22,9 @@
 // 8-channel group of one tile); four converter warps replace every raw value by its TF32 "big" part in place and
 // write the "small" part to the stage's second array (one load, two stores per element); NI issuing threads, each
 // owning one m-block of the tile and its private accumulator in tensor memory, issue per (channel group, filter row)
-//     D[:, 0:2NB] (+)= A_hi * [B_hi | B_lo]^T      D[:, 0:NB] += A_lo * B_hi^T        (or three NB-wide MMAs when 2NB > 256)
-// and hand the stage back with tcgen05.commit; 4 epilogue warps per issuer read D with tcgen05.ld, add the halves,
-// shift-sum the filter columns and store the output.  Every accumulator has one issuing thread that adds in a fixed
+//     D (+)= A_hi * B_hi^T;   D += A_hi * B_lo^T;   D += A_lo * B_hi^T          (the 3xTF32 products, fp32 accumulation)
+// and hand the stage back with tcgen05.commit; epilogue warps read D with tcgen05.ld, shift-sum the filter columns
+// and store the output.  Every accumulator has one issuing thread that adds in a fixed
 // order, so results are bit-reproducible from run to run.
 //
 // Replaces the im2col + mm lowering [ref: lib/sources/pulp_conv2d_fp32.c:85-113, :504-549;
@@ -40,10 +40,10 @@ using namespace tc;
 struct ConvMnParams {
     int n, Cout;                    // streams, channels of the output tensor
     int H, W;                       // plane of the computed grid (= the source plane)
-    int Hk, Wk, padU, padL;         // window of source positions per output pixel
+    int Hk, padU, padL;             // window rows, padding (the window width is the template parameter)
     int cigs;                       // 8-channel groups of the source
-    int NT, NB, stack, DC;          // output channels per CTA, Wk*NT, [hi|lo] stacked in N, accumulator columns
-    int NI, NBUF, VR, NSLOT;        // issuers (= m-blocks per tile), accumulators per issuer, image rows per tile (4 per m-block), slots per stage
+    int NT, NB;                     // output channels per CTA, accumulator columns = WK*NT
+    int NI, NE, NBUF, VR, NSLOT;    // issuers (= m-blocks per tile), epilogue groups, accumulators per issuer, image rows per tile, slots per stage
     int P;                          // streams side by side in one slot (32 / W)
     int stage_bytes, nstage;
     int tiles_per_image, n_tiles;
@@ -55,26 +55,31 @@ struct ConvMnParams {
     int *status;
 };
 
-#ifdef MN_DEBUG
-__device__ float mn_dbg[4096];
-#endif
-static constexpr int MN_CONV_WARPS = 4;
+static constexpr int MN_CONV_WARPS = 3;
 static constexpr int MN_MAX_STAGE = 8;
 static constexpr int MN_MAX_NI = 4;
-static constexpr uint32_t MN_NAP = 64u;
 static constexpr int MN_SLOT = 1024;            // bytes of one slot: 8 channels x 128 bytes
 static constexpr int MN_RPB = 4;                // slots (image rows) per m-block
+static constexpr int MN_MAX_NE = 2;             // epilogue groups of 4 warps (more bought nothing: the kernel is bound by shared-memory bandwidth)
+static constexpr int MN_MAX_THREADS = 32 * (4 * MN_MAX_NE + MN_MAX_NI + 1 + MN_CONV_WARPS);   // 16 warps, 4 per scheduler: 128 registers each
 
+// Every tcgen05 instruction (mma, commit, ld, fence) costs the thread that issues it about 130 cycles whatever its size
+// (measured on B200), so the kernel counts instructions, not bytes: NI threads issue side by side, the epilogue reads an
+// accumulator with the widest loads that fit the register file and the tensor-core fences sit only where tensor memory
+// changes hands.
+//
 // status ids of this kernel's waits: 11 stage free (TMA), 12 accumulator free (issuer), 13 operand ready (issuer),
 // 14 raw data landed (converter), 16 accumulator complete (epilogue)
-__global__ void __launch_bounds__(32 * (5 * MN_MAX_NI + 1 + MN_CONV_WARPS), 1)
+template <int WK, int PADL>
+__global__ void __launch_bounds__(MN_MAX_THREADS, 1)
 conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
 {
     extern __shared__ unsigned char smem_dyn[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int NI = p.NI;
-    const int first_issuer = 4 * NI, tma_warp = 5 * NI, first_conv = 5 * NI + 1;
+    const int first_issuer = 4 * p.NE, tma_warp = first_issuer + NI, first_conv = tma_warp + 1;
     const int nthreads = blockDim.x;
+    constexpr uint32_t nap_conv = 32u, nap_epi = 20u, nap_iss = 0u;      // ns between failed polls (no measurable effect on the run time between 0 and 255)
 
     // shared memory carve-up (stages first: swizzle atoms want 1024-byte alignment)
     const uint32_t base_u32 = smem_u32(smem_dyn);
@@ -99,25 +104,26 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
     }
     if (warp == tma_warp) { tmem_alloc(tmem_slot, 512u); tmem_relinquish(); }
     // B operand (weights of this CTA's output-channel slice), K-major core matrices of 8 rows x 16 bytes:
-    // step (g, a) = channel group g, window row a; inside a step [k4 = 0..1][row r = 0..2NB-1][j = 0..3] with
-    // row r = b*NT + c holding hi(w) and row NB + r holding lo(w) of output channel slice*NT + c, window column b,
-    // source channel g*8 + k4*4 + j.
+    // step (g, a) = channel group g, window row a; inside a step [k4 = 0..1][row r = 0..2NB-1][j = 0..3].
+    // Row r = chunk*(WK*16) + b*16 + c holds hi(w) and row NB + r lo(w) of output channel slice*NT + chunk*16 + c,
+    // window column b, source channel g*8 + k4*4 + j: the WK columns of 16 output channels sit side by side,
+    // so the epilogue fetches them with one wide load.
     {
         const int per_step = p.NB * 8;
         const int total = p.cigs * p.Hk * per_step;
         for (int e = threadIdx.x; e < total; e += nthreads) {
             const int j = e & 3, k4 = (e >> 2) & 1, r = (e >> 3) % p.NB, step = (e >> 3) / p.NB;
             const int a = step % p.Hk, g = step / p.Hk;
-            const int b = r / p.NT, c = r % p.NT;
+            const int chunk = r / (WK * 16), b = (r % (WK * 16)) >> 4, c = chunk * 16 + (r & 15);
             const int n_out = blockIdx.y * p.NT + c, k_in = g * 8 + k4 * 4 + j;
             float v = 0.f;
             if (p.cls) {
                 const int kh = p.kh_r + p.kstep * (p.kh_m - a), kw = p.kw_r + p.kstep * (p.kw_m - b);
                 if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.w_taps + kh * p.w_Wk + kw);
             } else if (!p.flip) {
-                if (n_out < p.Cout_w && k_in < p.Cin_w) v = __ldg(p.w + ((long long)n_out * p.Cin_w + k_in) * p.w_taps + a * p.Wk + b);
+                if (n_out < p.Cout_w && k_in < p.Cin_w) v = __ldg(p.w + ((long long)n_out * p.Cin_w + k_in) * p.w_taps + a * WK + b);
             } else {
-                if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.w_taps + (p.w_taps - 1 - (a * p.Wk + b)));
+                if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.w_taps + (p.w_taps - 1 - (a * WK + b)));
             }
             uint32_t hi, lo;
             split_tf32(v, hi, lo);
@@ -132,11 +138,6 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t stages_u32 = smem_u32(stages);
-#ifdef MN_DEBUG
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 256) mn_dbg[threadIdx.x] = Bs[threadIdx.x];
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { mn_dbg[4000] = (float)tmem_base; mn_dbg[4001] = (float)stages_u32; mn_dbg[4002] = (float)smem_u32(Bs); mn_dbg[4003] = (float)p.NI; mn_dbg[4004] = (float)p.DC; mn_dbg[4005] = (float)p.nstage; mn_dbg[4006]=(float)p.NB; mn_dbg[4007]=(float)p.stack; }
-#endif
-
     if (warp == tma_warp) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -147,7 +148,7 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
                 const int s0 = (t / p.tiles_per_image) * p.P, y0 = (t % p.tiles_per_image) * p.VR;
                 for (int g = 0; g < p.cigs; g++, k++) {
                     const int st = k % p.nstage;
-                    if (!wait_or_abort(&stage_empty[st], ((k / p.nstage) & 1) ^ 1, abort_flag, p.status, 11, 256u)) { ok = false; break; }
+                    if (!wait_or_abort(&stage_empty[st], ((k / p.nstage) & 1) ^ 1, abort_flag, p.status, 11, 128u)) { ok = false; break; }
                     mbar_arrive_expect_tx(&raw_full[st], chunk_tx);
                     tma_load_4d(stages + (size_t)st * 2 * half_bytes, &tmap, &raw_full[st], 0, s0, g * 8, y0 - p.padU);
                 }
@@ -155,33 +156,33 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
         }
     } else if (warp >= first_conv) {
         // ------------------------------------------------------------ converters: raw -> hi in place, lo beside it
-        // TMA writes the slots unswizzled (row R of a slot = channel R, 128 bytes = the 32 pixels).  The tensor core reads
-        // 32-byte pieces XOR-swizzled with R mod 4, so every 16-byte chunk i = R*8 + q of a slot moves to chunk
-        // R*8 + (((q >> 1) ^ (R & 3)) << 1 | (q & 1)) of the same row while it is split.  One warp does one slot per pass:
-        // lane l loads chunks l and l + 32, the warp synchronises (every source chunk has been read), then both parts are
-        // stored - the big part in place of the raw data.
+        // TMA writes a slot as [channel 0..7][32 pixels].  The tensor core is fastest on a K-major A operand (an MN-major
+        // tf32 operand was measured at ~130 cycles per MMA, four times slower), so each slot is transposed while it is
+        // split: pixel p gets one 32-byte row holding its 8 channels, rows 32 bytes apart, the two 16-byte halves of a
+        // row swapped when bit 2 of p is set (the 32-byte swizzle of the K-major layout).  One warp does one slot per
+        // pass: lane = pixel reads its 8 channel values (conflict-free: lanes are consecutive floats), the warp
+        // synchronises (the whole slot has been read), then hi goes back in place and lo to the second array.
         const int cw = warp - first_conv;
         uint32_t k = 0;
         bool ok = true;
-        const int R0 = lane >> 3, q = lane & 7;
-        const int dst0 = R0 * 8 + ((((q >> 1) ^ (R0 & 3)) << 1) | (q & 1));        // rows 0..3 (chunk l); rows 4..7 have the same R & 3
+        const int sw = (lane >> 2) & 1;
         for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
             for (int g = 0; g < p.cigs; g++, k++) {
                 const int st = k % p.nstage;
-                if (!warp_wait_or_abort(&raw_full[st], (k / p.nstage) & 1, abort_flag, p.status, 14, MN_NAP, lane)) { ok = false; break; }
-                float4 *hi4 = reinterpret_cast<float4 *>(stages + (size_t)st * 2 * half_bytes);
-                float4 *lo4 = reinterpret_cast<float4 *>(stages + (size_t)st * 2 * half_bytes + half_bytes);
+                if (!warp_wait_or_abort(&raw_full[st], (k / p.nstage) & 1, abort_flag, p.status, 14, nap_conv, lane)) { ok = false; break; }
+                float *hi_f = reinterpret_cast<float *>(stages + (size_t)st * 2 * half_bytes);
+                float *lo_f = reinterpret_cast<float *>(stages + (size_t)st * 2 * half_bytes + half_bytes);
                 for (int sl = cw; sl < p.NSLOT; sl += MN_CONV_WARPS) {
-                    float4 *h = hi4 + sl * (MN_SLOT / 16), *l = lo4 + sl * (MN_SLOT / 16);
-                    const float4 v0 = h[lane], v1 = h[lane + 32];
-                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
-                    split_tf32_fast(v0.x, a0, b0); split_tf32_fast(v0.y, a1, b1); split_tf32_fast(v0.z, a2, b2); split_tf32_fast(v0.w, a3, b3);
-                    split_tf32_fast(v1.x, c0, d0); split_tf32_fast(v1.y, c1, d1); split_tf32_fast(v1.z, c2, d2); split_tf32_fast(v1.w, c3, d3);
+                    float *h = hi_f + sl * (MN_SLOT / 4), *l = lo_f + sl * (MN_SLOT / 4);
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int c = 0; c < 8; c++) split_tf32_fast(h[c * 32 + lane], hi[c], lo[c]);
                     __syncwarp();
-                    h[dst0] = make_float4(__uint_as_float(a0), __uint_as_float(a1), __uint_as_float(a2), __uint_as_float(a3));
-                    l[dst0] = make_float4(__uint_as_float(b0), __uint_as_float(b1), __uint_as_float(b2), __uint_as_float(b3));
-                    h[dst0 + 32] = make_float4(__uint_as_float(c0), __uint_as_float(c1), __uint_as_float(c2), __uint_as_float(c3));
-                    l[dst0 + 32] = make_float4(__uint_as_float(d0), __uint_as_float(d1), __uint_as_float(d2), __uint_as_float(d3));
+                    float4 *h4 = reinterpret_cast<float4 *>(h) + lane * 2, *l4 = reinterpret_cast<float4 *>(l) + lane * 2;
+                    h4[sw] = make_float4(__uint_as_float(hi[0]), __uint_as_float(hi[1]), __uint_as_float(hi[2]), __uint_as_float(hi[3]));
+                    h4[sw ^ 1] = make_float4(__uint_as_float(hi[4]), __uint_as_float(hi[5]), __uint_as_float(hi[6]), __uint_as_float(hi[7]));
+                    l4[sw] = make_float4(__uint_as_float(lo[0]), __uint_as_float(lo[1]), __uint_as_float(lo[2]), __uint_as_float(lo[3]));
+                    l4[sw ^ 1] = make_float4(__uint_as_float(lo[4]), __uint_as_float(lo[5]), __uint_as_float(lo[6]), __uint_as_float(lo[7]));
                 }
                 fence_proxy_async();
                 __syncwarp();
@@ -192,40 +193,36 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
         // ------------------------------------------------------------ MMA issuers: issuer j owns m-block j of every tile
         if (lane == 0) {
             const int j = warp - first_issuer;
-            const uint32_t n_wide = (uint32_t)(p.stack ? 2 * p.NB : p.NB);
-            const uint32_t idesc_wide = mma_idesc(FMT_TF32, 128, n_wide) | IDESC_A_MN_MAJOR;
-            const uint32_t idesc_nb = mma_idesc(FMT_TF32, 128, (uint32_t)p.NB) | IDESC_A_MN_MAJOR;
-            const uint32_t b_u32 = smem_u32(Bs);
-            const uint32_t b_lbo = (uint32_t)(2 * p.NB) * 16u, b_sbo = 128u, b_lo_rows = (uint32_t)p.NB * 16u;
+            const uint32_t idesc_nb = mma_idesc(FMT_TF32, 128, (uint32_t)p.NB);
+            // Descriptors as (low word, high word): only the start-address field (low word, units of 16 bytes) moves between
+            // MMAs, so the loop keeps running low words and adds constants (the issue loop is latency-bound on one thread).
+            const uint64_t a_tmpl = smem_desc_swizzled(0u, 16u, 256u, LAYOUT_SW32);       // K-major, 32-byte swizzle: rows (pixels) 32 bytes apart, groups of 8 rows 256 bytes apart
+            const uint64_t b_tmpl = smem_desc_kmajor(0u, (uint32_t)(2 * p.NB) * 16u, 128u);
+            const uint32_t a_hiword = (uint32_t)(a_tmpl >> 32), a_loword = (uint32_t)a_tmpl;
+            const uint32_t b_hiword = (uint32_t)(b_tmpl >> 32), b_loword = (uint32_t)b_tmpl;
+            const uint32_t b_step16 = b_step_bytes >> 4, b_lo16 = ((uint32_t)p.NB * 16u) >> 4, half16 = half_bytes >> 4;
+            const uint32_t b_base16 = smem_u32(Bs) >> 4, a_base16 = (stages_u32 + (uint32_t)(j * MN_RPB) * (uint32_t)MN_SLOT) >> 4;
             uint32_t k = 0, tseq = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, tseq++) {
                 const int dbuf = (tseq % p.NBUF) * NI + j;
                 const uint32_t use = tseq / p.NBUF;
-                if (!wait_or_abort(&d_empty[dbuf], (use & 1) ^ 1, abort_flag, p.status, 12, MN_NAP)) break;
-                tc_fence_after();
-                const uint32_t d_addr = tmem_base + (uint32_t)(dbuf * p.DC);
+                if (!wait_or_abort(&d_empty[dbuf], (use & 1) ^ 1, abort_flag, p.status, 12, nap_iss)) break;
+                tc_fence_after();                               // the epilogue's tensor-memory loads of this accumulator come first
+                const uint32_t d_addr = tmem_base + (uint32_t)(dbuf * p.NB);
                 uint32_t acc = 0;
+                uint32_t bw = b_loword + b_base16;              // low word of B_hi's descriptor for step (g, a), advanced as the loop goes
                 for (int g = 0; g < p.cigs; g++, k++) {
                     const int st = k % p.nstage;
-                    if (!wait_or_abort(&a_full[st], (k / p.nstage) & 1, abort_flag, p.status, 13, MN_NAP)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t hi_u32 = stages_u32 + (uint32_t)st * 2u * half_bytes, lo_u32 = hi_u32 + half_bytes;
-                    for (int a = 0; a < p.Hk; a++) {
-                        const uint32_t a_off = (uint32_t)(j * MN_RPB + a) * (uint32_t)MN_SLOT;
-                        const uint64_t a_hi = smem_desc_mnmajor(hi_u32 + a_off, MN_SLOT, MN_SLOT / 2, LAYOUT_SW128_ATOM32);
-                        const uint64_t a_lo = smem_desc_mnmajor(lo_u32 + a_off, MN_SLOT, MN_SLOT / 2, LAYOUT_SW128_ATOM32);
-                        const uint32_t b_addr = b_u32 + (uint32_t)(g * p.Hk + a) * b_step_bytes;
-                        const uint64_t b_hi = smem_desc_kmajor(b_addr, b_lbo, b_sbo);
-                        if (p.stack) {
-                            mma_tf32_ss(d_addr, a_hi, b_hi, idesc_wide, acc);
-                            mma_tf32_ss(d_addr, a_lo, b_hi, idesc_nb, 1u);
-                        } else {
-                            const uint64_t b_lo = smem_desc_kmajor(b_addr + b_lo_rows, b_lbo, b_sbo);
-                            mma_tf32_ss(d_addr, a_hi, b_hi, idesc_nb, acc);
-                            mma_tf32_ss(d_addr, a_hi, b_lo, idesc_nb, 1u);
-                            mma_tf32_ss(d_addr, a_lo, b_hi, idesc_nb, 1u);
-                        }
+                    // (shared-memory operands: the converters' fence.proxy.async and the barrier order them, no tensor-core fence)
+                    if (!wait_or_abort(&a_full[st], (k / p.nstage) & 1, abort_flag, p.status, 13, nap_iss)) { ok = false; break; }
+                    uint32_t aw = a_loword + a_base16 + (uint32_t)st * 2u * half16;
+                    for (int a = 0; a < p.Hk; a++, aw += MN_SLOT / 16, bw += b_step16) {
+                        const uint64_t a_hi = ((uint64_t)a_hiword << 32) | aw, a_lo = ((uint64_t)a_hiword << 32) | (aw + half16);
+                        const uint64_t b_hi = ((uint64_t)b_hiword << 32) | bw, b_lo = ((uint64_t)b_hiword << 32) | (bw + b_lo16);
+                        mma_tf32_ss(d_addr, a_hi, b_hi, idesc_nb, acc);
+                        mma_tf32_ss(d_addr, a_hi, b_lo, idesc_nb, 1u);
+                        mma_tf32_ss(d_addr, a_lo, b_hi, idesc_nb, 1u);
                         acc = 1u;
                     }
                     mma_commit(&stage_empty[st]);
@@ -236,59 +233,73 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
         }
     } else {
         // ------------------------------------------------------------ epilogue: tensor memory -> shift-sum -> global
-        const int j = warp >> 2, q = warp & 3;
+        // Group e (4 warps = the 4 TMEM lane quarters = the 4 image rows of an m-block) serves the m-blocks e, e + NE, ...
+        const int e = warp >> 2, q = warp & 3;
         const int img = lane / p.W, x = lane % p.W;         // lane = pixel of the slot: stream `img` of the pack, column x
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         const long long plane = (long long)p.oH * p.oW;
         const int co0 = blockIdx.y * p.NT;
+        const int ox = x * p.osx + p.ox0;
+        int src[WK]; bool in_row[WK];
+#pragma unroll
+        for (int b = 0; b < WK; b++) { const int d = b - PADL; src[b] = (lane + d) & 31; in_row[b] = (unsigned)(x + d) < (unsigned)p.W; }
         uint32_t tseq = 0;
-        for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, tseq++) {
-            const int dbuf = (tseq % p.NBUF) * NI + j;
+        bool ok = true;
+        for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x, tseq++) {
             const uint32_t use = tseq / p.NBUF;
-            const int s = (t / p.tiles_per_image) * p.P + img, y = (t % p.tiles_per_image) * p.VR + j * MN_RPB + q;
-            const int oy = y * p.osy + p.oy0, ox = x * p.osx + p.ox0;
-            const bool valid = (s < p.n) && (y < p.H) && (oy < p.oH) && (ox < p.oW);
-            float *yp = p.y + ((long long)s * p.Cout + co0) * plane + (long long)oy * p.oW + ox;
-            if (!warp_wait_or_abort(&d_full[dbuf], use & 1, abort_flag, p.status, 16, MN_NAP, lane)) break;
-            tc_fence_after();
-            const uint32_t d_addr = tmem_base + (uint32_t)(dbuf * p.DC) + lane_addr;
-            for (int c0 = 0; c0 < p.NT; c0 += 8) {
-                float acc[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc[i] = 0.f;
-                for (int b = 0; b < p.Wk; b++) {
-                    uint32_t h[8], l[8];
-                    tmem_ld8(d_addr + (uint32_t)(b * p.NT + c0), h);
-                    if (p.stack) tmem_ld8(d_addr + (uint32_t)(p.NB + b * p.NT + c0), l);
+            const int s = (t / p.tiles_per_image) * p.P + img;
+            for (int j = e; j < NI; j += p.NE) {
+                const int dbuf = (tseq % p.NBUF) * NI + j;
+                const int y = (t % p.tiles_per_image) * p.VR + j * MN_RPB + q;
+                const int oy = y * p.osy + p.oy0;
+                const bool valid = (s < p.n) && (y < p.H) && (oy < p.oH) && (ox < p.oW);
+                float *yp = p.y + ((long long)s * p.Cout + co0) * plane + (long long)oy * p.oW + ox;
+                if (!warp_wait_or_abort(&d_full[dbuf], use & 1, abort_flag, p.status, 16, nap_epi, lane)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_addr = tmem_base + (uint32_t)(dbuf * p.NB) + lane_addr;
+                for (int c0 = 0; c0 < p.NT; c0 += 16) {
+                    uint32_t h[WK * 16];
+                    const uint32_t col = d_addr + (uint32_t)((c0 >> 4) * (WK * 16));
+                    if constexpr (WK == 1) { tmem_ld16w(col, h); }
+                    else if constexpr (WK == 2) { tmem_ld32w(col, h); }
+                    else { tmem_ld32w(col, h); tmem_ld16w(col + 32, h + 32); }
                     tmem_wait_ld();
-#ifdef MN_DEBUG
-                    if (blockIdx.x == 0 && blockIdx.y == 0 && tseq == 0 && warp == 0 && c0 == 0) { for (int i = 0; i < 8; i++) { mn_dbg[1280 + (b * 32 + lane) * 16 + i] = __uint_as_float(h[i]); mn_dbg[1280 + (b * 32 + lane) * 16 + 8 + i] = p.stack ? __uint_as_float(l[i]) : 0.f; } }
-#endif
-                    const int d = b - p.padL;
-                    const int src = (lane + d) & 31;
-                    const bool in_row = (unsigned)(x + d) < (unsigned)p.W;
-#pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        float v = __uint_as_float(h[i]);
-                        if (p.stack) v += __uint_as_float(l[i]);
-                        v = __shfl_sync(0xffffffffu, v, src);
-                        if (in_row) acc[i] += v;
+                    if (c0 + 16 >= p.NT) {
+                        // every value of this accumulator is in registers: hand it back before the arithmetic and the stores
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&d_empty[dbuf]);
                     }
-                }
-                if (c0 + 8 >= p.NT) {
-                    // every value of this accumulator has been read: hand it back before the last stores go out
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&d_empty[dbuf]);
-                }
-                if (valid) {
+                    // out = centre column (no shift) + the other columns fetched from the neighbouring lanes; one shuffle per
+                    // shifted column and channel (the SM does one warp shuffle per clock, they are the epilogue's main cost)
+                    float acc[16];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int co = co0 + c0 + i;
-                        if (co < p.Cout) {
-                            float v = acc[i];
-                            if (p.bias) v += __ldg(p.bias + co);
-                            yp[(long long)(c0 + i) * plane] = v;
+                    for (int i = 0; i < 16; i++) acc[i] = 0.f;
+#pragma unroll
+                    for (int b = 0; b < WK; b++) {
+                        if (b == PADL) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) acc[i] += __uint_as_float(h[b * 16 + i]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) {
+                                const float v = __shfl_sync(0xffffffffu, __uint_as_float(h[b * 16 + i]), src[b]);
+                                if (in_row[b]) acc[i] += v;
+                            }
+                        }
+                    }
+                    const int nco = min(16, p.Cout - co0 - c0);
+                    if (valid && nco > 0) {
+                        float *yc = yp + (long long)c0 * plane;
+                        if (p.bias) {
+                            for (int i = 0; i < 16; i++) if (i < nco) acc[i] += __ldg(p.bias + co0 + c0 + i);
+                        }
+                        if (nco == 16) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) yc[(long long)i * plane] = acc[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) if (i < nco) yc[(long long)i * plane] = acc[i];
                         }
                     }
                 }
@@ -318,10 +329,11 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
     const int W = W_dst, H = H_dst;
     if (W != 32 && W != 16 && W != 8) return false;
     if ((((uintptr_t)src) & 15) != 0 || n < 1) return false;
-    if (Hk < 1 || Wk < 1 || Hk > 7 || Wk > 5 || padU < 0 || padL < 0 || padU > Hk - 1 || padL > Wk - 1) return false;
+    if (Hk < 1 || Wk < 1 || Hk > 7 || Wk > 3 || padU < 0 || padL < 0 || padU > Hk - 1 || padL > Wk - 1) return false;
+    if (Wk == 3 && padL != 1) return false;
 
     ConvMnParams p;
-    p.n = n; p.Cout = C_dst; p.H = H; p.W = W; p.Hk = Hk; p.Wk = Wk; p.padU = padU; p.padL = padL;
+    p.n = n; p.Cout = C_dst; p.H = H; p.W = W; p.Hk = Hk; p.padU = padU; p.padL = padL;
     p.cigs = ceil_div(C_src, 8);
     p.P = 32 / W;
 
@@ -333,9 +345,7 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
         if (cpad % NT != 0 && NT != 16) continue;
         const int NB = Wk * NT;
         if (NB > 256) continue;
-        const int stack = (2 * NB <= 256) ? 1 : 0;
-        const int DC = stack ? 2 * NB : NB;
-        int NI = 512 / DC;
+        int NI = 512 / NB;
         if (NI > MN_MAX_NI) NI = MN_MAX_NI;
         for (; NI >= 1 && !found; NI--) {
             if (NI == 3) continue;
@@ -348,8 +358,9 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
             int nstage = (int)((220 * 1024 - (long long)fixed) / (2 * (long long)stage_bytes));
             if (nstage > MN_MAX_STAGE) nstage = MN_MAX_STAGE;
             if (nstage < 3 && !(nstage == 2 && NT == 16 && NI == 1)) continue;
-            p.NT = NT; p.NB = NB; p.stack = stack; p.DC = DC; p.NI = NI;
-            p.NBUF = (2 * NI * DC <= 512) ? 2 : 1;
+            p.NT = NT; p.NB = NB; p.NI = NI;
+            p.NE = NI < MN_MAX_NE ? NI : MN_MAX_NE;
+            p.NBUF = (2 * NI * NB <= 512) ? 2 : 1;
             p.VR = VR; p.NSLOT = NSLOT; p.stage_bytes = stage_bytes; p.nstage = nstage;
             p.tiles_per_image = H / VR;
             p.n_tiles = ceil_div(n, p.P) * p.tiles_per_image;
@@ -387,14 +398,16 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
     if (ctas < 1) ctas = 1;
     if (ctas > p.n_tiles) ctas = p.n_tiles;
     dim3 grid(ctas, co_tiles);
-    const int threads = 32 * (5 * p.NI + 1 + MN_CONV_WARPS);
-    static bool attr_set = false;
-    if (!attr_set) { cudaFuncSetAttribute(conv_mn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; }
-    TL_LAUNCH(conv_mn_kernel, grid, threads, smem, tmap, p);
+    const int threads = 32 * (4 * p.NE + p.NI + 1 + MN_CONV_WARPS);
+#define TL_MN_LAUNCH(WKV, PL)                                                                                          \
+    do {                                                                                                               \
+        static bool attr_set = false;                                                                                  \
+        if (!attr_set) { cudaFuncSetAttribute(conv_mn_kernel<WKV, PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; } \
+        TL_LAUNCH((conv_mn_kernel<WKV, PL>), grid, threads, smem, tmap, p);                                            \
+    } while (0)
+    if (Wk == 1) TL_MN_LAUNCH(1, 0); else if (Wk == 2 && padL == 0) TL_MN_LAUNCH(2, 0); else if (Wk == 2) TL_MN_LAUNCH(2, 1); else TL_MN_LAUNCH(3, 1);
+#undef TL_MN_LAUNCH
     return true;
 }
 
-#ifdef MN_DEBUG
-extern "C" __attribute__((visibility("default"))) int trainlib_mn_debug_read(float *out) { return (int)cudaMemcpyFromSymbol(out, mn_dbg, sizeof(float) * 4096); }
-#endif
 } // namespace tl

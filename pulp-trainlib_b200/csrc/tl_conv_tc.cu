@@ -76,7 +76,7 @@ static constexpr int MAX_ND = 4;            // accumulator buffers (2 when 4 wou
 // polls when every failed attempt slept 32 ns): the first attempt is bare, later ones sleep NAP_FAST / NAP_SLOW ns in
 // between, and the abort flag is only looked at every 16th attempt.
 static constexpr uint32_t NAP_FAST = 128u, NAP_SLOW = 512u;
-__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
+__device__ __forceinline__ bool tc_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id)
 {
     // ids 3..5 sit on the critical path and sleep least; about a second of attempts bounds the wait
     if (mbar_try_wait(bar, parity)) return true;
@@ -93,7 +93,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 
 // Whole-warp variant for callers that go on to warp-collective tcgen05 instructions: every lane polls the same
 // barrier in the same instruction, so the warp stays converged and all lanes get the same answer.
-__device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, int lane)
+__device__ __forceinline__ bool tc_warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, int lane)
 {
     if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
     const uint32_t nap = (id == 3 || id == 4 || id == 5) ? NAP_FAST : NAP_SLOW;
@@ -186,7 +186,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                 const int tw0 = (t % p.tiles_w) * p.TW, th0 = ((t / p.tiles_w) % p.tiles_h) * p.TH, s0 = (t / tiles_per_stream_group) * p.S_T;
                 for (int g = 0; g < p.groups; g++, pc++) {
                     const int slot = pc % PS;
-                    if (!wait_or_abort(&patch_empty[slot], ((pc / PS) & 1) ^ 1, abort_flag, p.status, 1)) break;
+                    if (!tc_wait_or_abort(&patch_empty[slot], ((pc / PS) & 1) ^ 1, abort_flag, p.status, 1)) break;
                     mbar_arrive_expect_tx(&patch_full[slot], patch_bytes);
                     tma_load_4d(patch + slot * patch_stride, &tmap, &patch_full[slot], p.x_base + tw0 * p.sw, p.y_base + th0 * p.sh, g * 16, s0);
                 }
@@ -207,13 +207,13 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
             bool ok = true;
             for (int t = blockIdx.x; t < p.n_tiles && ok && !*abort_flag; t += gridDim.x, tcnt++) {
                 const int dbuf = tcnt & (p.nd - 1);
-                if (!wait_or_abort(&d_empty[dbuf], (tcnt >> p.nd_log2) & 1, abort_flag, p.status, 2)) break;
+                if (!tc_wait_or_abort(&d_empty[dbuf], (tcnt >> p.nd_log2) & 1, abort_flag, p.status, 2)) break;
                 tc_fence_after();
                 const uint32_t d_addr = d_col0 + dbuf * N2;
                 for (int g = 0; g < p.groups && ok; g++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
                     for (int tap = (me - cbase) & (GROUPS - 1); tap < p.taps; tap += GROUPS) {
                         const int abuf = me * p.ring + rb;
-                        if (!wait_or_abort(&a_full[abuf], rph, abort_flag, p.status, 3)) { ok = false; break; }
+                        if (!tc_wait_or_abort(&a_full[abuf], rph, abort_flag, p.status, 3)) { ok = false; break; }
                         if (++rb == p.ring) { rb = 0; rph ^= 1u; }
                         tc_fence_after();
                         const uint32_t a_addr = a_col0 + abuf * 32;
@@ -254,7 +254,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
             for (int g = 0; g < p.groups && ok; g++, pc++, cbase = (cbase + p.taps) & (GROUPS - 1)) {
                 const int slot = pc % PS;
-                if (!warp_wait_or_abort(&patch_full[slot], (pc / PS) & 1, abort_flag, p.status, 4, lane)) { ok = false; break; }
+                if (!tc_warp_wait_or_abort(&patch_full[slot], (pc / PS) & 1, abort_flag, p.status, 4, lane)) { ok = false; break; }
                 const int first = (j - cbase) & (GROUPS - 1);
                 // Software pipeline over the taps n = first, first+4, ... of this group: while the tensor-memory
                 // stores of tap n drain, tap n+1 is split in registers and the raw values of tap n+2 are fetched
@@ -276,7 +276,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
                 }
                 for (int tap = first; tap < p.taps; tap += GROUPS) {
                     const int abuf = j * p.ring + rb;
-                    if (!warp_wait_or_abort(&a_empty[abuf], rph ^ 1u, abort_flag, p.status, 5, lane)) { ok = false; break; }
+                    if (!tc_warp_wait_or_abort(&a_empty[abuf], rph ^ 1u, abort_flag, p.status, 5, lane)) { ok = false; break; }
                     if (++rb == p.ring) { rb = 0; rph ^= 1u; }
                     tc_fence_after();
                     const uint32_t a_addr = a_col0 + abuf * 32 + lane_addr;
@@ -320,7 +320,7 @@ conv_tc_kernel(const __grid_constant__ CUtensorMap tmap, const ConvTcParams p)
         for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, tcnt++) {
             const int dbuf = tcnt & (p.nd - 1);
             const int tw0 = (t % p.tiles_w) * p.TW, th0 = ((t / p.tiles_w) % p.tiles_h) * p.TH, s0 = (t / tiles_per_stream_group) * p.S_T;
-            if (!warp_wait_or_abort(&d_full[dbuf], (tcnt >> p.nd_log2) & 1, abort_flag, p.status, 6, lane)) break;
+            if (!tc_warp_wait_or_abort(&d_full[dbuf], (tcnt >> p.nd_log2) & 1, abort_flag, p.status, 6, lane)) break;
             tc_fence_after();
             const int s = s0 + sl, ho = th0 + ph, wo = tw0 + pw;
             const int oy = ho * p.osy + p.oy0, ox = wo * p.osx + p.ox0;

@@ -60,14 +60,17 @@ __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarr
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ------------------------------------------------------------------ bounded waits with a CTA-wide abort flag
-// First attempt bare, later attempts sleep `nap` ns in between; about a second of attempts bounds the wait.  On expiry
-// the thread raises the CTA's abort flag and records `id` in the global status word (first failure wins); every role
-// of the CTA then leaves its loop, tensor memory is released and the kernel returns with invalid output.
+// First attempt bare, later attempts `nap` ns apart (0 = poll back to back), WAIT_ATTEMPTS attempts at most: about a
+// second.  (Parking the thread with mbarrier.try_wait's suspend-time hint instead was measured slower: it wakes late.)
+// On expiry the thread raises the CTA's abort flag and records `id` in the global status word (first failure wins);
+// every role of the CTA then leaves its loop, tensor memory is released and the kernel returns with invalid output.
+// Copies and MMAs still in flight at that moment are not waited for.
+constexpr uint32_t WAIT_ATTEMPTS = 4000000u;
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, uint32_t nap)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < 4000000u; i++) {
-        __nanosleep(nap);
+    for (uint32_t i = 0; i < WAIT_ATTEMPTS; i++) {
+        if (nap) __nanosleep(nap);
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 15u) == 15u && *abort_flag) return false;
     }
@@ -80,8 +83,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 __device__ __forceinline__ bool warp_wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int id, uint32_t nap, int lane)
 {
     if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
-    for (uint32_t i = 0; i < 4000000u; i++) {
-        __nanosleep(nap);
+    for (uint32_t i = 0; i < WAIT_ATTEMPTS; i++) {
+        if (nap) __nanosleep(nap);
         if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
         if ((i & 15u) == 15u && __any_sync(0xffffffffu, *abort_flag != 0)) return false;
     }
@@ -159,6 +162,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16])
                    "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]) : "r"(addr) : "memory");
 }
 
+// wider forms of the same load (one instruction whatever the width: the issue cost of a tcgen05 instruction is fixed)
+__device__ __forceinline__ void tmem_ld16w(uint32_t addr, uint32_t *v)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32w(uint32_t addr, uint32_t *v)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld64w(uint32_t addr, uint32_t *v)
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63]) : "r"(addr) : "memory");
+}
+
 // ------------------------------------------------------------------ descriptors
 // Shared-memory matrix descriptor, K-major, no swizzle ("interleaved" core matrices of 8 rows x 16 bytes):
 // element (row r, 16-byte K chunk c) lives at  start + (r % 8) * 16 + (r / 8) * sbo + c * lbo.
@@ -185,12 +205,13 @@ __device__ __forceinline__ uint64_t smem_desc_kmajor_sw128(uint32_t smem_addr, u
     return d;
 }
 
-// Descriptor of an MN-major operand in one of the swizzled layouts TMA writes: the M (or N) index runs fastest.
-// A span of consecutive M elements is contiguous (128 / 64 / 32 bytes for layout type 2, 1 / 4 / 6), the next span
-// follows `lbo` bytes later; consecutive K sit one swizzle row apart and groups of K rows (eight; four for layout
-// type 1) are `sbo` bytes apart.  32-bit operands (kind::tf32) accept only layout type 1: 128-byte rows whose
-// 32-byte pieces are XOR-swizzled with the row number mod 4 - what TMA writes with SWIZZLE_128B_ATOM_32B.
-__device__ __forceinline__ uint64_t smem_desc_mnmajor(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
+// Descriptor of an operand in one of the swizzled layouts (layout type 2 / 4 / 6 = rows of 128 / 64 / 32 bytes whose
+// 16-byte chunks are XOR-swizzled with the row number; type 1 = 128-byte rows swizzled in 32-byte pieces).
+// K-major (the default): a row holds consecutive K of one M (or N) index, groups of eight rows are `sbo` bytes apart,
+// `lbo` is not used.  MN-major (instruction descriptor bit set): a row holds consecutive M of one K, the next span of
+// M follows `lbo` bytes later and groups of K rows (eight; four for type 1) are `sbo` bytes apart; 32-bit operands
+// (kind::tf32) accept only type 1 there, and the tensor core then needs ~130 cycles per 128 x 8 operand (measured).
+__device__ __forceinline__ uint64_t smem_desc_swizzled(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout_type)
 {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
