@@ -109,6 +109,8 @@ class ResNet8Streams(object):
         fused = not getattr(args, "no_fusion", False)
         net.resnet8_set_fusion(1 if fused else 0)
 
+        loss_check = self.check_first_forward(net, d_img, d_lab, d_loss, first, n, total)
+
         graph = [None]
 
         def step():
@@ -225,7 +227,7 @@ class ResNet8Streams(object):
                            "replay": "forward + backward replayed as a CUDA graph of the entry-point calls" if graph[0] else "entry-point calls",
                            "calls": "norm + residual sum + ReLU and the shortcut gradient joins as one library call each (same bits as the separate calls; --no-fusion issues the reference's separate calls)" if fused
                                     else "the reference's separate calls for norm, residual sum, ReLU and gradient joins (--no-fusion)"},
-                "gpu_launches": int(launches), "clocks": clocks, "mean_loss": float(loss_host.mean()),
+                "gpu_launches": int(launches), "clocks": clocks, "mean_loss": float(loss_host.mean()), "loss_check": loss_check,
                 "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
                         "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n)},
                 "roofline": self.roofline(table, n, pk),
@@ -233,6 +235,30 @@ class ResNet8Streams(object):
         if world == 1 and not args.no_cpu_baseline and os.path.exists(NET_REF_MT):
             line["cpu_baseline"] = self.cpu_baseline()
         return line
+
+    def check_first_forward(self, net, d_img, d_lab, d_loss, first, n, total):
+        """One forward pass with the initial weights, before anything is timed: the per-stream losses of the first and the
+        last 64 streams of the job must equal the reference's own C code (tests/golden/resnet8_streams_golden.npz, written
+        by tests/golden/make_resnet8_golden.py) to 1e-5 of the largest loss.  Each rank checks the windows that fall into
+        its shard; a mismatch stops the benchmark, so a printed throughput always belongs to a correct forward pass."""
+        path = os.path.join(ROOT, "tests", "golden", "resnet8_streams_golden.npz")
+        if not os.path.exists(path):
+            return {"checked_streams": 0, "note": "golden file missing"}
+        gold = np.load(path)
+        net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr)
+        self.lib.trainlib_synchronize(); self.pkg.check(self.lib)
+        assert self.lib.trainlib_tc_status() == 0, "a bounded tensor-core wait gave up: id %d" % self.lib.trainlib_tc_status()
+        loss = d_loss.download(F, (n,))
+        checked, worst = 0, 0.0
+        for a in (0, total - 64):
+            key = "loss_%d" % a
+            if key in gold.files and a >= first and a + 64 <= first + n:
+                want = gold[key]; got = loss[a - first:a - first + 64]
+                err = float(np.abs(got.astype(np.float64) - want).max() / np.abs(want).max())
+                if not (err <= 1e-5):
+                    raise RuntimeError("first-step loss of streams %d..%d differs from the reference: rel err %.3e" % (a, a + 63, err))
+                checked += 64; worst = max(worst, err)
+        return {"checked_streams": checked, "max_rel_err": worst, "bar": 1e-5, "against": "reference C code, per-stream CrossEntropy of the first and last 64 streams, initial weights"}
 
     def roofline(self, table, n, pk):
         """Dominant kernel family of the profiled step against the bound that limits it.  The template variants

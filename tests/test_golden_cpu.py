@@ -7,6 +7,8 @@ import numpy as np
 import pytest
 
 import golden_cases
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 from metrics import assert_close, assert_exact
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -76,3 +78,17 @@ def test_oracle_layernorm_and_gelu_backward_match_autograd(oracle):
     assert np.abs(oracle.act_fw(3, xg) - g.detach().numpy()).max() <= 1e-5
     got = oracle.act_bw(3, xg, oracle.act_fw(3, xg), dyg)
     assert np.abs(got - t.grad.numpy()).max() <= 1e-4 * np.abs(t.grad.numpy()).max()
+
+
+def test_resnet8_golden_is_the_reference(pkg):
+    """pins tests/golden/resnet8_streams_golden.npz on the reference's own C code where that is built (streams 1984-1987
+    recomputed; the file's generator is tests/golden/make_resnet8_golden.py)"""
+    import sys
+    sys.path.insert(0, ROOT)
+    import bench_nets
+    if not os.path.exists(bench_nets.NET_REF_SEQ):
+        pytest.skip("oracle/_ref/libresnet8_ref_seq.so not built (needs the reference checkout at build time)")
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "resnet8_streams_golden.npz"))
+    r = bench_nets.reference_step(bench_nets.bind_net(bench_nets.NET_REF_SEQ), 4, first_stream=1984)
+    assert np.array_equal(r["loss"], gold["loss_1984"][:4]) and np.array_equal(r["logits"], gold["logits_1984"][:4])
+    assert gold["grads_0"].shape == gold["grads_1984"].shape == r["grads"].shape

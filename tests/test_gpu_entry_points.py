@@ -1,0 +1,298 @@
+"""GPU parity of the exported entry points that the layer-level tests do not reach: tensor helpers
+(layout change, copy, fill, vector sum, casts), the bias-add and mm_manager paths, the naive
+convolution kernels called by name, the softmax pieces, mean/std, pointwise convolutions with
+C_in != C_out and in HWC, depthwise forward with stride and padding, and the fp16 twins of
+pointwise / depthwise conv, CrossEntropy, residual, average pooling, im2row and transpose.
+
+Expected values: the semantics written out in numpy from the reference source cited per test, the
+CPU oracle where it has the function, and - when oracle/_ref/libpulp_ref.so travelled with the
+repository - the reference's own code driven through the same structs.
+Bars: bit-exact for data movement, 1e-5 (fp32) / 1e-2 (fp16 storage) for arithmetic."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+from abi_runner import AbiRunner
+from metrics import FP16_TOL, FP32_TOL, assert_close, assert_exact, seeded
+from oracle_bind import geom, out_hw
+
+pytestmark = pytest.mark.gpu
+F = np.float32
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture()
+def run(pkg, gpulib):
+    rs = []
+
+    def make(device=False, half=False):
+        gpulib.trainlib_set_streams(1)
+        r = AbiRunner(pkg, gpulib, device=device, half=half)
+        rs.append(r)
+        return r
+    yield make
+    for r in rs:
+        r.close()
+    gpulib.trainlib_set_streams(1)
+
+
+@pytest.fixture(scope="module")
+def ref_runner(pkg):
+    """The reference's own C code on the host, or None when the library did not travel."""
+    path = os.path.join(ROOT, "oracle", "_ref", "libpulp_ref.so")
+    if not os.path.exists(path):
+        return None
+    return AbiRunner(pkg, pkg.bind(ctypes.CDLL(path)), is_ref=True)
+
+
+def h16(a):
+    return np.asarray(a, F).astype(np.float16).astype(F)
+
+
+# ------------------------------------------------------------------ data movement (bit-exact)
+@pytest.mark.parametrize("device", [False, True])
+def test_layout_change_is_bit_exact(run, ref_runner, device):
+    """HWC_to_CHW / CHW_to_HWC [ref: lib/sources/pulp_train_utils_fp32.c:821-927]: data and/or gradient of a blob,
+    in place, through the caller's transpose buffer"""
+    rng = seeded(31)
+    C, H, W = 5, 6, 7
+    chw = rng.standard_normal((C, H, W)).astype(F); gchw = rng.standard_normal((C, H, W)).astype(F)
+    hwc = np.ascontiguousarray(chw.transpose(1, 2, 0)); ghwc = np.ascontiguousarray(gchw.transpose(1, 2, 0))
+
+    def go(r, fn, data, diff, td, tg):
+        D, G, buf = r.t(data), r.t(diff), r.zeros(C * H * W)
+        args = r.args("layout_args", tensor=r.blob(D, G, C=C, H=H, W=W), transp_buffer=buf, transpose_data=td, transpose_grad=tg)
+        r.call(fn, args)
+        return D.get().copy().ravel(), G.get().copy().ravel()
+    for r in [run(device=device)] + ([ref_runner] if ref_runner else []):
+        d, g_ = go(r, "HWC_to_CHW", hwc, ghwc, 1, 1)
+        assert_exact(d, chw.ravel(), "HWC_to_CHW data"); assert_exact(g_, gchw.ravel(), "HWC_to_CHW grad")
+        d, g_ = go(r, "CHW_to_HWC", chw, gchw, 1, 0)
+        assert_exact(d, hwc.ravel(), "CHW_to_HWC data"); assert_exact(g_, gchw.ravel(), "CHW_to_HWC leaves the gradient alone")
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_copy_fill_sum_are_bit_exact(run, half):
+    """copy, set_to_value, vect_sum [ref: lib/sources/pulp_train_utils_fp32.c:186-222] and their fp16 twins"""
+    rng = seeded(32)
+    n = 1000
+    r = run(device=True, half=half)
+    dt = r.dt
+    a = rng.standard_normal(n).astype(dt); b = rng.standard_normal(n).astype(dt)
+    A, B, O = r.t(a), r.t(b), r.zeros(n)
+    r.call("copy" + r.sfx, r.args(r.sname("copy_args"), **{"from": A, "to": O, "size": n}))
+    assert_exact(O.get(), a, "copy")
+    r.call("set_to_value" + r.sfx, r.args(r.sname("set_to_value_args"), to=O, value=0.375, size=n - 3))
+    want = a.copy(); want[:n - 3] = dt(0.375)
+    assert_exact(O.get(), want, "set_to_value writes `size` elements and no more")
+    r.call("vect_sum" + r.sfx, r.args(r.sname("vect_sum_args"), op_1=A, op_2=B, dest=O, size=n))
+    assert_exact(O.get(), (a.astype(F) + b.astype(F)).astype(dt), "vect_sum")
+
+
+def test_casts(run):
+    """cast_fp32_tensor_to_fp16 / cast_fp16_tensor_to_fp32 [ref: lib/sources/pulp_train_utils_fp16.c:45-80]: round to nearest even, exact widening"""
+    rng = seeded(33)
+    n = 777
+    x = (rng.standard_normal(n) * 10.0 ** rng.integers(-6, 5, n)).astype(F)
+    r = run(device=True)
+    X = r.t(x); Hh = Tens16(r, n); Back = r.zeros(n)
+    r.call("cast_fp32_tensor_to_fp16", r.args("cast_32t16_args", source=X, destination=Hh.arg, size=n))
+    assert_exact(Hh.get(), x.astype(np.float16), "fp32 -> fp16")
+    r.call("cast_fp16_tensor_to_fp32", r.args("cast_16t32_args", source=Hh.arg, destination=Back, size=n))
+    assert_exact(Back.get(), x.astype(np.float16).astype(F), "fp16 -> fp32")
+    Hh.free()
+
+
+class Tens16(object):
+    """a device buffer of n fp16 values beside an fp32 runner"""
+    def __init__(self, r, n):
+        self.r, self.n = r, n
+        self.dev = r.pkg.DeviceBuffer(r.lib, np.zeros(n, np.float16))
+        self.arg = self.dev.ptr
+
+    def get(self):
+        return self.dev.download(np.float16, (self.n,))
+
+    def free(self):
+        self.dev.free()
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_transpose_and_im2row_fp16_twins(run, oracle, half):
+    """transpose (N-d permute) and pulp_im2row: bit-exact in either precision (pure data movement)"""
+    rng = seeded(34)
+    r = run(device=True, half=half)
+    x = rng.standard_normal((3, 4, 5)).astype(r.dt)
+    assert_exact(r.transpose(x, (2, 0, 1)), np.ascontiguousarray(x.transpose(2, 0, 1)), "transpose")
+    g = geom(3, 7, 6, 4, 3, stride=1, pad=1)
+    xi = rng.standard_normal((3, 7, 6)).astype(r.dt)
+    Ho, Wo = out_hw(g)
+    want = oracle.im2row(xi.astype(F), 3, 7, 6, 3, 3, Ho, Wo, 1, 1, 1, 1).astype(r.dt)
+    assert_exact(r.im2row(xi, g), want.ravel(), "im2row")
+
+
+# ------------------------------------------------------------------ bias add, mm_manager, scalar helpers
+@pytest.mark.parametrize("t", [0, 1])
+@pytest.mark.parametrize("half", [False, True])
+def test_mm_bias_add_transposed(run, ref_runner, t, half):
+    """[ref: lib/sources/pulp_train_utils_fp32.c:1286-1323] t = 0: mat[i][j] += bias[j];  t = 1: mat[i][j] += bias[i]"""
+    rng = seeded(35 + t)
+    H, W = 9, 13
+    mat = rng.standard_normal((H, W)).astype(F); bias = rng.standard_normal(H if t else W).astype(F)
+    if half:
+        mat, bias = h16(mat), h16(bias)
+    want = mat + (bias[:, None] if t else bias[None, :])
+    runners = [run(device=True, half=half)] + ([ref_runner] if (ref_runner and not half) else [])
+    for r in runners:
+        M, B = r.t(mat), r.t(bias)
+        r.call("mm_bias_add_transposed" + r.sfx, r.args(r.sname("mm_bias_add_args"), mat=M, bias=B, H=H, W=W, t=t))
+        assert_close(M.get().astype(F), want, FP16_TOL if half else 1e-7, "mm_bias_add_transposed t=%d" % t)
+
+
+@pytest.mark.parametrize("bias_transposed", [0, 1])
+@pytest.mark.parametrize("trans_B", [0, 1])
+def test_mm_manager_product_and_bias(run, oracle, bias_transposed, trans_B):
+    """mm_manager [ref: lib/sources/pulp_train_utils_fp32.c:1330-1683]: the selected product, then, with USE_BIASES = 1,
+    mm_bias_add_transposed over C[N x M] with t = bias_transposed"""
+    rng = seeded(37 + 2 * bias_transposed + trans_B)
+    N, K, M = 11, 29, 17
+    A = rng.standard_normal((N, K)).astype(F); B = rng.standard_normal((M, K) if trans_B else (K, M)).astype(F)
+    bias = rng.standard_normal(N if bias_transposed else M).astype(F)
+    want = oracle.mm(A, B, N, K, M, trans_B) + (bias[:, None] if bias_transposed else bias[None, :])
+    r = run(device=True)
+    a, b, c, bb = r.t(A), r.t(B), r.zeros(N, M), r.t(bias)
+    mm_args = r.args("matMul_args", A=a, B=b, C=c, N=N, K=K, M=M, trans_B=trans_B, bias=bb, bias_dim=bias.size, USE_BIASES=1, bias_transposed=bias_transposed)
+    for layer, step in ((3, 0), (0, 0), (2, 2)):     # LAYER_LINEAR forward, LAYER_CONV2D forward, LAYER_PW_CONV input gradient
+        r.call("mm_manager", r.args("mm_manager_args", mm_args=mm_args, layer_type=layer, step_type=step, matmul_type=10))
+        assert_close(c.get(), want, FP32_TOL, "mm_manager layer %d" % layer)
+    # without the flag the bias pointer is ignored
+    mm_args.USE_BIASES = 0
+    r.call("mm_manager", r.args("mm_manager_args", mm_args=mm_args, layer_type=3, step_type=0, matmul_type=0))
+    assert_close(c.get(), oracle.mm(A, B, N, K, M, trans_B), FP32_TOL, "mm_manager without bias")
+
+
+def test_scalar_mul_row_pieces_mean_std(run, ref_runner, oracle):
+    """pulp_scalar_mul_fp32_cl [ref: pulp_train_utils_fp32.c:1191]; the softmax pieces pulp_row_max / pulp_exp_sum / pulp_row_div
+    [ref: :1046-1189] (exp = the reference's bit-trick fastexp_gist); pulp_mean_std_fp32_cl [ref: :1693-1730]"""
+    rng = seeded(39)
+    H, W = 12, 37
+    x = rng.standard_normal((H, W)).astype(F)
+
+    def pieces(r):
+        X, mx, out, sums = r.t(x), r.t(np.full(H, -np.inf, F) if not r.is_ref else np.full(H, -3.0e38, F)), r.zeros(H, W), r.zeros(H)
+        r.call("pulp_row_max_fp32_cl", r.args("max_args", input=X, H=H, W=W, maxes=mx))
+        r.call("pulp_exp_sum_fp32_cl", r.args("exp_sum_args", input=X, output=out, H=H, W=W, maxes=mx, sums=sums))
+        e = out.get().copy()
+        r.call("pulp_row_div_fp32_cl", r.args("row_div_args", input=out, H=H, W=W, sums=sums))
+        sc = r.t(x.ravel())
+        r.call("pulp_scalar_mul_fp32_cl", r.args("scalar_mul_args", input=sc, scalar=0.3125, dim=H * W))
+        m, v, s = r.zeros(1), r.zeros(1), r.zeros(1)
+        r.call("pulp_mean_std_fp32_cl", r.args("mean_std_args", input=X, mean=m, var=v, std=s, epsilon=1e-5, dim=H * W))
+        return dict(max=mx.get().copy(), exp=e, sums=sums.get().copy(), soft=out.get().copy(), scaled=sc.get().copy(),
+                    mean=m.get().copy(), var=v.get().copy(), std=s.get().copy())
+    got = pieces(run(device=True))
+    assert_exact(got["max"], x.max(axis=1), "row max")
+    assert_exact(got["scaled"], (x.ravel() * F(0.3125)), "scalar mul")
+    assert_close(got["soft"], oracle.softmax_fw(x), FP32_TOL, "row_max + exp_sum + row_div = softmax forward")
+    assert_close(got["sums"], got["exp"].sum(axis=1), FP32_TOL, "row sums of the exponentials")
+    xm = x.astype(np.float64)
+    assert_close(got["mean"], [xm.mean()], FP32_TOL, "mean"); assert_close(got["var"], [xm.var() + 1e-5], 2e-5, "var + eps")
+    assert_close(got["std"], [np.sqrt(xm.var() + 1e-5)], FP32_TOL, "std")
+    if ref_runner:
+        want = pieces(ref_runner)
+        for k in ("max", "scaled"):
+            assert_exact(got[k], want[k], k + " vs reference")
+        for k in ("exp", "sums", "soft", "mean", "var", "std"):
+            assert_close(got[k], want[k], FP32_TOL, k + " vs reference")
+
+
+# ------------------------------------------------------------------ convolutions by other doors
+def test_naive_conv_kernels_by_name(run, oracle):
+    """naive_conv2d_{fw,param_grad,in_grad}_kernel_CHW [ref: lib/sources/pulp_conv_naive_fp32.c:198-516] take a matMul_args with
+    A = input (or its gradient), B = weights (or their gradient), C = output (or its gradient) and the geometry fields"""
+    rng = seeded(40)
+    g = geom(5, 9, 8, 7, 3, stride=2, pad=1)
+    Ho, Wo = out_hw(g)
+    x = rng.uniform(-1, 1, (5, 9, 8)).astype(F); w = rng.uniform(-1, 1, (7, 5, 3, 3)).astype(F); dy = rng.standard_normal((7, Ho, Wo)).astype(F)
+    bias = rng.standard_normal(7).astype(F)
+    r = run(device=True)
+    geo = dict(H=g["Hin"], W=g["Win"], pH=3, pW=3, pCin=5, pCout=7, stride_h=2, stride_w=2, Lpad=1, Rpad=1, Upad=1, Dpad=1, HWC=0)
+    X, W_, Y, Bt = r.t(x), r.t(w), r.zeros(7, Ho, Wo), r.t(bias)
+    r.call("naive_conv2d_fw_kernel_CHW", r.args("matMul_args", A=X, B=W_, C=Y, bias=Bt, USE_BIASES=1, **geo))
+    assert_close(Y.get(), oracle.conv2d_fw(x, w, bias, g), FP32_TOL, "naive fw")
+    dW, dY, dB = r.zeros(*w.shape), r.t(dy), r.zeros(7)
+    r.call("naive_conv2d_param_grad_kernel_CHW", r.args("matMul_args", A=X, B=dW, C=dY, bias=dB, USE_BIASES=1, **geo))
+    want_dw, want_db = oracle.conv2d_wg(x, dy, g, with_bias=True)
+    assert_close(dW.get(), want_dw, FP32_TOL, "naive wg"); assert_close(dB.get(), want_db, FP32_TOL, "naive bias grad")
+    dX = r.zeros(*x.shape)
+    r.call("naive_conv2d_in_grad_kernel_CHW", r.args("matMul_args", A=dX, B=W_, C=dY, USE_BIASES=0, **geo))
+    assert_close(dX.get(), oracle.conv2d_ig(dy, w, g), FP32_TOL, "naive ig")
+
+
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("Cin,Cout,hwc", [(8, 8, 0), (6, 20, 0), (24, 5, 0), (6, 20, 1), (8, 8, 1)])
+def test_pointwise_conv(run, oracle, Cin, Cout, hwc, half):
+    """pulp_conv_pw_* [ref: lib/sources/pulp_conv_pw_fp32.c:27-330] against the 1x1 convolution of the oracle, also where
+    C_in != C_out (the reference's own input gradient swaps two dimensions there) and in HWC"""
+    rng = seeded(41 + Cin + Cout)
+    H, W = 6, 5
+    g = geom(Cin, H, W, Cout, 1)
+    x = rng.uniform(-1, 1, (Cin, H, W)).astype(F); w = rng.uniform(-1, 1, (Cout, Cin, 1, 1)).astype(F); dy = rng.standard_normal((Cout, H, W)).astype(F)
+    if half:
+        x, w, dy = h16(x), h16(w), h16(dy)
+    want = dict(y=oracle.conv2d_fw(x, w, None, g), dw=oracle.conv2d_wg(x, dy, g)[0], dx=oracle.conv2d_ig(dy, w, g))
+    r = run(device=True, half=half)
+    if hwc:
+        xi, dyi = np.ascontiguousarray(x.transpose(1, 2, 0)), np.ascontiguousarray(dy.transpose(1, 2, 0))
+        # HWC: activations [H][W][C], coefficients [C_in][C_out] (the reference multiplies X[HW x C_in] by them untransposed, :75-81)
+        wi = np.ascontiguousarray(w.reshape(Cout, Cin).T)
+        got = r.pw(xi.astype(r.dt), wi.astype(r.dt), dyi.astype(r.dt), Cin, Cout, H, W, hwc=1)
+        got = dict(y=got["y"].reshape(H, W, Cout).transpose(2, 0, 1), dw=got["dw"].reshape(Cin, Cout).T, dx=got["dx"].reshape(H, W, Cin).transpose(2, 0, 1))
+    else:
+        got = r.pw(x.astype(r.dt), w.astype(r.dt), dy.astype(r.dt), Cin, Cout, H, W)
+    tol = FP16_TOL if half else FP32_TOL
+    for k in ("y", "dw", "dx"):
+        assert_close(np.asarray(got[k], F).reshape(want[k].shape), want[k], tol, "pointwise %s" % k)
+
+
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("stride,pad", [(1, 0), (1, 1), (2, 1)])
+def test_depthwise_conv(run, oracle, stride, pad, half):
+    """pulp_conv_dw_* [ref: lib/sources/pulp_conv_dw_fp32.c:27-86, pulp_conv_naive_fp32.c:29-194]: the forward honours stride
+    and padding; the gradients are checked where the reference's are defined (stride 1, no padding) and against the
+    correct convolution otherwise"""
+    rng = seeded(50 + 3 * stride + pad)
+    C, H, W, k = 6, 9, 10, 3
+    g = dict(geom(C, H, W, C, k, stride=stride, pad=pad))
+    Ho, Wo = out_hw(g)
+    x = rng.uniform(-1, 1, (C, H, W)).astype(F); w = rng.uniform(-1, 1, (C, k, k)).astype(F); dy = rng.standard_normal((C, Ho, Wo)).astype(F)
+    if half:
+        x, w, dy = h16(x), h16(w), h16(dy)
+        if stride != 1:
+            pytest.skip("DepthWise_Conv_args_fp16 has no stride fields")
+    r = run(device=True, half=half)
+    got = r.dw(x.astype(r.dt), w.astype(r.dt), dy.astype(r.dt), g)
+    tol = FP16_TOL if half else FP32_TOL
+    assert_close(got["y"].astype(F), oracle.dw_fw(x, w, g), tol, "depthwise fw s%d p%d" % (stride, pad))
+    assert_close(got["dw"].astype(F), oracle.dw_wg(x, dy, g), tol, "depthwise wg")
+    assert_close(got["dx"].astype(F), oracle.dw_ig(dy, w, g), tol, "depthwise ig")
+
+
+def test_fp16_twins_of_loss_residual_pool(run, oracle):
+    """fp16 storage twins of CrossEntropy, the residual trio and average pooling against the fp32 oracle on the rounded inputs"""
+    rng = seeded(60)
+    r = run(device=True, half=True)
+    z = h16(rng.standard_normal(10) * 2); t = np.zeros(10, F); t[3] = 1
+    loss, dz = r.loss("CrossEntropyLoss", z.astype(np.float16), t.astype(np.float16))
+    wl, wdz = oracle.ce(z, t)
+    assert_close([loss], [wl], FP16_TOL, "CrossEntropy fp16"); assert_close(dz.astype(F), wdz, FP16_TOL, "CrossEntropy backward fp16")
+    a, b, d, e = [h16(rng.standard_normal(200)) for _ in range(4)]
+    res = r.residual(a.astype(np.float16), b.astype(np.float16), d.astype(np.float16), e.astype(np.float16))
+    assert_close(res["out"].astype(F), a + b, FP16_TOL, "residual fw fp16")
+    assert_close(res["dskip"].astype(F), e + d, FP16_TOL, "sumnode bw fp16"); assert_close(res["dlout"].astype(F), d, FP16_TOL, "residual bw fp16")
+    x = h16(rng.standard_normal((4, 8, 8))); dyp = h16(rng.standard_normal((4, 4, 4)))
+    got = r.avgpool(x.astype(np.float16), dyp.astype(np.float16), 2, 2, 2, 2)
+    want = oracle.avgpool(x, dyp, 2, 2, 2, 2)
+    assert_close(got["y"].astype(F), want[0], FP16_TOL, "avgpool fw fp16"); assert_close(got["dx"].astype(F), want[1], FP16_TOL, "avgpool bw fp16")

@@ -105,3 +105,38 @@ def test_resnet8_fused_norm_calls_change_nothing(pkg, gpulib):
         net.resnet8_set_fusion(1); gpulib.trainlib_set_gemm_path(0)
     for k in ("logits", "loss", "grads"):
         assert np.array_equal(fused[k], plain[k]), "%s differs between fused and separate calls" % k
+
+
+def param_slices(net):
+    import ctypes
+    net.resnet8_param_offset.restype = ctypes.c_size_t
+    out = []
+    for i in range(net.resnet8_param_blobs()):
+        cnt = ctypes.c_size_t(0)
+        off = net.resnet8_param_offset(i, ctypes.byref(cnt))
+        out.append(slice(off, off + cnt.value))
+    return out
+
+
+def test_resnet8_2048_streams_against_the_reference(pkg, gpulib):
+    """The size the benchmark runs per GPU at N = 2 (and the kernel choices that go with it: two-pass column sums for
+    d(gamma), d(beta) and the Linear bias, which only launches of more than 1024 streams take; long persistent loops in
+    the convolutions).  Streams 0-63 and 1984-2047 of one 2048-stream launch against the reference's own C code
+    (tests/golden/resnet8_streams_golden.npz, written by make_resnet8_golden.py): per-stream logits and loss.  The
+    gradient of every parameter tensor summed over all 2048 streams against reference(0-63) + GPU(64-1983, a launch of
+    its own, also above 1024 streams) + reference(1984-2047)."""
+    import bench_nets
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "resnet8_streams_golden.npz"))
+    net = bench_nets.bind_net(bench_nets.NET_B200)
+    n = 2048
+    whole = gpu_step(pkg, gpulib, net, n, first=0)
+    assert gpulib.trainlib_tc_status() == 0
+    for a, sl in ((0, slice(0, 64)), (1984, slice(1984, 2048))):
+        assert_close(whole["logits"][sl], gold["logits_%d" % a], FP32_TOL, "logits of streams %d.." % a)
+        assert_close(whole["loss"][sl], gold["loss_%d" % a], FP32_TOL, "loss of streams %d.." % a)
+    mid = gpu_step(pkg, gpulib, net, n - 128, first=64)
+    want = gold["grads_0"].astype(np.float64) + mid["grads"].astype(np.float64) + gold["grads_1984"].astype(np.float64)
+    worst = 0.0
+    for i, sl in enumerate(param_slices(net)):
+        worst = max(worst, assert_close(whole["grads"][sl], want[sl], 2e-5, "summed gradient of parameter tensor %d over 2048 streams" % i))
+    print("largest relative error of a summed gradient tensor at 2048 streams: %.2e" % worst)
