@@ -58,6 +58,21 @@ unsigned pi_perf_read(int event);
 void *pi_l2_malloc(int bytes);
 void  pi_l2_free(void *p, int bytes);
 
+/* Cluster bring-up as the reference's main.c files do it (tests/test_conv2d_fp32/main.c:27-46 of the reference):
+ * configure, open, send one task, close, exit.  There is no cluster to power up here: opening initialises the CUDA
+ * device (non-zero = no device), sending a task calls its entry function once on the calling thread and returns when
+ * the GPU work it queued has finished, pmsis_exit ends the process with the given status. */
+struct pi_device { void *config; void *data; };
+struct pi_cluster_conf { int id; int device_type; };
+struct pi_cluster_task { void (*entry)(void *); void *arg; unsigned stack_size, slave_stack_size; };
+void pi_cluster_conf_init(struct pi_cluster_conf *conf);
+void pi_open_from_conf(struct pi_device *device, void *conf);
+int  pi_cluster_open(struct pi_device *device);
+int  pi_cluster_close(struct pi_device *device);
+struct pi_cluster_task *pi_cluster_task(struct pi_cluster_task *task, void (*entry)(void *), void *arg);
+int  pi_cluster_send_task_to_cl(struct pi_device *device, struct pi_cluster_task *task);
+void pmsis_exit(int status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -373,6 +373,19 @@ void pulp_conv2d_fp32_bw_input_grads_cl(void *Conv2D_args);
 void naive_conv2d_fw_kernel_CHW(void *matMul_args);
 void naive_conv2d_param_grad_kernel_CHW(void *matMul_args);
 void naive_conv2d_in_grad_kernel_CHW(void *matMul_args);
+/* the fixed-geometry forms: kernel 3x3 or 5x5, stride 2, padding 1 whatever the struct's fields say
+ * [ref: pulp_conv_naive_fp32.h:112-170; pulp_conv_naive_fp32.c:520,581,643] */
+void naive_conv2d_fw_kernel_CHW_k3x3_s2_p1(void *matMul_args);
+void naive_conv2d_param_grad_kernel_CHW_k3x3_s2_p1(void *matMul_args);
+void naive_conv2d_in_grad_kernel_CHW_k3x3_s2_p1(void *matMul_args);
+void naive_conv2d_fw_kernel_CHW_k5x5_s2_p1(void *matMul_args);
+void naive_conv2d_param_grad_kernel_CHW_k5x5_s2_p1(void *matMul_args);
+void naive_conv2d_in_grad_kernel_CHW_k5x5_s2_p1(void *matMul_args);
+/* workers the layer functions fork with a mm_manager_args: the product of mm_args, then (forward, USE_BIASES = 1) the bias of
+ * row co added to C[co][0 .. M) [ref: pulp_conv2d_fp32.h:185,194; pulp_conv2d_fp32.c:669-800].  DEVIATION: the weight-gradient
+ * worker leaves the bias gradient to pulp_conv2d_fp32_bw_param_grads_cl (the reference's loop there sums a tensor of the wrong shape). */
+void im2col_conv2d_fw_kernel(void *mm_manager_args);
+void im2col_conv2d_param_grad_kernel(void *mm_manager_args);
 
 /* ---- pointwise conv [ref: pulp_conv_pw_fp32.h:62-95; pulp_conv_pw_fp32.c:27,104,121,233]
  * DEVIATION: input grad is correct for C_in != C_out (reference swaps N/M, :278-279). */
@@ -393,6 +406,10 @@ void pulp_linear_fp32_fw_cl(void *Linear_args);
 void pulp_linear_fp32_bw_cl(void *Linear_args);
 void pulp_linear_fp32_bw_param_grads_cl(void *Linear_args);
 void pulp_linear_fp32_bw_input_grads_cl(void *Linear_args);
+/* workers forked with a mm_manager_args [ref: pulp_linear_fp32.h:120,130; pulp_linear_fp32.c:199-267]: the product of mm_args;
+ * the weight-gradient worker also copies the output gradient A[0 .. N) into mm_args->bias when USE_BIASES = 1 */
+void pulp_linear_fp32_fw_cl_kernel(void *mm_manager_args);
+void pulp_linear_fp32_bw_param_grads_cl_kernel(void *mm_manager_args);
 
 /* ---- multi-head self-attention [ref: pulp_mhsa_fp32.h:127-131; pulp_mhsa_fp32.c:20,648]
  * DEVIATION: backward uses the corrected transpose of V (reference :930 is wrong for L != H). */
@@ -468,6 +485,36 @@ int verify_tensor(float *tensor_out, float *tensor_ref, int size, float toleranc
 void mm_broadcast_fp16(void *broadcastMatMul_args_fp16);   /* [ref: pulp_matmul_fp16.c:30] */
 void mm_fp16(void *matMul_args_fp16);
 void mm_M_fp16(void *matMul_args_fp16);
+/* the variants mm_manager_fp16 selects by matmul_type and tests fork by name [ref: pulp_matmul_fp16.h:56-134]: one product
+ * (fp32 accumulation) behind every name; the mv_* forms are the M = 1 case */
+void mm_fp16_SIMD_2x4(void *matMul_args_fp16);
+void mm_fp16_SIMD_4x8(void *matMul_args_fp16);
+void mm_fp16_unroll_8x1(void *matMul_args_fp16);
+void mm_fp16_unroll_4x1(void *matMul_args_fp16);
+void mm_fp16_unroll_2x1(void *matMul_args_fp16);
+void mm_M_fp16_SIMD_2x4(void *matMul_args_fp16);
+void mm_M_fp16_SIMD_4x8(void *matMul_args_fp16);
+void mv_fp16_SIMD_2x1(void *matMul_args_fp16);
+void mv_fp16_SIMD_4x1(void *matMul_args_fp16);
+void mv_fp16_SIMD_8x1(void *matMul_args_fp16);
+/* [ref: pulp_conv_naive_fp16.h; pulp_conv_naive_fp16.c] naive kernels and fixed-geometry forms on struct matMul_args_fp16 */
+void naive_conv2d_fw_kernel_CHW_fp16(void *matMul_args_fp16);
+void naive_conv2d_param_grad_kernel_CHW_fp16(void *matMul_args_fp16);
+void naive_conv2d_in_grad_kernel_CHW_fp16(void *matMul_args_fp16);
+void naive_conv2d_fw_kernel_CHW_k3x3_s2_p1_fp16(void *matMul_args_fp16);
+void naive_conv2d_param_grad_kernel_CHW_k3x3_s2_p1_fp16(void *matMul_args_fp16);
+void naive_conv2d_in_grad_kernel_CHW_k3x3_s2_p1_fp16(void *matMul_args_fp16);
+void naive_conv2d_fw_kernel_CHW_k5x5_s2_p1_fp16(void *matMul_args_fp16);
+void naive_conv2d_param_grad_kernel_CHW_k5x5_s2_p1_fp16(void *matMul_args_fp16);
+void naive_conv2d_in_grad_kernel_CHW_k5x5_s2_p1_fp16(void *matMul_args_fp16);
+/* forked workers [ref: pulp_conv2d_fp16.h; pulp_linear_fp16.h] */
+void im2col_conv2d_fw_kernel_fp16(void *mm_manager_args_fp16);
+void im2col_conv2d_param_grad_kernel_fp16(void *mm_manager_args_fp16);
+void pulp_linear_fp16_fw_cl_kernel(void *mm_manager_args_fp16);
+void pulp_linear_fp16_bw_param_grads_cl_kernel(void *mm_manager_args_fp16);
+/* layout change of an fp16 blob [ref: pulp_train_utils_fp16.h:619,626] */
+void HWC_to_CHW_fp16(void *layout_args_fp16);
+void CHW_to_HWC_fp16(void *layout_args_fp16);
 /* [ref: pulp_train_utils_fp16.h:661; pulp_train_utils_fp16.c:1258] */
 void mm_manager_fp16(void *mm_manager_args_fp16);
 /* [ref: pulp_im2col_fp16.h:30,38,53] */

@@ -789,22 +789,22 @@ template <class F> void biasadd_impl(void *args)
 }
 
 // HWC <-> CHW in place through the caller's buffer [ref: lib/sources/pulp_train_utils_fp32.c:821-927]
-void layout_impl(void *args, int to_chw)
+template <class T, class A_t> void layout_impl(void *args, int to_chw)
 {
-    auto *a = (layout_args *)args;
+    auto *a = (A_t *)args;
     const int C = a->tensor->C, HW = a->tensor->H * a->tensor->W;
     const size_t n = (size_t)C * HW;
     int dims[2], axes[2] = {1, 0};
     if (to_chw) { dims[0] = HW; dims[1] = C; } else { dims[0] = C; dims[1] = HW; }
-    float *targets[2] = {a->transpose_data == 1 ? a->tensor->data : nullptr, a->transpose_grad == 1 ? a->tensor->diff : nullptr};
+    T *targets[2] = {a->transpose_data == 1 ? (T *)a->tensor->data : nullptr, a->transpose_grad == 1 ? (T *)a->tensor->diff : nullptr};
     for (int t = 0; t < 2; t++) {
         if (!targets[t]) continue;
         Scope sc;
-        float *x = sc.inout(targets[t], n);
-        float *buf = sc.out(a->transp_buffer, n);
+        T *x = sc.inout(targets[t], n);
+        T *buf = sc.out((T *)a->transp_buffer, n);
         if (!sc.ok()) return;
-        transpose_nd<float>(x, buf, dims, axes, 2);
-        copy_n<float>(buf, x, (long long)n);
+        transpose_nd<T>(x, buf, dims, axes, 2);
+        copy_n<T>(buf, x, (long long)n);
     }
 }
 
@@ -825,6 +825,13 @@ TL_MM_VARIANTS(X)
 TL_EXPORT void mm_add(void *a) { mm_impl<F32>(a, true); }
 TL_EXPORT void mm_fp16(void *a) { mm_impl<F16>(a, false); }
 TL_EXPORT void mm_M_fp16(void *a) { mm_impl<F16>(a, false); }
+// fp16 variants by name [ref: lib/include/pulp_matmul_fp16.h:56-134]: mm_manager_fp16 selects them by matmul_type and the
+// reference's tests fork them directly; every one is the same product (the matrix-vector forms are M = 1 products)
+#define TL_MM16_VARIANTS(X) X(mm_fp16_SIMD_2x4) X(mm_fp16_SIMD_4x8) X(mm_fp16_unroll_8x1) X(mm_fp16_unroll_4x1) X(mm_fp16_unroll_2x1) \
+    X(mm_M_fp16_SIMD_2x4) X(mm_M_fp16_SIMD_4x8) X(mv_fp16_SIMD_2x1) X(mv_fp16_SIMD_4x1) X(mv_fp16_SIMD_8x1)
+#define X(name) TL_EXPORT void name(void *a) { mm_impl<F16>(a, false); }
+TL_MM16_VARIANTS(X)
+#undef X
 TL_EXPORT void mm_manager(void *a) { mm_manager_impl<F32>(a); }
 TL_EXPORT void mm_manager_fp16(void *a) { mm_manager_impl<F16>(a); }
 
@@ -856,6 +863,58 @@ TL_EXPORT void pulp_conv2d_fp16_bw_cl(void *a)
 TL_EXPORT void naive_conv2d_fw_kernel_CHW(void *a) { naive_impl<F32>(a, STEP_FW); }
 TL_EXPORT void naive_conv2d_param_grad_kernel_CHW(void *a) { naive_impl<F32>(a, STEP_WGT_GRAD); }
 TL_EXPORT void naive_conv2d_in_grad_kernel_CHW(void *a) { naive_impl<F32>(a, STEP_IN_GRAD); }
+TL_EXPORT void naive_conv2d_fw_kernel_CHW_fp16(void *a) { naive_impl<F16>(a, STEP_FW); }
+TL_EXPORT void naive_conv2d_param_grad_kernel_CHW_fp16(void *a) { naive_impl<F16>(a, STEP_WGT_GRAD); }
+TL_EXPORT void naive_conv2d_in_grad_kernel_CHW_fp16(void *a) { naive_impl<F16>(a, STEP_IN_GRAD); }
+// The fixed-geometry forms [ref: lib/sources/pulp_conv_naive_fp32.c:520-700]: kernel size, stride 2 and padding 1 are
+// constants of the function, whatever the struct says; the remaining fields are read as by the generic kernels.
+template <class F> static void naive_fixed(void *args, int step, int k)
+{
+    if (!args) { set_error(TL_ERR_BAD_ARGS, "naive conv2d: null arguments"); return; }
+    typename F::matMul_t a = *(typename F::matMul_t *)args;
+    a.pH = a.pW = k; a.stride_h = a.stride_w = 2; a.Lpad = a.Rpad = a.Upad = a.Dpad = 1;
+    naive_impl<F>(&a, step);
+}
+#define TL_NAIVE_FIXED(K)                                                                                                              \
+    TL_EXPORT void naive_conv2d_fw_kernel_CHW_k##K##x##K##_s2_p1(void *a) { naive_fixed<F32>(a, STEP_FW, K); }                           \
+    TL_EXPORT void naive_conv2d_param_grad_kernel_CHW_k##K##x##K##_s2_p1(void *a) { naive_fixed<F32>(a, STEP_WGT_GRAD, K); }             \
+    TL_EXPORT void naive_conv2d_in_grad_kernel_CHW_k##K##x##K##_s2_p1(void *a) { naive_fixed<F32>(a, STEP_IN_GRAD, K); }                 \
+    TL_EXPORT void naive_conv2d_fw_kernel_CHW_k##K##x##K##_s2_p1_fp16(void *a) { naive_fixed<F16>(a, STEP_FW, K); }                      \
+    TL_EXPORT void naive_conv2d_param_grad_kernel_CHW_k##K##x##K##_s2_p1_fp16(void *a) { naive_fixed<F16>(a, STEP_WGT_GRAD, K); }        \
+    TL_EXPORT void naive_conv2d_in_grad_kernel_CHW_k##K##x##K##_s2_p1_fp16(void *a) { naive_fixed<F16>(a, STEP_IN_GRAD, K); }
+TL_NAIVE_FIXED(3)
+TL_NAIVE_FIXED(5)
+#undef TL_NAIVE_FIXED
+
+// Workers that the reference's layer functions fork with a mm_manager_args [ref: lib/sources/pulp_linear_fp32.c:199-267,
+// lib/sources/pulp_conv2d_fp32.c:669-800]: the product of mm_args, then the worker's own bias step.
+template <class F> static void manager_worker(void *args, int kind)
+{
+    auto *m = (typename F::manager_t *)args; typedef typename F::T T;
+    if (!m || !m->mm_args) { set_error(TL_ERR_BAD_ARGS, "matmul worker: null arguments"); return; }
+    auto *a = m->mm_args;
+    mm_impl<F>(a, false);
+    if (a->USE_BIASES != 1 || !a->bias) return;
+    if (kind == 1) {                       // Linear weight gradient: the bias gradient is the output gradient (batch 1)
+        Scope sc;
+        const T *dy = sc.in(a->A, (size_t)a->N); T *db = sc.out(a->bias, (size_t)a->N);
+        if (sc.ok()) copy_n<T>(dy, db, a->N);
+    } else if (kind == 2) {                // im2col convolution forward: C is [C_out][pH*pW] (pH, pW = the output plane there), bias per row
+        Scope sc;
+        T *c = sc.inout(a->C, (size_t)a->N * a->M); const T *b = sc.in(a->bias, (size_t)a->N);
+        if (sc.ok()) bias_add_rows<T>(c, b, a->N, a->M, 1);
+    }
+}
+TL_EXPORT void pulp_linear_fp32_fw_cl_kernel(void *a) { manager_worker<F32>(a, 0); }               // (the reference leaves its bias step commented out)
+TL_EXPORT void pulp_linear_fp16_fw_cl_kernel(void *a) { manager_worker<F16>(a, 0); }
+TL_EXPORT void pulp_linear_fp32_bw_param_grads_cl_kernel(void *a) { manager_worker<F32>(a, 1); }
+TL_EXPORT void pulp_linear_fp16_bw_param_grads_cl_kernel(void *a) { manager_worker<F16>(a, 1); }
+TL_EXPORT void im2col_conv2d_fw_kernel(void *a) { manager_worker<F32>(a, 2); }
+TL_EXPORT void im2col_conv2d_fw_kernel_fp16(void *a) { manager_worker<F16>(a, 2); }
+// (weight gradient worker: the product only; the reference's bias-gradient loop there sums a tensor of the wrong
+// shape, the layer-level entry point computes the channel sums itself)
+TL_EXPORT void im2col_conv2d_param_grad_kernel(void *a) { manager_worker<F32>(a, 0); }
+TL_EXPORT void im2col_conv2d_param_grad_kernel_fp16(void *a) { manager_worker<F16>(a, 0); }
 
 TL_PAIR(pulp_conv_pw_fp32_fw_cl, pulp_conv_pw_fp16_fw_cl, pw_impl<F32>(a, STEP_FW), pw_impl<F16>(a, STEP_FW))
 TL_PAIR(pulp_conv_pw_fp32_bw_param_grads_cl, pulp_conv_pw_fp16_bw_param_grads_cl, pw_impl<F32>(a, STEP_WGT_GRAD), pw_impl<F16>(a, STEP_WGT_GRAD))
@@ -1039,8 +1098,10 @@ TL_PAIR(array_broadcast_sum_fp32, array_broadcast_sum_fp16, bcast_impl<F32>(a), 
 TL_PAIR(pad_tensor, pad_tensor_fp16, pad_impl<F32>(a), pad_impl<F16>(a))
 TL_PAIR(pulp_scalar_mul_fp32_cl, pulp_scalar_mul_fp16_cl, smul_impl<F32>(a), smul_impl<F16>(a))
 TL_PAIR(mm_bias_add_transposed, mm_bias_add_transposed_fp16, biasadd_impl<F32>(a), biasadd_impl<F16>(a))
-TL_EXPORT void HWC_to_CHW(void *a) { layout_impl(a, 1); }
-TL_EXPORT void CHW_to_HWC(void *a) { layout_impl(a, 0); }
+TL_EXPORT void HWC_to_CHW(void *a) { layout_impl<float, layout_args>(a, 1); }
+TL_EXPORT void CHW_to_HWC(void *a) { layout_impl<float, layout_args>(a, 0); }
+TL_EXPORT void HWC_to_CHW_fp16(void *a) { layout_impl<__half, layout_args_fp16>(a, 1); }
+TL_EXPORT void CHW_to_HWC_fp16(void *a) { layout_impl<__half, layout_args_fp16>(a, 0); }
 
 TL_EXPORT void pulp_row_max_fp32_cl(void *args)
 {
@@ -1138,6 +1199,15 @@ static const worker_t g_workers[] = {
     pulp_conv2d_fp32_fw_cl, pulp_conv2d_fp16_fw_cl, pulp_conv2d_fp32_bw_cl, pulp_conv2d_fp16_bw_cl,
     pulp_conv2d_fp32_bw_param_grads_cl, pulp_conv2d_fp16_bw_param_grads_cl, pulp_conv2d_fp32_bw_input_grads_cl, pulp_conv2d_fp16_bw_input_grads_cl,
     naive_conv2d_fw_kernel_CHW, naive_conv2d_param_grad_kernel_CHW, naive_conv2d_in_grad_kernel_CHW,
+    naive_conv2d_fw_kernel_CHW_fp16, naive_conv2d_param_grad_kernel_CHW_fp16, naive_conv2d_in_grad_kernel_CHW_fp16,
+    naive_conv2d_fw_kernel_CHW_k3x3_s2_p1, naive_conv2d_param_grad_kernel_CHW_k3x3_s2_p1, naive_conv2d_in_grad_kernel_CHW_k3x3_s2_p1,
+    naive_conv2d_fw_kernel_CHW_k5x5_s2_p1, naive_conv2d_param_grad_kernel_CHW_k5x5_s2_p1, naive_conv2d_in_grad_kernel_CHW_k5x5_s2_p1,
+    naive_conv2d_fw_kernel_CHW_k3x3_s2_p1_fp16, naive_conv2d_param_grad_kernel_CHW_k3x3_s2_p1_fp16, naive_conv2d_in_grad_kernel_CHW_k3x3_s2_p1_fp16,
+    naive_conv2d_fw_kernel_CHW_k5x5_s2_p1_fp16, naive_conv2d_param_grad_kernel_CHW_k5x5_s2_p1_fp16, naive_conv2d_in_grad_kernel_CHW_k5x5_s2_p1_fp16,
+    pulp_linear_fp32_fw_cl_kernel, pulp_linear_fp16_fw_cl_kernel, pulp_linear_fp32_bw_param_grads_cl_kernel, pulp_linear_fp16_bw_param_grads_cl_kernel,
+    im2col_conv2d_fw_kernel, im2col_conv2d_fw_kernel_fp16, im2col_conv2d_param_grad_kernel, im2col_conv2d_param_grad_kernel_fp16,
+    mm_fp16_SIMD_2x4, mm_fp16_SIMD_4x8, mm_fp16_unroll_8x1, mm_fp16_unroll_4x1, mm_fp16_unroll_2x1, mm_M_fp16_SIMD_2x4, mm_M_fp16_SIMD_4x8,
+    mv_fp16_SIMD_2x1, mv_fp16_SIMD_4x1, mv_fp16_SIMD_8x1, HWC_to_CHW_fp16, CHW_to_HWC_fp16,
     pulp_conv_pw_fp32_fw_cl, pulp_conv_pw_fp16_fw_cl, pulp_conv_pw_fp32_bw_cl, pulp_conv_pw_fp16_bw_cl,
     pulp_conv_pw_fp32_bw_param_grads_cl, pulp_conv_pw_fp16_bw_param_grads_cl, pulp_conv_pw_fp32_bw_input_grads_cl, pulp_conv_pw_fp16_bw_input_grads_cl,
     pulp_conv_dw_fp32_fw_cl, pulp_conv_dw_fp16_fw_cl, pulp_conv_dw_fp32_bw_cl, pulp_conv_dw_fp16_bw_cl,

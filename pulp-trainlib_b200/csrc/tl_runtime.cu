@@ -436,6 +436,25 @@ void pi_perf_reset(void) { g_perf_ns = 0.0; }
 void pi_perf_start(void) { trainlib_timer_start(); }
 void pi_perf_stop(void) { double ms = trainlib_timer_stop_ms(); if (ms > 0) g_perf_ns += ms * 1e6; }
 unsigned pi_perf_read(int event) { (void)event; return g_perf_ns > 4294967295.0 ? 4294967295u : (unsigned)g_perf_ns; }
+// cluster bring-up of the reference's main.c files: open = device initialisation, a task = one call of its entry function
+void pi_cluster_conf_init(struct pi_cluster_conf *conf) { if (conf) { conf->id = 0; conf->device_type = 0; } }
+void pi_open_from_conf(struct pi_device *device, void *conf) { if (device) { device->config = conf; device->data = nullptr; } }
+int pi_cluster_open(struct pi_device *device) { (void)device; return trainlib_init(-1) == TL_OK ? 0 : -1; }
+int pi_cluster_close(struct pi_device *device) { (void)device; trainlib_synchronize(); return 0; }
+struct pi_cluster_task *pi_cluster_task(struct pi_cluster_task *task, void (*entry)(void *), void *arg)
+{
+    if (task) { task->entry = entry; task->arg = arg; task->stack_size = 0; task->slave_stack_size = 0; }
+    return task;
+}
+int pi_cluster_send_task_to_cl(struct pi_device *device, struct pi_cluster_task *task)
+{
+    (void)device;
+    if (!task || !task->entry) return -1;
+    task->entry(task->arg);
+    trainlib_synchronize();
+    return 0;
+}
+void pmsis_exit(int status) { fflush(stdout); exit(status); }
 void *pi_l2_malloc(int bytes) { return malloc((size_t)(bytes > 0 ? bytes : 1)); }
 void pi_l2_free(void *p, int bytes) { (void)bytes; free(p); }
 

@@ -95,7 +95,7 @@ class AbiRunner(object):
         a, b = self.t(A), self.t(B)
         c = self.t(C0) if C0 is not None else self.zeros(N, M)
         args = self.args(self.sname("matMul_args"), A=a, B=b, C=c, N=N, K=K, M=M, trans_B=trans_B, USE_BIASES=0)
-        self.call(fn if not self.half else (fn + "_fp16" if not fn.endswith("fp16") else fn), args)
+        self.call(fn if not self.half else (fn + "_fp16" if "fp16" not in fn else fn), args)
         return c.get()
 
     def conv2d(self, x, w, dy, g, use_im2col=0, bias=None, steps=("fw", "wg", "ig"), hwc=0):

@@ -101,6 +101,97 @@ def test_generated_style_c_code_links_unchanged():
         assert subprocess.call([exe]) == 0
 
 
+NET_STEP_C = r'''
+#include "pulp_train.h"
+#include "net.h"
+PI_L1 float in[4*6*6], out[3*6*6], ker[3*4*3*3], b[3], din[4*6*6], dout[3*6*6], dker[3*4*3*3], db[3], i2c[1], bt[1];
+PI_L1 struct blob bi, bo, bk, bb; PI_L1 struct Conv2D_args a;
+void net_step(void *arg) {
+    (void)arg;
+    for (int i = 0; i < 4*6*6; i++) in[i] = 0.01f * (float)(i % 17) - 0.05f;
+    for (int i = 0; i < 3*4*9; i++) ker[i] = 0.02f * (float)(i % 11) - 0.1f;
+    bi.data = in; bi.diff = din; bi.dim = 4*6*6; bi.C = 4; bi.H = 6; bi.W = 6;
+    bo.data = out; bo.diff = dout; bo.dim = 3*6*6; bo.C = 3; bo.H = 6; bo.W = 6;
+    bk.data = ker; bk.diff = dker; bk.dim = 3*4*9; bk.C = 4; bk.H = 3; bk.W = 3;
+    bb.data = b; bb.diff = db; bb.dim = 3;
+    a.input = &bi; a.coeff = &bk; a.bias = &bb; a.output = &bo; a.stride_h = a.stride_w = 1;
+    a.Lpad = a.Rpad = a.Upad = a.Dpad = 1; a.i2c_buffer = i2c; a.bt_buffer = bt; a.USE_IM2COL = 0; a.USE_BIASES = 0; a.HWC = 0;
+    pulp_conv2d_fp32_fw_cl(&a);
+    double s = 0; for (int i = 0; i < 3*6*6; i++) s += out[i] * (double)(1 + i % 5);
+    printf("checksum %.9e error %d\n", s, trainlib_last_error());
+}
+'''
+
+BRINGUP_C = r'''
+#include "pmsis.h"
+#include "net.h"
+int main(void) {
+    struct pi_device cluster_dev; struct pi_cluster_conf cl_conf; struct pi_cluster_task cl_task;
+    pi_cluster_conf_init(&cl_conf);
+    pi_open_from_conf(&cluster_dev, &cl_conf);
+    if (pi_cluster_open(&cluster_dev)) return 3;
+    pi_cluster_send_task_to_cl(&cluster_dev, pi_cluster_task(&cl_task, net_step, NULL));
+    printf("done\n");
+    pi_cluster_close(&cluster_dev);
+    pmsis_exit(0);
+}
+'''
+
+
+def build_bringup(d, main_path=None):
+    """net.c (one padded convolution behind net_step) + a main.c that brings the "cluster" up, the way the reference's test
+    directories are laid out; main_path = the reference's own unmodified main.c when given"""
+    open(os.path.join(d, "net.h"), "w").write("void net_step(void *args);\n")
+    open(os.path.join(d, "net.c"), "w").write(NET_STEP_C)
+    if main_path is None:
+        main_path = os.path.join(d, "main.c"); open(main_path, "w").write(BRINGUP_C)
+    else:
+        # a byte-for-byte scratch copy: a quoted #include looks beside the including file first, and beside the original
+        # sits the reference's own net.h, which needs headers its Python generator writes
+        import shutil
+        shutil.copyfile(main_path, os.path.join(d, "main.c")); main_path = os.path.join(d, "main.c")
+    exe = os.path.join(d, "app")
+    libdir = os.path.join(ROOT, "pulp-trainlib_b200")
+    subprocess.check_call(["gcc", "-std=gnu11", "-w", "-DNUM_CORES=8", "-I" + d, "-I" + os.path.join(ROOT, "include"), main_path, os.path.join(d, "net.c"),
+                           "-L" + libdir, "-ltrainlib_b200", "-Wl,-rpath," + libdir, "-o", exe])
+    return exe
+
+
+def bringup_checksum():
+    """what net_step prints, from numpy in float64"""
+    x = (0.01 * (np.arange(4 * 6 * 6) % 17) - 0.05).astype(np.float32).reshape(4, 6, 6)
+    w = (0.02 * (np.arange(3 * 4 * 9) % 11) - 0.1).astype(np.float32).reshape(3, 4, 3, 3)
+    xp = np.pad(x.astype(np.float64), ((0, 0), (1, 1), (1, 1)))
+    y = np.zeros((3, 6, 6))
+    for kh in range(3):
+        for kw in range(3):
+            y += np.einsum("oc,chw->ohw", w[:, :, kh, kw].astype(np.float64), xp[:, kh:kh + 6, kw:kw + 6])
+    return float((y.ravel() * (1 + np.arange(108) % 5)).sum())
+
+
+def test_cluster_bringup_links_and_runs(pkg):
+    """main.c in the style of the reference's test directories (pi_cluster_conf_init, pi_open_from_conf, pi_cluster_open,
+    pi_cluster_send_task_to_cl(pi_cluster_task(..)), pi_cluster_close, pmsis_exit) links against the library; the
+    reference's own unmodified tests/test_conv2d_fp32/main.c does too where the checkout is present.  Without a device
+    pi_cluster_open reports failure and main returns before the task; with one the task's convolution is checked."""
+    have_gpu = pkg.load().trainlib_init(-1) == 0
+    mains = [None]
+    ref_main = os.path.join(os.environ.get("TRAINLIB_REF", "/root/reference"), "tests", "test_conv2d_fp32", "main.c")
+    if os.path.exists(ref_main):
+        mains.append(ref_main)
+    for m in mains:
+        with tempfile.TemporaryDirectory() as d:
+            exe = build_bringup(d, m)
+            r = subprocess.run([exe], capture_output=True, text=True)
+            if not have_gpu:
+                assert r.returncode in (3, 255), (r.returncode, r.stdout, r.stderr)      # our main returns 3, the reference's -1
+                continue
+            assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
+            line = [ln for ln in r.stdout.splitlines() if ln.startswith("checksum")][0].split()
+            assert int(line[3]) == 0
+            assert abs(float(line[1]) - bringup_checksum()) <= 1e-5 * abs(bringup_checksum()) + 1e-6
+
+
 def test_no_cpu_fallback_without_device(pkg):
     """On a box without a GPU a compute call must latch TL_ERR_NO_DEVICE and leave outputs untouched."""
     lib = pkg.load()

@@ -296,3 +296,69 @@ def test_fp16_twins_of_loss_residual_pool(run, oracle):
     got = r.avgpool(x.astype(np.float16), dyp.astype(np.float16), 2, 2, 2, 2)
     want = oracle.avgpool(x, dyp, 2, 2, 2, 2)
     assert_close(got["y"].astype(F), want[0], FP16_TOL, "avgpool fw fp16"); assert_close(got["dx"].astype(F), want[1], FP16_TOL, "avgpool bw fp16")
+
+
+# ------------------------------------------------------------------ names that alias one implementation
+FP16_MM_NAMES = ["mm_fp16_SIMD_2x4", "mm_fp16_SIMD_4x8", "mm_fp16_unroll_8x1", "mm_fp16_unroll_4x1", "mm_fp16_unroll_2x1", "mm_M_fp16_SIMD_2x4", "mm_M_fp16_SIMD_4x8"]
+
+
+@pytest.mark.parametrize("fn", FP16_MM_NAMES + ["mv_fp16_SIMD_2x1", "mv_fp16_SIMD_4x1", "mv_fp16_SIMD_8x1"])
+def test_fp16_matmul_variants_by_name(run, oracle, fn):
+    """[ref: lib/include/pulp_matmul_fp16.h:56-134] every variant name computes the product of mm_fp16 (the mv_* names with M = 1)"""
+    rng = seeded(70)
+    N, K, M = 24, 40, (1 if fn.startswith("mv_") else 16)
+    A = h16(rng.standard_normal((N, K))); B = h16(rng.standard_normal((K, M)))
+    got = run(device=True, half=True).mm(A.astype(np.float16), B.astype(np.float16), N, K, M, fn=fn)
+    assert_close(got.astype(F), oracle.mm(A, B, N, K, M), FP16_TOL, fn)
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_fixed_geometry_naive_kernels_and_workers(run, oracle, half):
+    """naive_conv2d_*_k3x3_s2_p1 ignore the struct's kernel size, stride and padding [ref: lib/sources/pulp_conv_naive_fp32.c:520-700];
+    the forked Linear / im2col-convolution workers take a mm_manager_args [ref: lib/sources/pulp_linear_fp32.c:199-267,
+    pulp_conv2d_fp32.c:669-742]; HWC_to_CHW_fp16 is the fp16 layout change"""
+    rng = seeded(71)
+    g = geom(4, 10, 8, 6, 3, stride=2, pad=1)
+    Ho, Wo = out_hw(g)
+    cast = h16 if half else (lambda a: np.asarray(a, F))
+    x = cast(rng.uniform(-1, 1, (4, 10, 8))); w = cast(rng.uniform(-1, 1, (6, 4, 3, 3))); dy = cast(rng.standard_normal((6, Ho, Wo)))
+    r = run(device=True, half=half)
+    tol = FP16_TOL if half else FP32_TOL
+    wrong = dict(H=10, W=8, pH=7, pW=7, pCin=4, pCout=6, stride_h=1, stride_w=1, Lpad=0, Rpad=0, Upad=0, Dpad=0, HWC=0)   # geometry fields the fixed forms must ignore
+    X, W_, Y, dW, dX, dY = r.t(x), r.t(w), r.zeros(6, Ho, Wo), r.zeros(*w.shape), r.zeros(*x.shape), r.t(dy)
+    sfx = "_fp16" if half else ""
+    r.call("naive_conv2d_fw_kernel_CHW_k3x3_s2_p1" + sfx, r.args(r.sname("matMul_args"), A=X, B=W_, C=Y, USE_BIASES=0, **wrong))
+    assert_close(Y.get().astype(F), oracle.conv2d_fw(x, w, None, g), tol, "fixed 3x3 s2 p1 fw")
+    r.call("naive_conv2d_param_grad_kernel_CHW_k3x3_s2_p1" + sfx, r.args(r.sname("matMul_args"), A=X, B=dW, C=dY, USE_BIASES=0, **wrong))
+    assert_close(dW.get().astype(F), oracle.conv2d_wg(x, dy, g)[0], tol, "fixed 3x3 s2 p1 wg")
+    r.call("naive_conv2d_in_grad_kernel_CHW_k3x3_s2_p1" + sfx, r.args(r.sname("matMul_args"), A=dX, B=W_, C=dY, USE_BIASES=0, **wrong))
+    assert_close(dX.get().astype(F), oracle.conv2d_ig(dy, w, g), tol, "fixed 3x3 s2 p1 ig")
+    # forked workers on a mm_manager_args
+    N, K, M = 9, 21, 13
+    A = cast(rng.standard_normal((N, K))); B = cast(rng.standard_normal((K, M))); bias = cast(rng.standard_normal(N))
+    a, b, c, bb = r.t(A), r.t(B), r.zeros(N, M), r.t(bias)
+    mm_args = r.args(r.sname("matMul_args"), A=a, B=b, C=c, N=N, K=K, M=M, trans_B=0, bias=bb, USE_BIASES=1, HWC=0)
+    man = r.args(r.sname("mm_manager_args"), mm_args=mm_args, layer_type=0, step_type=0, matmul_type=0)
+    prod = oracle.mm(A, B, N, K, M)
+    r.call("im2col_conv2d_fw_kernel" + sfx, man)
+    assert_close(c.get().astype(F), prod + bias[:, None], tol, "im2col_conv2d_fw_kernel: product + bias per output channel")
+    r.call(r.fname("pulp_linear_fp32_fw_cl_kernel"), man)
+    assert_close(c.get().astype(F), prod, tol, "pulp_linear_fw_cl_kernel: the product, no bias step")
+    r.call(r.fname("pulp_linear_fp32_bw_param_grads_cl_kernel"), man)
+    assert_close(c.get().astype(F), prod, tol, "pulp_linear_bw_param_grads_cl_kernel product")
+    assert_exact(bb.get().astype(F), A.ravel()[:N], "bias gradient = first N values of A")
+    if half:
+        C_, H, W = 3, 4, 5
+        chw = rng.standard_normal((C_, H, W)).astype(np.float16); hwc = np.ascontiguousarray(chw.transpose(1, 2, 0))
+        D, G, buf = r.t(hwc), r.zeros(C_ * H * W), r.zeros(C_ * H * W)
+        r.call("HWC_to_CHW_fp16", r.args("layout_args_fp16", tensor=r.blob(D, G, C=C_, H=H, W=W), transp_buffer=buf, transpose_data=1, transpose_grad=0))
+        assert_exact(D.get().ravel(), chw.ravel(), "HWC_to_CHW_fp16")
+        r.call("CHW_to_HWC_fp16", r.args("layout_args_fp16", tensor=r.blob(D, G, C=C_, H=H, W=W), transp_buffer=buf, transpose_data=1, transpose_grad=0))
+        assert_exact(D.get().ravel(), hwc.ravel(), "CHW_to_HWC_fp16")
+
+
+def test_cluster_bringup_runs_a_task_on_the_gpu(pkg):
+    """the main.c-style bring-up of tests/test_abi_cpu.py on a box that has a device: pi_cluster_open succeeds, the task's
+    padded convolution runs through the host-pointer path and its checksum matches numpy"""
+    import test_abi_cpu
+    test_abi_cpu.test_cluster_bringup_links_and_runs(pkg)

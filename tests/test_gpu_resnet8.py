@@ -122,9 +122,17 @@ def test_resnet8_2048_streams_against_the_reference(pkg, gpulib):
     """The size the benchmark runs per GPU at N = 2 (and the kernel choices that go with it: two-pass column sums for
     d(gamma), d(beta) and the Linear bias, which only launches of more than 1024 streams take; long persistent loops in
     the convolutions).  Streams 0-63 and 1984-2047 of one 2048-stream launch against the reference's own C code
-    (tests/golden/resnet8_streams_golden.npz, written by make_resnet8_golden.py): per-stream logits and loss.  The
-    gradient of every parameter tensor summed over all 2048 streams against reference(0-63) + GPU(64-1983, a launch of
-    its own, also above 1024 streams) + reference(1984-2047)."""
+    (tests/golden/resnet8_streams_golden.npz, written by make_resnet8_golden.py): per-stream logits and loss at 1e-5.
+
+    Gradients summed over all 2048 streams are checked twice: against reference(0-63) + GPU(64-1983, a launch of its
+    own, also above 1024 streams) + reference(1984-2047), and against the sum of two 1024-stream GPU launches (which
+    take the one-pass column sums).  Bar 3e-3 (measured: 4e-4 .. 1e-3 from run to run), not 1e-5, and why: a weight gradient of this network is a sum of
+    N = 2 M signed terms of similar size, so it is about sqrt(N) times one term, and one term is 7e-4 of the result.
+    Two fp32 evaluations of the forward pass (reference and GPU, or two GPU launches whose tensor-core accumulation
+    order differs) agree to 1e-6 but can put a pre-activation on different sides of zero; the ReLU behind it then
+    passes or blocks that element's whole gradient, which moves single terms of the sum (hence also the element-wise
+    bar of 0.3 on elements a hundred times smaller than the largest).  A wrong reduction (a dropped stream, a partial
+    counted twice) would be off by 1/64 or more of the whole tensor."""
     import bench_nets
     gold = np.load(os.path.join(ROOT, "tests", "golden", "resnet8_streams_golden.npz"))
     net = bench_nets.bind_net(bench_nets.NET_B200)
@@ -136,7 +144,11 @@ def test_resnet8_2048_streams_against_the_reference(pkg, gpulib):
         assert_close(whole["loss"][sl], gold["loss_%d" % a], FP32_TOL, "loss of streams %d.." % a)
     mid = gpu_step(pkg, gpulib, net, n - 128, first=64)
     want = gold["grads_0"].astype(np.float64) + mid["grads"].astype(np.float64) + gold["grads_1984"].astype(np.float64)
-    worst = 0.0
+    lo, hi = gpu_step(pkg, gpulib, net, 1024, first=0), gpu_step(pkg, gpulib, net, 1024, first=1024)
+    assert_close(np.concatenate([lo["logits"], hi["logits"]]), whole["logits"], 1e-6, "logits do not depend on the launch size")
+    shards = lo["grads"].astype(np.float64) + hi["grads"].astype(np.float64)
+    worst = [0.0, 0.0]
     for i, sl in enumerate(param_slices(net)):
-        worst = max(worst, assert_close(whole["grads"][sl], want[sl], 2e-5, "summed gradient of parameter tensor %d over 2048 streams" % i))
-    print("largest relative error of a summed gradient tensor at 2048 streams: %.2e" % worst)
+        worst[0] = max(worst[0], assert_close(whole["grads"][sl], want[sl], 3e-3, "summed gradient of parameter tensor %d over 2048 streams vs reference + GPU shards" % i, elem_tol=0.3))
+        worst[1] = max(worst[1], assert_close(whole["grads"][sl], shards[sl], 3e-3, "summed gradient of parameter tensor %d: 2048 streams vs 2 x 1024" % i, elem_tol=0.3))
+    print("largest relative error of a summed gradient tensor at 2048 streams: %.2e vs reference + shard, %.2e vs two GPU shards" % tuple(worst))
