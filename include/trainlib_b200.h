@@ -20,7 +20,8 @@ enum {
     TL_ERR_BAD_ARGS = 3,       /* inconsistent sizes, unsupported flag combination */
     TL_ERR_UNSUPPORTED = 4,    /* a branch the reference itself leaves unimplemented */
     TL_ERR_TOO_LARGE = 5,      /* request exceeds a fixed capacity */
-    TL_ERR_TIMEOUT = 6         /* a bounded device-side wait gave up */
+    TL_ERR_TIMEOUT = 6,        /* a bounded device-side wait gave up: the kernel returned early, its output is invalid */
+    TL_ERR_NO_MEMORY = 7       /* a device or pinned allocation failed; clearable, nothing else is affected */
 };
 int         trainlib_last_error(void);
 const char *trainlib_last_error_string(void);

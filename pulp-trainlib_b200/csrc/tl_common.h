@@ -58,7 +58,7 @@ public:
     template <class T> T *scratch(size_t n) { return (T *)alloc(n * sizeof(T)); }   // device-only temporary
     bool ok() const { return ok_; }
 private:
-    struct Entry { void *host; void *dev; size_t bytes; bool write_back; };
+    struct Entry { void *host; void *dev; size_t bytes; bool write_back; bool copied_in; };
     void *map(void *p, size_t bytes, bool copy_in, bool copy_out);
     void *alloc(size_t bytes);
     std::vector<Entry> entries_;

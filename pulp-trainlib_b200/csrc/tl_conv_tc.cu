@@ -379,12 +379,14 @@ static EncodeTiledFn encode_fn()
     return fn;
 }
 
+static int *g_status_dev = nullptr;
 static int *status_word()
 {
-    static int *dev = nullptr;
-    if (!dev) { if (cudaMalloc(&dev, sizeof(int)) != cudaSuccess) return nullptr; cudaMemset(dev, 0, sizeof(int)); }
-    return dev;
+    if (!g_status_dev) { if (cudaMalloc(&g_status_dev, sizeof(int)) != cudaSuccess) { cudaGetLastError(); return nullptr; } cudaMemset(g_status_dev, 0, sizeof(int)); }
+    return g_status_dev;
 }
+// the word if a tensor-core kernel has ever been launched, else null (never allocates)
+int *tc_status_word_if_any() { return g_status_dev; }
 // shared with the tensor-core GEMM (tl_gemm_tc.cu): one status word for every bounded wait of the library
 int *tc_status_word() { return status_word(); }
 void *tc_encode_tiled_fn() { return (void *)encode_fn(); }
@@ -503,9 +505,12 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
 // Non-zero after a kernel gave up on a bounded wait (which wait is encoded in the value).
 int conv_tc_status()
 {
-    int *dev = status_word();
+    int *dev = g_status_dev;
+    if (!dev) return 0;                     // no tensor-core kernel has run
     int h = 0;
-    if (dev && cudaMemcpy(&h, dev, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess) return h;
+    // on the library's stream: ordered behind the kernels that may still write the word
+    if (cudaMemcpyAsync(&h, dev, sizeof(int), cudaMemcpyDeviceToHost, stream()) == cudaSuccess && cudaStreamSynchronize(stream()) == cudaSuccess) return h;
+    cudaGetLastError();
     return -1;
 }
 

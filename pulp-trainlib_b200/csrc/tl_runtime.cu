@@ -1,7 +1,7 @@
 // Runtime of libtrainlib_b200: device context, error state, staging arena, memory modes,
 // streams mode, timers and the PMSIS stand-in (pi_cl_team_fork & friends).
 #include "tl_common.h"
-namespace tl { int conv_tc_status(); }
+namespace tl { int conv_tc_status(); int *tc_status_word_if_any(); }
 #include "../../include/pmsis.h"
 #include <cstdarg>
 #include <cstring>
@@ -28,6 +28,7 @@ struct Context {
     bool arena_pinned = false;     // a captured graph holds arena addresses: never free or merge chunks again
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     int err = TL_OK;
+    bool cuda_sticky = false;      // the context is lost: TL_ERR_CUDA cannot be cleared
     char err_msg[512] = {0};
 };
 static Context g;
@@ -40,14 +41,34 @@ void set_error(int code, const char *fmt, ...)
     vsnprintf(buf, sizeof buf, fmt, ap);
     va_end(ap);
     fprintf(stderr, "[trainlib_b200] %s\n", buf);
-    if (g.err == TL_OK || code == TL_ERR_CUDA) {     // first error wins; CUDA errors are sticky
-        if (!(g.err == TL_ERR_CUDA)) { g.err = code; snprintf(g.err_msg, sizeof g.err_msg, "%s", buf); }
+    if (g.err == TL_OK || (code == TL_ERR_CUDA && g.err != TL_ERR_CUDA)) {     // first error wins, except that a CUDA failure replaces a softer one
+        g.err = code; snprintf(g.err_msg, sizeof g.err_msg, "%s", buf);
+    }
+}
+
+// Errors that leave the CUDA context unusable (every later call fails too): only these make TL_ERR_CUDA permanent.
+static bool cuda_error_is_sticky(cudaError_t e)
+{
+    switch (e) {
+    case cudaErrorIllegalAddress: case cudaErrorLaunchFailure: case cudaErrorIllegalInstruction: case cudaErrorMisalignedAddress:
+    case cudaErrorInvalidAddressSpace: case cudaErrorInvalidPc: case cudaErrorHardwareStackError: case cudaErrorAssert:
+    case cudaErrorLaunchTimeout: case cudaErrorECCUncorrectable: case cudaErrorDevicesUnavailable: case cudaErrorNoDevice:
+    case cudaErrorInsufficientDriver: case cudaErrorCudartUnloading: case cudaErrorContextIsDestroyed:
+        return true;
+    default:
+        return false;
     }
 }
 
 bool cuda_ok(cudaError_t e, const char *what)
 {
     if (e == cudaSuccess) return true;
+    cudaGetLastError();                              // a non-sticky error must not resurface at the next launch check
+    if (e == cudaErrorMemoryAllocation) {            // recoverable: callers fall back (smaller scratch, other kernel) or report it
+        set_error(TL_ERR_NO_MEMORY, "allocation failed (%s) in %s", cudaGetErrorString(e), what);
+        return false;
+    }
+    if (cuda_error_is_sticky(e)) g.cuda_sticky = true;
     set_error(TL_ERR_CUDA, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
     return false;
 }
@@ -80,7 +101,7 @@ static int init_device(int device)
     return TL_OK;
 }
 
-bool ready() { return init_device(-1) == TL_OK && g.err != TL_ERR_CUDA && g.err != TL_ERR_NO_DEVICE; }
+bool ready() { return init_device(-1) == TL_OK && !g.cuda_sticky && g.err != TL_ERR_NO_DEVICE; }
 cudaStream_t stream() { return g.cur_stream; }
 int streams() { return g.n_streams; }
 int sm_count() { return g.sms; }
@@ -215,7 +236,23 @@ void *Scope::map(void *p, size_t bytes, bool copy_in, bool copy_out)
     if (p == nullptr || !ok_) return nullptr;
     if (is_device_pointer(p)) return p;
     for (auto &e : entries_) {
-        if (e.host == p && e.bytes >= bytes) { e.write_back |= copy_out; return e.dev; }
+        if (e.host == p && e.bytes >= bytes) {
+            // same host range again: one mirror.  It was filled only if some earlier mapping asked for it.
+            if (copy_in && !e.copied_in) {
+                if (!TL_CUDA(cudaMemcpyAsync(e.dev, p, e.bytes, cudaMemcpyHostToDevice, g.cur_stream))) ok_ = false;
+                e.copied_in = true;
+            }
+            e.write_back |= copy_out;
+            return e.dev;
+        }
+        // ranges that overlap without being the same (an in-place operation at an offset, a longer view of the same array)
+        // would get two mirrors and the last write-back would win silently: refuse
+        const char *a0 = (const char *)e.host, *a1 = a0 + e.bytes, *b0 = (const char *)p, *b1 = b0 + bytes;
+        if (b0 < a1 && a0 < b1) {
+            set_error(TL_ERR_BAD_ARGS, "host buffers of one call overlap without being identical (%p+%zu and %p+%zu)", e.host, e.bytes, p, bytes);
+            ok_ = false;
+            return nullptr;
+        }
     }
     void *d = arena_alloc(bytes);
     if (!d) { ok_ = false; return nullptr; }
@@ -223,7 +260,7 @@ void *Scope::map(void *p, size_t bytes, bool copy_in, bool copy_out)
     if (copy_in) {
         if (!TL_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, g.cur_stream))) ok_ = false;
     }
-    entries_.push_back({p, d, bytes, copy_out});
+    entries_.push_back({p, d, bytes, copy_out, copy_in});
     return d;
 }
 
@@ -248,13 +285,26 @@ extern "C" {
 
 int trainlib_last_error(void) { return g.err; }
 const char *trainlib_last_error_string(void) { return g.err_msg; }
-void trainlib_clear_error(void) { if (g.err != TL_ERR_CUDA && g.err != TL_ERR_NO_DEVICE) { g.err = TL_OK; g.err_msg[0] = 0; } }
+void trainlib_clear_error(void) { if (!(g.err == TL_ERR_CUDA && g.cuda_sticky) && g.err != TL_ERR_NO_DEVICE) { g.err = TL_OK; g.err_msg[0] = 0; } }
 
 int trainlib_init(int device) { return init_device(device); }
 int trainlib_device(void) { return g.device; }
 void trainlib_set_stream(void *s) { if (ready()) g.cur_stream = s ? (cudaStream_t)s : g.own_stream; }
 void *trainlib_stream(void) { return ready() ? (void *)g.cur_stream : nullptr; }
-void trainlib_synchronize(void) { if (ready()) TL_CUDA(cudaStreamSynchronize(g.cur_stream)); }
+static bool g_capturing_now();
+// A tensor-core kernel whose bounded wait gave up returns early and records the wait's id in a device word.  Every
+// synchronisation point of the API reads that word ON THE LIBRARY'S STREAM (ordered behind the kernels) and latches
+// TL_ERR_TIMEOUT, so results of a broken launch cannot be taken for good ones.
+static void check_tc_status()
+{
+    int *dev = tc_status_word_if_any();
+    if (!dev || g_capturing_now()) return;
+    int h = 0;
+    if (cudaMemcpyAsync(&h, dev, sizeof(int), cudaMemcpyDeviceToHost, g.cur_stream) != cudaSuccess) { cudaGetLastError(); return; }
+    if (cudaStreamSynchronize(g.cur_stream) != cudaSuccess) { cudaGetLastError(); return; }
+    if (h != 0) set_error(TL_ERR_TIMEOUT, "a tensor-core kernel gave up on bounded wait %d and returned early: its output is invalid", h);
+}
+void trainlib_synchronize(void) { if (ready() && TL_CUDA(cudaStreamSynchronize(g.cur_stream))) check_tc_status(); }
 
 void trainlib_set_memory_mode(int mode) { if (mode >= TL_MEM_AUTO && mode <= TL_MEM_HOST) g.mem_mode = mode; }
 int trainlib_memory_mode(void) { return g.mem_mode; }
@@ -334,6 +384,7 @@ double trainlib_timer_stop_ms(void)
     if (!TL_CUDA(cudaEventRecord(g.ev1, g.cur_stream))) return -1.0;
     if (!TL_CUDA(cudaEventSynchronize(g.ev1))) return -1.0;
     if (!TL_CUDA(cudaEventElapsedTime(&ms, g.ev0, g.ev1))) return -1.0;
+    check_tc_status();
     return (double)ms;
 }
 long long trainlib_kernel_launches(void) { return g.launches; }
@@ -342,6 +393,7 @@ long long trainlib_kernel_launches(void) { return g.launches; }
 struct TlGraph { cudaGraphExec_t exec; cudaGraph_t graph; long long kernels; };
 static long long g_capture_launches0 = 0;
 static bool g_capturing = false;
+static bool g_capturing_now() { return g_capturing; }
 int trainlib_graph_begin(void)
 {
     if (!ready()) return g.err;
