@@ -109,27 +109,36 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
     // window column b, source channel g*8 + k4*4 + j: the WK columns of 16 output channels sit side by side,
     // so the epilogue fetches them with one wide load.
     {
-        const int per_step = p.NB * 8;
-        const int total = p.cigs * p.Hk * per_step;
-        for (int e = threadIdx.x; e < total; e += nthreads) {
-            const int j = e & 3, k4 = (e >> 2) & 1, r = (e >> 3) % p.NB, step = (e >> 3) / p.NB;
+        // one item = one row of one step: its 8 source channels are fetched, split and stored as two 16-byte chunks (hi) + two (lo)
+        const int steps = p.cigs * p.Hk, items = steps * p.NB;
+        for (int it = threadIdx.x; it < items; it += nthreads) {
+            const int r = it % p.NB, step = it / p.NB;
             const int a = step % p.Hk, g = step / p.Hk;
             const int chunk = r / (WK * 16), b = (r % (WK * 16)) >> 4, c = chunk * 16 + (r & 15);
-            const int n_out = blockIdx.y * p.NT + c, k_in = g * 8 + k4 * 4 + j;
-            float v = 0.f;
+            const int n_out = blockIdx.y * p.NT + c;
+            const float *src; long long kstride; int k_lim; bool row_ok;
             if (p.cls) {
                 const int kh = p.kh_r + p.kstep * (p.kh_m - a), kw = p.kw_r + p.kstep * (p.kw_m - b);
-                if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.w_taps + kh * p.w_Wk + kw);
+                src = p.w + (long long)n_out * p.w_taps + kh * p.w_Wk + kw; kstride = (long long)p.Cin_w * p.w_taps; k_lim = p.Cout_w; row_ok = n_out < p.Cin_w;
             } else if (!p.flip) {
-                if (n_out < p.Cout_w && k_in < p.Cin_w) v = __ldg(p.w + ((long long)n_out * p.Cin_w + k_in) * p.w_taps + a * WK + b);
+                src = p.w + (long long)n_out * p.Cin_w * p.w_taps + a * WK + b; kstride = p.w_taps; k_lim = p.Cin_w; row_ok = n_out < p.Cout_w;
             } else {
-                if (n_out < p.Cin_w && k_in < p.Cout_w) v = __ldg(p.w + ((long long)k_in * p.Cin_w + n_out) * p.w_taps + (p.w_taps - 1 - (a * WK + b)));
+                src = p.w + (long long)n_out * p.w_taps + (p.w_taps - 1 - (a * WK + b)); kstride = (long long)p.Cin_w * p.w_taps; k_lim = p.Cout_w; row_ok = n_out < p.Cin_w;
             }
-            uint32_t hi, lo;
-            split_tf32(v, hi, lo);
-            float *dst = Bs + (size_t)step * (b_step_bytes / 4) + (size_t)k4 * (2 * p.NB * 4) + j;
-            dst[r * 4] = __uint_as_float(hi);
-            dst[(p.NB + r) * 4] = __uint_as_float(lo);
+            uint32_t hi[8], lo[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int k_in = g * 8 + k;
+                const float v = (row_ok && k_in < k_lim) ? __ldg(src + (long long)k_in * kstride) : 0.f;
+                split_tf32(v, hi[k], lo[k]);
+            }
+            float *dst = Bs + (size_t)step * (b_step_bytes / 4);
+#pragma unroll
+            for (int k4 = 0; k4 < 2; k4++) {
+                float *d = dst + (size_t)k4 * (2 * p.NB * 4);
+                *reinterpret_cast<float4 *>(d + r * 4) = make_float4(__uint_as_float(hi[4 * k4]), __uint_as_float(hi[4 * k4 + 1]), __uint_as_float(hi[4 * k4 + 2]), __uint_as_float(hi[4 * k4 + 3]));
+                *reinterpret_cast<float4 *>(d + (p.NB + r) * 4) = make_float4(__uint_as_float(lo[4 * k4]), __uint_as_float(lo[4 * k4 + 1]), __uint_as_float(lo[4 * k4 + 2]), __uint_as_float(lo[4 * k4 + 3]));
+            }
         }
     }
     fence_proxy_async();

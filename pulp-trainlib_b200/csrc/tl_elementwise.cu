@@ -322,19 +322,27 @@ __global__ void __launch_bounds__(256) column_partial_kernel(const T *__restrict
 }
 // One pass for few rows: a single slice, the 8 warp sums go straight to the output (with the pair mapping of the second pass).
 template <class TI, class TO>
-__global__ void __launch_bounds__(256) column_direct_kernel(const TI *__restrict__ in, TO *__restrict__ out, int n, int dim, int pairs)
+__global__ void __launch_bounds__(1024) column_direct_kernel(const TI *__restrict__ in, TO *__restrict__ out, int n, int dim, int pairs)
 {
-    __shared__ float sm[8][33];
+    // 32 columns x 32 row lanes; a lane walks rows r, r + 32, ... four at a time (independent loads in flight, the four partial
+    // sums are then added in a fixed order), the 32 lane sums of a column are added in lane order: one fixed summation tree.
+    __shared__ float sm[32][33];
     const int c = threadIdx.x & 31, r = threadIdx.x >> 5, j = blockIdx.x * 32 + c;
-    float s = 0.f;
-    if (j < dim)
-        for (int i = r; i < n; i += 8) s += ld(in + (long long)i * dim + j);
-    sm[r][c] = s;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    if (j < dim) {
+        int i = r;
+        for (; i + 96 < n; i += 128) {
+            s0 += ld(in + (long long)i * dim + j); s1 += ld(in + (long long)(i + 32) * dim + j);
+            s2 += ld(in + (long long)(i + 64) * dim + j); s3 += ld(in + (long long)(i + 96) * dim + j);
+        }
+        for (; i < n; i += 32) s0 += ld(in + (long long)i * dim + j);
+    }
+    sm[r][c] = (s0 + s1) + (s2 + s3);
     __syncthreads();
     if (r == 0 && j < dim) {
         float t = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; k++) t += sm[k][c];
+        for (int k = 0; k < 32; k++) t += sm[k][c];
         st(out + (pairs > 0 ? (j & 1) * pairs + (j >> 1) : j), t);
     }
 }
@@ -352,7 +360,7 @@ static bool column_sum_launch(Scope &sc, const TI *in, TO *out, int n, int dim, 
 {
     if (n <= 0 || dim <= 0) return true;
     if (n <= 1024) {        // 128 rows per thread at most: one launch instead of two
-        TL_LAUNCH((column_direct_kernel<TI, TO>), (unsigned)((dim + 31) / 32), 256, 0, in, out, n, dim, pairs);
+        TL_LAUNCH((column_direct_kernel<TI, TO>), (unsigned)((dim + 31) / 32), 1024, 0, in, out, n, dim, pairs);
         return true;
     }
     const int rows_per_slice = n >= 4096 ? 64 : (n >= 256 ? 32 : 8), slices = (n + rows_per_slice - 1) / rows_per_slice;
