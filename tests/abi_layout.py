@@ -35,7 +35,10 @@ def ours(structs):
     return measure(structs, [os.path.join(ROOT, "include")], '#include "pulp_train.h"')
 
 
-def reference(structs, ref="/root/reference"):
+REF_DEFAULT = os.environ.get("TRAINLIB_REF", os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "reference"))
+
+
+def reference(structs, ref=REF_DEFAULT):
     shim = os.path.join(ROOT, "oracle", "shim")
     return measure(structs, [shim, os.path.join(ref, "lib", "include")], '#include "pulp_train.h"',
                    extra_flags=["-include", os.path.join(shim, "pmsis.h")])

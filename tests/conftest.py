@@ -45,7 +45,7 @@ def reflib(pkg):
     """The reference's own C sources compiled for the host (oracle/_ref/libpulp_ref.so)."""
     path = os.path.join(ROOT, "oracle", "_ref", "libpulp_ref.so")
     if not os.path.exists(path):
-        if os.path.isdir("/root/reference/lib/sources"):
+        if os.path.isdir(os.path.join(os.environ.get("TRAINLIB_REF", os.path.join(ROOT, "..", "reference")), "lib", "sources")):
             subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), "ref"], stdout=subprocess.DEVNULL)
         else:
             pytest.skip("oracle/_ref/libpulp_ref.so not built (needs the reference sources)")

@@ -24,7 +24,7 @@ sys.path.insert(0, TESTS)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("TRAINLIB_REF", os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference")))
     a = ap.parse_args()
     from conftest import load_pkg
     from abi_runner import AbiRunner

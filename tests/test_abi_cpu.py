@@ -23,7 +23,10 @@ def test_struct_layout_matches_reference_golden(pkg):
         assert got[name] == want[name], "struct %s differs: %s vs %s" % (name, got[name], want[name])
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/lib/include"), reason="reference checkout not present")
+REF = os.environ.get("TRAINLIB_REF", os.path.join(ROOT, "..", "reference"))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "lib", "include")), reason="reference checkout not present")
 def test_struct_layout_matches_reference_headers(pkg):
     assert abi_layout.reference(pkg.abi.STRUCT_FIELDS) == abi_layout.ours(pkg.abi.STRUCT_FIELDS)
 
@@ -176,7 +179,7 @@ def test_cluster_bringup_links_and_runs(pkg):
     pi_cluster_open reports failure and main returns before the task; with one the task's convolution is checked."""
     have_gpu = pkg.load().trainlib_init(-1) == 0
     mains = [None]
-    ref_main = os.path.join(os.environ.get("TRAINLIB_REF", "/root/reference"), "tests", "test_conv2d_fp32", "main.c")
+    ref_main = os.path.join(REF, "tests", "test_conv2d_fp32", "main.c")
     if os.path.exists(ref_main):
         mains.append(ref_main)
     for m in mains:
