@@ -60,6 +60,7 @@ def reference_step(net_ref, n, first_stream=0, lr=LR, params=None, steps=1, allr
     p = host_params(net_ref) if params is None else params.copy()
     g = np.zeros_like(p)
     ws = np.zeros(net_ref.resnet8_workspace_floats(n), F)
+    ws[::1024] = 0                                                  # touch every page now, not inside the timed steps
     img, lab = synthetic_batch(n, first_stream)
     loss = np.zeros(n, F)
     assert net_ref.resnet8_bind(n, p.ctypes.data, g.ctypes.data, ws.ctypes.data) == 0
@@ -208,11 +209,30 @@ class ResNet8Streams(object):
         e2e_ms /= e2e_steps
         pkg.check(lib)
 
+        # the same step with no pipelining at all: the entry points get HOST pointers for the batch and the losses, so the
+        # library stages the upload before the first kernel and the read-back after the last one of the call, in line
+        def step_strict():
+            net.resnet8_forward_host(h_img.ctypes.data, h_lab.ctypes.data, h_loss.ctypes.data)
+            net.resnet8_backward()
+            if torch is not None:
+                dist.all_reduce(t_grads)
+            net.resnet8_update(LR)
+        step_strict(); sync()
+        lib.trainlib_timer_start()
+        for _ in range(3):
+            step_strict()
+        strict_ms = lib.trainlib_timer_stop_ms()
+        sync()
+        if torch is not None:
+            t = torch.tensor([strict_ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); strict_ms = float(t.item())
+        strict_ms /= 3
+        pkg.check(lib)
+
         # per-kernel durations of one more step, CUDA events around every launch on the library stream
         lib.trainlib_profile(1)
         net.resnet8_forward(d_img.ptr, d_lab.ptr, d_loss.ptr); net.resnet8_backward(); net.resnet8_update(LR)
         lib.trainlib_profile(0)
-        table = pkg.profile_table(lib)
+        table = pkg.profile_table(lib, flops=True)
         pkg.check(lib)
         if rank != 0:
             return None
@@ -229,9 +249,12 @@ class ResNet8Streams(object):
                                     else "the reference's separate calls for norm, residual sum, ReLU and gradient joins (--no-fusion)"},
                 "gpu_launches": int(launches), "clocks": clocks, "mean_loss": float(loss_host.mean()), "loss_check": loss_check,
                 "e2e": {"value": total / (e2e_ms * 1e-3), "unit": "samples/s", "ms_per_step": e2e_ms,
-                        "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n)},
+                        "h2d_bytes_per_step": int(img.nbytes + lab.nbytes), "d2h_bytes_per_step": int(4 * n),
+                        "how": "upload of the next batch overlapped with this step's kernels (two device slots), losses read back every step" if graph[0] else "host-pointer entry points",
+                        "strict": {"value": total / (strict_ms * 1e-3), "unit": "samples/s", "ms_per_step": strict_ms,
+                                   "how": "host pointers handed to the reference's entry points: staging copies in line with the kernels, no graph, no overlap"}},
                 "roofline": self.roofline(table, n, pk),
-                "kernel_table": [{"kernel": k, "launches": c, "ms": round(ms, 4)} for k, c, ms in table[:40]]}
+                "kernel_table": [{"kernel": k, "launches": c, "ms": round(ms, 4), "gflop": round(fl * 1e-9, 2)} for k, c, ms, fl in table[:40]]}
         if world == 1 and not args.no_cpu_baseline and os.path.exists(NET_REF_MT):
             line["cpu_baseline"] = self.cpu_baseline()
         return line
@@ -260,75 +283,98 @@ class ResNet8Streams(object):
                 checked += 64; worst = max(worst, err)
         return {"checked_streams": checked, "max_rel_err": worst, "bar": 1e-5, "against": "reference C code, per-stream CrossEntropy of the first and last 64 streams, initial weights"}
 
+    # kernel families of the step: template variants (plane sizes, tile widths) and the kernels that share one job count as one
+    FAMILIES = (
+        ("conv_fw_ig_tensor", ("conv_mn_kernel", "conv_tc_kernel"), "tensor",
+         "forward of the 9 convolutions and input gradient of the 3x3 ones as tcgen05 3xTF32 implicit GEMMs (useful FLOP: zeros of a dilated dY are not counted)"),
+        ("conv_wg_tensor", ("conv_wgt_kernel",), "tensor", "weight gradient of the stride-1 3x3 convolutions with 32+ channels as a tcgen05 3xTF32 pixel-contraction GEMM"),
+        ("conv_wg_ffma", ("conv_wg3x3_partial_kernel", "conv_wg_partial_kernel", "conv_wg_direct_kernel"), "ffma", "weight gradient of the other convolutions, fp32 FFMA"),
+        ("conv_1x1_ig_ffma", ("conv1x1_strided_ig_kernel",), "ffma", "input gradient of the two 1x1 stride-2 shortcut convolutions, fp32 FFMA"),
+        ("conv_fw_ig_ffma", ("conv_fw_kernel", "conv_ig_kernel"), "ffma", "convolutions on the FFMA path"),
+    )
+    # DRAM traffic of one launch from ncu captures at 512 streams (bytes read + written inside the launch), keyed by
+    # family; scaled by the stream count, which is exact here: every stream brings its own planes
+    NCU_TRAFFIC_512 = {}
+
     def roofline(self, table, n, pk):
-        """Dominant kernel family of the profiled step against the bound that limits it.  The template variants
-        of one kernel (plane sizes, tile widths) count as one family."""
+        """The kernel family that takes most of the profiled step, against the bound that limits it.  FLOPs are the useful
+        ones the library credits to each launch (2 per multiply-add of the operator's definition), times are CUDA events
+        around every launch of one step.  `frac` is against the sustained peak (the kernels run inside a long step under
+        the power cap); `frac_of_burst` is the same figure against the burst peak.  `families` lists the others."""
         if not table:
             return None
-        fam = {}
-        for name, count, ms in table:
+        base = {}
+        for name, count, ms, fl in table:
             key = name.strip("()").split("<")[0]
-            c, t = fam.get(key, (0, 0.0))
-            fam[key] = (c + count, t + ms)
+            c, t, f = base.get(key, (0, 0.0, 0.0))
+            base[key] = (c + count, t + ms, f + fl)
         total_ms = sum(r[2] for r in table)
-        name, (count, ms) = max(fam.items(), key=lambda kv: kv[1][1])
-        # (Cin, H, Cout, k, stride) of the nine convolutions
-        spec = [(3, 32, 16, 3, 1), (16, 32, 16, 3, 1), (16, 32, 16, 3, 1), (16, 32, 32, 3, 2), (32, 16, 32, 3, 1), (16, 32, 32, 1, 2), (32, 16, 64, 3, 2), (64, 8, 64, 3, 1), (32, 16, 64, 1, 2)]
-        conv_flops = sum(2.0 * co * ci * k * k * (h // s) ** 2 for ci, h, co, k, s in spec) * n
-        ig_flops = conv_flops - 2.0 * 16 * 3 * 9 * 32 * 32 * n          # the stem has no input gradient
-        act_bytes = sum(4.0 * (ci * h * h + co * (h // s) ** 2) for ci, h, co, k, s in spec) * n
-        r = {"kernel": name, "launches_per_step": count, "ms_per_step": ms, "share_of_kernel_time": ms / total_ms if total_ms else None,
-             "traffic": None, "peak_source": pk["source"]}
-        if name in ("conv_tc_kernel", "conv_fw_kernel", "conv_ig_kernel", "conv_wg3x3_partial_kernel", "conv_wg_partial_kernel"):
-            if name == "conv_tc_kernel":
-                fl, what = conv_flops + ig_flops, "forward of 9 convolutions + input gradient of 8 (useful FLOP: the zeros of a dilated dY are not counted)"
-                # DRAM bytes of the 16 -> 16 forward launch in the ncu capture at 512 streams (33.61 MB read + 0.60 MB
-                # written inside the launch; the 33.5 MB output is still dirty in L2 when it ends), scaled by the stream
-                # count: traffic grows in proportion because every stream brings its own planes
-                r["traffic"] = (33.61e6 + 0.60e6) * n / 512.0
-                r["traffic_note"] = "per launch of the 16->16 32x32 forward convolution, ncu at 512 streams scaled by streams; algorithmic bytes of that launch: %.0f MB in + %.0f MB out" % (n * 65536e-6, n * 65536e-6)
-            elif "wg" in name:
-                fl, what = conv_flops, "weight gradient of 9 convolutions"
+        fams, used = [], set()
+        for fam, members, bound, what in self.FAMILIES:
+            c = sum(base[m][0] for m in members if m in base); t = sum(base[m][1] for m in members if m in base); f = sum(base[m][2] for m in members if m in base)
+            used.update(members)
+            if c:
+                fams.append({"family": fam, "kernels": [m for m in members if m in base], "bound": bound, "launches_per_step": c, "ms_per_step": t, "flops": f, "work": what})
+        for key, (c, t, f) in base.items():
+            if key not in used:
+                fams.append({"family": key, "kernels": [key], "bound": "hbm", "launches_per_step": c, "ms_per_step": t, "flops": 0.0, "work": "bandwidth-bound"})
+        # fp32 on the tensor cores is 3xTF32: one third of the TF32 rate, TF32 = half the bf16 rate
+        tensor_sus, tensor_burst = pk["bf16_tflops_sustained"] / 6.0, pk["bf16_tflops"] / 6.0
+        ffma_peak = 72.8
+        for f in fams:
+            f["share_of_kernel_time"] = f["ms_per_step"] / total_ms if total_ms else None
+            if f["bound"] == "hbm":
+                continue
+            f["achieved"] = f["flops"] / (f["ms_per_step"] * 1e-3) / 1e12 if f["ms_per_step"] > 0 else None
+            f["unit"] = "TFLOP/s"
+            if f["bound"] == "tensor":
+                f.update({"peak": tensor_sus, "peak_burst": tensor_burst, "frac": f["achieved"] / tensor_sus, "frac_of_burst": f["achieved"] / tensor_burst,
+                          "peak_note": "3xTF32-effective fp32 peak = measured bf16 / 6: sustained figure (kernels timed inside a long step), burst beside it"})
             else:
-                fl, what = (ig_flops if "ig" in name else conv_flops), "convolutions on the FFMA path"
-            ach = fl / (ms * 1e-3) / 1e12
-            if name == "conv_tc_kernel":
-                # fp32 on the tensor cores is 3xTF32: one third of the TF32 rate, TF32 = half the bf16 rate
-                peak, note = pk["bf16_tflops_sustained"] / 6.0, "3xTF32-effective fp32 peak = measured sustained bf16 / 6"
-            else:
-                peak, note = 72.8, "FFMA peak measured on this part: 125 MAC/clk/SM x 148 SMs x 1965 MHz"
-            r.update({"bound": "tensor" if name == "conv_tc_kernel" else "ffma", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                      "algorithmic_flops": fl, "algorithmic_bytes": 2 * act_bytes if name == "conv_tc_kernel" else act_bytes, "work": what, "peak_note": note})
-        else:
-            r.update({"bound": "hbm", "achieved": None, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": None})
-        return r
+                f.update({"peak": ffma_peak, "frac": f["achieved"] / ffma_peak, "peak_note": "FFMA peak of this part: 125 MAC/clk/SM x 148 SMs x 1965 MHz"})
+        fams.sort(key=lambda f: -f["ms_per_step"])
+        compute = [f for f in fams if f["bound"] != "hbm"]
+        top = dict(compute[0] if compute else fams[0])
+        top["kernel"] = "+".join(top.pop("kernels"))
+        top["algorithmic_flops"] = top.pop("flops")
+        tr = self.NCU_TRAFFIC_512.get(top["family"])
+        top["traffic"] = tr["bytes"] * n / 512.0 if tr else None
+        if tr:
+            top["traffic_note"] = tr["note"]
+        top["peak_source"] = pk["source"]
+        top["families"] = [{k: (round(v, 4) if isinstance(v, float) else v) for k, v in f.items() if k not in ("work", "peak_note", "unit")} for f in fams[:10] if f["family"] != top["family"]]
+        return top
 
     # ------------------------------------------------------------------ reference arm (host cores)
     @staticmethod
     def _ref_worker(job):
         first, n, steps = job
         net = bind_net(NET_REF_MT)
-        reference_step(net, n, first_stream=first, steps=1)            # warm-up (page faults, thread team start)
+        reference_step(net, min(n, 32), first_stream=first, steps=1)   # warm-up (code pages, thread team start)
         t0 = time.perf_counter()
         reference_step(net, n, first_stream=first, steps=steps)
         return time.perf_counter() - t0
 
-    def _reference_throughput(self, per_proc=128, steps=1):
+    def _reference_throughput(self, per_proc=128, steps=1, total=None):
         """The reference library parallelises one call over a team of 8 threads (NUM_CORES is a compile-time constant of its
         sources).  Streams are independent, so all host cores are used by running cpu_count // 8 processes side by side, each
         with its own team on its own slice of the sample; throughput = streams finished / wall time of the slowest."""
         import multiprocessing as mp
         procs = max(1, (os.cpu_count() or 8) // 8)
-        jobs = [(i * per_proc, per_proc, steps) for i in range(procs)]
+        if total is not None:                       # the whole job, split into one contiguous block of streams per process
+            jobs = [shard_streams(total, i, procs) + (steps,) for i in range(procs)]
+        else:
+            jobs = [(i * per_proc, per_proc, steps) for i in range(procs)]
         if procs == 1:
             times = [self._ref_worker(jobs[0])]
         else:
             with mp.get_context("fork").Pool(procs) as pool:
                 times = pool.map(ResNet8Streams._ref_worker, jobs)
         wall = max(times)
-        return {"samples_per_s": procs * per_proc * steps / wall, "procs": procs, "cores": 8 * procs, "sample": procs * per_proc, "steps": steps, "wall_s": wall}
+        done = sum(j[1] for j in jobs)
+        return {"samples_per_s": done * steps / wall, "procs": procs, "cores": 8 * procs, "sample": done, "steps": steps, "wall_s": wall}
 
-    def cpu_baseline(self, sample=128, steps=1):
+    def cpu_baseline(self, sample=512, steps=1):
         r = self._reference_throughput(sample, steps)
         return {"value": r["samples_per_s"], "unit": "samples/s", "cores": r["cores"], "kind": "reference",
                 "sample": "%d of the %d streams (%d processes x %d streams, pthread team of 8 each), %d step(s), reference C sources" % (r["sample"], STREAMS, r["procs"], sample, steps),
@@ -337,11 +383,12 @@ class ResNet8Streams(object):
     def run_reference(self, ref_lib, args):
         if not os.path.exists(NET_REF_MT):
             return {"unavailable": "oracle/_ref/libresnet8_ref.so was not built (needs the reference checkout at build time)", "value": None, "unit": "samples/s"}
-        steps = max(1, min(args.steps, 3))
-        r = self._reference_throughput(128, steps)
+        # every timed step is the whole job: all 4096 streams once through the reference's code (about 20 s on 16 cores)
+        steps = max(1, min(args.steps, 2))
+        r = self._reference_throughput(steps=steps, total=STREAMS)
         v = r["samples_per_s"]
         return {"metric": "train_step_samples_per_s", "value": v, "unit": "samples/s", "ms_per_step": 1e3 * STREAMS / v, "dtype": "f32",
-                "config": {"workload": self.name, "streams_total": STREAMS, "sample_streams": r["sample"]},
+                "config": {"workload": self.name, "streams_total": STREAMS, "streams_per_step": r["sample"], "same_config": r["sample"] == STREAMS, "timed_steps": steps},
                 "cpu_baseline": {"value": v, "unit": "samples/s", "cores": r["cores"], "kind": "reference",
-                                 "sample": "%d of the %d streams per step: %d processes x 128 streams, each with the reference's pthread team of 8 "
-                                           "(streams are independent, so samples/s does not depend on the count)" % (r["sample"], STREAMS, r["procs"])}}
+                                 "sample": "all %d streams per step (%d timed step(s), %.1f s each): %d processes side by side, each with the reference's pthread "
+                                           "team of 8 on its own block of streams" % (r["sample"], steps, r["wall_s"] / steps, r["procs"])}}

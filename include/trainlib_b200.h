@@ -80,6 +80,9 @@ long long trainlib_kernel_launches(void);     /* kernels launched by this librar
 void        trainlib_profile(int on);          /* 1 = clear and start, 0 = stop */
 int         trainlib_profile_entries(void);
 const char *trainlib_profile_entry(int i, long long *launches, double *total_ms);
+/* useful floating-point operations the convolution kernels of entry i were launched for (2 per multiply-add of the
+ * operator's definition, full windows at the borders, no credit for zeros a kernel inserts); 0 for other kernels */
+double      trainlib_profile_entry_flops(int i);
 
 /* ---- layer norm and GELU beyond the reference, which has an fp32 layer-norm forward and GELU forwards only
  * [ref: lib/include/pulp_layernorm_fp32.h:26-34, lib/sources/pulp_act_fp32.c:714].  The first seven fields are

@@ -68,6 +68,8 @@ def load(path=LIB_PATH):
     lib.trainlib_profile_entries.restype = ctypes.c_int
     lib.trainlib_profile_entry.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_double)]
     lib.trainlib_profile_entry.restype = ctypes.c_char_p
+    lib.trainlib_profile_entry_flops.argtypes = [ctypes.c_int]
+    lib.trainlib_profile_entry_flops.restype = ctypes.c_double
     lib.trainlib_graph_begin.restype = ctypes.c_int
     lib.trainlib_graph_end.restype = ctypes.c_void_p
     lib.trainlib_graph_launch.argtypes = [ctypes.c_void_p]; lib.trainlib_graph_launch.restype = ctypes.c_int
@@ -138,13 +140,15 @@ def call(lib, name, args):
     getattr(lib, name)(ctypes.byref(args))
 
 
-def profile_table(lib):
-    """[(kernel name, launches, total ms)] gathered since trainlib_profile(1), longest first."""
+def profile_table(lib, flops=False):
+    """[(kernel name, launches, total ms)] gathered since trainlib_profile(1), longest first; with flops=True a fourth
+    field holds the useful floating-point operations the convolution kernels of that entry were launched for."""
     rows = []
     for i in range(lib.trainlib_profile_entries()):
         n = ctypes.c_longlong(0); ms = ctypes.c_double(0.0)
         name = lib.trainlib_profile_entry(i, ctypes.byref(n), ctypes.byref(ms))
-        rows.append((name.decode(), int(n.value), float(ms.value)))
+        row = (name.decode(), int(n.value), float(ms.value))
+        rows.append(row + (float(lib.trainlib_profile_entry_flops(i)),) if flops else row)
     return sorted(rows, key=lambda r: -r[2])
 
 

@@ -32,6 +32,9 @@ void count_launch();
 bool profiling();
 void profile_begin(const char *kernel_name);
 void profile_end();
+// Useful floating-point operations of the launch begun last (2 per multiply-add of the operator's definition:
+// zeros a kernel multiplies for its own convenience are not work).  No-op unless profiling is on.
+void profile_add_flops(double flops);
 
 // Launch a kernel on the library stream, count it, latch launch errors.
 #define TL_LAUNCH(kernel, grid, block, smem, ...)                                   \

@@ -8,6 +8,9 @@
 
 namespace tl {
 
+// multiply-adds of the operator's definition x 2 (borders counted as full windows)
+static double conv_flops(const ConvGeom &g) { return 2.0 * g.n * g.Cout * (g.depthwise ? 1 : g.Cin) * g.Hk * g.Wk * g.Hout * g.Wout; }
+
 static constexpr int CONV_THREADS = 256;
 static constexpr int CO_T = 16;            // output channels per thread (register tile)
 
@@ -313,6 +316,7 @@ static bool try_conv1x1_ig(const ConvGeom &g, const float *dy, const float *w, f
     if (PX == 256) { if (acc) TL_1X1(256, true); else TL_1X1(256, false); }
     else { if (acc) TL_1X1(64, true); else TL_1X1(64, false); }
 #undef TL_1X1
+    profile_add_flops(conv_flops(g));
     return true;
 }
 template <class T> static bool try_conv1x1_ig(const ConvGeom &, const T *, const T *, T *, bool) { return false; }
@@ -368,8 +372,10 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
     if (!dil) return false;
     const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count() * 32);
     TL_LAUNCH(conv_dilate_dy_kernel, blocks, 256, 0, dy, dil, (unsigned)total, g.Hout, g.Wout, g.Hin, g.Win, g.sh, g.sw);
-    return conv_tc_run(sc, dil, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hin, g.Win, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
-                       g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
+    const bool ok = conv_tc_run(sc, dil, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hin, g.Win, g.Cin, g.Hin, g.Win, g.Hk, g.Wk, 1, 1,
+                                g.Hk - 1 - g.padU, g.Wk - 1 - g.padL, g.Cout, g.Cin, true);
+    if (ok) profile_add_flops(conv_flops(g) - 2.0 * g.n * g.Cin * g.Cout * g.Hk * g.Wk * g.Hin * g.Win);   // the zeros between the samples are not work
+    return ok;
 }
 
 template <class T> void conv_fw(Scope &sc, const ConvGeom &g, const T *x, const T *w, const T *bias, T *y)
@@ -387,6 +393,7 @@ template <class T> void conv_fw(Scope &sc, const ConvGeom &g, const T *x, const 
     int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH), tiles_s = ceil_div(g.n, S_T);
     dim3 grid(tiles_w * tiles_h * tiles_s, ceil_div(g.Cout, CO_T));
     TL_LAUNCH((conv_fw_kernel<T>), grid, CONV_THREADS, smem, g, x, w, bias, y, TH, TW, S_T, CC, tiles_w, tiles_h);
+    profile_add_flops(conv_flops(g));
 }
 
 // ------------------------------------------------------------------ input gradient
@@ -521,6 +528,7 @@ template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const
     int tiles_w = ceil_div(g.Win, TW), tiles_h = ceil_div(g.Hin, TH), tiles_s = ceil_div(g.n, S_T);
     dim3 grid(tiles_w * tiles_h * tiles_s, ceil_div(g.Cin, CO_T));
     TL_LAUNCH((conv_ig_kernel<T>), grid, CONV_THREADS, smem, g, dy, w, dx, TH, TW, S_T, CC, tiles_w, tiles_h, PH, PW);
+    profile_add_flops(conv_flops(g));
 }
 
 // ------------------------------------------------------------------ weight gradient
@@ -941,6 +949,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
             else        { if (TW == 16) TL_WG3_LAUNCH(2, 16, 8, 1); else TL_WG3_LAUNCH(2, 8, 8, 2); }
 #undef TL_WG3_LAUNCH
 #undef TL_WG3_LAUNCH2
+            profile_add_flops(conv_flops(g));
             TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
             return;
         }
@@ -953,6 +962,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     const bool tiled = (g.Hk == g.Wk) && (g.Hk == 1 || g.Hk == 3 || g.Hk == 5) && smem <= 200 * 1024;
     if (!tiled) {
         TL_LAUNCH((conv_wg_direct_kernel<T>), g.Cout * g.Cin * KK, 256, 0, g, x, dy, dw);
+        profile_add_flops(conv_flops(g));
         return;
     }
     int tiles_w = ceil_div(g.Wout, TW), tiles_h = ceil_div(g.Hout, TH);
@@ -973,6 +983,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     else if (g.Hk == 3) TL_WG_LAUNCH(3, 3);
     else TL_WG_LAUNCH(5, 5);
 #undef TL_WG_LAUNCH
+    profile_add_flops(conv_flops(g));
     TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
 }
 

@@ -416,6 +416,7 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
     } while (0)
     if (Wk == 1) TL_MN_LAUNCH(1, 0); else if (Wk == 2 && padL == 0) TL_MN_LAUNCH(2, 0); else if (Wk == 2) TL_MN_LAUNCH(2, 1); else TL_MN_LAUNCH(3, 1);
 #undef TL_MN_LAUNCH
+    profile_add_flops(2.0 * n * C_dst * C_src * Hk * Wk * H_dst * W_dst);
     return true;
 }
 

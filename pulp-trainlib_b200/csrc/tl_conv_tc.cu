@@ -499,6 +499,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     default: TL_TC_LAUNCH(0); break;
     }
 #undef TL_TC_LAUNCH
+    profile_add_flops(2.0 * n * C_dst * C_src * Hk * Wk * H_dst * W_dst);
     return true;
 }
 

@@ -316,6 +316,7 @@ bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups,
     static bool attr_set = false;
     if (!attr_set) { cudaFuncSetAttribute(conv_wgt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; }
     TL_LAUNCH(conv_wgt_kernel, ctas, WGT_THREADS, smem, tx, tdy, p);
+    profile_add_flops(2.0 * n * Cout * Cin * 9.0 * H * W);
     *groups_out = ctas;
     return true;
 }

@@ -109,13 +109,14 @@ int gemm_path() { return g.gemm_path; }
 void count_launch() { g.launches++; }
 
 // ---------------------------------------------------------------- per-kernel profile
-struct ProfEntry { const char *name; long long launches; double ms; };
+struct ProfEntry { const char *name; long long launches; double ms; double flops; };
 struct ProfPending { int entry; cudaEvent_t a, b; };
 static bool g_prof_on = false;
 static std::vector<ProfEntry> g_prof;
 static std::vector<ProfPending> g_prof_pending;
 static std::vector<cudaEvent_t> g_prof_free;
 static int g_prof_cur = -1;
+static int g_prof_last = -1;          // entry of the launch begun last: profile_add_flops credits it
 static const size_t PROF_MAX_PENDING = 8192;
 
 bool profiling() { return g_prof_on; }
@@ -143,8 +144,9 @@ void profile_begin(const char *name)
     if (g_prof_pending.size() >= PROF_MAX_PENDING) prof_drain();
     int idx = -1;
     for (size_t i = 0; i < g_prof.size(); i++) if (g_prof[i].name == name || strcmp(g_prof[i].name, name) == 0) { idx = (int)i; break; }
-    if (idx < 0) { g_prof.push_back({name, 0, 0.0}); idx = (int)g_prof.size() - 1; }
+    if (idx < 0) { g_prof.push_back({name, 0, 0.0, 0.0}); idx = (int)g_prof.size() - 1; }
     g_prof[idx].launches++;
+    g_prof_last = idx;
     ProfPending p; p.entry = idx; p.a = prof_event(); p.b = prof_event();
     cudaEventRecord(p.a, g.cur_stream);
     g_prof_pending.push_back(p);
@@ -155,6 +157,11 @@ void profile_end()
 {
     if (g_prof_cur >= 0) cudaEventRecord(g_prof_pending[g_prof_cur].b, g.cur_stream);
     g_prof_cur = -1;
+}
+
+void profile_add_flops(double flops)
+{
+    if (g_prof_on && g_prof_last >= 0 && g_prof_last < (int)g_prof.size()) g_prof[g_prof_last].flops += flops;
 }
 
 bool is_device_pointer(const void *p)
@@ -434,7 +441,7 @@ void trainlib_graph_destroy(void *handle)
 void trainlib_profile(int on)
 {
     if (!ready()) return;
-    if (on) { g_prof.clear(); g_prof_on = true; }
+    if (on) { g_prof.clear(); g_prof_last = -1; g_prof_on = true; }
     else { prof_drain(); g_prof_on = false; }
 }
 int trainlib_profile_entries(void) { prof_drain(); return (int)g_prof.size(); }
@@ -445,6 +452,7 @@ const char *trainlib_profile_entry(int i, long long *launches, double *total_ms)
     if (total_ms) *total_ms = g_prof[i].ms;
     return g_prof[i].name;
 }
+double trainlib_profile_entry_flops(int i) { return (i < 0 || i >= (int)g_prof.size()) ? 0.0 : g_prof[i].flops; }
 int trainlib_tc_status(void) { return ready() ? conv_tc_status() : -1; }
 void trainlib_set_gemm_path(int p) { g.gemm_path = (p >= 0 && p <= 4) ? p : 0; }
 int trainlib_gemm_path(void) { return g.gemm_path; }
