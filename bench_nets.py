@@ -294,7 +294,13 @@ class ResNet8Streams(object):
     )
     # DRAM traffic of one launch from ncu captures at 512 streams (bytes read + written inside the launch), keyed by
     # family; scaled by the stream count, which is exact here: every stream brings its own planes
-    NCU_TRAFFIC_512 = {}
+    NCU_TRAFFIC_512 = {
+        # conv_mn_kernel<3, 1>, 16 -> 16 forward at 1024 streams: 67.17 MB read (= the layer's input) + 19.21 MB written
+        # inside the launch (the rest of the 67.1 MB output was still dirty in L2 when the kernel ended); halved to 512
+        "conv_fw_ig_tensor": {"bytes": 0.5 * (67.17e6 + 19.21e6),
+                              "note": "per launch of the 16->16 32x32 forward convolution (conv_mn_kernel<3,1>), ncu at 1024 streams scaled by streams; "
+                                      "reads = the layer's input bytes (65 536 B per stream), no re-reads; algorithmic bytes of that launch are 65 536 B in + 65 536 B out per stream"},
+    }
 
     def roofline(self, table, n, pk):
         """The kernel family that takes most of the profiled step, against the bound that limits it.  FLOPs are the useful
