@@ -17,6 +17,8 @@
 #ifndef TRAINLIB_B200_ABI_H
 #define TRAINLIB_B200_ABI_H
 
+#include "pmsis.h"   /* pi_cl_dma_cmd_t of the tiled-attention arguments, as pulp_mhsa_fp32.h includes it */
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -176,6 +178,15 @@ struct Mhsa_args {
     struct blob *head_buffer; struct blob *softmax_buffer;
     float *global_max; float *partial_exp_sum; float *maxes; float *sums;
 };
+/* [ref: pulp_mhsa_fp32.h:91-122] tile sizes of the L1-tiled attention; the tiles are a memory plan for the cluster's
+ * scratchpad and change no result, so this library reads none of them */
+struct Tiled_Matmul_Mhsa_args {
+    struct matMul_args *mm_args; struct mm_manager_args *man_args; float *BUFF;
+    int tile_h; int tile_w; int tile_dim; int tile_h_p; int tile_w_p; int tile_dim_p; int tile_h_sm; int tile_w_sm; int tile_dim_sm;
+    int tile_h_tr; int tile_w_tr; int tile_dim_tr; int tile_h_attv; int tile_w_attv; int tile_dim_attv;
+    int tile_h_out_tr; int tile_w_out_tr; int tile_dim_out_tr;
+    pi_cl_dma_cmd_t *cmd_store; pi_cl_dma_cmd_t *cmd_load;
+};
 /* [ref: pulp_act_fp32.h:27-32] */
 struct act_args { struct blob *input; struct blob *output; int H; int W; };
 /* [ref: pulp_act_fp32.h:40-44] */
@@ -307,6 +318,14 @@ struct Mhsa_args_fp16 {
     struct blob_fp16 *head_buffer; struct blob_fp16 *softmax_buffer;
     fp16 *global_max; fp16 *partial_exp_sum; fp16 *maxes; fp16 *sums;
 };
+/* [ref: pulp_mhsa_fp16.h:90-114] */
+struct Tiled_Matmul_Mhsa_args_fp16 {
+    struct matMul_args_fp16 *mm_args; struct mm_manager_args_fp16 *man_args; fp16 *BUFF;
+    int tile_h; int tile_w; int tile_dim; int tile_h_p; int tile_w_p; int tile_dim_p; int tile_h_sm; int tile_w_sm; int tile_dim_sm;
+    int tile_h_tr; int tile_w_tr; int tile_dim_tr; int tile_h_attv; int tile_w_attv; int tile_dim_attv;
+    int tile_h_out_tr; int tile_w_out_tr; int tile_dim_out_tr;
+    pi_cl_dma_cmd_t *cmd_store; pi_cl_dma_cmd_t *cmd_load;
+};
 /* [ref: pulp_act_fp16.h:28-33] */
 struct act_args_fp16 { struct blob_fp16 *input; struct blob_fp16 *output; int H; int W; };
 /* [ref: pulp_act_fp16.h:41-45] */
@@ -415,6 +434,23 @@ void pulp_linear_fp32_bw_param_grads_cl_kernel(void *mm_manager_args);
  * DEVIATION: backward uses the corrected transpose of V (reference :930 is wrong for L != H). */
 void pulp_mhsa_fp32_fw_cl(void *Mhsa_args);
 void pulp_mhsa_fp32_bw_cl(void *Mhsa_args);
+/* Attention of the MobileBERT encoder block [ref: pulp_mhsa_fp32.h:147-156; pulp_mhsa_fp32.c:1749,2037,2111,2162,2413].
+ * Token-major activations: input L x E (H = L, W = E), input_bn L x Kb, output L x No; coeff_in_q / coeff_in_k are
+ * F x Kb, coeff_in_v is F x E, coeff_out is No x F, every projection adds its bias (as the reference does when built
+ * with -DOPTIMIZE, which is how its tests build it).  The inference entry points take F = Kb = No = input_bn->W as the
+ * reference does; the tiled entry point reads F, Kb and No from the H / W fields of the coefficient blobs.  q, k, v,
+ * attention_map (F x L) and softmax_buffer (heads x L x L) are written as in the training path.
+ * DEVIATION (backward): the reference's backward does not compile and reads output.diff as E x L although its forward
+ * writes the output as L x No; here it is the gradient of the forward in the forward's layouts: coefficient gradients
+ * in the coefficients' layouts, input.diff += the gradient through v, input_bn.diff += the gradient through q and k
+ * (into input.diff instead when input_bn has no diff buffer and Kb = E, which is where the reference adds all three).
+ * tiled_matmul_mhsa is the product (+ bias) of its matMul_args, tiled_transpose_mhsa the N x M transpose of its
+ * transp_args; `projection` only selects tile sizes and is ignored. */
+void pulp_mhsa_mobilebert_inference_fp32_fw_cl(void *Mhsa_args);
+void pulp_mhsa_mobilebert_inference_fp32_bw_cl(void *Mhsa_args);
+void tiled_mhsa_fp32(void *Mhsa_args, void *Tiled_Matmul_Mhsa_args);
+void tiled_matmul_mhsa(void *matMul_args, void *Tiled_Matmul_Mhsa_args, int projection);
+void tiled_transpose_mhsa(void *transp_args, void *Tiled_Matmul_Mhsa_args, int projection);
 
 /* ---- activations and softmax [ref: pulp_act_fp32.h:89-289; pulp_act_fp32.c:25-392,714] */
 void pulp_sigmoid_fp32_fw_cl(void *act_args);   void pulp_sigmoid_fp32_bw_cl(void *act_args);
@@ -544,6 +580,13 @@ void pulp_linear_fp16_bw_input_grads_cl(void *Linear_args_fp16);
 /* [ref: pulp_mhsa_fp16.h:164-165; pulp_mhsa_fp16.c:20,645] */
 void pulp_mhsa_fp16_fw_cl(void *Mhsa_args_fp16);
 void pulp_mhsa_fp16_bw_cl(void *Mhsa_args_fp16);
+/* [ref: pulp_mhsa_fp16.h:184-192; pulp_mhsa_fp16.c:1731] fp16 twins of the MobileBERT attention entry points (the
+ * backward is this library's addition: the reference has no fp16 one) */
+void pulp_mhsa_mobilebert_inference_fp16_fw_cl(void *Mhsa_args_fp16);
+void pulp_mhsa_mobilebert_inference_fp16_bw_cl(void *Mhsa_args_fp16);
+void tiled_mhsa_fp16(void *Mhsa_args_fp16, void *Tiled_Matmul_Mhsa_args_fp16);
+void tiled_matmul_mhsa_fp16(void *matMul_args_fp16, void *Tiled_Matmul_Mhsa_args_fp16, int projection);
+void tiled_transpose_mhsa_fp16(void *transp_args_fp16, void *Tiled_Matmul_Mhsa_args_fp16, int projection);
 /* [ref: pulp_act_fp16.h:90-204; pulp_act_fp16.c:185,226,359] */
 void pulp_relu_fp16_fw_cl(void *act_args_fp16);       void pulp_relu_fp16_bw_cl(void *act_args_fp16);
 void relu_core_fw_fp16(void *act_args_fp16);          void relu_core_bw_fp16(void *act_args_fp16);

@@ -370,6 +370,80 @@ void orc_mhsa_bw(const float *x, const float *wq, const float *wk, const float *
     for (int p = 0; p < 3; p++) mm_strided(ws[p], F, 1, dps[p], L, 1, dx, L, E, F, L, 1.0f, 1);   /* [ref: :1605-1745] */
 }
 
+/* Attention of the MobileBERT encoder block ("inference" entry points and their tiled twins)
+ * [ref: lib/sources/pulp_mhsa_fp32.c:1749-2035 forward, :2162-2412 the same arithmetic through DMA tiles, :2413-2840
+ * backward].  PARITY UNPINNED: these reference functions do not compile against the reference's own headers (they
+ * fill `struct transp_args` fields N / M / matrix / transp_matrix that lib/include/pulp_train_utils_fp32.h no longer
+ * declares, and the tiled ones need the cluster DMA), so they cannot be run here; this is a restatement of the
+ * forward's loops, and the backward is the exact gradient of that forward in the forward's own layouts (the
+ * reference's backward reads output.diff as E x L although the forward writes the output as L x N).
+ * x: L x E; xb (bottleneck input): L x Kb; Wq, Wk: F x Kb; Wv: F x E; Wo: No x F; biases per output row;
+ * q, k, v, att: F x L; softmax: heads x L x L as [head][query][key]; y: L x No. */
+void orc_mhsa_mobilebert_fw(const float *x, const float *xb, const float *wq, const float *wk, const float *wv,
+                            const float *bq, const float *bk, const float *bv, const float *wo, const float *bo,
+                            float *q, float *k, float *v, float *softmax, float *att, float *y,
+                            int L, int E, int Kb, int F, int No, int heads)
+{
+    const int H = F / heads;
+    const float scaling = orc_q_rsqrt((float)H);
+    mm_strided(wq, Kb, 1, xb, 1, Kb, q, L, F, Kb, L, 1.0f, 0);                 /* Wq xb^T  [ref: :1789-1815] */
+    mm_strided(wk, Kb, 1, xb, 1, Kb, k, L, F, Kb, L, 1.0f, 0);                 /* [ref: :1818-1843] */
+    mm_strided(wv, E, 1, x, 1, E, v, L, F, E, L, 1.0f, 0);                     /* Wv x^T  [ref: :1918-1943] */
+    for (int f = 0; f < F; f++)
+        for (int l = 0; l < L; l++) { q[f * L + l] += bq[f]; k[f * L + l] += bk[f]; v[f * L + l] += bv[f]; }
+    float *scores = (float *)malloc(sizeof(float) * L * L);
+    for (int h = 0; h < heads; h++) {
+        const float *qh = q + h * H * L, *kh = k + h * H * L, *vh = v + h * H * L;
+        for (int a = 0; a < L; a++)                                             /* [ref: :1846-1915] */
+            for (int b = 0; b < L; b++) {
+                float temp = 0;
+                for (int d = 0; d < H; d++) temp += kh[d * L + b] * qh[d * L + a];
+                scores[a * L + b] = temp * scaling;
+            }
+        orc_softmax_fw(scores, softmax + (long)h * L * L, L, L);
+        mm_strided(vh, L, 1, softmax + (long)h * L * L, 1, L, att + h * H * L, L, H, L, L, 1.0f, 0);   /* [ref: :1946-1975] */
+    }
+    free(scores);
+    for (int n = 0; n < No; n++)                                                /* Wo att + bo, stored transposed  [ref: :1978-2034] */
+        for (int l = 0; l < L; l++) {
+            float temp = 0;
+            for (int f = 0; f < F; f++) temp += wo[n * F + f] * att[f * L + l];
+            y[l * No + n] = temp + bo[n];
+        }
+}
+
+/* dy: L x No.  dwq, dwk: F x Kb; dwv: F x E; dwo: No x F; dx: L x E and dxb: L x Kb are accumulated into. */
+void orc_mhsa_mobilebert_bw(const float *x, const float *xb, const float *wq, const float *wk, const float *wv, const float *wo,
+                            const float *q, const float *k, const float *v, const float *softmax, const float *att, const float *dy,
+                            float *dq, float *dk, float *dv, float *dsoftmax, float *datt,
+                            float *dwq, float *dwk, float *dwv, float *dwo, float *dx, float *dxb,
+                            int L, int E, int Kb, int F, int No, int heads)
+{
+    const int H = F / heads;
+    const float scaling = orc_q_rsqrt((float)H);
+    mm_strided(dy, 1, No, att, 1, L, dwo, F, No, L, F, 1.0f, 0);               /* dWo[n][f] = sum_l dy[l][n] att[f][l] */
+    mm_strided(wo, 1, F, dy, 1, No, datt, L, F, No, L, 1.0f, 0);               /* datt[f][l] = sum_n wo[n][f] dy[l][n] */
+    float *dS = (float *)malloc(sizeof(float) * L * L);
+    for (int h = 0; h < heads; h++) {
+        const float *P = softmax + (long)h * L * L;
+        float *dP = dsoftmax + (long)h * L * L;
+        const float *qh = q + h * H * L, *kh = k + h * H * L, *vh = v + h * H * L, *dah = datt + h * H * L;
+        mm_strided(dah, L, 1, P, L, 1, dv + h * H * L, L, H, L, L, 1.0f, 0);
+        mm_strided(dah, 1, L, vh, L, 1, dP, L, L, H, L, 1.0f, 0);
+        orc_softmax_bw(P, dP, dS, L, L);
+        for (int i = 0; i < L * L; i++) dS[i] = dS[i] * scaling;
+        mm_strided(qh, L, 1, dS, L, 1, dk + h * H * L, L, H, L, L, 1.0f, 0);
+        mm_strided(kh, L, 1, dS, 1, L, dq + h * H * L, L, H, L, L, 1.0f, 0);
+    }
+    free(dS);
+    mm_strided(dq, L, 1, xb, Kb, 1, dwq, Kb, F, L, Kb, 1.0f, 0);               /* dWq[f][c] = sum_l dq[f][l] xb[l][c] */
+    mm_strided(dk, L, 1, xb, Kb, 1, dwk, Kb, F, L, Kb, 1.0f, 0);
+    mm_strided(dv, L, 1, x, E, 1, dwv, E, F, L, E, 1.0f, 0);
+    mm_strided(dq, 1, L, wq, Kb, 1, dxb, Kb, L, F, Kb, 1.0f, 1);               /* dxb[l][c] += sum_f dq[f][l] wq[f][c] */
+    mm_strided(dk, 1, L, wk, Kb, 1, dxb, Kb, L, F, Kb, 1.0f, 1);
+    mm_strided(dv, 1, L, wv, E, 1, dx, E, L, F, E, 1.0f, 1);
+}
+
 /* ------------------------------------------------------------------ activations */
 
 /* kind: 0 relu, 1 leaky relu, 2 sigmoid, 3 gelu (rational tanh)

@@ -28,6 +28,8 @@ void orc_softmax_fw(const float *in, float *out, int rows, int width);
 void orc_softmax_bw(const float *out, const float *dout, float *din, int rows, int width);
 void orc_mhsa_fw(const float *x, const float *wq, const float *wk, const float *wv, const float *bq, const float *bk, const float *bv, const float *wo, float *q, float *k, float *v, float *softmax, float *att, float *y, int L, int E, int F, int heads);
 void orc_mhsa_bw(const float *x, const float *wq, const float *wk, const float *wv, const float *wo, const float *q, const float *k, const float *v, const float *softmax, const float *att, const float *dy, float *dq, float *dk, float *dv, float *dsoftmax, float *datt, float *dwq, float *dwk, float *dwv, float *dwo, float *dx, int L, int E, int F, int heads);
+void orc_mhsa_mobilebert_fw(const float *x, const float *xb, const float *wq, const float *wk, const float *wv, const float *bq, const float *bk, const float *bv, const float *wo, const float *bo, float *q, float *k, float *v, float *softmax, float *att, float *y, int L, int E, int Kb, int F, int No, int heads);
+void orc_mhsa_mobilebert_bw(const float *x, const float *xb, const float *wq, const float *wk, const float *wv, const float *wo, const float *q, const float *k, const float *v, const float *softmax, const float *att, const float *dy, float *dq, float *dk, float *dv, float *dsoftmax, float *datt, float *dwq, float *dwk, float *dwv, float *dwo, float *dx, float *dxb, int L, int E, int Kb, int F, int No, int heads);
 void orc_act_fw(int kind, const float *x, float *y, long n, float slope);
 void orc_act_bw(int kind, const float *x, const float *y, const float *dy, float *dx, long n, float slope);
 void orc_instnorm_fw(const float *x, float *y, const float *gb, float *mean, float *var, float *stdev, int C, int D);

@@ -507,6 +507,71 @@ template <class F> void mhsa_bw_impl(void *args)
     mhsa_bw<T>(sc, d, x, wq, wk, wv, wo, q, k, v, sm, att, dy, dq, dk, dv, dsm, datt, (T *)nullptr, dwq, dwk, dwv, dwo, dx);
 }
 
+// MobileBERT attention: `tiled` reads the sizes from the coefficient blobs as tiled_mhsa_fp32 does
+// [ref: lib/sources/pulp_mhsa_fp32.c:2201, :2213-2214, :2365-2366], else F = Kb = No = input_bn->W [ref: :1784].
+template <class F> bool mobilebert_dims(const typename F::mhsa_t *a, MobileBertDims &d, bool tiled, const char *who)
+{
+    if (!a || !a->input || !a->input_bn || !a->output || !a->coeff_in_q || !a->coeff_in_k || !a->coeff_in_v || !a->coeff_out ||
+        !a->q || !a->k || !a->v || !a->attention_map || !a->softmax_buffer) { set_error(TL_ERR_BAD_ARGS, "%s: null blob", who); return false; }
+    d.L = a->input->H; d.E = a->input->W; d.heads = a->n_heads;
+    if (tiled) { d.F = a->coeff_in_q->H; d.Kb = a->coeff_in_q->W; d.No = a->coeff_out->H; }
+    else { d.F = d.Kb = d.No = a->input_bn->W; }
+    if (d.L < 1 || d.E < 1 || d.F < 1 || d.Kb < 1 || d.No < 1 || d.heads < 1 || d.F % d.heads || (tiled && a->coeff_out->W != d.F)) {
+        set_error(TL_ERR_BAD_ARGS, "%s: L=%d E=%d Kb=%d F=%d No=%d heads=%d", who, d.L, d.E, d.Kb, d.F, d.No, d.heads);
+        return false;
+    }
+    if (streams() != 1) { set_error(TL_ERR_UNSUPPORTED, "%s: streams mode is not available for attention", who); return false; }
+    return true;
+}
+template <class F> void mobilebert_fw_impl(void *args, bool tiled)
+{
+    auto *a = (typename F::mhsa_t *)args; typedef typename F::T T;
+    MobileBertDims d; if (!mobilebert_dims<F>(a, d, tiled, "mobilebert attention forward")) return;
+    const size_t FL = (size_t)d.F * d.L, SM = (size_t)d.heads * d.L * d.L;
+    Scope sc;
+    const T *x = sc.in(a->input->data, (size_t)d.L * d.E), *xb = sc.in(a->input_bn->data, (size_t)d.L * d.Kb);
+    const T *wq = sc.in(a->coeff_in_q->data, (size_t)d.F * d.Kb), *wk = sc.in(a->coeff_in_k->data, (size_t)d.F * d.Kb);
+    const T *wv = sc.in(a->coeff_in_v->data, (size_t)d.F * d.E), *wo = sc.in(a->coeff_out->data, (size_t)d.No * d.F);
+    const T *bq = a->bias_in_q ? sc.in(a->bias_in_q->data, (size_t)d.F) : nullptr;
+    const T *bk = a->bias_in_k ? sc.in(a->bias_in_k->data, (size_t)d.F) : nullptr;
+    const T *bv = a->bias_in_v ? sc.in(a->bias_in_v->data, (size_t)d.F) : nullptr;
+    const T *bo = a->bias_out ? sc.in(a->bias_out->data, (size_t)d.No) : nullptr;
+    T *q = sc.out(a->q->data, FL), *k = sc.out(a->k->data, FL), *v = sc.out(a->v->data, FL);
+    T *sm = sc.out(a->softmax_buffer->data, SM), *att = sc.out(a->attention_map->data, FL), *y = sc.out(a->output->data, (size_t)d.L * d.No);
+    if (!sc.ok()) return;
+    mhsa_mobilebert_fw<T>(sc, d, x, xb, wq, wk, wv, bq, bk, bv, wo, bo, q, k, v, sm, att, y);
+}
+template <class F> void mobilebert_bw_impl(void *args)
+{
+    auto *a = (typename F::mhsa_t *)args; typedef typename F::T T;
+    MobileBertDims d; if (!mobilebert_dims<F>(a, d, false, "mobilebert attention backward")) return;
+    const size_t FL = (size_t)d.F * d.L, SM = (size_t)d.heads * d.L * d.L;
+    Scope sc;
+    const T *x = sc.in(a->input->data, (size_t)d.L * d.E), *xb = sc.in(a->input_bn->data, (size_t)d.L * d.Kb);
+    const T *wq = sc.in(a->coeff_in_q->data, (size_t)d.F * d.Kb), *wk = sc.in(a->coeff_in_k->data, (size_t)d.F * d.Kb);
+    const T *wv = sc.in(a->coeff_in_v->data, (size_t)d.F * d.E), *wo = sc.in(a->coeff_out->data, (size_t)d.No * d.F);
+    const T *q = sc.in(a->q->data, FL), *k = sc.in(a->k->data, FL), *v = sc.in(a->v->data, FL);
+    const T *sm = sc.in(a->softmax_buffer->data, SM), *att = sc.in(a->attention_map->data, FL), *dy = sc.in(a->output->diff, (size_t)d.L * d.No);
+    T *dq = sc.out(a->q->diff, FL), *dk = sc.out(a->k->diff, FL), *dv = sc.out(a->v->diff, FL);
+    T *dsm = sc.out(a->softmax_buffer->diff, SM), *datt = sc.out(a->attention_map->diff, FL);
+    T *dwq = sc.out(a->coeff_in_q->diff, (size_t)d.F * d.Kb), *dwk = sc.out(a->coeff_in_k->diff, (size_t)d.F * d.Kb);
+    T *dwv = sc.out(a->coeff_in_v->diff, (size_t)d.F * d.E), *dwo = sc.out(a->coeff_out->diff, (size_t)d.No * d.F);
+    T *dx = sc.inout(a->input->diff, (size_t)d.L * d.E);
+    T *dxb = nullptr;
+    if (a->input_bn->diff && a->input_bn->diff != a->input->diff) dxb = sc.inout(a->input_bn->diff, (size_t)d.L * d.Kb);
+    else if (d.Kb == d.E) dxb = dx;
+    if (!sc.ok()) return;
+    mhsa_mobilebert_bw<T>(sc, d, x, xb, wq, wk, wv, wo, q, k, v, sm, att, dy, dq, dk, dv, dsm, datt, dwq, dwk, dwv, dwo, dx, dxb);
+}
+// tiled_matmul_mhsa: the product of its matMul_args with the bias handling of mm_manager [ref: pulp_mhsa_fp32.c:2037-2109]
+template <class F> void tiled_matmul_impl(void *mm_args)
+{
+    typename F::manager_t m;
+    memset(&m, 0, sizeof(m));
+    m.mm_args = (decltype(m.mm_args))mm_args; m.layer_type = LAYER_LINEAR; m.step_type = STEP_FW; m.matmul_type = 0;
+    mm_manager_impl<F>(&m);
+}
+
 // ------------------------------------------------------------------ activations / softmax
 template <class F, class A> void act_fw_impl(void *args, int kind, float slope)
 {
@@ -968,6 +1033,12 @@ TL_EXPORT void pulp_linear_fp16_bw_cl(void *a)
 
 TL_PAIR(pulp_mhsa_fp32_fw_cl, pulp_mhsa_fp16_fw_cl, mhsa_fw_impl<F32>(a), mhsa_fw_impl<F16>(a))
 TL_PAIR(pulp_mhsa_fp32_bw_cl, pulp_mhsa_fp16_bw_cl, mhsa_bw_impl<F32>(a), mhsa_bw_impl<F16>(a))
+TL_PAIR(pulp_mhsa_mobilebert_inference_fp32_fw_cl, pulp_mhsa_mobilebert_inference_fp16_fw_cl, mobilebert_fw_impl<F32>(a, false), mobilebert_fw_impl<F16>(a, false))
+TL_PAIR(pulp_mhsa_mobilebert_inference_fp32_bw_cl, pulp_mhsa_mobilebert_inference_fp16_bw_cl, mobilebert_bw_impl<F32>(a), mobilebert_bw_impl<F16>(a))
+TL_EXPORT void tiled_mhsa_fp32(void *a, void *) { mobilebert_fw_impl<F32>(a, true); }
+TL_EXPORT void tiled_mhsa_fp16(void *a, void *) { mobilebert_fw_impl<F16>(a, true); }
+TL_EXPORT void tiled_matmul_mhsa(void *a, void *, int) { tiled_matmul_impl<F32>(a); }
+TL_EXPORT void tiled_matmul_mhsa_fp16(void *a, void *, int) { tiled_matmul_impl<F16>(a); }
 
 #define ACT32(kind) act_fw_impl<F32, act_args>(a, kind, 0.f)
 #define ACT16(kind) act_fw_impl<F16, act_args_fp16>(a, kind, 0.f)
@@ -1090,6 +1161,9 @@ TL_PAIR(pulp_avgpool_fp32_fw_cl, pulp_avgpool_fp16_fw_cl, avgpool_impl<F32>(a, 0
 TL_PAIR(pulp_avgpool_fp32_bw_cl, pulp_avgpool_fp16_bw_cl, avgpool_impl<F32>(a, 1), avgpool_impl<F16>(a, 1))
 
 TL_PAIR(transpose_matrix, transpose_matrix_fp16, transpose_matrix_impl<F32>(a), transpose_matrix_impl<F16>(a))
+// tiled_transpose_mhsa: out[j][i] = in[i][j] for the N x M matrix of transp_args [ref: pulp_mhsa_fp32.c:2111-2160]
+TL_EXPORT void tiled_transpose_mhsa(void *a, void *, int) { transpose_matrix_impl<F32>(a); }
+TL_EXPORT void tiled_transpose_mhsa_fp16(void *a, void *, int) { transpose_matrix_impl<F16>(a); }
 TL_PAIR(transpose, transpose_fp16, transpose_impl<F32>(a), transpose_impl<F16>(a))
 TL_PAIR(copy, copy_fp16, copy_impl<F32>(a), copy_impl<F16>(a))
 TL_PAIR(set_to_value, set_to_value_fp16, setval_impl<F32>(a), setval_impl<F16>(a))
@@ -1215,6 +1289,8 @@ static const worker_t g_workers[] = {
     pulp_linear_fp32_fw_cl, pulp_linear_fp16_fw_cl, pulp_linear_fp32_bw_cl, pulp_linear_fp16_bw_cl,
     pulp_linear_fp32_bw_param_grads_cl, pulp_linear_fp16_bw_param_grads_cl, pulp_linear_fp32_bw_input_grads_cl, pulp_linear_fp16_bw_input_grads_cl,
     pulp_mhsa_fp32_fw_cl, pulp_mhsa_fp16_fw_cl, pulp_mhsa_fp32_bw_cl, pulp_mhsa_fp16_bw_cl,
+    pulp_mhsa_mobilebert_inference_fp32_fw_cl, pulp_mhsa_mobilebert_inference_fp16_fw_cl,
+    pulp_mhsa_mobilebert_inference_fp32_bw_cl, pulp_mhsa_mobilebert_inference_fp16_bw_cl,
     pulp_relu_fp32_fw_cl, pulp_relu_fp16_fw_cl, pulp_relu_fp32_bw_cl, pulp_relu_fp16_bw_cl, relu_core_fw_fp32, relu_core_fw_fp16, relu_core_bw_fp32, relu_core_bw_fp16,
     pulp_sigmoid_fp32_fw_cl, pulp_sigmoid_fp16_fw_cl, pulp_sigmoid_fp32_bw_cl, pulp_sigmoid_fp16_bw_cl, sigmoid_core_fw_fp32, sigmoid_core_bw_fp32,
     pulp_gelu_tanh_approx_fp32_fw_cl, pulp_gelu_fp16_fw_cl,

@@ -104,6 +104,18 @@ void cast_f2h(const float *src, __half *dst, long long n);
 
 // ---------------------------------------------------------------- attention
 struct MhsaDims { int L, E, F, heads; };
+struct MobileBertDims { int L, E, Kb, F, No, heads; };
+template <class T> void mhsa_mobilebert_fw(Scope &sc, const MobileBertDims &d, const T *x, const T *xb, const T *wq, const T *wk, const T *wv,
+                                           const T *bq, const T *bk, const T *bv, const T *wo, const T *bo,
+                                           T *q, T *k, T *v, T *softmax, T *att, T *y);
+template <class T> void mhsa_mobilebert_bw(Scope &sc, const MobileBertDims &d, const T *x, const T *xb, const T *wq, const T *wk, const T *wv, const T *wo,
+                                           const T *q, const T *k, const T *v, const T *softmax, const T *att, const T *dy,
+                                           T *dq, T *dk, T *dv, T *dsoftmax, T *datt, T *dwq, T *dwk, T *dwv, T *dwo, T *dx, T *dxb);
+// fused attention core (tl_attn.cu): q, k, v, att are F x L with head h in rows h*H..; P, dP are heads x L x L
+bool attn_fused_ok(int L, int H);
+template <class T> void attn_fw(const T *q, const T *k, const T *v, T *P, T *att, int L, int H, int heads, float scaling);
+template <class T> void attn_bw(const T *datt, const T *q, const T *k, const T *v, const T *P, T *dP, float *rowdot,
+                                T *dq, T *dk, T *dv, int L, int H, int heads, float scaling);
 template <class T> void mhsa_fw(Scope &sc, const MhsaDims &d, const T *x, const T *wq, const T *wk, const T *wv,
                                 const T *bq, const T *bk, const T *bv, const T *wo,
                                 T *q, T *k, T *v, T *softmax, T *att, T *y);

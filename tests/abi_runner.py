@@ -199,6 +199,47 @@ class AbiRunner(object):
                      dq=dq.get().copy(), dk=dk.get().copy(), dv=dv.get().copy(), datt=datt.get().copy(), dsoftmax=dsm.get().copy())
         return r
 
+    def mobilebert(self, x, xb, wq, wk, wv, bq, bk, bv, wo, bo, dy, L, E, Kb, F, No, heads, tiled=False, share_input_diff=False):
+        """MobileBERT attention: x L x E, xb L x Kb, Wq/Wk F x Kb, Wv F x E, Wo No x F, output L x No.  `tiled` calls
+        tiled_mhsa_* (sizes from the coefficient blobs) instead of the inference entry point (F = Kb = No);
+        dy = None skips the backward (the reference library has none that compiles)."""
+        z = self.zeros
+        X, dX, XB, dXB = self.t(x), z(L, E), self.t(xb), z(L, Kb)
+        ws = [self.t(a) for a in (wq, wk, wv, wo)]
+        dws = [z(F, Kb), z(F, Kb), z(F, E), z(No, F)]
+        bs = [self.t(a) for a in (bq, bk, bv, bo)]
+        dbs = [z(F), z(F), z(F), z(No)]
+        q, k, v, att = z(F, L), z(F, L), z(F, L), z(F, L)
+        dq, dk, dv, datt = z(F, L), z(F, L), z(F, L), z(F, L)
+        sm, dsm = z(heads, L, L), z(heads, L, L)
+        Y, dY = z(L, No), self.t(dy if dy is not None else np.zeros((L, No)))
+        tmax = max(L * L, F * Kb, L * F, E * L, No * L, F * E)
+        temp, grad, maxes, sums = z(tmax), z(L * L), z(L), z(L)
+        args = self.args(self.sname("Mhsa_args"),
+                         input=self.blob(X, dX, C=1, H=L, W=E), input_bn=self.blob(XB, None if share_input_diff else dXB, C=1, H=L, W=Kb),
+                         n_heads=heads, output=self.blob(Y, dY, C=1, H=L, W=No),
+                         coeff_in_q=self.blob(ws[0], dws[0], C=1, H=F, W=Kb), coeff_in_k=self.blob(ws[1], dws[1], C=1, H=F, W=Kb),
+                         coeff_in_v=self.blob(ws[2], dws[2], C=1, H=F, W=E), coeff_out=self.blob(ws[3], dws[3], C=1, H=No, W=F),
+                         bias_in_q=self.blob(bs[0], dbs[0], dim=F, W=F), bias_in_k=self.blob(bs[1], dbs[1], dim=F, W=F),
+                         bias_in_v=self.blob(bs[2], dbs[2], dim=F, W=F), bias_out=self.blob(bs[3], dbs[3], dim=No, W=No),
+                         q=self.blob(q, dq, C=1, H=L, W=F), k=self.blob(k, dk, C=1, H=L, W=F), v=self.blob(v, dv, C=1, H=L, W=F),
+                         attention_map=self.blob(att, datt, C=1, H=L, W=F), temp_buffer=temp, grad=grad,
+                         softmax_buffer=self.blob(sm, dsm, C=1, H=heads, W=L * L), maxes=maxes, sums=sums,
+                         opt_matmul_type_fw=0, opt_matmul_type_wg=0, opt_matmul_type_ig=0)
+        if tiled:
+            targs = self.args(self.sname("Tiled_Matmul_Mhsa_args"), tile_h=1, tile_w=1, tile_dim=1)
+            getattr(self.lib, "tiled_mhsa_fp16" if self.half else "tiled_mhsa_fp32")(ctypes.byref(args), ctypes.byref(targs))
+            self.pkg.check(self.lib)
+        else:
+            self.call(self.fname("pulp_mhsa_mobilebert_inference_fp32_fw_cl"), args)
+        r = dict(y=Y.get().copy(), q=q.get().copy(), k=k.get().copy(), v=v.get().copy(), softmax=sm.get().copy(), att=att.get().copy())
+        if dy is not None:
+            self.call(self.fname("pulp_mhsa_mobilebert_inference_fp32_bw_cl"), args)
+            r.update(dx=dX.get().copy(), dxb=dXB.get().copy(), dwq=dws[0].get().copy(), dwk=dws[1].get().copy(), dwv=dws[2].get().copy(),
+                     dwo=dws[3].get().copy(), dq=dq.get().copy(), dk=dk.get().copy(), dv=dv.get().copy(), datt=datt.get().copy(),
+                     dsoftmax=dsm.get().copy())
+        return r
+
     def act(self, kind, x, dy, slope=0.01):
         """kind: relu | leakyrelu | sigmoid | gelu"""
         X, dX, Y, dY = self.t(x), self.zeros(*x.shape), self.zeros(*x.shape), self.t(dy)

@@ -137,6 +137,34 @@ def _mhsa_case(name, L, E, Fd, heads):
     case(name, 1e-5)(C)
 
 
+def _mobilebert_inputs(L, E, Kb, Fd, No):
+    def make(rng):
+        d = dict(x=rng.standard_normal((L, E)).astype(F), xb=rng.standard_normal((L, Kb)).astype(F), dy=rng.standard_normal((L, No)).astype(F))
+        d["wq"] = (rng.standard_normal((Fd, Kb)) / np.sqrt(Kb)).astype(F); d["wk"] = (rng.standard_normal((Fd, Kb)) / np.sqrt(Kb)).astype(F)
+        d["wv"] = (rng.standard_normal((Fd, E)) / np.sqrt(E)).astype(F); d["wo"] = (rng.standard_normal((No, Fd)) / np.sqrt(Fd)).astype(F)
+        for n, m in (("bq", Fd), ("bk", Fd), ("bv", Fd), ("bo", No)):
+            d[n] = (0.1 * rng.standard_normal(m)).astype(F)
+        return d
+    return make
+
+
+def _mobilebert_case(name, L, E, Fd, heads):
+    """forward of the MobileBERT inference attention (F = Kb = No) through the reference's own function, built with -DOPTIMIZE"""
+    class C(object):
+        inputs = staticmethod(_mobilebert_inputs(L, E, Fd, Fd, Fd))
+
+        @staticmethod
+        def abi(r, i):
+            return r.mobilebert(i["x"], i["xb"], i["wq"], i["wk"], i["wv"], i["bq"], i["bk"], i["bv"], i["wo"], i["bo"], None, L, E, Fd, Fd, Fd, heads)
+
+        @staticmethod
+        def oracle(o, i):
+            return o.mobilebert(i["x"], i["xb"], i["wq"], i["wk"], i["wv"], i["bq"], i["bk"], i["bv"], i["wo"], i["bo"], None, L, E, Fd, Fd, Fd, heads)
+    case(name, 1e-5)(C)
+
+
+_mobilebert_case("mhsa_mobilebert_L24_E20_F32_h4", 24, 20, 32, 4)
+_mobilebert_case("mhsa_mobilebert_L37_E48_F40_h5", 37, 48, 40, 5)
 _mhsa_case("mhsa_ref_default", 10, 10, 160, 5)      # tests/test_mhsa_fp32/Makefile:4-7
 _mhsa_case("mhsa_L24_E12_F32_h4", 24, 12, 32, 4)
 

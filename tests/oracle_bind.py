@@ -128,6 +128,22 @@ class Oracle(object):
                                  _p(_ptr(r["dx"])), _i(L), _i(E), _i(F), _i(heads))
         return r
 
+    def mobilebert(self, x, xb, wq, wk, wv, bq, bk, bv, wo, bo, dy, L, E, Kb, F, No, heads):
+        """x: L x E, xb: L x Kb, Wq/Wk: F x Kb, Wv: F x E, Wo: No x F, dy: L x No (None: forward only)."""
+        z = lambda *s: np.zeros(s, np.float32)
+        r = dict(q=z(F, L), k=z(F, L), v=z(F, L), softmax=z(heads, L, L), att=z(F, L), y=z(L, No))
+        P = lambda a: _p(_ptr(a))
+        dims = (_i(L), _i(E), _i(Kb), _i(F), _i(No), _i(heads))
+        self.lib.orc_mhsa_mobilebert_fw(P(x), P(xb), P(wq), P(wk), P(wv), P(bq), P(bk), P(bv), P(wo), P(bo),
+                                        P(r["q"]), P(r["k"]), P(r["v"]), P(r["softmax"]), P(r["att"]), P(r["y"]), *dims)
+        if dy is not None:
+            r.update(dq=z(F, L), dk=z(F, L), dv=z(F, L), dsoftmax=z(heads, L, L), datt=z(F, L),
+                     dwq=z(F, Kb), dwk=z(F, Kb), dwv=z(F, E), dwo=z(No, F), dx=z(L, E), dxb=z(L, Kb))
+            self.lib.orc_mhsa_mobilebert_bw(P(x), P(xb), P(wq), P(wk), P(wv), P(wo), P(r["q"]), P(r["k"]), P(r["v"]), P(r["softmax"]), P(r["att"]),
+                                            P(dy), P(r["dq"]), P(r["dk"]), P(r["dv"]), P(r["dsoftmax"]), P(r["datt"]),
+                                            P(r["dwq"]), P(r["dwk"]), P(r["dwv"]), P(r["dwo"]), P(r["dx"]), P(r["dxb"]), *dims)
+        return r
+
     def act_fw(self, kind, x, slope=0.0):
         y = np.zeros_like(x)
         self.lib.orc_act_fw(_i(kind), _p(_ptr(x)), _p(_ptr(y)), _l(x.size), _f(slope))

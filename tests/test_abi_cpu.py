@@ -44,6 +44,15 @@ def test_library_exports_every_declared_symbol(pkg):
     lib = ctypes.CDLL(pkg.LIB_PATH)
     missing = [f for f in pkg.FUNCTIONS if not hasattr(lib, f)]
     assert not missing, missing
+    # ... and the declarations with other signatures (two-argument tiled attention, scalar helpers), both ABI headers
+    import re
+    for header in ("trainlib_b200_abi.h", "pmsis.h"):
+        src = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", header)).read(), flags=re.S)
+        src = re.sub(r"\{[^{}]*\}", "{}", src)                     # struct bodies and inline functions are not declarations
+        names = set(re.findall(r"\b(?:void|int|float|double|unsigned|fp16)\s+\*?\s*(\w+)\s*\([^;{()]*\)\s*;", src))
+        assert len(names) > 5, header
+        missing = sorted(f for f in names if not hasattr(lib, f))
+        assert not missing, (header, missing)
     ext = ["trainlib_init", "trainlib_last_error", "trainlib_last_error_string", "trainlib_clear_error", "trainlib_device",
            "trainlib_set_stream", "trainlib_stream", "trainlib_synchronize", "trainlib_set_memory_mode", "trainlib_memory_mode",
            "trainlib_malloc", "trainlib_free", "trainlib_malloc_host", "trainlib_free_host", "trainlib_memcpy_h2d", "trainlib_memcpy_d2h",

@@ -92,3 +92,43 @@ def test_resnet8_golden_is_the_reference(pkg):
     r = bench_nets.reference_step(bench_nets.bind_net(bench_nets.NET_REF_SEQ), 4, first_stream=1984)
     assert np.array_equal(r["loss"], gold["loss_1984"][:4]) and np.array_equal(r["logits"], gold["logits_1984"][:4])
     assert gold["grads_0"].shape == gold["grads_1984"].shape == r["grads"].shape
+
+
+def test_mobilebert_attention_backward_is_the_gradient_of_its_forward(oracle):
+    """The reference's MobileBERT backward does not compile, so the oracle's is pinned against the chain rule written
+    independently in float64 numpy (einsum over named axes) from the tensors the forward stored: P is taken as given,
+    as in the training path's backward, so the Schraudolph exponential does not enter."""
+    L, E, Kb, Fd, No, heads = 13, 10, 12, 16, 9, 4
+    H = Fd // heads
+    rng = np.random.default_rng(99)
+    f = lambda *s: rng.standard_normal(s).astype(np.float32)
+    x, xb, dy = f(L, E), f(L, Kb), f(L, No)
+    wq, wk, wv, wo = f(Fd, Kb) / 3, f(Fd, Kb) / 3, f(Fd, E) / 3, f(No, Fd) / 4
+    bq, bk, bv, bo = f(Fd) / 10, f(Fd) / 10, f(Fd) / 10, f(No) / 10
+    o = oracle.mobilebert(x, xb, wq, wk, wv, bq, bk, bv, wo, bo, dy, L, E, Kb, Fd, No, heads)
+    D = np.float64
+    # forward pieces in float64 from the same inputs
+    q = wq.astype(D) @ xb.astype(D).T + bq[:, None]; k = wk.astype(D) @ xb.astype(D).T + bk[:, None]; v = wv.astype(D) @ x.astype(D).T + bv[:, None]
+    for name, want in (("q", q), ("k", k), ("v", v)):
+        assert np.abs(o[name] - want).max() <= 1e-5 * np.abs(want).max(), name
+    P = o["softmax"].astype(D)                                            # [head][query][key]
+    vh = o["v"].astype(D).reshape(heads, H, L); qh = o["q"].astype(D).reshape(heads, H, L); kh = o["k"].astype(D).reshape(heads, H, L)
+    att = np.einsum("hdk,hqk->hdq", vh, P).reshape(Fd, L)
+    assert np.abs(o["att"] - att).max() <= 1e-5 * np.abs(att).max()
+    y = (wo.astype(D) @ o["att"].astype(D)).T + bo[None, :]
+    assert np.abs(o["y"] - y).max() <= 1e-5 * np.abs(y).max()
+    # backward
+    scaling = D(oracle.q_rsqrt(float(H)))
+    dwo = dy.astype(D).T @ o["att"].astype(D).T                           # [n][f]
+    datt = wo.astype(D).T @ dy.astype(D).T                                # [f][l]
+    dah = datt.reshape(heads, H, L)
+    dv = np.einsum("hdq,hqk->hdk", dah, P)
+    dP = np.einsum("hdq,hdk->hqk", dah, vh)
+    dS = (dP - (dP * P).sum(-1, keepdims=True)) * P * scaling
+    dk = np.einsum("hdq,hqk->hdk", qh, dS); dq = np.einsum("hdk,hqk->hdq", kh, dS)
+    dqf, dkf, dvf = dq.reshape(Fd, L), dk.reshape(Fd, L), dv.reshape(Fd, L)
+    want = dict(dwo=dwo, datt=datt, dv=dvf, dsoftmax=dP, dk=dkf, dq=dqf, dwq=dqf @ xb.astype(D), dwk=dkf @ xb.astype(D), dwv=dvf @ x.astype(D),
+                dxb=dqf.T @ wq.astype(D) + dkf.T @ wk.astype(D), dx=dvf.T @ wv.astype(D))
+    for name, w in want.items():
+        err = np.abs(o[name] - w).max() / np.abs(w).max()
+        assert err <= 2e-5, (name, err)

@@ -236,6 +236,112 @@ def test_mhsa_config3(run, oracle):
         assert_close(got[k], want[k], FP32_TOL, "mhsa c3 %s" % k)
 
 
+@pytest.mark.parametrize("L,E,Fd,heads", [(37, 24, 36, 3), (100, 48, 80, 2), (256, 64, 128, 4), (8, 16, 16, 1), (1, 8, 8, 2)])
+def test_mhsa_fused_attention_core(run, pkg, gpulib, oracle, L, E, Fd, heads):
+    """ragged sequence lengths and head sizes through the fused score-softmax-value kernels; the same call with the fused
+    kernels switched off (gemm path 1) must agree too, and the kernel names prove which path ran"""
+    rng = seeded(31 + L)
+    x = rng.standard_normal((E, L)).astype(F); dy = rng.standard_normal((E, L)).astype(F)
+    ws = [(rng.standard_normal((E, Fd)) / np.sqrt(E)).astype(F) for _ in range(3)] + [(rng.standard_normal((E, Fd)) / np.sqrt(Fd)).astype(F)]
+    bs = [(0.1 * rng.standard_normal(Fd)).astype(F) for _ in range(3)]
+    want = oracle.mhsa(x, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dy, L, E, Fd, heads)
+    gpulib.trainlib_profile(1)
+    got = run(device=True).mhsa(x, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dy, L, E, Fd, heads)
+    gpulib.trainlib_profile(0)
+    names = [r[0] for r in pkg.profile_table(gpulib)]
+    for kernel in ("attn_fw_kernel", "attn_bw_query_kernel", "attn_bw_key_kernel"):
+        assert any(kernel in n for n in names), "%s did not run: %s" % (kernel, names)
+    assert not any("softmax" in n for n in names), "the separate softmax kernels ran beside the fused ones: %s" % names
+    try:
+        gpulib.trainlib_set_gemm_path(1)
+        plain = run(device=True).mhsa(x, ws[0], ws[1], ws[2], bs[0], bs[1], bs[2], ws[3], dy, L, E, Fd, heads)
+    finally:
+        gpulib.trainlib_set_gemm_path(0)
+    for k in ("q", "k", "v", "softmax", "att", "y", "dwo", "datt", "dv", "dsoftmax", "dk", "dq", "dwq", "dwk", "dwv", "dx"):
+        assert_close(got[k], want[k], FP32_TOL, "fused mhsa %s" % k)
+        assert_close(plain[k], want[k], FP32_TOL, "unfused mhsa %s" % k)
+
+
+def _mobilebert_inputs(rng, L, E, Kb, Fd, No, cast=lambda a: a):
+    f = lambda *s: rng.standard_normal(s).astype(F)
+    d = dict(x=f(L, E), xb=f(L, Kb), dy=f(L, No), wq=f(Fd, Kb) / np.sqrt(Kb), wk=f(Fd, Kb) / np.sqrt(Kb), wv=f(Fd, E) / np.sqrt(E),
+             wo=f(No, Fd) / np.sqrt(Fd), bq=0.1 * f(Fd), bk=0.1 * f(Fd), bv=0.1 * f(Fd), bo=0.1 * f(No))
+    return {k: cast(v.astype(F)) for k, v in d.items()}
+
+
+MB_KEYS = ("q", "k", "v", "softmax", "att", "y", "dwo", "datt", "dv", "dsoftmax", "dk", "dq", "dwq", "dwk", "dwv", "dx", "dxb")
+
+
+@pytest.mark.parametrize("L,E,Fd,heads", [(24, 20, 32, 4), (128, 512, 128, 4), (37, 48, 40, 5)])
+def test_mobilebert_attention_forward_backward(run, oracle, L, E, Fd, heads):
+    """pulp_mhsa_mobilebert_inference_fp32_{fw,bw}_cl (F = Kb = No) against the oracle; the middle case is the attention
+    of config 4's block (sequence 128, hidden 512, bottleneck 128, 4 heads of 32)"""
+    i = _mobilebert_inputs(seeded(L + E), L, E, Fd, Fd, Fd)
+    a = (i["x"], i["xb"], i["wq"], i["wk"], i["wv"], i["bq"], i["bk"], i["bv"], i["wo"], i["bo"], i["dy"], L, E, Fd, Fd, Fd, heads)
+    want = oracle.mobilebert(*a)
+    got = run(device=True).mobilebert(*a)
+    for k in MB_KEYS:
+        assert_close(got[k], want[k], FP32_TOL, "mobilebert attention %s" % k)
+    # host pointers (staging mirrors) give the same bits as device pointers
+    host = run(device=False).mobilebert(*a)
+    for k in MB_KEYS:
+        assert_exact(host[k], got[k], "mobilebert attention, host pointers, %s" % k)
+
+
+def test_mobilebert_attention_input_gradients_into_one_buffer(run, oracle):
+    """input_bn without a diff buffer and Kb = E: all three input gradients are added into input.diff, as the reference does"""
+    L, E, heads = 16, 24, 3
+    i = _mobilebert_inputs(seeded(8), L, E, E, E, E)
+    a = (i["x"], i["xb"], i["wq"], i["wk"], i["wv"], i["bq"], i["bk"], i["bv"], i["wo"], i["bo"], i["dy"], L, E, E, E, E, heads)
+    want = oracle.mobilebert(*a)
+    got = run(device=True).mobilebert(*a, share_input_diff=True)
+    assert_close(got["dx"], want["dx"] + want["dxb"], FP32_TOL, "summed input gradient")
+
+
+def test_tiled_mhsa_sizes_from_the_coefficient_blobs(run, oracle):
+    """tiled_mhsa_fp32: F, Kb and No come from the coefficient blobs and differ from one another; tile sizes are ignored"""
+    L, E, Kb, Fd, No, heads = 40, 36, 28, 48, 20, 6
+    i = _mobilebert_inputs(seeded(9), L, E, Kb, Fd, No)
+    a = (i["x"], i["xb"], i["wq"], i["wk"], i["wv"], i["bq"], i["bk"], i["bv"], i["wo"], i["bo"], None, L, E, Kb, Fd, No, heads)
+    want = oracle.mobilebert(*a)
+    got = run(device=True).mobilebert(*a, tiled=True)
+    for k in ("q", "k", "v", "softmax", "att", "y"):
+        assert_close(got[k], want[k], FP32_TOL, "tiled attention %s" % k)
+
+
+def test_tiled_matmul_and_transpose_mhsa(pkg, gpulib, oracle):
+    rng = seeded(10)
+    N, K, M = 24, 16, 40
+    A = rng.standard_normal((N, K)).astype(F); B = rng.standard_normal((M, K)).astype(F); bias = rng.standard_normal(N).astype(F)
+    r = AbiRunner(pkg, gpulib, device=True)
+    a, b, c, bi = r.t(A), r.t(B), r.zeros(N, M), r.t(bias)
+    args = r.args("matMul_args", A=a, B=b, C=c, N=N, K=K, M=M, trans_B=1, USE_BIASES=1, bias=bi, bias_transposed=1, bias_dim=N)
+    targs = r.args("Tiled_Matmul_Mhsa_args", tile_h=8, tile_w=8, tile_dim=64)
+    import ctypes
+    gpulib.tiled_matmul_mhsa(ctypes.byref(args), ctypes.byref(targs), 1); pkg.check(gpulib)
+    want = oracle.mm(A, B, N, K, M, 1) + bias[:, None]
+    assert_close(c.get(), want, FP32_TOL, "tiled_matmul_mhsa")
+    out = r.zeros(M, N)
+    targ = r.args("transp_args", in_matrix=c, out_matrix=out, N=N, M=M)
+    gpulib.tiled_transpose_mhsa(ctypes.byref(targ), ctypes.byref(targs), 0); pkg.check(gpulib)
+    assert_exact(out.get(), c.get().T, "tiled_transpose_mhsa")
+    r.close()
+
+
+def test_mobilebert_attention_fp16(run, oracle):
+    """fp16 twins (inference forward / backward and tiled forward) against the fp32 oracle on fp16-representable inputs"""
+    L, E, Fd, heads = 128, 512, 128, 4
+    h = lambda a: a.astype(np.float16).astype(F)
+    i = _mobilebert_inputs(seeded(12), L, E, Fd, Fd, Fd, cast=h)
+    a = (i["x"], i["xb"], i["wq"], i["wk"], i["wv"], i["bq"], i["bk"], i["bv"], i["wo"], i["bo"], i["dy"], L, E, Fd, Fd, Fd, heads)
+    want = oracle.mobilebert(*a)
+    got = run(device=True, half=True).mobilebert(*a)
+    for k in ("y", "softmax", "att", "dx", "dxb", "dwq", "dwk", "dwv", "dwo"):
+        assert_close(got[k].astype(F), want[k], 2e-2, "mobilebert attention fp16 %s" % k)     # intermediates are rounded to fp16 between the kernels
+    tiled = run(device=True, half=True).mobilebert(*(a[:10] + (None,) + a[11:]), tiled=True)
+    assert_exact(tiled["y"], got["y"], "tiled_mhsa_fp16 = inference forward on square shapes")
+
+
 def test_mhsa_fp16(run, oracle):
     rng = seeded(4)
     L, E, Fd, heads = 128, 128, 128, 4
