@@ -222,6 +222,15 @@ struct optim_args { struct blob *weights; struct blob *biases; float learning_ra
 struct SkipConn_args { struct blob *skip; struct blob *lout; struct blob *output; int skip_in_grad; };
 /* [ref: pulp_pooling_fp32.h:34-41] */
 struct pool_args { struct blob *input; struct blob *output; int Hker; int Wker; int Hstride; int Wstride; };
+/* [ref: pulp_losses_fp32.h:45-50] */
+struct berHu_loss_args { struct blob *output; float *target; float *wr_loss; float alpha; };
+/* [ref: pulp_nonorm_fp32.h:35-40] */
+struct Nonorm_args { struct blob *input; struct blob *coeff; struct blob *bias; struct blob *output; };
+/* [ref: pulp_rmsnorm_fp32.h:17-31] */
+struct weighted_scaling_args { float *out; float *in; float *w; float scaling_factor; unsigned int size; };
+struct sum_of_squares_args { float *out; float *in; unsigned int size; };
+/* [ref: pulp_act_fp32.h:76-81] */
+struct swiglu_args { float *in1; float *in2; float *out; int dim; };
 
 /* ================================================================== fp16 structs */
 /* Field-for-field twins of the above on `fp16` storage. */
@@ -350,6 +359,23 @@ struct optim_args_fp16 { struct blob_fp16 *weights; struct blob_fp16 *biases; fp
 struct SkipConn_args_fp16 { struct blob_fp16 *skip; struct blob_fp16 *lout; struct blob_fp16 *output; int skip_in_grad; };
 /* [ref: pulp_pooling_fp16.h:34-41] */
 struct pool_args_fp16 { struct blob_fp16 *input; struct blob_fp16 *output; int Hker; int Wker; int Hstride; int Wstride; };
+/* [ref: pulp_losses_fp16.h:46-51] */
+struct berHu_loss_args_fp16 { struct blob_fp16 *output; fp16 *target; fp16 *wr_loss; fp16 alpha; };
+/* [ref: pulp_nonorm_fp16.h:36-41] */
+struct Nonorm_args_fp16 { struct blob_fp16 *input; struct blob_fp16 *coeff; struct blob_fp16 *bias; struct blob_fp16 *output; };
+/* [ref: pulp_rmsnorm_fp16.h:4-16] */
+struct weighted_scaling_args_fp16 { fp16 *out; fp16 *in; fp16 *w; fp16 scaling_factor; unsigned int size; };
+struct sum_of_squares_args_fp16 { fp16 *out; fp16 *in; unsigned int size; };
+/* [ref: pulp_act_fp16.h:195-200] */
+struct swiglu_args_fp16 { fp16 *in1; fp16 *in2; fp16 *out; int dim; };
+/* [ref: pulp_train_utils_fp16.h:387-393, 427-432, 441-445, 470-477, 488-513, 786-792] */
+struct max_args_fp16 { fp16 *input; int H; int W; fp16 *maxes; int dim; };
+struct row_div_args_fp16 { fp16 *input; int H; int W; fp16 *sums; };
+struct div_args_fp16 { fp16 *input; fp16 n; int dim; };
+struct mean_std_args_fp16 { fp16 *input; fp16 *mean; fp16 *var; fp16 *std; fp16 epsilon; int dim; };
+struct sm_bw_op_1_args_fp16 { fp16 *A; fp16 *B; fp16 *S; int H; int W; };
+struct sm_bw_op_2_args_fp16 { fp16 *A; fp16 *B; fp16 *S; fp16 *output; int H; int W; };
+struct vector_exp_sum_args_fp16 { fp16 *input; fp16 *sums; fp16 *output; int dim; fp16 max; };
 
 /* ================================================================== fp32 entry points */
 
@@ -625,6 +651,41 @@ void pad_tensor_fp16(void *pad_args_fp16);
 void cast_fp32_tensor_to_fp16(void *cast_32t16_args);
 void pulp_scalar_mul_fp16_cl(void *scalar_mul_args_fp16);
 void mm_bias_add_transposed_fp16(void *mm_bias_add_args_fp16);
+
+/* ---- the rest of the element-wise family [ref: pulp_losses_fp32.h:79-121, pulp_pooling_fp32.h:64-70, pulp_nonorm_fp32.h:53,
+ * pulp_rmsnorm_fp32.h:33-49, pulp_act_fp32.h:274-281; the fp16 twins in the _fp16 headers].  Losses and pooling work on
+ * every stream in streams mode like their MSE / average-pool siblings.  The "one value per core" outputs of the
+ * reference's workers (maxes[core], sums[core], out[core]) have one entry here, index 0: this library is one core. */
+void pulp_L1Loss(void *loss_args);                 void pulp_L1Loss_backward(void *loss_args);
+void pulp_L1Loss_fp16(void *loss_args_fp16);       void pulp_L1Loss_backward_fp16(void *loss_args_fp16);
+void pulp_berHuLoss(void *berHu_loss_args);        void pulp_berHuLoss_backward(void *berHu_loss_args);
+void pulp_berHuLoss_fp16(void *berHu_loss_args_fp16);  void pulp_berHuLoss_backward_fp16(void *berHu_loss_args_fp16);
+void pulp_maxpool_fp32_fw_cl(void *pool_args);     void pulp_maxpool_fp32_bw_cl(void *pool_args);
+void pulp_maxpool_fp16_fw_cl(void *pool_args_fp16); void pulp_maxpool_fp16_bw_cl(void *pool_args_fp16);
+void pulp_nonorm_fp32_fw_cl(void *Nonorm_args);    void pulp_nonorm_fp16_fw_cl(void *Nonorm_args_fp16);
+void weighted_scaling_fp32_cl(void *weighted_scaling_args);  void weighted_scaling_fp16_cl(void *weighted_scaling_args_fp16);
+void sum_of_squares_fp32_cl(void *sum_of_squares_args);      void sum_of_squares_fp16_cl(void *sum_of_squares_args_fp16);
+void rmsnorm_parallelized_fp32(float *o, float *x, float *weight, float *buffer_n_cores, int size);
+void rmsnorm_parallelized_fp16(fp16 *o, fp16 *x, fp16 *weight, fp16 *buffer_n_cores, int size);
+void pulp_swiglu_fp32_cl(void *swiglu_args);       void pulp_swiglu_fp16_cl(void *swiglu_args_fp16);
+void pulp_vector_softmax_fp32(float *out, float *in, float *buffer_n_cores, unsigned int size);
+void pulp_vector_softmax_fp16(fp16 *out, fp16 *in, fp16 *buffer_n_cores, unsigned int size);
+/* pieces of the reference's softmax [ref: pulp_train_utils_fp32.h:707-834; pulp_train_utils_fp16.h:399-760] */
+void pulp_max_fp32_cl(void *max_args);             void pulp_max_fp16_cl(void *max_args_fp16);
+void pulp_div_fp32_cl(void *div_args);             void pulp_div_fp16_cl(void *div_args_fp16);
+void pulp_shift_sum_fp32_cl(void *shift_sum_args);
+void vector_exp_sum_fp32_cl(void *vector_exp_sum_args);  void vector_exp_sum_fp16_cl(void *vector_exp_sum_args_fp16);
+void pulp_sm_bw_op_1(void *sm_bw_op_1_args);       void pulp_sm_bw_op_1_fp16(void *sm_bw_op_1_args_fp16);
+void pulp_sm_bw_op_2(void *sm_bw_op_2_args);       void pulp_sm_bw_op_2_fp16(void *sm_bw_op_2_args_fp16);
+void pulp_row_max_fp16_cl(void *max_args_fp16);    void pulp_exp_sum_fp16_cl(void *exp_sum_args_fp16);
+void pulp_row_div_fp16_cl(void *row_div_args_fp16); void pulp_mean_std_fp16_cl(void *mean_std_args_fp16);
+/* fp16 twins of the forkable activation workers and of the parallelised instance norm
+ * [ref: pulp_act_fp16.h; pulp_instnorm_fp16.h] */
+void sigmoid_core_fw_fp16(void *act_args_fp16);    void sigmoid_core_bw_fp16(void *act_args_fp16);
+void leakyrelu_core_fw_fp16(void *leakyrelu_args_fp16);  void leakyrelu_core_bw_fp16(void *leakyrelu_args_fp16);
+void pulp_instnorm_parallelized_fp16_fw_cl(void *InstNorm_args_fp16);
+void pulp_instnorm_parallelized_fp16_bw_input_grads_cl(void *InstNorm_args_fp16);
+void pulp_instnorm_parallelized_fp16_bw_param_grads_cl(void *InstNorm_args_fp16);
 
 #ifdef __cplusplus
 }

@@ -1052,6 +1052,8 @@ TL_PAIR(pulp_sigmoid_fp32_fw_cl, pulp_sigmoid_fp16_fw_cl, ACT32(ACT_SIGMOID), AC
 TL_PAIR(pulp_sigmoid_fp32_bw_cl, pulp_sigmoid_fp16_bw_cl, ACTB32(ACT_SIGMOID), ACTB16(ACT_SIGMOID))
 TL_EXPORT void sigmoid_core_fw_fp32(void *a) { ACT32(ACT_SIGMOID); }
 TL_EXPORT void sigmoid_core_bw_fp32(void *a) { ACTB32(ACT_SIGMOID); }
+TL_EXPORT void sigmoid_core_fw_fp16(void *a) { ACT16(ACT_SIGMOID); }
+TL_EXPORT void sigmoid_core_bw_fp16(void *a) { ACTB16(ACT_SIGMOID); }
 TL_PAIR(pulp_gelu_tanh_approx_fp32_fw_cl, pulp_gelu_fp16_fw_cl, ACT32(ACT_GELU), ACT16(ACT_GELU))
 TL_EXPORT void pulp_leakyrelu_fp32_fw_cl(void *a) { act_fw_impl<F32, leakyrelu_args>(a, ACT_LEAKY, ((leakyrelu_args *)a)->negative_slope); }
 TL_EXPORT void pulp_leakyrelu_fp32_bw_cl(void *a) { act_bw_impl<F32, leakyrelu_args>(a, ACT_LEAKY, ((leakyrelu_args *)a)->negative_slope); }
@@ -1059,6 +1061,8 @@ TL_EXPORT void leakyrelu_core_fw_fp32(void *a) { pulp_leakyrelu_fp32_fw_cl(a); }
 TL_EXPORT void leakyrelu_core_bw_fp32(void *a) { pulp_leakyrelu_fp32_bw_cl(a); }
 TL_EXPORT void pulp_leakyrelu_fp16_fw_cl(void *a) { act_fw_impl<F16, leakyrelu_args_fp16>(a, ACT_LEAKY, __half2float(((leakyrelu_args_fp16 *)a)->negative_slope)); }
 TL_EXPORT void pulp_leakyrelu_fp16_bw_cl(void *a) { act_bw_impl<F16, leakyrelu_args_fp16>(a, ACT_LEAKY, __half2float(((leakyrelu_args_fp16 *)a)->negative_slope)); }
+TL_EXPORT void leakyrelu_core_fw_fp16(void *a) { pulp_leakyrelu_fp16_fw_cl(a); }
+TL_EXPORT void leakyrelu_core_bw_fp16(void *a) { pulp_leakyrelu_fp16_bw_cl(a); }
 TL_PAIR(pulp_softmax_fp32_fw_cl, pulp_softmax_fp16_fw_cl, softmax_fw_impl<F32>(a), softmax_fw_impl<F16>(a))
 TL_PAIR(pulp_softmax_fp32_bw_cl, pulp_softmax_fp16_bw_cl, softmax_bw_impl<F32>(a), softmax_bw_impl<F16>(a))
 
@@ -1070,6 +1074,9 @@ TL_PAIR(trainlib_instnorm_act_fp32_bw_cl, trainlib_instnorm_act_fp16_bw_cl, inst
 TL_EXPORT void pulp_instnorm_parallelized_fp32_fw_cl(void *a) { instnorm_impl<F32>(a, STEP_FW); }
 TL_EXPORT void pulp_instnorm_parallelized_fp32_bw_input_grads_cl(void *a) { instnorm_impl<F32>(a, STEP_IN_GRAD); }
 TL_EXPORT void pulp_instnorm_parallelized_fp32_bw_param_grads_cl(void *a) { instnorm_impl<F32>(a, STEP_WGT_GRAD); }
+TL_EXPORT void pulp_instnorm_parallelized_fp16_fw_cl(void *a) { instnorm_impl<F16>(a, STEP_FW); }
+TL_EXPORT void pulp_instnorm_parallelized_fp16_bw_input_grads_cl(void *a) { instnorm_impl<F16>(a, STEP_IN_GRAD); }
+TL_EXPORT void pulp_instnorm_parallelized_fp16_bw_param_grads_cl(void *a) { instnorm_impl<F16>(a, STEP_WGT_GRAD); }
 TL_EXPORT void pulp_instnorm_fp32_bw_cl(void *a)
 {
     auto *c = (InstNorm_args *)a;
@@ -1265,6 +1272,14 @@ TL_EXPORT int verify_tensor(float *tensor_out, float *tensor_ref, int size, floa
 // ---- table of library workers for pi_cl_team_fork
 typedef void (*worker_t)(void *);
 static const worker_t g_workers[] = {
+    pulp_L1Loss, pulp_L1Loss_backward, pulp_L1Loss_fp16, pulp_L1Loss_backward_fp16, pulp_berHuLoss, pulp_berHuLoss_backward,
+    pulp_berHuLoss_fp16, pulp_berHuLoss_backward_fp16, pulp_maxpool_fp32_fw_cl, pulp_maxpool_fp32_bw_cl, pulp_maxpool_fp16_fw_cl,
+    pulp_maxpool_fp16_bw_cl, pulp_nonorm_fp32_fw_cl, pulp_nonorm_fp16_fw_cl, weighted_scaling_fp32_cl, weighted_scaling_fp16_cl,
+    sum_of_squares_fp32_cl, sum_of_squares_fp16_cl, pulp_swiglu_fp32_cl, pulp_swiglu_fp16_cl, pulp_max_fp32_cl, pulp_max_fp16_cl,
+    pulp_div_fp32_cl, pulp_div_fp16_cl, pulp_shift_sum_fp32_cl, vector_exp_sum_fp32_cl, vector_exp_sum_fp16_cl,
+    pulp_sm_bw_op_1, pulp_sm_bw_op_1_fp16, pulp_sm_bw_op_2, pulp_sm_bw_op_2_fp16, pulp_row_max_fp16_cl, pulp_exp_sum_fp16_cl,
+    pulp_row_div_fp16_cl, pulp_mean_std_fp16_cl, sigmoid_core_fw_fp16, sigmoid_core_bw_fp16, leakyrelu_core_fw_fp16, leakyrelu_core_bw_fp16,
+    pulp_instnorm_parallelized_fp16_fw_cl, pulp_instnorm_parallelized_fp16_bw_input_grads_cl, pulp_instnorm_parallelized_fp16_bw_param_grads_cl,
 #define X(name) name,
     TL_MM_VARIANTS(X)
 #undef X

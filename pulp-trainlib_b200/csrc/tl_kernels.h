@@ -99,6 +99,22 @@ template <class T> void row_max(const T *in, T *maxes, int rows, int width);
 template <class T> void exp_sum(const T *in, T *out, const T *maxes, T *sums, int rows, int width);
 template <class T> void row_div(T *io, const T *sums, int rows, int width);
 template <class T> void mean_std(const T *x, T *mean, T *var, T *stdev, int D, float eps);
+// the rest of the element-wise family (tl_family.cu)
+template <class T> void l1_fw(const T *y, const T *t, T *loss, int dim, int n, bool berhu, float alpha);
+template <class T> void l1_bw(const T *y, const T *t, T *dy, int dim, int n, bool berhu, float alpha);
+template <class T> void maxpool_fw(const T *x, T *y, long long planes, int H, int W, int Ho, int Wo, int Hk, int Wk, int Hs, int Ws);
+template <class T> void maxpool_bw(const T *x, const T *dy, T *dx, long long planes, int H, int W, int Ho, int Wo, int Hk, int Wk, int Hs, int Ws);
+template <class T> void nonorm_fw(const T *x, const T *w, const T *b, T *y, long long rows, int width);
+template <class T> void weighted_scaling(const T *x, const T *w, T *y, long long n, float sf, const T *sumsq);
+template <class T> void sum_of_squares(const T *x, T *out, long long n);
+template <class T> void swiglu(const T *a, const T *b, T *y, long long n);
+template <class T> void vec_max(const T *x, T *out, long long n);
+template <class T> void vec_exp_sum(const T *x, T *y, T *sum, long long n, float mx);
+template <class T> void vector_softmax(const T *x, T *y, long long n);
+template <class T> void vec_div(T *io, long long n, float d);
+template <class T> void shift_sum(const T *x, const T *maxes, T *y, T *sums, int dim);
+template <class T> void sm_bw_op1(const T *A, const T *B, T *S, int H, int W);
+template <class T> void sm_bw_op2(const T *A, const T *B, const T *S, T *out, int H, int W);
 void cast_h2f(const __half *src, float *dst, long long n);
 void cast_f2h(const float *src, __half *dst, long long n);
 

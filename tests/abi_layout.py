@@ -40,5 +40,6 @@ REF_DEFAULT = os.environ.get("TRAINLIB_REF", os.path.join(os.path.dirname(os.pat
 
 def reference(structs, ref=REF_DEFAULT):
     shim = os.path.join(ROOT, "oracle", "shim")
-    return measure(structs, [shim, os.path.join(ref, "lib", "include")], '#include "pulp_train.h"',
+    # pulp_train.h of the reference leaves out the RMS-norm headers
+    return measure(structs, [shim, os.path.join(ref, "lib", "include")], '#include "pulp_train.h"\n#include "pulp_rmsnorm_fp32.h"\n#include "pulp_rmsnorm_fp16.h"',
                    extra_flags=["-include", os.path.join(shim, "pmsis.h")])

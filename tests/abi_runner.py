@@ -403,6 +403,81 @@ class AbiRunner(object):
         self.call(self.fname("pulp_avgpool_fp32_bw_cl"), args)
         return dict(y=Y.get().copy(), dx=dX.get().copy())
 
+    def family(self, i):
+        """The rest of the element-wise family on the inputs of golden_cases._Family; returns every output by name."""
+        r = {}
+        h = self.half
+        nm = lambda base: base + ("_fp16" if h else "")            # names that append _fp16
+        # --- L1 and berHu
+        y, t = i["y"], i["t"]
+        Y, dY, T, L = self.t(y), self.zeros(*y.shape), self.t(t), self.zeros(1)
+        la = self.args(self.sname("loss_args"), output=self.blob(Y, dY, dim=y.size, W=y.size), target=T, wr_loss=L)
+        self.call(nm("pulp_L1Loss"), la); r["l1"] = L.get().copy()
+        self.call("pulp_L1Loss_backward" + self.sfx, la); r["l1_dy"] = dY.get().copy()
+        ba = self.args(self.sname("berHu_loss_args"), output=self.blob(Y, dY, dim=y.size, W=y.size), target=T, wr_loss=L, alpha=float(i["alpha"][0]))
+        self.call(nm("pulp_berHuLoss"), ba); r["berhu"] = L.get().copy()
+        self.call("pulp_berHuLoss_backward" + self.sfx, ba); r["berhu_dy"] = dY.get().copy()
+        # --- max pooling: disjoint 2x2 windows, and overlapping 3x3 stride-1 windows with ties
+        for tag, x, g, (Hk, Wk, sh, sw) in (("mp2", i["px"], i["pdy2"], (2, 2, 2, 2)), ("mp3", i["pxt"], i["pdy3"], (3, 3, 1, 1))):
+            C, H, W = x.shape
+            Ho, Wo = (H - Hk + sh) // sh, (W - Wk + sw) // sw
+            X, dX, O, dO = self.t(x), self.zeros(C, H, W), self.zeros(C, Ho, Wo), self.t(g)
+            pa = self.args(self.sname("pool_args"), input=self.blob(X, dX, C=C, H=H, W=W), output=self.blob(O, dO, C=C, H=Ho, W=Wo), Hker=Hk, Wker=Wk, Hstride=sh, Wstride=sw)
+            self.call(self.fname("pulp_maxpool_fp32_fw_cl"), pa); self.call(self.fname("pulp_maxpool_fp32_bw_cl"), pa)
+            r[tag + "_y"] = O.get().copy(); r[tag + "_dx"] = dX.get().copy()
+        # --- NoNorm
+        nx = i["nx"]; rows, width = nx.shape
+        NX, NW, NB, NO = self.t(nx), self.t(i["nw"]), self.t(i["nb"]), self.zeros(rows, width)
+        na = self.args(self.sname("Nonorm_args"), input=self.blob(NX, None, C=1, H=rows, W=width), coeff=self.blob(NW, None, dim=width, W=width),
+                       bias=self.blob(NB, None, dim=width, W=width), output=self.blob(NO, None, C=1, H=rows, W=width))
+        self.call(self.fname("pulp_nonorm_fp32_fw_cl"), na); r["nonorm"] = NO.get().copy()
+        # --- RMS norm and its pieces
+        v, w = i["v"], i["w"]; n = v.size
+        V, W_, O, B = self.t(v), self.t(w), self.zeros(n), self.zeros(8)
+        wa = self.args(self.sname("weighted_scaling_args"), out=O, **{"in": V}, w=W_, scaling_factor=0.37, size=n)
+        self.call(self.fname("weighted_scaling_fp32_cl"), wa); r["wscale"] = O.get().copy()
+        sa = self.args(self.sname("sum_of_squares_args"), out=B, **{"in": V}, size=n)
+        self.call(self.fname("sum_of_squares_fp32_cl"), sa); r["sumsq"] = B.get()[:1].copy()
+        fn = getattr(self.lib, "rmsnorm_parallelized_fp16" if h else "rmsnorm_parallelized_fp32")
+        fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int]; fn.restype = None
+        ptr = lambda a: a.arg if not isinstance(a.arg, np.ndarray) else a.arg.ctypes.data
+        fn(ptr(O), ptr(V), ptr(W_), ptr(B), n)
+        if not self.is_ref:
+            self.pkg.check(self.lib)
+        r["rmsnorm"] = O.get().copy()
+        # --- SwiGLU, vector softmax
+        G1, G2, GO = self.t(v), self.t(w), self.zeros(n)
+        ga = self.args(self.sname("swiglu_args"), in1=G1, in2=G2, out=GO, dim=n)
+        self.call(self.fname("pulp_swiglu_fp32_cl"), ga); r["swiglu"] = GO.get().copy()
+        fn = getattr(self.lib, "pulp_vector_softmax_fp16" if h else "pulp_vector_softmax_fp32")
+        fn.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_uint]; fn.restype = None
+        fn(ptr(GO), ptr(V), ptr(B), n)
+        if not self.is_ref:
+            self.pkg.check(self.lib)
+        r["vsoftmax"] = GO.get().copy()
+        # --- pieces of the softmax
+        MX = self.zeros(8)
+        ma = self.args(self.sname("max_args"), input=V, H=1, W=n, maxes=MX)
+        self.call(self.fname("pulp_max_fp32_cl"), ma); r["vmax"] = MX.get()[:1].copy()
+        EO, ES = self.zeros(n), self.zeros(8)
+        ea = self.args(self.sname("vector_exp_sum_args"), input=V, sums=ES, output=EO, dim=n, max=float(v.max()))
+        self.call("vector_exp_sum_fp16_cl" if h else "vector_exp_sum_fp32_cl", ea); r["vexp"] = EO.get().copy(); r["vexp_sum"] = ES.get()[:1].copy()
+        D = self.t(v)
+        da = self.args(self.sname("div_args"), input=D, n=1.7, dim=n)
+        self.call(self.fname("pulp_div_fp32_cl"), da); r["vdiv"] = D.get().copy()
+        A, Bm = i["A"], i["B"]; Hh, Ww = A.shape
+        AA, BB, SS, OO = self.t(A), self.t(Bm), self.zeros(Hh), self.zeros(Hh, Ww)
+        o1 = self.args(self.sname("sm_bw_op_1_args"), A=AA, B=BB, S=SS, H=Hh, W=Ww)
+        self.call(nm("pulp_sm_bw_op_1"), o1); r["op1"] = SS.get().copy()
+        o2 = self.args(self.sname("sm_bw_op_2_args"), A=AA, B=BB, S=SS, output=OO, H=Hh, W=Ww)
+        self.call(nm("pulp_sm_bw_op_2"), o2); r["op2"] = OO.get().copy()
+        if not h:
+            sq = i["sq"]; d = sq.shape[0]
+            SQ, SM, SO, SU = self.t(sq), self.t(sq.max(axis=1)), self.zeros(d, d), self.zeros(d)
+            sha = self.args("shift_sum_args", input=SQ, sums=SU, output=SO, dim=d, dim2=d, maxes=SM)
+            self.call("pulp_shift_sum_fp32_cl", sha); r["shift"] = SO.get().copy(); r["shift_sum"] = SU.get().copy()
+        return r
+
     def transpose(self, x, axes):
         X, O = self.t(x), self.zeros(x.size)
         dims = (ctypes.c_int * x.ndim)(*x.shape); ax = (ctypes.c_int * x.ndim)(*axes)

@@ -334,5 +334,101 @@ class _IDX(object):
                     badd=o.broadcast_add(i["a"], i["b"]), pad=o.pad(i["p"], 1, 1, 1, 1))
 
 
+def family_oracle(i, with_shift=True):
+    """numpy float32 restatement of the element-wise family, loop for loop where a sum's order matters
+    [ref: lib/sources/pulp_losses_fp32.c:140-365, pulp_pooling_fp32.c:123-237, pulp_nonorm_fp32.c:30-58,
+    pulp_rmsnorm_fp32.c:29-95, pulp_act_fp32.c:651-712, pulp_train_utils_fp32.c:987-1264, :1730-1756]"""
+    f = np.float32
+    r = {}
+    y, t = i["y"].ravel(), i["t"].ravel(); n = y.size
+    mean = f(1.0) / f(n)
+    loss = f(0)
+    for k in range(n):
+        loss = f(loss + f(mean * abs(f(t[k] - y[k]))))
+    d = (y - t).astype(f)
+    r["l1"] = np.array([loss], f); r["l1_dy"] = (np.sign(d) * mean).astype(f).reshape(i["y"].shape)
+    c = f(f(i["alpha"][0]) * np.abs(d).max())
+    loss = f(0)
+    for k in range(n):
+        v = abs(d[k])
+        loss = f(loss + (v if v < c else f(f(f(v * v) - f(c * c)) / f(f(2) * c))))
+    r["berhu"] = np.array([f(loss * mean)], f)
+    r["berhu_dy"] = np.where(np.abs(d) < c, np.sign(d) * mean, f(mean) * d / c).astype(f).reshape(i["y"].shape)
+    for tag, x, g, (Hk, Wk, sh, sw) in (("mp2", i["px"], i["pdy2"], (2, 2, 2, 2)), ("mp3", i["pxt"], i["pdy3"], (3, 3, 1, 1))):
+        C, H, W = x.shape
+        Ho, Wo = (H - Hk + sh) // sh, (W - Wk + sw) // sw
+        out = np.zeros((C, Ho, Wo), f); dx = np.zeros_like(x)
+        for ch in range(C):
+            for ho in range(Ho):
+                for wo in range(Wo):
+                    win = x[ch, ho * sh:ho * sh + Hk, wo * sw:wo * sw + Wk]
+                    out[ch, ho, wo] = win.max()
+                    a, b = np.unravel_index(np.argmax(win), win.shape)         # first maximum in row-major order
+                    dx[ch, ho * sh + a, wo * sw + b] += g[ch, ho, wo]
+        r[tag + "_y"] = out; r[tag + "_dx"] = dx
+    r["nonorm"] = (i["nx"] * i["nw"][None, :]).astype(f) + i["nb"][None, :]
+    v, w = i["v"], i["w"]
+    r["wscale"] = (w * (f(0.37) * v).astype(f)).astype(f)
+    ss = f(0)
+    for k in range(v.size):
+        ss = f(ss + f(v[k] * v[k]))
+    r["sumsq"] = np.array([ss], f)
+    sf = f(f(1) / np.sqrt(f(f(ss / f(v.size)) + f(1e-5)), dtype=f))
+    r["rmsnorm"] = (w * (sf * v).astype(f)).astype(f)
+    sig = (f(1) / (f(1) + np.exp(-v, dtype=f))).astype(f)
+    r["swiglu"] = ((v * sig).astype(f) * w).astype(f)
+    e = np.exp((v - v.max()).astype(f), dtype=f)
+    es = f(0)
+    for k in range(v.size):
+        es = f(es + e[k])
+    r["vsoftmax"] = (e / es).astype(f)
+    r["vmax"] = np.array([v.max()], f); r["vexp"] = e; r["vexp_sum"] = np.array([es], f)
+    r["vdiv"] = (v / f(1.7)).astype(f)
+    A, B = i["A"], i["B"]
+    S = np.zeros(A.shape[0], f)
+    for row in range(A.shape[0]):
+        acc = f(0)
+        for col in range(A.shape[1]):
+            acc = f(acc + f(A[row, col] * B[row, col]))
+        S[row] = acc
+    r["op1"] = S; r["op2"] = ((A - S[:, None]).astype(f) * B).astype(f)
+    if with_shift:
+        sq = i["sq"]; x = (sq.max(axis=1)[:, None] - sq).astype(f)
+        x2 = (x * x).astype(f); x3 = (x2 * x).astype(f); x4 = (x3 * x).astype(f); x5 = (x4 * x).astype(f)
+        p = f(1.0) - (f(0.6931471805599453) * x).astype(f)
+        p = p + ((f(0.5) * x2).astype(f) * f(0.4804530139182014)).astype(f)
+        p = p - ((f(0.16) * x3).astype(f) * f(0.3330246519889294)).astype(f)
+        p = p + ((f(0.0416) * x4).astype(f) * f(0.2308350985830834)).astype(f)
+        p = p - ((f(0.008) * x5).astype(f) * f(0.1600026977571413)).astype(f)
+        o = np.where(x >= f(3.14), f(0), p).astype(f)
+        r["shift"] = o
+        su = np.zeros(o.shape[0], f)
+        for row in range(o.shape[0]):
+            acc = f(0)
+            for col in range(o.shape[1]):
+                acc = f(acc + o[row, col])
+            su[row] = acc
+        r["shift_sum"] = su
+    return r
+
+
+@case("elementwise_family", 1e-5)
+class _Family(object):
+    @staticmethod
+    def inputs(rng):
+        g = lambda *s: rng.standard_normal(s).astype(F)
+        pxt = np.round(2 * g(3, 7, 6)).astype(F) / 2                       # many equal values: ties inside overlapping windows
+        return dict(y=g(9, 7), t=g(9, 7), alpha=np.array([0.2], F), px=g(3, 8, 6), pdy2=g(3, 4, 3), pxt=pxt, pdy3=g(3, 5, 4),
+                    nx=g(11, 24), nw=g(24), nb=g(24), v=(1.5 * g(203)).astype(F), w=g(203), A=g(7, 33), B=g(7, 33), sq=(2 * g(12, 12)).astype(F))
+
+    @staticmethod
+    def abi(r, i):
+        return r.family(i)
+
+    @staticmethod
+    def oracle(o, i):
+        return family_oracle(i)
+
+
 def case_seed(name):
     return sum(ord(c) * (k + 1) for k, c in enumerate(name)) % (2 ** 31)

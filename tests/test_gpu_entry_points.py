@@ -362,3 +362,35 @@ def test_cluster_bringup_runs_a_task_on_the_gpu(pkg):
     padded convolution runs through the host-pointer path and its checksum matches numpy"""
     import test_abi_cpu
     test_abi_cpu.test_cluster_bringup_links_and_runs(pkg)
+
+
+def test_elementwise_family_fp16(pkg, gpulib):
+    """fp16 twins of L1 / berHu, max pooling, NoNorm, RMS norm, SwiGLU, vector softmax and the softmax pieces against the
+    float32 restatement on fp16-representable inputs; host-pointer and device-pointer calls give the same bits"""
+    import golden_cases
+    name, make_inputs, _, _, _ = [c for c in golden_cases.CASES if c[0] == "elementwise_family"][0]
+    i = make_inputs(np.random.default_rng(golden_cases.case_seed(name)))
+    i = {k: v.astype(np.float16).astype(np.float32) for k, v in i.items()}
+    want = golden_cases.family_oracle(i, with_shift=False)
+    r = AbiRunner(pkg, gpulib, device=True, half=True)
+    got = r.family(i)
+    r.close()
+    for k, w in want.items():
+        tol = 3e-2 if k in ("berhu", "berhu_dy", "mp3_dx", "rmsnorm") else 1e-2      # a rounded threshold c / sums of rounded terms
+        assert_close(got[k].astype(np.float32), w, tol, "fp16 family %s" % k)
+    rh = AbiRunner(pkg, gpulib, device=False, half=True)
+    host = rh.family(i)
+    rh.close()
+    for k in want:
+        assert_exact(host[k], got[k], "fp16 family %s: host pointers vs device pointers" % k)
+
+
+def test_maxpool_rejects_a_wrong_output_size(pkg, gpulib):
+    r = AbiRunner(pkg, gpulib, device=True)
+    X, dX, O, dO = r.zeros(2, 8, 8), r.zeros(2, 8, 8), r.zeros(2, 3, 3), r.zeros(2, 3, 3)
+    pa = r.args("pool_args", input=r.blob(X, dX, C=2, H=8, W=8), output=r.blob(O, dO, C=2, H=3, W=3), Hker=2, Wker=2, Hstride=2, Wstride=2)
+    import ctypes
+    gpulib.pulp_maxpool_fp32_fw_cl(ctypes.byref(pa))
+    assert gpulib.trainlib_last_error() == 3          # TL_ERR_BAD_ARGS
+    gpulib.trainlib_clear_error()
+    r.close()
