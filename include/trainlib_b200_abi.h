@@ -652,6 +652,14 @@ void cast_fp32_tensor_to_fp16(void *cast_32t16_args);
 void pulp_scalar_mul_fp16_cl(void *scalar_mul_args_fp16);
 void mm_bias_add_transposed_fp16(void *mm_bias_add_args_fp16);
 
+/* ---- the depthwise workers behind pulp_conv_dw_* [ref: pulp_conv_naive_fp32.h:27-45; pulp_conv_naive_fp32.c:29-330;
+ * pulp_conv_naive_fp16.h:27-45].  The fp32 ones read stride and padding from kernel_DW_args; the fp16 struct has only
+ * the three blobs (stride 1, no padding).  weight_grad writes weights.diff, input_grad writes input.diff. */
+struct kernel_DW_args_fp16 { struct blob_fp16 *input; struct blob_fp16 *weights; struct blob_fp16 *output; };
+void dw_kernel_forward(void *kernel_DW_args);           void dw_kernel_forward_fp16(void *kernel_DW_args_fp16);
+void dw_kernel_weight_grad(void *kernel_DW_args);       void dw_kernel_weight_grad_fp16(void *kernel_DW_args_fp16);
+void dw_kernel_input_grad(void *kernel_DW_args);        void dw_kernel_input_grad_fp16(void *kernel_DW_args_fp16);
+
 /* ---- the rest of the element-wise family [ref: pulp_losses_fp32.h:79-121, pulp_pooling_fp32.h:64-70, pulp_nonorm_fp32.h:53,
  * pulp_rmsnorm_fp32.h:33-49, pulp_act_fp32.h:274-281; the fp16 twins in the _fp16 headers].  Losses and pooling work on
  * every stream in streams mode like their MSE / average-pool siblings.  The "one value per core" outputs of the

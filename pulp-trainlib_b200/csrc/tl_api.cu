@@ -416,6 +416,25 @@ template <class F> void dw_impl(void *args, int step)
     else { const T *dy = sc.in(a->output->diff, ny), *w = sc.in(a->coeff->data, nw); T *dx = sc.out(a->input->diff, nx); if (sc.ok()) conv_ig<T>(sc, g, dy, w, dx); }
 }
 
+// the forkable workers of the depthwise layer: same kernels, geometry from kernel_DW_args
+// [ref: lib/sources/pulp_conv_naive_fp32.c:29-330]
+template <class T, class A> void dwk_impl(void *args, int step, int sh, int sw, int pl, int pr, int pu, int pd)
+{
+    auto *a = (A *)args;
+    TL_REQUIRE(a && a->input && a->weights && a->output, "dw_kernel: null arguments");
+    ConvGeom g;
+    g.Cin = g.Cout = a->input->C; g.Hin = a->input->H; g.Win = a->input->W; g.Hk = a->weights->H; g.Wk = a->weights->W;
+    g.sh = sh < 1 ? 1 : sh; g.sw = sw < 1 ? 1 : sw; g.padU = pu; g.padL = pl;
+    g.Hout = a->output->H; g.Wout = a->output->W; g.n = streams(); g.depthwise = true; g.hwc = false;
+    TL_REQUIRE(g.Hout == (g.Hin - g.Hk + pu + pd) / g.sh + 1 && g.Wout == (g.Win - g.Wk + pl + pr) / g.sw + 1,
+               "dw_kernel: output blob %dx%d does not match the geometry", g.Hout, g.Wout);
+    Scope sc;
+    const size_t nx = (size_t)g.n * g.Cin * g.Hin * g.Win, ny = (size_t)g.n * g.Cin * g.Hout * g.Wout, nw = (size_t)g.Cin * g.Hk * g.Wk;
+    if (step == STEP_FW) { const T *x = sc.in((T *)a->input->data, nx), *w = sc.in((T *)a->weights->data, nw); T *y = sc.out((T *)a->output->data, ny); if (sc.ok()) conv_fw<T>(sc, g, x, w, (const T *)nullptr, y); }
+    else if (step == STEP_WGT_GRAD) { const T *x = sc.in((T *)a->input->data, nx), *dy = sc.in((T *)a->output->diff, ny); T *dw = sc.out((T *)a->weights->diff, nw); if (sc.ok()) conv_wg<T>(sc, g, x, dy, dw, (T *)nullptr); }
+    else { const T *dy = sc.in((T *)a->output->diff, ny), *w = sc.in((T *)a->weights->data, nw); T *dx = sc.out((T *)a->input->diff, nx); if (sc.ok()) conv_ig<T>(sc, g, dy, w, dx); }
+}
+
 // ------------------------------------------------------------------ linear
 // W is [out x in]; y = W x (+ b); dW = dy (x) x, db = dy; dx = W^T dy
 // [ref: lib/sources/pulp_linear_fp32.c:25-267].  With n streams the three become GEMMs.
@@ -997,6 +1016,13 @@ TL_EXPORT void pulp_conv_pw_fp16_bw_cl(void *a)
     if (c->skip_in_grad == 0) pulp_conv_pw_fp16_bw_input_grads_cl(a);
 }
 
+#define DWK32(step) do { auto *k = (kernel_DW_args *)a; if (k) dwk_impl<float, kernel_DW_args>(a, step, k->stride_h, k->stride_w, k->Lpad, k->Rpad, k->Upad, k->Dpad); } while (0)
+TL_EXPORT void dw_kernel_forward(void *a) { DWK32(STEP_FW); }
+TL_EXPORT void dw_kernel_weight_grad(void *a) { DWK32(STEP_WGT_GRAD); }
+TL_EXPORT void dw_kernel_input_grad(void *a) { DWK32(STEP_IN_GRAD); }
+TL_EXPORT void dw_kernel_forward_fp16(void *a) { dwk_impl<__half, kernel_DW_args_fp16>(a, STEP_FW, 1, 1, 0, 0, 0, 0); }
+TL_EXPORT void dw_kernel_weight_grad_fp16(void *a) { dwk_impl<__half, kernel_DW_args_fp16>(a, STEP_WGT_GRAD, 1, 1, 0, 0, 0, 0); }
+TL_EXPORT void dw_kernel_input_grad_fp16(void *a) { dwk_impl<__half, kernel_DW_args_fp16>(a, STEP_IN_GRAD, 1, 1, 0, 0, 0, 0); }
 TL_PAIR(pulp_conv_dw_fp32_fw_cl, pulp_conv_dw_fp16_fw_cl, dw_impl<F32>(a, STEP_FW), dw_impl<F16>(a, STEP_FW))
 TL_PAIR(pulp_conv_dw_fp32_bw_param_grads_cl, pulp_conv_dw_fp16_bw_param_grads_cl, dw_impl<F32>(a, STEP_WGT_GRAD), dw_impl<F16>(a, STEP_WGT_GRAD))
 TL_PAIR(pulp_conv_dw_fp32_bw_input_grads_cl, pulp_conv_dw_fp16_bw_input_grads_cl, dw_impl<F32>(a, STEP_IN_GRAD), dw_impl<F16>(a, STEP_IN_GRAD))
@@ -1272,6 +1298,7 @@ TL_EXPORT int verify_tensor(float *tensor_out, float *tensor_ref, int size, floa
 // ---- table of library workers for pi_cl_team_fork
 typedef void (*worker_t)(void *);
 static const worker_t g_workers[] = {
+    dw_kernel_forward, dw_kernel_weight_grad, dw_kernel_input_grad, dw_kernel_forward_fp16, dw_kernel_weight_grad_fp16, dw_kernel_input_grad_fp16,
     pulp_L1Loss, pulp_L1Loss_backward, pulp_L1Loss_fp16, pulp_L1Loss_backward_fp16, pulp_berHuLoss, pulp_berHuLoss_backward,
     pulp_berHuLoss_fp16, pulp_berHuLoss_backward_fp16, pulp_maxpool_fp32_fw_cl, pulp_maxpool_fp32_bw_cl, pulp_maxpool_fp16_fw_cl,
     pulp_maxpool_fp16_bw_cl, pulp_nonorm_fp32_fw_cl, pulp_nonorm_fp16_fw_cl, weighted_scaling_fp32_cl, weighted_scaling_fp16_cl,

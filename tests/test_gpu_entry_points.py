@@ -394,3 +394,31 @@ def test_maxpool_rejects_a_wrong_output_size(pkg, gpulib):
     assert gpulib.trainlib_last_error() == 3          # TL_ERR_BAD_ARGS
     gpulib.trainlib_clear_error()
     r.close()
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_depthwise_workers_by_name(pkg, gpulib, oracle, half):
+    """dw_kernel_forward / weight_grad / input_grad (kernel_DW_args): the fp32 struct carries stride and padding, the fp16 one
+    only the blobs (stride 1, no padding)"""
+    rng = seeded(41)
+    C, H, W, k = 5, 11, 9, 3
+    sh, pad = (1, 0) if half else (2, 1)
+    g = dict(geom(C, H, W, C, k, stride=sh, pad=pad))
+    Ho, Wo = out_hw(g)
+    cast = (lambda a: a.astype(np.float16).astype(np.float32)) if half else (lambda a: a)
+    x, w, dy = cast(rng.standard_normal((C, H, W)).astype(np.float32)), cast(rng.standard_normal((C, k, k)).astype(np.float32)), cast(rng.standard_normal((C, Ho, Wo)).astype(np.float32))
+    r = AbiRunner(pkg, gpulib, device=True, half=half)
+    X, dX, Wt, dW, Y, dY = r.t(x), r.zeros(C, H, W), r.t(w), r.zeros(C, k, k), r.zeros(C, Ho, Wo), r.t(dy)
+    blobs = dict(input=r.blob(X, dX, C=C, H=H, W=W), weights=r.blob(Wt, dW, C=C, H=k, W=k, dim=w.size), output=r.blob(Y, dY, C=C, H=Ho, W=Wo))
+    if half:
+        args = r.args("kernel_DW_args_fp16", **blobs)
+    else:
+        args = r.args("kernel_DW_args", stride_h=sh, stride_w=sh, Lpad=pad, Rpad=pad, Upad=pad, Dpad=pad, **blobs)
+    sfx = "_fp16" if half else ""
+    for fn in ("dw_kernel_forward", "dw_kernel_weight_grad", "dw_kernel_input_grad"):
+        r.call(fn + sfx, args)
+    tol = FP16_TOL if half else FP32_TOL
+    assert_close(Y.get().astype(np.float32), oracle.dw_fw(x, w, g), tol, "dw_kernel_forward")
+    assert_close(dW.get().astype(np.float32), oracle.dw_wg(x, dy, g), tol, "dw_kernel_weight_grad")
+    assert_close(dX.get().astype(np.float32), oracle.dw_ig(dy, w, g), tol, "dw_kernel_input_grad")
+    r.close()
