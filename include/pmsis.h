@@ -26,8 +26,25 @@ extern "C" {
 #define PI_L2
 #define PI_CL_DMA_DIR_EXT2LOC 1
 #define PI_CL_DMA_DIR_LOC2EXT 0
+/* performance-counter events named by the reference's stats.h (tools/TrainLib_Deployer/deployer_utils/srcfiles/stats.h:57-75);
+ * only the two cycle counters have a meaning here, the others read 0 */
 #define PI_PERF_CYCLES 0
 #define PI_PERF_INSTR  1
+#define PI_PERF_LD_STALL 2
+#define PI_PERF_JR_STALL 3
+#define PI_PERF_IMISS 4
+#define PI_PERF_LD 5
+#define PI_PERF_ST 6
+#define PI_PERF_JUMP 7
+#define PI_PERF_BRANCH 8
+#define PI_PERF_BTAKEN 9
+#define PI_PERF_RVC 10
+#define PI_PERF_LD_EXT 12
+#define PI_PERF_ST_EXT 13
+#define PI_PERF_LD_EXT_CYC 14
+#define PI_PERF_ST_EXT_CYC 15
+#define PI_PERF_TCDM_CONT 16
+#define PI_PERF_ACTIVE_CYCLES 17
 
 #ifndef __CUDACC__
 typedef _Float16 float16alt;

@@ -56,8 +56,41 @@ void pi_cl_dma_wait(void *c);
 void pi_cl_dma_cmd_2d(uintptr_t ext, uintptr_t loc, int size, int stride, int length, int dir, pi_cl_dma_cmd_t *c);
 void pi_cl_dma_cmd(uintptr_t ext, uintptr_t loc, int size, int dir, pi_cl_dma_cmd_t *c);
 void pi_cl_dma_cmd_wait(pi_cl_dma_cmd_t *c);
+/* performance-counter events named by the reference's stats.h (tools/TrainLib_Deployer/deployer_utils/srcfiles/stats.h:57-75);
+ * only the two cycle counters have a meaning here, the others read 0 */
+#define PI_PERF_CYCLES 0
+#define PI_PERF_INSTR  1
+#define PI_PERF_LD_STALL 2
+#define PI_PERF_JR_STALL 3
+#define PI_PERF_IMISS 4
+#define PI_PERF_LD 5
+#define PI_PERF_ST 6
+#define PI_PERF_JUMP 7
+#define PI_PERF_BRANCH 8
+#define PI_PERF_BTAKEN 9
+#define PI_PERF_RVC 10
+#define PI_PERF_LD_EXT 12
+#define PI_PERF_ST_EXT 13
+#define PI_PERF_LD_EXT_CYC 14
+#define PI_PERF_ST_EXT_CYC 15
+#define PI_PERF_TCDM_CONT 16
+#define PI_PERF_ACTIVE_CYCLES 17
+void pi_perf_conf(unsigned events);
+void pi_perf_reset(void);
 void pi_perf_start(void);
 void pi_perf_stop(void);
+unsigned pi_perf_read(int event);
+/* cluster bring-up of the reference's main.c files: the task's entry function is called once */
+struct pi_device { void *config; void *data; };
+struct pi_cluster_conf { int id; int device_type; };
+struct pi_cluster_task { void (*entry)(void *); void *arg; int stack_size; int slave_stack_size; };
+void pi_cluster_conf_init(struct pi_cluster_conf *conf);
+void pi_open_from_conf(struct pi_device *device, void *conf);
+int  pi_cluster_open(struct pi_device *device);
+int  pi_cluster_close(struct pi_device *device);
+struct pi_cluster_task *pi_cluster_task(struct pi_cluster_task *task, void (*entry)(void *), void *arg);
+int  pi_cluster_send_task_to_cl(struct pi_device *device, struct pi_cluster_task *task);
+void pmsis_exit(int code);
 void *pi_l2_malloc(int n);
 void pi_l2_free(void *p, int n);
 void pi_cl_fs_read(pi_fs_file_t *f, void *b, int n, pi_cl_fs_req_t *r);

@@ -495,7 +495,11 @@ void pi_perf_conf(unsigned events) { (void)events; }
 void pi_perf_reset(void) { g_perf_ns = 0.0; }
 void pi_perf_start(void) { trainlib_timer_start(); }
 void pi_perf_stop(void) { double ms = trainlib_timer_stop_ms(); if (ms > 0) g_perf_ns += ms * 1e6; }
-unsigned pi_perf_read(int event) { (void)event; return g_perf_ns > 4294967295.0 ? 4294967295u : (unsigned)g_perf_ns; }
+unsigned pi_perf_read(int event)
+{
+    if (event != PI_PERF_CYCLES && event != PI_PERF_ACTIVE_CYCLES) return 0;      // no such counter on this device
+    return g_perf_ns > 4294967295.0 ? 4294967295u : (unsigned)g_perf_ns;
+}
 // cluster bring-up of the reference's main.c files: open = device initialisation, a task = one call of its entry function
 void pi_cluster_conf_init(struct pi_cluster_conf *conf) { if (conf) { conf->id = 0; conf->device_type = 0; } }
 void pi_open_from_conf(struct pi_device *device, void *conf) { if (device) { device->config = conf; device->data = nullptr; } }
