@@ -8,7 +8,13 @@ writes oracle/_ref/deployer/<name>/ (git-ignored; it travels to the GPU machine 
     main.c net.c net.h stats.h Makefile      as the Deployer writes them (tools/TrainLib_Deployer/deployer_utils)
     io_data.h init-defines.h                 written by the project's own utils/GM.py (PyTorch golden model)
     reference_run.txt                        stdout of the project linked against the reference's C sources
-                                             (oracle/_ref/libpulp_ref.so) and run on this host
+                                             (oracle/_ref/libpulp_ref.so) and run on this host.  The reference's fp32
+                                             Linear forward drops its bias (lib/sources/pulp_linear_fp32.c:39-55: the
+                                             worker it forks never reads matMul_args.bias), so that run does NOT pass
+                                             the project's own check against the golden model; it is kept as a record.
+                                             The acceptance test of a generated project is the project's own: the
+                                             per-epoch losses it prints beside the golden model's, and
+                                             check_post_training_output().
 
 The network is the Deployer's own default example (TrainLib_Deployer.py, NET = 0): conv2d 3x3 stride 2 with bias, ReLU,
 three depthwise + pointwise pairs with ReLU / Sigmoid / LeakyReLU between them, Linear 512 -> 2 with bias; MSE loss,
@@ -76,6 +82,9 @@ def parse_run(text):
     """numbers a run prints: outputs of the last layer before and after training, the loss of every epoch, and the bit
     patterns of the final output where the project prints them"""
     out = {"loss": [float(m) for m in re.findall(r"train_loss = ([-+0-9.eE]+|nan|inf)", text)],
+           "gm_loss": [float(m) for m in re.findall(r"\(GM: ([-+0-9.eE]+|nan|inf)\)", text)],
+           "ideal_hex": [int(h, 16) for h in re.findall(r"Ideal = [-+0-9.eE]+ \[HEX: 0x([0-9a-fA-F]+)\]", text)],
+           "mismatch": "NOT MATCHING GOLDEN MODEL" in text,
            "hex": [int(h, 16) for h in re.findall(r"Actual = [-+0-9.eE]+ \[HEX: 0x([0-9a-fA-F]+)\]", text)],
            "outputs": []}
     for block in re.findall(r"Layer \d+ output:\s*\n((?:[-+0-9.eE]+ *\n)+)", text):

@@ -165,9 +165,9 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
         }
     } else if (warp >= first_conv) {
         // ------------------------------------------------------------ converters: raw -> hi in place, lo beside it
-        // TMA writes a slot as [channel 0..7][32 pixels].  The tensor core is fastest on a K-major A operand (an MN-major
-        // tf32 operand was measured at ~130 cycles per MMA, four times slower), so each slot is transposed while it is
-        // split: pixel p gets one 32-byte row holding its 8 channels, rows 32 bytes apart, the two 16-byte halves of a
+        // TMA writes a slot as [channel 0..7][32 pixels].  The A operand is K-major (an MN-major tf32 operand, which would
+        // need no transpose, accepts a single swizzle mode and was measured no faster: ~130 cycles of issue time per MMA
+        // either way), so each slot is transposed while it is split: pixel p gets one 32-byte row holding its 8 channels, rows 32 bytes apart, the two 16-byte halves of a
         // row swapped when bit 2 of p is set (the 32-byte swizzle of the K-major layout).  One warp does one slot per
         // pass: lane = pixel reads its 8 channel values (conflict-free: lanes are consecutive floats), the warp
         // synchronises (the whole slot has been read), then hi goes back in place and lo to the second array.
