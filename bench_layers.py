@@ -173,7 +173,7 @@ class MhsaStep(_Layer):
     def roofline(self, ms, pk):
         tf = self.flops / (ms * 1e-3) / 1e12
         return {"bound": "ffma", "achieved": tf, "peak": 72.8, "unit": "TFLOP/s", "frac": tf / 72.8, "traffic": None, "peak_source": pk["source"],
-                "kernel": "attention forward + backward (strided / batched FFMA GEMMs + softmax kernels)", "algorithmic_flops": self.flops,
+                "kernel": "attention forward + backward: 15 launches (fused score-softmax-value kernel and its two backward kernels, projections and weight gradients as strided FFMA GEMMs)", "algorithmic_flops": self.flops,
                 "algorithmic_bytes": self.bytes, "us_per_step": 1e3 * ms,
                 "peak_note": "FFMA peak measured on this part (125 MAC/clk/SM); the 256^3 products stay on the FFMA tiles because their summation "
                              "order keeps the backward inside 1e-5 of the reference"}
@@ -190,7 +190,7 @@ class MobileBertBlock(_Layer):
     library's entry points on device-resident tensors (tokens row-major, [L x features]):
 
         x1 = LN(X Wbi)                       bottleneck 512 -> 128
-        x2 = LN(x1 + MHSA(x1))               L = 128, E = F = 128, 4 heads of 32 (the attention entry points work on E x L)
+        x2 = LN(x1 + MHSA(x1))               L = 128, E = F = 128, 4 heads of 32 (the MobileBERT attention entry points, token-major)
         x  = LN(x + GELU(x W1) W2)   x 4     feed-forward 128 -> 512 -> 128
         Y  = LN(X + x Wbo)                   128 -> 512
         loss = MSE(Y, target)
@@ -295,9 +295,10 @@ class MobileBertBlock(_Layer):
         return copy, add
 
     def mhsa(self, x, y):
-        """x, y: [L x E] row-major; the attention entry points want E x L, so both are transposed around the call"""
+        """x, y: [L x E] row-major (token-major), which is what the MobileBERT attention entry points take: the block's
+        bottleneck activation is both `input` (source of V) and `input_bn` (source of Q and K); no transposes around the call.
+        Wq, Wk, Wv, Wo are F x E row-major ([output feature][input feature]); all four biases are zero tensors."""
         L, E = self.shape(x); Fd, h = E, self.HEADS
-        xt, yt = self._t(x + "_T", (E, L)), self._t(y + "_T", (E, L))
         names = {}
         for n, shp in (("q", (Fd, L)), ("k", (Fd, L)), ("v", (Fd, L)), ("att", (Fd, L)), ("sm", (h, L, L))):
             names[n] = self._t("mhsa_" + n, shp)
@@ -305,22 +306,20 @@ class MobileBertBlock(_Layer):
         tmax = max(L * L, E * Fd, L * Fd, E * L)
         temp, grad, maxes, sums = self._t("mhsa_temp", (tmax,)), self._t("mhsa_grad", (L * L,)), self._t("mhsa_maxes", (L,)), self._t("mhsa_sums", (L,))
         b2 = lambda n, Hh, Ww: self.pkg.make_blob(self.keep, self.d(n), self.g(n), C=1, H=Hh, W=Ww, half=self.half)
+        nodiff = lambda n, Hh, Ww: self.pkg.make_blob(self.keep, self.d(n), None, C=1, H=Hh, W=Ww, half=self.half)
         bias = lambda: self.pkg.make_blob(self.keep, self.d(zb), self.g(zb), dim=Fd, W=Fd, half=self.half)
-        a = self.pkg.make_args(self.keep, "Mhsa_args" + self.sfx, input=b2(xt, L, E), n_heads=h, output=b2(yt, L, E),
-                               coeff_in_q=b2("Wq", Fd, E), coeff_in_k=b2("Wk", Fd, E), coeff_in_v=b2("Wv", Fd, E), coeff_out=b2("Wo", E, Fd),
-                               bias_in_q=bias(), bias_in_k=bias(), bias_in_v=bias(),
+        a = self.pkg.make_args(self.keep, "Mhsa_args" + self.sfx, input=b2(x, L, E), input_bn=nodiff(x, L, E), n_heads=h, output=b2(y, L, Fd),
+                               coeff_in_q=b2("Wq", Fd, E), coeff_in_k=b2("Wk", Fd, E), coeff_in_v=b2("Wv", Fd, E), coeff_out=b2("Wo", Fd, Fd),
+                               bias_in_q=bias(), bias_in_k=bias(), bias_in_v=bias(), bias_out=bias(),
                                q=b2(names["q"], L, Fd), k=b2(names["k"], L, Fd), v=b2(names["v"], L, Fd), attention_map=b2(names["att"], L, Fd),
                                temp_buffer=self.d(temp), grad=self.d(grad), softmax_buffer=b2(names["sm"], h, L * L), maxes=self.d(maxes), sums=self.d(sums),
                                opt_matmul_type_fw=0, opt_matmul_type_wg=0, opt_matmul_type_ig=0)
-        self._transpose(self.fw, self.d(x), self.d(xt), L, E)
-        self._call(self.fw, "pulp_mhsa_fp16_fw_cl" if self.half else "pulp_mhsa_fp32_fw_cl", a)
-        self._transpose(self.fw, self.d(yt), self.d(y), E, L)
+        t = "fp16" if self.half else "fp32"
+        self._call(self.fw, "pulp_mhsa_mobilebert_inference_%s_fw_cl" % t, a)
         bw = []
-        self._transpose(bw, self.g(y), self.g(yt), L, E)
-        zero = self.pkg.make_args(self.keep, "transp_args" + self.sfx, in_matrix=self.d("zeros_EL"), out_matrix=self.g(xt), N=1, M=E * L)
+        zero = self.pkg.make_args(self.keep, "transp_args" + self.sfx, in_matrix=self.d("zeros_EL"), out_matrix=self.g(x), N=1, M=E * L)
         self._call(bw, "transpose_matrix" + self.sfx, zero)                       # the backward accumulates into input.diff: clear it (copy of zeros)
-        self._call(bw, "pulp_mhsa_fp16_bw_cl" if self.half else "pulp_mhsa_fp32_bw_cl", a)
-        self._transpose(bw, self.g(xt), self.g(x), E, L)
+        self._call(bw, "pulp_mhsa_mobilebert_inference_%s_bw_cl" % t, a)
         return bw
 
     # ---------------------------------------------------------------- graph of the block

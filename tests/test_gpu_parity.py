@@ -557,6 +557,22 @@ def test_mobilebert_block_fp16_against_its_fp32_twin(pkg, gpulib):
     assert_close(blk.get("x1"), ((t0 - m) / np.sqrt(v + 1e-3) * w + b).astype(F), 1e-4, "bottleneck + layer norm vs numpy")
 
 
+def test_mobilebert_block_against_the_cpu_composition(pkg, gpulib, oracle):
+    """config 4's block through the fp32 entry points against the same block composed on the CPU from the oracle's
+    primitives (tests/block_oracle.py): forward activations, loss, and the gradient of every kind of parameter"""
+    import bench_layers
+    import block_oracle
+    blk = bench_layers.MobileBertBlock(pkg, gpulib, half=False)
+    blk.setup_device(); blk.step_device()
+    gpulib.trainlib_synchronize(); pkg.check(gpulib)
+    P = {n: blk.get(n) for n in blk.params}
+    acts, grads = block_oracle.run_block(oracle, P, blk.get("X"), blk.get("target"), blk.HEADS, blk.NFFN, blk.LOSS_SCALE)
+    for name, key in (("x1", "x1"), ("att", "att"), ("x2", "x2"), ("Y", "Y"), ("loss", "loss")):
+        assert_close(blk.get(name), acts[key].reshape(blk.get(name).shape), 2e-5, "block forward %s" % name)
+    for name in ("Wbo", "W2_3", "W1_0", "ln2_w", "ln2_b", "Wq", "Wk", "Wv", "Wo", "ln1_w", "Wbi", "X", "lnf_2_w"):
+        assert_close(blk.get(name, grad=True), grads[name].reshape(blk.get(name, grad=True).shape), 5e-5, "block gradient of %s" % name)
+
+
 @pytest.mark.parametrize("half", [False, True], ids=["fp32", "fp16"])
 @pytest.mark.parametrize("sa,sb", [((3, 5, 7), (3, 7, 4)), ((2, 1, 6, 5), (3, 5, 8)), ((1, 4, 9), (2, 3, 1, 9, 2)), ((4, 64, 96), (1, 96, 80)), ((70, 33), (33, 9))])
 def test_mm_broadcast(run, oracle, sa, sb, half):
