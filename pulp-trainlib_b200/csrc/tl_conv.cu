@@ -886,17 +886,19 @@ template <class T> static bool try_tc_wg(Scope &, const ConvGeom &, const T *, c
 template <> bool try_tc_wg<float>(Scope &sc, const ConvGeom &g, const float *x, const float *dy, float *dw)
 {
     if (gemm_path() == 1 || g.depthwise) return false;
-    if (!(g.Hk == 3 && g.Wk == 3 && g.padL == 1 && g.padU == 1 && g.sh == 1 && g.sw == 1 && g.Hout == g.Hin && g.Wout == g.Win)) return false;
+    if (!(g.Hk == 3 && g.Wk == 3 && g.padL == 1 && g.padU == 1 && g.sh == g.sw && (g.sh == 1 || g.sh == 2))) return false;
+    if (g.Hin != g.Hout * g.sh || g.Win != g.Wout * g.sw) return false;
     const long long work = (long long)g.n * g.Hout * g.Wout * g.Cout * g.Cin * 9;
     // Measured at 4096 streams: 2.2x (32 channels) and 2.5x (64) faster than the register-tiled FFMA kernel, no gain at 16
-    // channels, where an MMA is too small (N = 96) to pay for its issue and operand-fetch cost.
-    if (gemm_path() != 2 && (work < (1ll << 28) || g.Cin < 32)) return false;
+    // channels with stride 1, where M = (kh, ci) fills 48 of the 128 rows of an MMA.  Stride 2 doubles the rows per
+    // channel (even and odd pixels), so it pays from 16 channels on.
+    if (gemm_path() != 2 && (work < (1ll << 28) || g.Cin < (g.sh == 2 ? 16 : 32))) return false;
     int groups = 0;
-    if (!conv_wgt_run(x, dy, nullptr, sm_count(), &groups, g.n, g.Cin, g.Cout, g.Hin, g.Win, true)) return false;
+    if (!conv_wgt_run(x, dy, nullptr, sm_count(), &groups, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, true)) return false;
     const long long nw = (long long)g.Cout * g.Cin * 9;
     float *part = sc.scratch<float>((size_t)groups * nw);
     if (!part) return false;
-    if (!conv_wgt_run(x, dy, part, groups, &groups, g.n, g.Cin, g.Cout, g.Hin, g.Win, false)) return false;
+    if (!conv_wgt_run(x, dy, part, groups, &groups, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, false)) return false;
     TL_LAUNCH((reduce_partials_kernel<float>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
     return true;
 }

@@ -21,6 +21,14 @@
 // own accumulators, and the epilogue adds the sets in a fixed order and writes the CTA's partial dW, which
 // reduce_partials_kernel sums over the CTAs (fixed order: bit-reproducible).
 //
+// Stride 2 (3x3, pad 1, input rows twice as long as dY rows): X[2y + a - 1][2x + b - 1].  The converters de-interleave
+// every input row into its even and odd pixels (two slots E and O per row and channel group, same 32-position K layout
+// as dY: P streams of W output pixels), so that b = 1 pairs E[x] with dY[x], b = 2 pairs O[x] with dY[x] and b = 0
+// pairs O[x - 1] with dY[x], i.e. O[x] with the copy dY[x + 1].  M = (input row, parity, ci): the three input rows
+// 2y - 1, 2y, 2y + 1 of an output row are consecutive in the array [input row][parity][channel group], and moving to
+// the next output row moves the descriptor by TWO input rows.  N = two copies of dY (x, x + 1).  One of the four
+// (parity, copy) blocks, E with dY[x + 1], is computed and not used.
+//
 // Replaces the im2col + mm lowering of the weight gradient [ref: lib/sources/pulp_conv2d_fp32.c:294-333] and the
 // naive kernel [ref: lib/sources/pulp_conv_naive_fp32.c:302-408].
 #include "tl_kernels.h"
@@ -31,9 +39,11 @@ namespace tl {
 using namespace tc;
 
 struct WgtParams {
-    int n, Cin, Cout, H, W, P;
+    int n, Cin, Cout, H, W, P;      // H, W: rows and row length of dY; P = 32 / W streams side by side in a 32-pixel slot
     int cigs, cogs;                 // 8-channel groups of X and dY
-    int T;                          // dY rows per tile (X rows: T + 2)
+    int s2;                         // 1: stride-2 convolution (see the note on strides in the header comment)
+    int xg, ncopy;                  // 8-row groups of one X row in the operand array (cigs, or 2 * cigs for stride 2); shifted dY copies (3 or 2)
+    int T;                          // dY rows per tile (X rows: T + 2, or 2T + 1 for stride 2)
     int MB, KS, stack;              // M-blocks (16 groups each), k-step split, [hi|lo] stacked in N
     int DC;                         // accumulator columns per (set, M-block)
     int NR, NC;                     // stages of the raw ring (TMA -> converters) and of the operand ring (converters -> MMAs)
@@ -83,8 +93,9 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const int XS = p.T + 2;                         // X row slots per stage
-    const uint32_t x_row_bytes = (uint32_t)p.cigs * WGT_SLOT, dyc_row_bytes = 6u * p.cogs * WGT_SLOT;
+    const int XS = p.s2 ? 2 * p.T + 1 : p.T + 2;    // X rows per stage
+    const uint32_t x_row_bytes = (uint32_t)p.xg * WGT_SLOT, dyc_row_bytes = 2u * p.ncopy * p.cogs * WGT_SLOT;
+    const int rowstep = p.s2 ? 2 : 1;               // X rows per dY row
     const uint32_t xraw_bytes = (uint32_t)XS * x_row_bytes;
 
     if (warp == tma_warp) {
@@ -97,7 +108,7 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 const int s0 = (t / p.tiles_per_image) * p.P, y0 = (t % p.tiles_per_image) * p.T;
                 unsigned char *rb = raws + (size_t)rs * p.raw_bytes;
                 mbar_arrive_expect_tx(&raw_full[rs], p.raw_bytes);
-                tma_load_4d(rb, &tmap_x, &raw_full[rs], 0, s0, 0, y0 - 1);
+                tma_load_4d(rb, &tmap_x, &raw_full[rs], 0, s0, 0, rowstep * y0 - 1);
                 tma_load_4d(rb + xraw_bytes, &tmap_dy, &raw_full[rs], 0, s0, 0, y0);
             }
         }
@@ -120,7 +131,25 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             unsigned char *cb = conv + (size_t)cs * p.conv_bytes;
             const int nx = XS * p.cigs, ndy = p.T * p.cogs;
             for (int sl = warp; sl < nx + ndy; sl += WGT_CONV_WARPS) {
-                if (sl < nx) {
+                if (sl < nx && p.s2) {
+                    // a raw row of a channel = P streams x 2W pixels = 64 floats; 8 channels = 2 KB.  Even pixels go to slot E,
+                    // odd pixels to slot O of (row, channel group); each in hi and lo.
+                    const int row = sl / p.cigs, cig = sl % p.cigs;
+                    const float4 *r4 = reinterpret_cast<const float4 *>(rb + (size_t)sl * 2 * WGT_SLOT);
+                    unsigned char *eb = cb + (size_t)((row * 2 + 0) * p.cigs + cig) * WGT_SLOT, *ob = cb + (size_t)((row * 2 + 1) * p.cigs + cig) * WGT_SLOT;
+#pragma unroll
+                    for (int half = 0; half < 2; half++) {
+                        const int R = R0 + 4 * half, dst = half ? d1 : d0;
+                        const float4 v0 = r4[R * 16 + 2 * q], v1 = r4[R * 16 + 2 * q + 1];
+                        uint32_t eh0, eh1, eh2, eh3, el0, el1, el2, el3, oh0, oh1, oh2, oh3, ol0, ol1, ol2, ol3;
+                        split_tf32_fast(v0.x, eh0, el0); split_tf32_fast(v0.z, eh1, el1); split_tf32_fast(v1.x, eh2, el2); split_tf32_fast(v1.z, eh3, el3);
+                        split_tf32_fast(v0.y, oh0, ol0); split_tf32_fast(v0.w, oh1, ol1); split_tf32_fast(v1.y, oh2, ol2); split_tf32_fast(v1.w, oh3, ol3);
+                        reinterpret_cast<float4 *>(eb)[dst] = make_float4(__uint_as_float(eh0), __uint_as_float(eh1), __uint_as_float(eh2), __uint_as_float(eh3));
+                        reinterpret_cast<float4 *>(eb + p.xh_bytes)[dst] = make_float4(__uint_as_float(el0), __uint_as_float(el1), __uint_as_float(el2), __uint_as_float(el3));
+                        reinterpret_cast<float4 *>(ob)[dst] = make_float4(__uint_as_float(oh0), __uint_as_float(oh1), __uint_as_float(oh2), __uint_as_float(oh3));
+                        reinterpret_cast<float4 *>(ob + p.xh_bytes)[dst] = make_float4(__uint_as_float(ol0), __uint_as_float(ol1), __uint_as_float(ol2), __uint_as_float(ol3));
+                    }
+                } else if (sl < nx) {
                     const float4 *r4 = reinterpret_cast<const float4 *>(rb + (size_t)sl * WGT_SLOT);
                     float4 *h = reinterpret_cast<float4 *>(cb + (size_t)sl * WGT_SLOT), *l = reinterpret_cast<float4 *>(cb + p.xh_bytes + (size_t)sl * WGT_SLOT);
                     const float4 v0 = r4[lane], v1 = r4[lane + 32];
@@ -146,10 +175,11 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                         const int dst = half ? d1 : d0;
 #pragma unroll
                         for (int b = 0; b < 3; b++) {
+                            if (b >= p.ncopy) break;                 // stride 2 needs dY[x + 1] and dY[x] only
                             uint32_t h0, h1, h2, h3, l0, l1, l2, l3;
                             split_tf32_fast(sh[b][0], h0, l0); split_tf32_fast(sh[b][1], h1, l1); split_tf32_fast(sh[b][2], h2, l2); split_tf32_fast(sh[b][3], h3, l3);
-                            float4 *hh = reinterpret_cast<float4 *>(crow + (size_t)((0 * 3 + b) * p.cogs + cog) * WGT_SLOT);
-                            float4 *ll = reinterpret_cast<float4 *>(crow + (size_t)((1 * 3 + b) * p.cogs + cog) * WGT_SLOT);
+                            float4 *hh = reinterpret_cast<float4 *>(crow + (size_t)((0 * p.ncopy + b) * p.cogs + cog) * WGT_SLOT);
+                            float4 *ll = reinterpret_cast<float4 *>(crow + (size_t)((1 * p.ncopy + b) * p.cogs + cog) * WGT_SLOT);
                             hh[dst] = make_float4(__uint_as_float(h0), __uint_as_float(h1), __uint_as_float(h2), __uint_as_float(h3));
                             ll[dst] = make_float4(__uint_as_float(l0), __uint_as_float(l1), __uint_as_float(l2), __uint_as_float(l3));
                         }
@@ -167,11 +197,11 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
                 const long long nw = (long long)p.Cout * p.Cin * 9;
                 float *out = p.part + (long long)blockIdx.x * nw;
-                const int NBc = 3 * p.Cout;                            // columns of one product block
+                const int NBc = p.ncopy * p.Cout;                      // columns of one product block
                 for (int m = 0; m < p.MB; m++) {
                     const int grp = m * 16 + (warp * 32 + lane) / 8, ci8 = lane & 7;
-                    const int a = grp / p.cigs, cig = grp % p.cigs, ci = cig * 8 + ci8;
-                    const bool valid = grp < 3 * p.cigs;
+                    const int a = grp / p.xg, par = (grp % p.xg) / p.cigs, cig = grp % p.cigs, ci = cig * 8 + ci8;
+                    const bool valid = grp < 3 * p.xg;
                     for (int c0 = 0; c0 < NBc; c0 += 16) {
                         float acc[16];
 #pragma unroll
@@ -189,8 +219,10 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
 #pragma unroll
                             for (int i = 0; i < 16; i++) {
                                 const int col = c0 + i, b = col / p.Cout, co = col % p.Cout;
-                                // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b
-                                out[((long long)co * p.Cin + ci) * 9 + a * 3 + b] = acc[i];
+                                // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b;
+                                // stride 2: even pixels with dY[x] are column 1, odd pixels with dY[x] column 2, with dY[x + 1] column 0
+                                const int kw = !p.s2 ? b : (par == 0 ? (b == 1 ? 1 : -1) : (b == 1 ? 2 : 0));
+                                if (kw >= 0) out[((long long)co * p.Cin + ci) * 9 + a * 3 + kw] = acc[i];
                             }
                         }
                     }
@@ -202,7 +234,7 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
         const int j = warp - first_issuer;
         if (lane == 0 && j < NISS) {
             const int m = j % p.MB, qs = j / p.MB;
-            const uint32_t n_wide = (uint32_t)(p.stack ? 6 * p.Cout : 3 * p.Cout), n_nb = (uint32_t)(3 * p.Cout);
+            const uint32_t n_nb = (uint32_t)(p.ncopy * p.Cout), n_wide = p.stack ? 2u * n_nb : n_nb;
             const uint32_t idesc_wide = mma_idesc(FMT_TF32, 128, n_wide), idesc_nb = mma_idesc(FMT_TF32, 128, n_nb);
             const uint64_t tmpl = smem_desc_kmajor_sw128(0u, WGT_SLOT);            // K-major rows of 128 bytes (32 pixels), a k-step advances 32 bytes inside the row
             const uint32_t hiword = (uint32_t)(tmpl >> 32), loword = (uint32_t)tmpl;
@@ -215,7 +247,7 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 if (!wait_or_abort(&conv_full[cs], (k / p.NC) & 1, abort_flag, p.status, 23, 0u)) { ok = false; break; }
                 const uint32_t sb = conv_u32 + (uint32_t)cs * p.conv_bytes;
                 for (int r = 0; r < p.T; r++) {
-                    const uint32_t a16 = (sb + (uint32_t)r * x_row_bytes + (uint32_t)m * 16u * WGT_SLOT) >> 4;        // rows r, r+1, r+2 of X = input rows y-1, y, y+1
+                    const uint32_t a16 = (sb + (uint32_t)(r * rowstep) * x_row_bytes + (uint32_t)m * 16u * WGT_SLOT) >> 4;   // three consecutive rows of X = input rows y-1, y, y+1 (2y-1, 2y, 2y+1)
                     const uint32_t b16 = (sb + 2 * p.xh_bytes + (uint32_t)r * dyc_row_bytes) >> 4;
                     for (int kk = 0; kk < 4; kk++, kstep++) {
                         if ((int)(kstep % (uint32_t)p.KS) != qs) continue;
@@ -225,7 +257,7 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                             mma_tf32_ss(d_addr, a_hi, b_hi, idesc_wide, acc);
                             mma_tf32_ss(d_addr, a_lo, b_hi, idesc_nb, 1u);
                         } else {
-                            const uint64_t b_lo = ((uint64_t)hiword << 32) | (loword + b16 + ((3u * p.cogs * WGT_SLOT) >> 4) + 2u * kk);
+                            const uint64_t b_lo = ((uint64_t)hiword << 32) | (loword + b16 + (((uint32_t)p.ncopy * p.cogs * WGT_SLOT) >> 4) + 2u * kk);
                             mma_tf32_ss(d_addr, a_hi, b_hi, idesc_nb, acc);
                             mma_tf32_ss(d_addr, a_hi, b_lo, idesc_nb, 1u);
                             mma_tf32_ss(d_addr, a_lo, b_hi, idesc_nb, 1u);
@@ -250,36 +282,46 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 void *tc_encode_tiled_fn();
 int *tc_status_word();
 
-// Weight gradient on the tensor cores for 3x3 / stride 1 / pad 1 on 32-, 16- or 8-pixel rows with channel counts that are
-// multiples of 8 (C_out a multiple of 16).  Writes `*groups` partial results of Cout*Cin*9 floats each into `part`
-// (capacity part_groups); the caller sums them.  false = geometry not covered (nothing launched).
-bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, bool dry_run)
+// Weight gradient on the tensor cores for 3x3 / pad 1 with stride 1 or 2 and channel counts that are multiples of 8
+// (C_out a multiple of 16).  H x W is the size of the dY planes (rows of 32, 16 or 8 pixels; stride 2: 16 or 8), the X
+// planes are stride times as large.  Writes `*groups` partial results of Cout*Cin*9 floats each into `part` (capacity
+// part_groups); the caller sums them.  false = geometry not covered (nothing launched).
+bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, int stride, bool dry_run)
 {
     EncodeTiledFn enc = (EncodeTiledFn)tc_encode_tiled_fn();
     if (!enc) return false;
+    if (stride != 1 && stride != 2) return false;
     if (W != 32 && W != 16 && W != 8) return false;
+    if (stride == 2 && W == 32) return false;                  // an input row of 64 pixels does not fit the 64-float raw row of the converter
     if (Cin % 8 != 0 || Cout % 16 != 0 || Cin > 64 || Cout > 64 || Cin < 8 || n < 1) return false;
     if ((((uintptr_t)x | (uintptr_t)dy) & 15) != 0) return false;
     WgtParams p;
     p.n = n; p.Cin = Cin; p.Cout = Cout; p.H = H; p.W = W; p.P = 32 / W;
     p.cigs = Cin / 8; p.cogs = Cout / 8;
-    p.MB = ceil_div(3 * p.cigs, 16);
-    p.stack = (6 * Cout <= 256) ? 1 : 0;
-    p.DC = p.stack ? 6 * Cout : 3 * Cout;
+    p.s2 = stride == 2 ? 1 : 0;
+    p.xg = p.s2 ? 2 * p.cigs : p.cigs; p.ncopy = p.s2 ? 2 : 3;
+    p.MB = ceil_div(3 * p.xg, 16);
+    if (p.MB > WGT_MAX_ISS) return false;
+    p.stack = (2 * p.ncopy * Cout <= 256) ? 1 : 0;
+    p.DC = p.stack ? 2 * p.ncopy * Cout : p.ncopy * Cout;
     p.KS = 512 / (p.MB * p.DC);
     if (p.KS > WGT_MAX_ISS / p.MB) p.KS = WGT_MAX_ISS / p.MB;
     if (p.KS < 1) return false;
-    // Rows per tile and ring depths within 205 KB: operand stages first (up to 3, leaving room for at least 3 raw
+    // Rows per tile and ring depths within 224 KB: operand stages first (up to 3, leaving room for at least 2 raw
     // stages), the rest goes to raw stages.  Two rows per tile when that still leaves two operand stages, else one.
     bool found = false;
     size_t smem = 0;
     for (int T = 2; T >= 1 && !found; T--) {
         if (H % T != 0) continue;
-        const uint32_t raw = ((uint32_t)(T + 2) * p.cigs + (uint32_t)T * p.cogs) * WGT_SLOT;
-        const uint32_t xh = (uint32_t)(T + 2) * p.cigs * WGT_SLOT, cv = 2 * xh + 6u * T * p.cogs * WGT_SLOT;
-        const long long budget = 205 * 1024;
+        const uint32_t XS = p.s2 ? 2u * T + 1u : (uint32_t)T + 2u;
+        const uint32_t raw = (XS * p.xg + (uint32_t)T * p.cogs) * WGT_SLOT;
+        const uint32_t xh = XS * p.xg * WGT_SLOT, cv = 2 * xh + 2u * p.ncopy * T * p.cogs * WGT_SLOT;
+        // two operand stages (converting and multiplying overlap) matter more than a deep raw ring: two raw stages
+        // suffice (measured: 32 -> 32 with T = 2, two operand and two raw stages 0.19 ms against 0.25 ms with T = 1, three
+        // and three); more rows per tile (T = 4, 8) gained nothing further
+        const long long budget = 224 * 1024, min_raw = 2;
         int NC = 0;
-        for (int c = 3; c >= 1; c--) if ((long long)c * cv + 3ll * raw <= budget) { NC = c; break; }
+        for (int c = 3; c >= 1; c--) if ((long long)c * cv + min_raw * raw <= budget) { NC = c; break; }
         if (NC == 0 || (NC < 2 && T > 1)) continue;
         int NR = (int)((budget - (long long)NC * cv) / raw);
         if (NR > WGT_MAX_NR) NR = WGT_MAX_NR;
@@ -297,9 +339,10 @@ bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups,
     if (dry_run) { *groups_out = ctas; return true; }
 
     CUtensorMap tx, tdy;
-    cuuint64_t gstr_x[3] = {(cuuint64_t)W * H * Cin * 4, (cuuint64_t)W * H * 4, (cuuint64_t)W * 4};
-    cuuint64_t gdim_x[4] = {(cuuint64_t)W, (cuuint64_t)n, (cuuint64_t)Cin, (cuuint64_t)H};
-    cuuint32_t box_x[4] = {(cuuint32_t)W, (cuuint32_t)p.P, (cuuint32_t)Cin, (cuuint32_t)(p.T + 2)};
+    const int Wx = W * stride, Hx = H * stride;
+    cuuint64_t gstr_x[3] = {(cuuint64_t)Wx * Hx * Cin * 4, (cuuint64_t)Wx * Hx * 4, (cuuint64_t)Wx * 4};
+    cuuint64_t gdim_x[4] = {(cuuint64_t)Wx, (cuuint64_t)n, (cuuint64_t)Cin, (cuuint64_t)Hx};
+    cuuint32_t box_x[4] = {(cuuint32_t)Wx, (cuuint32_t)p.P, (cuuint32_t)Cin, (cuuint32_t)(p.s2 ? 2 * p.T + 1 : p.T + 2)};
     cuuint64_t gstr_y[3] = {(cuuint64_t)W * H * Cout * 4, (cuuint64_t)W * H * 4, (cuuint64_t)W * 4};
     cuuint64_t gdim_y[4] = {(cuuint64_t)W, (cuuint64_t)n, (cuuint64_t)Cout, (cuuint64_t)H};
     cuuint32_t box_y[4] = {(cuuint32_t)W, (cuuint32_t)p.P, (cuuint32_t)Cout, (cuuint32_t)p.T};
@@ -316,7 +359,7 @@ bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups,
     static bool attr_set = false;
     if (!attr_set) { cudaFuncSetAttribute(conv_wgt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; }
     TL_LAUNCH(conv_wgt_kernel, ctas, WGT_THREADS, smem, tx, tdy, p);
-    profile_add_flops(2.0 * n * Cout * Cin * 9.0 * H * W);
+    profile_add_flops(2.0 * n * Cout * Cin * 9.0 * H * W);          // H x W = the dY plane for either stride
     *groups_out = ctas;
     return true;
 }

@@ -51,7 +51,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
                  const ConvTcClass *cls = nullptr);
 int conv_tc_status();
 // tensor-core weight gradient (tl_conv_wgt.cu): partial results per CTA into `part`; false = geometry not covered
-bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, bool dry_run);
+bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, int stride, bool dry_run);
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
                                int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
 template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk, int Wk, int hwc);

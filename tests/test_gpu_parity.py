@@ -194,6 +194,18 @@ def test_conv2d_tensor_core_path(pkg, gpulib, oracle, g, n):
         for s in range(n):
             assert_close(y[s], oracle.conv2d_fw(xs[s], w, None, g), FP32_TOL, "tc fw stream %d" % s)
             assert_close(dx[s], oracle.conv2d_ig(dys[s], w, g), FP32_TOL, "tc ig stream %d" % s)
+        # the weight gradient (sum over the streams); 3x3 / pad 1 layers with stride 1 or 2 and channel counts in multiples of
+        # 8 / 16 go through the tensor-core pixel-contraction kernel when forced, which the kernel names prove
+        gpulib.trainlib_profile(1)
+        r.call("pulp_conv2d_fp32_bw_param_grads_cl", args)
+        gpulib.trainlib_profile(0)
+        assert gpulib.trainlib_tc_status() == 0, "a bounded tensor-core wait gave up: id %d" % gpulib.trainlib_tc_status()
+        names = [row[0] for row in pkg.profile_table(gpulib)]
+        eligible = (g["Hk"] == 3 and g["padU"] == 1 and g["Cin"] % 8 == 0 and g["Cout"] % 16 == 0 and g["Cin"] <= 64 and g["Cout"] <= 64
+                    and Wo in (8, 16, 32) and not (g["sh"] == 2 and Wo == 32))
+        assert any("conv_wgt_kernel" in nm for nm in names) == eligible, (names, eligible)
+        want = sum(oracle.conv2d_wg(xs[s], dys[s], g)[0].astype(np.float64) for s in range(n)).astype(F)
+        assert_close(dW.get(), want, FP32_TOL, "tc weight gradient")
         r.close()
     finally:
         gpulib.trainlib_set_streams(1); gpulib.trainlib_set_gemm_path(0)
