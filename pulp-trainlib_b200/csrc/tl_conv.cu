@@ -332,6 +332,29 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
     // strided, general filter: one launch per parity class of dX.  Pixels (sh*i + ph, sw*j + pw) only see the filter taps
     // kh = r + sh*m with r = (ph + padU) mod sh, and those taps read dY rows i + q - m with q = (ph + padU) / sh: a dense
     // stride-1 convolution of dY with an (m_max+1)-row window, written to every sh-th row of dX.  No zeros are multiplied.
+    if (g.sh == 2 && g.sw == 2 && g.Hk == 3 && g.Wk == 3 && g.padU == 1 && g.padL == 1 && g.Win == 2 * g.Wout && g.Hin == 2 * g.Hout && gemm_path() != 1) {
+        // 3x3, pad 1, stride 2: one launch per ROW parity, both column parities together (pixel pairs, contiguous output rows)
+        ConvTcClass cls[2];
+        int Ah[2], pu[2];
+        for (int ph = 0; ph < 2; ph++) {
+            const int rh = (ph + 1) % 2, qh = (ph + 1) / 2, mh = (2 - rh) / 2;
+            ConvTcClass &c = cls[ph];
+            c.kstep = 2; c.kh_r = rh; c.kh_m = mh; c.kw_r = 0; c.kw_m = 0; c.w_Hk = 3; c.w_Wk = 3;
+            c.oH = g.Hin; c.oW = g.Win; c.osy = 2; c.osx = 2; c.oy0 = ph; c.ox0 = 0; c.up = 1;
+            Ah[ph] = mh + 1; pu[ph] = mh - qh;
+        }
+        bool ok = true;
+        for (int ph = 0; ph < 2 && ok; ph++)
+            ok = pu[ph] >= 0 && conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hout, g.Wout, Ah[ph], 3, 1, 1,
+                                            pu[ph], 1, g.Cout, g.Cin, true, true, &cls[ph]);
+        if (ok) {
+            for (int ph = 0; ph < 2; ph++)
+                if (!conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, g.Hout, g.Wout, Ah[ph], 3, 1, 1,
+                                 pu[ph], 1, g.Cout, g.Cin, true, false, &cls[ph]))
+                    return false;
+            return true;
+        }
+    }
     if (g.sh == g.sw && g.sh >= 2 && g.sh <= 4 && gemm_path() != 1) {
         ConvTcClass cls[16];
         int Hc[16], Wc[16], Ah[16], Aw[16], pu[16], pl[16], ncls = 0;
@@ -344,7 +367,7 @@ template <> bool try_tc_ig<float>(Scope &sc, const ConvGeom &g, const float *dy,
                 if (mh - qh < 0 || mw - qw < 0) { ok = false; break; }
                 ConvTcClass &c = cls[ncls];
                 c.kstep = g.sh; c.kh_r = rh; c.kh_m = mh; c.kw_r = rw; c.kw_m = mw; c.w_Hk = g.Hk; c.w_Wk = g.Wk;
-                c.oH = g.Hin; c.oW = g.Win; c.osy = g.sh; c.osx = g.sw; c.oy0 = ph; c.ox0 = pw;
+                c.oH = g.Hin; c.oW = g.Win; c.osy = g.sh; c.osx = g.sw; c.oy0 = ph; c.ox0 = pw; c.up = 0;
                 Hc[ncls] = (g.Hin - ph + g.sh - 1) / g.sh; Wc[ncls] = (g.Win - pw + g.sw - 1) / g.sw;
                 Ah[ncls] = mh + 1; Aw[ncls] = mw + 1; pu[ncls] = mh - qh; pl[ncls] = mw - qw;
                 ok = conv_tc_run(sc, dy, w, (const float *)nullptr, dx, g.n, g.Cout, g.Hout, g.Wout, g.Cin, Hc[ncls], Wc[ncls], Ah[ncls], Aw[ncls], 1, 1,

@@ -48,7 +48,7 @@ struct ConvMnParams {
     int stage_bytes, nstage;
     int tiles_per_image, n_tiles;
     const float *w;                 // filters; see the operand builder for the three roles
-    int Cout_w, Cin_w, flip, cls, kstep, kh_r, kh_m, kw_r, kw_m, w_Wk, w_taps;
+    int Cout_w, Cin_w, flip, cls, up, kstep, kh_r, kh_m, kw_r, kw_m, w_Wk, w_taps;
     int oH, oW, osy, osx, oy0, ox0; // output pixel (y, x) of the grid lands at (y*osy + oy0, x*osx + ox0) of an oH x oW plane
     const float *bias;
     float *y;
@@ -70,7 +70,10 @@ static constexpr int MN_MAX_THREADS = 32 * (4 * MN_MAX_NE + MN_MAX_NI + 1 + MN_C
 //
 // status ids of this kernel's waits: 11 stage free (TMA), 12 accumulator free (issuer), 13 operand ready (issuer),
 // 14 raw data landed (converter), 16 accumulator complete (epilogue)
-template <int WK, int PADL>
+// UP (stride-2 input gradient, 3x3, pad 1, one row parity per launch): the grid is the dY plane, accumulator column b
+// holds filter column kw = b, and grid pixel j produces the TWO output pixels 2j (= T1[j]) and 2j + 1 (= T2[j] + T0[j + 1]),
+// written as one 8-byte store: whole output rows are written contiguously instead of every second pixel per launch.
+template <int WK, int PADL, bool UP = false>
 __global__ void __launch_bounds__(MN_MAX_THREADS, 1)
 conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
 {
@@ -118,7 +121,7 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
             const int n_out = blockIdx.y * p.NT + c;
             const float *src; long long kstride; int k_lim; bool row_ok;
             if (p.cls) {
-                const int kh = p.kh_r + p.kstep * (p.kh_m - a), kw = p.kw_r + p.kstep * (p.kw_m - b);
+                const int kh = p.kh_r + p.kstep * (p.kh_m - a), kw = UP ? b : p.kw_r + p.kstep * (p.kw_m - b);
                 src = p.w + (long long)n_out * p.w_taps + kh * p.w_Wk + kw; kstride = (long long)p.Cin_w * p.w_taps; k_lim = p.Cout_w; row_ok = n_out < p.Cin_w;
             } else if (!p.flip) {
                 src = p.w + (long long)n_out * p.Cin_w * p.w_taps + a * WK + b; kstride = p.w_taps; k_lim = p.Cin_w; row_ok = n_out < p.Cout_w;
@@ -279,6 +282,18 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&d_empty[dbuf]);
                     }
+                    if constexpr (UP) {
+                        // even output pixel: the centre column; odd one: column 2 of this pixel + column 0 of the next pixel of the row
+                        const bool next_in_row = x + 1 < p.W;
+                        const int nco = min(16, p.Cout - co0 - c0);
+                        float *yc = yp + (long long)c0 * plane;
+#pragma unroll
+                        for (int i = 0; i < 16; i++) {
+                            const float v = __shfl_sync(0xffffffffu, __uint_as_float(h[i]), (lane + 1) & 31);
+                            const float ev = __uint_as_float(h[16 + i]), od = __uint_as_float(h[32 + i]) + (next_in_row ? v : 0.f);
+                            if (valid && i < nco) *reinterpret_cast<float2 *>(yc + (long long)i * plane) = make_float2(ev, od);
+                        }
+                    } else {
                     // out = centre column (no shift) + the other columns fetched from the neighbouring lanes; one shuffle per
                     // shifted column and channel (the SM does one warp shuffle per clock, they are the epilogue's main cost)
                     float acc[16];
@@ -311,6 +326,7 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
                             for (int i = 0; i < 16; i++) if (i < nco) yc[(long long)i * plane] = acc[i];
                         }
                     }
+                    }   // !UP
                 }
             }
         }
@@ -340,6 +356,7 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
     if ((((uintptr_t)src) & 15) != 0 || n < 1) return false;
     if (Hk < 1 || Wk < 1 || Hk > 7 || Wk > 3 || padU < 0 || padL < 0 || padU > Hk - 1 || padL > Wk - 1) return false;
     if (Wk == 3 && padL != 1) return false;
+    if (cls && cls->up && (Wk != 3 || cls->osx != 2 || cls->ox0 != 0 || cls->oW != 2 * W)) return false;
 
     ConvMnParams p;
     p.n = n; p.Cout = C_dst; p.H = H; p.W = W; p.Hk = Hk; p.padU = padU; p.padL = padL;
@@ -395,10 +412,10 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
     if (!status) return false;
     p.w = w; p.Cout_w = Cout_w; p.Cin_w = Cin_w; p.flip = flip ? 1 : 0;
     p.oH = H; p.oW = W; p.osy = p.osx = 1; p.oy0 = p.ox0 = 0;
-    p.cls = 0; p.kstep = 1; p.kh_r = p.kh_m = p.kw_r = p.kw_m = 0; p.w_Wk = Wk; p.w_taps = Hk * Wk;
+    p.cls = 0; p.up = 0; p.kstep = 1; p.kh_r = p.kh_m = p.kw_r = p.kw_m = 0; p.w_Wk = Wk; p.w_taps = Hk * Wk;
     if (cls) {
         p.cls = 1; p.kstep = cls->kstep; p.kh_r = cls->kh_r; p.kh_m = cls->kh_m; p.kw_r = cls->kw_r; p.kw_m = cls->kw_m;
-        p.w_Wk = cls->w_Wk; p.w_taps = cls->w_Hk * cls->w_Wk;
+        p.w_Wk = cls->w_Wk; p.w_taps = cls->w_Hk * cls->w_Wk; p.up = cls->up;
         p.oH = cls->oH; p.oW = cls->oW; p.osy = cls->osy; p.osx = cls->osx; p.oy0 = cls->oy0; p.ox0 = cls->ox0;
     }
     p.bias = bias; p.y = dst; p.status = status;
@@ -408,13 +425,14 @@ bool conv_mn_run(const float *src, const float *w, const float *bias, float *dst
     if (ctas > p.n_tiles) ctas = p.n_tiles;
     dim3 grid(ctas, co_tiles);
     const int threads = 32 * (4 * p.NE + p.NI + 1 + MN_CONV_WARPS);
-#define TL_MN_LAUNCH(WKV, PL)                                                                                          \
+#define TL_MN_LAUNCH(WKV, PL, ...)                                                                                     \
     do {                                                                                                               \
         static bool attr_set = false;                                                                                  \
-        if (!attr_set) { cudaFuncSetAttribute(conv_mn_kernel<WKV, PL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; } \
-        TL_LAUNCH((conv_mn_kernel<WKV, PL>), grid, threads, smem, tmap, p);                                            \
+        if (!attr_set) { cudaFuncSetAttribute(conv_mn_kernel<WKV, PL, ##__VA_ARGS__>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); attr_set = true; } \
+        TL_LAUNCH((conv_mn_kernel<WKV, PL, ##__VA_ARGS__>), grid, threads, smem, tmap, p);                             \
     } while (0)
-    if (Wk == 1) TL_MN_LAUNCH(1, 0); else if (Wk == 2 && padL == 0) TL_MN_LAUNCH(2, 0); else if (Wk == 2) TL_MN_LAUNCH(2, 1); else TL_MN_LAUNCH(3, 1);
+    if (p.up) TL_MN_LAUNCH(3, 1, true);
+    else if (Wk == 1) TL_MN_LAUNCH(1, 0); else if (Wk == 2 && padL == 0) TL_MN_LAUNCH(2, 0); else if (Wk == 2) TL_MN_LAUNCH(2, 1); else TL_MN_LAUNCH(3, 1);
 #undef TL_MN_LAUNCH
     profile_add_flops(2.0 * n * C_dst * C_src * Hk * Wk * H_dst * W_dst);
     return true;

@@ -418,6 +418,7 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
     if (gemm_path() != 4 && conv_mn_run(src, w, bias, dst, n, C_src, H_src, W_src, C_dst, H_dst, W_dst, Hk, Wk, sh, sw, padU, padL,
                                         Cout_w, Cin_w, flip, dry_run, cls))
         return true;
+    if (cls && cls->up) return false;          // pixel-pair classes exist in the row-slot kernel only
 
     ConvTcParams p;
     p.n = n; p.Cin = C_src; p.Cout = C_dst; p.Hout = H_dst; p.Wout = W_dst;

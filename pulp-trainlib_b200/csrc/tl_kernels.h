@@ -44,7 +44,9 @@ template <class T> void conv_ig(Scope &sc, const ConvGeom &g, const T *dy, const
 template <class T> void conv_ig_accumulate(Scope &sc, const ConvGeom &g, const T *dy, const T *w, T *dx);   // dx += input gradient
 // tensor-core implicit GEMM (tl_conv_tc.cu); false = geometry does not qualify, use the FFMA kernels
 // One parity class of a strided input gradient as a stride-1 convolution over dY (see tl_conv_tc.cu)
-struct ConvTcClass { int kstep, kh_r, kh_m, kw_r, kw_m, w_Hk, w_Wk; int oH, oW, osy, osx, oy0, ox0; };
+// One parity class of a strided input gradient.  up = 1 (row-slot kernel only): both column parities of a row parity in one
+// launch; accumulator column b holds filter column kw = b and the epilogue writes pixel pairs (see tl_conv_mn.cu).
+struct ConvTcClass { int kstep, kh_r, kh_m, kw_r, kw_m, w_Hk, w_Wk; int oH, oW, osy, osx, oy0, ox0; int up; };
 bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias, float *dst,
                  int n, int C_src, int H_src, int W_src, int C_dst, int H_dst, int W_dst,
                  int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false,
