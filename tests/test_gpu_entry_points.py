@@ -422,3 +422,32 @@ def test_depthwise_workers_by_name(pkg, gpulib, oracle, half):
     assert_close(dW.get().astype(np.float32), oracle.dw_wg(x, dy, g), tol, "dw_kernel_weight_grad")
     assert_close(dX.get().astype(np.float32), oracle.dw_ig(dy, w, g), tol, "dw_kernel_input_grad")
     r.close()
+
+
+def test_profile_credits_useful_flops_to_the_kernel_that_ran(pkg, gpulib):
+    """trainlib_profile: every convolution launch is credited 2 x (multiply-adds of the operator's definition); the bench's
+    roofline fractions are built on these figures, so they are checked here against the closed form"""
+    rng = seeded(77)
+    n, C, H = 40, 16, 32
+    g = dict(geom(C, H, H, C, 3, pad=1))
+    xs = rng.uniform(-1, 1, (n, C, H, H)).astype(np.float32); w = rng.uniform(-1, 1, (C, C, 3, 3)).astype(np.float32)
+    gpulib.trainlib_set_streams(n)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        X, W_, dY = r.t(xs), r.t(w), r.t(xs)
+        Y, dX, dW, one = r.zeros(n, C, H, H), r.zeros(n, C, H, H), r.zeros(C, C, 3, 3), r.zeros(1)
+        args = r.args("Conv2D_args", input=r.blob(X, dX, C=C, H=H, W=H), coeff=r.blob(W_, dW, C=C, H=3, W=3, dim=w.size), bias=r.blob(one, one),
+                      output=r.blob(Y, dY, C=C, H=H, W=H), Lpad=1, Rpad=1, Upad=1, Dpad=1, stride_h=1, stride_w=1, i2c_buffer=one, bt_buffer=one,
+                      USE_BIASES=0, USE_IM2COL=1, HWC=0)
+        gpulib.trainlib_profile(1)
+        for fn in ("pulp_conv2d_fp32_fw_cl", "pulp_conv2d_fp32_bw_input_grads_cl", "pulp_conv2d_fp32_bw_param_grads_cl"):
+            r.call(fn, args)
+        gpulib.trainlib_profile(0)
+        table = pkg.profile_table(gpulib, flops=True)
+        want = 2.0 * n * C * C * 9 * H * H
+        credited = sum(row[3] for row in table)
+        assert abs(credited - 3 * want) <= 1e-6 * want, (credited, 3 * want, table)
+        assert all(row[3] == 0.0 for row in table if "reduce" in row[0] or "column" in row[0])
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1)
