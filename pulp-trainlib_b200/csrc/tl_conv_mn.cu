@@ -7,25 +7,31 @@
 //
 // i.e. the filter columns b are moved from the contraction index into the GEMM's N dimension, so the A operand
 // never needs a copy of the input shifted by one float: for every filter row `a` and group of eight input channels
-// it is the very block of image rows that TMA dropped into shared memory, read by the tensor core as an MN-major
-// (pixel-contiguous) operand through a descriptor whose start address moves by whole rows.  The column shift is
-// paid in the epilogue, where thread = pixel and a warp = whole image rows: one warp shuffle per filter column.
+// it is the very block of image rows that TMA dropped into shared memory (after one in-place conversion pass), read
+// through a descriptor whose start address moves by whole row slots.  The column shift is paid in the epilogue,
+// where thread = pixel and a warp = whole image rows: one warp shuffle per shifted filter column.
 //
-// Shared-memory "row slots": one slot = 8 channels x 32 pixels = 8 rows of 128 bytes, the unit of the only MN-major
-// layout kind::tf32 accepts (128-byte swizzle with 32-byte atoms).  The 32 pixels are one image row of P = 32 / W
-// streams side by side (W = 32 / 16 / 8 -> P = 1 / 2 / 4), which is what one row of a TMA box {W, P streams,
-// 8 channels, rows} of the tensor map (x, stream, channel, row) produces (unswizzled: a swizzling TMA copy pads
-// rows shorter than 128 bytes, so the converters apply the swizzle while they split).  A block of 128 output pixels (one MMA,
-// "m-block") is 4 consecutive slots = 4 image rows of P streams; filter row `a` reads the slots `a` further down.
+// Shared-memory "row slots": one slot = 8 channels x 32 pixels = 1 KB.  The 32 pixels are one image row of
+// P = 32 / W streams side by side (W = 32 / 16 / 8 -> P = 1 / 2 / 4), which is what one row of a TMA box {W, P streams,
+// 8 channels, rows} of the tensor map (x, stream, channel, row) produces.  TMA writes a slot as [channel][pixel],
+// unswizzled (a swizzling TMA copy pads rows shorter than 128 bytes, so narrow planes could not be packed); the
+// converter warps transpose it to the K-major layout [pixel][8 channels] (32-byte rows, 32-byte swizzle) while they
+// split.  A block of 128 output pixels (one MMA, "m-block") is 4 consecutive slots = 4 image rows of P streams; filter
+// row `a` reads the slots `a` further down.
 //
 // Pipeline per CTA (persistent, one per SM): a TMA thread fills a ring of stages (one stage = all slots of one
-// 8-channel group of one tile); four converter warps replace every raw value by its TF32 "big" part in place and
-// write the "small" part to the stage's second array (one load, two stores per element); NI issuing threads, each
-// owning one m-block of the tile and its private accumulator in tensor memory, issue per (channel group, filter row)
+// 8-channel group of one tile); three converter warps replace every raw value by its TF32 "big" part in place and
+// write the "small" part to the stage's second array; NI issuing threads, each owning one m-block of the tile and its
+// private accumulator in tensor memory, issue per (channel group, filter row)
 //     D (+)= A_hi * B_hi^T;   D += A_hi * B_lo^T;   D += A_lo * B_hi^T          (the 3xTF32 products, fp32 accumulation)
 // and hand the stage back with tcgen05.commit; epilogue warps read D with tcgen05.ld, shift-sum the filter columns
-// and store the output.  Every accumulator has one issuing thread that adds in a fixed
-// order, so results are bit-reproducible from run to run.
+// and store the output.  Every accumulator has one issuing thread that adds in a fixed order, so results are
+// bit-reproducible from run to run.
+//
+// A strided (3x3, pad 1, stride 2) input gradient runs as two launches, one per output-row parity, in the UP form of
+// the kernel: the grid is the dY plane, accumulator column b holds filter column kw = b, and every grid pixel writes
+// two neighbouring output pixels (see the template comment).  Other strides and filters go out as one launch per
+// parity class, each a small dense stride-1 convolution written to every s-th pixel.
 //
 // Replaces the im2col + mm lowering [ref: lib/sources/pulp_conv2d_fp32.c:85-113, :504-549;
 // lib/sources/pulp_im2col_fp32.c:157-232; lib/sources/pulp_matmul_fp32.c:190-262] and the naive kernels
