@@ -201,6 +201,7 @@ static bool conv_fw_plan(const ConvGeom &g, int &TH, int &TW, int &S_T, int &CC,
 template <class T> static bool try_tc_fw(Scope &, const ConvGeom &, const T *, const T *, const T *, T *) { return false; }
 template <> bool try_tc_fw<float>(Scope &sc, const ConvGeom &g, const float *x, const float *w, const float *bias, float *y)
 {
+    if (conv1x1s_fw(g, x, w, bias, y)) return true;          // strided 1x1: memory-bound, CUDA cores
     return conv_tc_run(sc, x, w, bias, y, g.n, g.Cin, g.Hin, g.Win, g.Cout, g.Hout, g.Wout, g.Hk, g.Wk, g.sh, g.sw, g.padU, g.padL, g.Cout, g.Cin, false);
 }
 // dY of a strided convolution spread onto the input grid: dil[s][co][h][w] = dY[s][co][h/sh][w/sw] where both
@@ -297,6 +298,7 @@ __global__ void __launch_bounds__(256) zero_f4_kernel(float4 *__restrict__ p, si
 // no tensor cores.  False when the geometry or the path selection rules it out.
 static bool try_conv1x1_ig(const ConvGeom &g, const float *dy, const float *w, float *dx, bool acc)
 {
+    if (acc && conv1x1s_ig(g, dy, w, dx)) return true;    // added in place: nothing to zero first
     if (!(g.Hk == 1 && g.Wk == 1 && g.padU == 0 && g.padL == 0 && !g.depthwise && gemm_path() != 1 && (((uintptr_t)dx) & 15) == 0 && (g.Hin * g.Win) % 4 == 0 &&
           (g.sh > 1 || g.sw > 1) && (long long)(g.Hout - 1) * g.sh < g.Hin && (long long)(g.Wout - 1) * g.sw < g.Win))
         return false;
@@ -926,6 +928,20 @@ template <> bool try_tc_wg<float>(Scope &sc, const ConvGeom &g, const float *x, 
     return true;
 }
 
+// strided 1x1 weight gradient: per-CTA partials + the fixed-order reduction
+template <class T> static bool try_1x1_wg(Scope &, const ConvGeom &, const T *, const T *, T *) { return false; }
+template <> bool try_1x1_wg<float>(Scope &sc, const ConvGeom &g, const float *x, const float *dy, float *dw)
+{
+    int groups = 0;
+    if (!conv1x1s_wg(g, x, dy, nullptr, 8 * sm_count(), &groups, true)) return false;
+    const long long nw = (long long)g.Cout * g.Cin;
+    float *part = sc.scratch<float>((size_t)groups * nw);
+    if (!part) return false;
+    if (!conv1x1s_wg(g, x, dy, part, groups, &groups, false)) return false;
+    TL_LAUNCH((reduce_partials_kernel<float>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
+    return true;
+}
+
 template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const T *dy, T *dw, T *dbias)
 {
     if (dbias) TL_LAUNCH((channel_sum_kernel<T>), g.Cout, 256, 0, dy, dbias, g.n, g.Cout, (long long)g.Hout * g.Wout);
@@ -938,6 +954,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     const int ci_tiles = ceil_div(g.Cin, 16), co_tiles = ceil_div(g.Cout, 16);
     const bool k3 = g.Hk == 3 && g.Wk == 3 && g.padL == 1, k1 = g.Hk == 1 && g.Wk == 1 && g.padL == 0 && g.padU == 0;
     if (try_tc_wg<T>(sc, g, x, dy, dw)) return;
+    if (try_1x1_wg<T>(sc, g, x, dy, dw)) return;
     if ((k3 || k1) && g.sh == g.sw && (g.sh == 1 || g.sh == 2) && g.Win == g.sw * g.Wout && (g.Wout == 8 || g.Wout == 16 || g.Wout == 32)) {
         // about 256 (stride 1) or 128 (stride 2) pixels per item: whole output rows, two streams for 8-pixel rows.
         // The item shape is part of the kernel type: (TW, TH, S_T) = (32, 8, 1), (16, 16, 1), (8, 8, 2) for stride 1

@@ -52,6 +52,10 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
                  int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false,
                  const ConvTcClass *cls = nullptr);
 int conv_tc_status();
+// 1x1 strided convolutions on CUDA cores (tl_conv1x1.cu); false = geometry not covered, nothing launched
+bool conv1x1s_fw(const ConvGeom &g, const float *x, const float *w, const float *bias, float *y);
+bool conv1x1s_ig(const ConvGeom &g, const float *dy, const float *w, float *dx);   // dX += gradient
+bool conv1x1s_wg(const ConvGeom &g, const float *x, const float *dy, float *part, int part_groups, int *groups_out, bool dry_run);
 // tensor-core weight gradient (tl_conv_wgt.cu): partial results per CTA into `part`; false = geometry not covered
 bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, int stride, bool dry_run);
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,

@@ -211,6 +211,54 @@ def test_conv2d_tensor_core_path(pkg, gpulib, oracle, g, n):
         gpulib.trainlib_set_streams(1); gpulib.trainlib_set_gemm_path(0)
 
 
+C1_CASES = [(geom(16, 32, 32, 32, 1, stride=2), 5), (geom(32, 16, 16, 64, 1, stride=2), 3), (geom(8, 18, 18, 12, 1, stride=3), 2),
+            (geom(64, 10, 10, 64, 1, stride=2), 300), (geom(4, 33, 33, 4, 1, stride=2), 1), (geom(16, 17, 17, 16, 1, stride=2), 7),
+            (geom(32, 20, 20, 32, 1, stride=3), 4), (geom(64, 8, 8, 128, 1, stride=2), 2), (geom(32, 64, 64, 16, 1, stride=2), 2)]
+
+
+@pytest.mark.parametrize("g,n", C1_CASES, ids=lambda v: str(v) if isinstance(v, int) else "c%d_%d_o%d_s%d" % (v["Cin"], v["Hin"], v["Cout"], v["sh"]))
+def test_conv2d_1x1_strided_kernels(pkg, gpulib, oracle, g, n):
+    """projection shortcuts (1x1, stride > 1, no padding) at the default dispatch: forward with bias, weight gradient summed
+    over the streams, input gradient stored and added in place; pixel counts that are not multiples of the tile included"""
+    rng = seeded(5 * g["Cin"] + g["Cout"] + n)
+    Ho, Wo = out_hw(g)
+    xs = rng.uniform(-1, 1, (n, g["Cin"], g["Hin"], g["Win"])).astype(F); w = rng.uniform(-1, 1, (g["Cout"], g["Cin"], 1, 1)).astype(F)
+    b = rng.uniform(-1, 1, g["Cout"]).astype(F); dys = rng.standard_normal((n, g["Cout"], Ho, Wo)).astype(F)
+    base = rng.uniform(-1, 1, xs.shape).astype(F)
+    gpulib.trainlib_set_streams(n)
+    try:
+        r = AbiRunner(pkg, gpulib, device=True)
+        X, W_, B, dY = r.t(xs), r.t(w), r.t(b), r.t(dys)
+        Y, dX, dW, dB, one = r.zeros(n, g["Cout"], Ho, Wo), r.t(base), r.zeros(*w.shape), r.zeros(g["Cout"]), r.zeros(1)
+        args = r.args("Conv2D_args", input=r.blob(X, dX, C=g["Cin"], H=g["Hin"], W=g["Win"]), coeff=r.blob(W_, dW, C=g["Cin"], H=1, W=1, dim=w.size),
+                      bias=r.blob(B, dB, dim=g["Cout"]), output=r.blob(Y, dY, C=g["Cout"], H=Ho, W=Wo), Lpad=0, Rpad=0, Upad=0, Dpad=0,
+                      stride_h=g["sh"], stride_w=g["sw"], i2c_buffer=one, bt_buffer=one, USE_BIASES=1, USE_IM2COL=1, HWC=0)
+        gpulib.trainlib_profile(1)
+        r.call("pulp_conv2d_fp32_fw_cl", args); r.call("pulp_conv2d_fp32_bw_param_grads_cl", args)
+        r.call("trainlib_conv2d_fp32_bw_input_grads_acc_cl", args)
+        gpulib.trainlib_profile(0)
+        names = [row[0] for row in pkg.profile_table(gpulib)]
+        # channel counts in multiples of 16 run on the dedicated kernels (the contraction of the input gradient up to 64)
+        if g["Cin"] % 16 == 0 and g["Cout"] % 16 == 0:
+            want_names = ["conv1x1s_mma_kernel<%d, " % (g["Cin"] // 8), "conv1x1s_wg_kernel"] + (["conv1x1s_mma_kernel<%d, " % (g["Cout"] // 8)] if g["Cout"] <= 64 else [])
+            for k in want_names:
+                assert any(k in nm for nm in names), (k, names)
+        y, dx_acc = Y.get(), dX.get()
+        r.call("pulp_conv2d_fp32_bw_input_grads_cl", args)
+        dx = dX.get()
+        for s in sorted({0, n // 2, n - 1}):
+            assert_close(y[s], oracle.conv2d_fw(xs[s], w, b, g), FP32_TOL, "1x1 fw stream %d" % s)
+            ig = oracle.conv2d_ig(dys[s], w, g)
+            assert_close(dx[s], ig, FP32_TOL, "1x1 ig stream %d" % s)
+            assert_close(dx_acc[s], (base[s].astype(np.float64) + ig).astype(F), FP32_TOL, "1x1 ig added in place, stream %d" % s)
+        want = sum(oracle.conv2d_wg(xs[s], dys[s], g)[0].astype(np.float64) for s in range(n)).astype(F)
+        assert_close(dW.get(), want, FP32_TOL, "1x1 weight gradient")
+        assert_close(dB.get(), dys.astype(np.float64).sum(axis=(0, 2, 3)).astype(F), FP32_TOL, "1x1 bias gradient")
+        r.close()
+    finally:
+        gpulib.trainlib_set_streams(1)
+
+
 def test_conv2d_tensor_core_many_tiles(pkg, gpulib, oracle):
     """long persistent loops (hundreds of tiles per CTA): every barrier ring wraps many times; a few streams are checked"""
     g = geom(16, 32, 32, 16, 3, pad=1)
@@ -698,10 +746,7 @@ def test_conv2d_input_gradient_accumulate(pkg, gpulib, oracle, g, n):
         plain, acc = dX_plain.get(), dX_acc.get()
         for s in range(n):
             assert_close(plain[s], oracle.conv2d_ig(dy[s], w, g), FP32_TOL, "plain input gradient")
-        if g["sh"] > 1 and g["Hk"] == 1:
-            assert np.array_equal(acc, plain + base), "accumulated input gradient differs from plain + base"
-        else:
-            assert_close(acc, plain + base, FP32_TOL, "accumulated input gradient")     # tensor-core path: not run-to-run bit-stable
+        assert_close(acc, plain + base, FP32_TOL, "accumulated input gradient")     # the two calls may run on different kernels
         r.close()
     finally:
         gpulib.trainlib_set_streams(1)
