@@ -286,10 +286,11 @@ class ResNet8Streams(object):
     # kernel families of the step: template variants (plane sizes, tile widths) and the kernels that share one job count as one
     FAMILIES = (
         ("conv_fw_ig_tensor", ("conv_mn_kernel", "conv_tc_kernel"), "tensor",
-         "forward of the 9 convolutions and input gradient of the 3x3 ones as tcgen05 3xTF32 implicit GEMMs (useful FLOP: zeros of a dilated dY are not counted)"),
+         "forward of the 7 3x3 convolutions and their input gradients as tcgen05 3xTF32 implicit GEMMs (useful FLOP: zeros of a dilated dY are not counted)"),
         ("conv_wg_tensor", ("conv_wgt_kernel",), "tensor", "weight gradient of the stride-1 3x3 convolutions with 32+ channels as a tcgen05 3xTF32 pixel-contraction GEMM"),
         ("conv_wg_ffma", ("conv_wg3x3_partial_kernel", "conv_wg_partial_kernel", "conv_wg_direct_kernel"), "ffma", "weight gradient of the other convolutions, fp32 FFMA"),
-        ("conv_1x1_ig_ffma", ("conv1x1_strided_ig_kernel",), "ffma", "input gradient of the two 1x1 stride-2 shortcut convolutions, fp32 FFMA"),
+        ("conv_1x1_strided", ("conv1x1s_mma_kernel", "conv1x1s_wg_kernel", "conv1x1_strided_ig_kernel"), "hbm",
+         "forward, weight gradient and in-place input gradient of the two 1x1 stride-2 shortcut convolutions: 2 FLOP per byte, bound by memory traffic and instruction issue"),
         ("conv_fw_ig_ffma", ("conv_fw_kernel", "conv_ig_kernel"), "ffma", "convolutions on the FFMA path"),
     )
     # DRAM traffic of one launch from ncu captures at 512 streams (bytes read + written inside the launch), keyed by

@@ -147,7 +147,7 @@ __device__ __forceinline__ void mma_3x(float (&d)[4], const uint32_t (&ah)[4], c
 // m_groups x n_groups: a warp owns MTW 16-channel blocks, whose weight fragments it keeps in registers, and every
 // n_groups-th 8-pixel column block of a tile.
 template <int KT, int MTW, bool IG>
-__global__ void __launch_bounds__(C1_THREADS) conv1x1s_mma_kernel(Conv1x1Params p, const float *__restrict__ src, const float *__restrict__ w,
+__global__ void __launch_bounds__(C1_THREADS, (KT * MTW <= 4) ? 4 : 2) conv1x1s_mma_kernel(Conv1x1Params p, const float *__restrict__ src, const float *__restrict__ w,
                                                                   const float *__restrict__ bias, float *__restrict__ dst)
 {
     constexpr int LD = C1_LDK, K = KT * 8;
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(C1_THREADS) conv1x1s_mma_kernel(Conv1x1Params 
 // blocks and every k_groups-th 8-pixel slice of a tile.  Both operands change with every tile and are split on the way
 // from shared memory to the instruction.
 template <int MTW, int NT>
-__global__ void __launch_bounds__(C1_THREADS) conv1x1s_wg_kernel(Conv1x1Params p, const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ part)
+__global__ void __launch_bounds__(C1_THREADS, (MTW * NT <= 4) ? 4 : 2) conv1x1s_wg_kernel(Conv1x1Params p, const float *__restrict__ x, const float *__restrict__ dy, float *__restrict__ part)
 {
     constexpr int LD = C1_LDM;
     extern __shared__ __align__(16) float c1_smem[];
