@@ -125,8 +125,7 @@ class LinearSweep(object):
         for a in self.args_dev:
             p = ctypes.byref(a)
             getattr(self.lib, "pulp_linear_%s_fw_cl" % ("fp16" if self.half else "fp32"))(p)
-            getattr(self.lib, "pulp_linear_%s_bw_param_grads_cl" % ("fp16" if self.half else "fp32"))(p)
-            getattr(self.lib, "pulp_linear_%s_bw_input_grads_cl" % ("fp16" if self.half else "fp32"))(p)
+            getattr(self.lib, "pulp_linear_%s_bw_cl" % ("fp16" if self.half else "fp32"))(p)      # weight and input gradient
 
     def setup_host(self, lib):
         """host-pointer arguments (pinned when our library provides the allocator)"""
@@ -146,8 +145,7 @@ class LinearSweep(object):
         for a in self.args_host:
             p = ctypes.byref(a)
             getattr(lib, "pulp_linear_%s_fw_cl" % ("fp16" if self.half else "fp32"))(p)
-            getattr(lib, "pulp_linear_%s_bw_param_grads_cl" % ("fp16" if self.half else "fp32"))(p)
-            getattr(lib, "pulp_linear_%s_bw_input_grads_cl" % ("fp16" if self.half else "fp32"))(p)
+            getattr(lib, "pulp_linear_%s_bw_cl" % ("fp16" if self.half else "fp32"))(p)           # weight and input gradient
 
     def metric(self, ms):
         return {"metric": "train_step_tflops", "unit": "TFLOP/s", "value": self.flops / (ms * 1e-3) / 1e12}
@@ -155,7 +153,7 @@ class LinearSweep(object):
     def roofline(self, ms, pk):
         gbs = self.bytes / (ms * 1e-3) / 1e9
         return {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "traffic": None,
-                "peak_source": pk["source"], "kernel": "linear_fw/wg/ig (whole step)", "algorithmic_bytes": self.bytes}
+                "peak_source": pk["source"], "kernel": "linear_fw_kernel + linear_bw_fused_kernel (whole step)", "algorithmic_bytes": self.bytes}
 
 
 class MmSweep(object):

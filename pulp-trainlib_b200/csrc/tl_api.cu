@@ -480,6 +480,28 @@ template <class F> void linear_impl(void *args, int step)
     }
 }
 
+// pulp_linear_*_bw_cl with both gradients wanted, one stream: one launch for the two [ref: lib/sources/pulp_linear_fp32.c:60-75]
+template <class F> bool linear_bw_both(void *args)
+{
+    auto *a = (typename F::linear_t *)args; typedef typename F::T T;
+    const int in = a->input->dim, out = a->output->dim;
+    if (streams() != 1 || in <= 0 || out <= 0 || gemm_path() == 1) return false;
+    const bool ub = (a->use_biases == 1) && a->bias;
+    // what the kernel needs is checked before anything is staged: 16-byte strips (host buffers get aligned device mirrors)
+    if (in % (16 / (int)sizeof(T)) != 0 || in / (16 / (int)sizeof(T)) > 8192 * 32) return false;
+    const void *ptrs[4] = {a->coeff->data, a->coeff->diff, a->input->data, a->input->diff};
+    for (const void *q : ptrs)
+        if (!q || (is_device_pointer(q) && (((uintptr_t)q) & 15) != 0)) return false;
+    Scope sc;
+    const T *dy = sc.in(a->output->diff, (size_t)out), *x = sc.in(a->input->data, (size_t)in), *w = sc.in(a->coeff->data, (size_t)out * in);
+    T *dw = sc.out(a->coeff->diff, (size_t)out * in), *dx = sc.out(a->input->diff, (size_t)in);
+    T *db = ub ? sc.out(a->bias->diff, (size_t)out) : nullptr;
+    if (!sc.ok()) return true;                                     // the error is set; the separate calls would fail the same way
+    if (!linear_bw_fused<T>(sc, w, dy, x, dw, dx, out, in)) return true;   // only a failed scratch allocation is left: the error is set
+    if (db) column_sum<T>(sc, dy, db, 1, out);
+    return true;
+}
+
 // ------------------------------------------------------------------ MHSA
 template <class F> bool mhsa_dims(const typename F::mhsa_t *a, MhsaDims &d)
 {
@@ -1047,12 +1069,14 @@ TL_PAIR(pulp_linear_fp32_bw_input_grads_cl, pulp_linear_fp16_bw_input_grads_cl, 
 TL_EXPORT void pulp_linear_fp32_bw_cl(void *a)
 {
     auto *c = (Linear_args *)a;
+    if (c->skip_wg_grad == 0 && c->skip_in_grad == 0 && linear_bw_both<F32>(a)) return;
     if (c->skip_wg_grad == 0) pulp_linear_fp32_bw_param_grads_cl(a);
     if (c->skip_in_grad == 0) pulp_linear_fp32_bw_input_grads_cl(a);
 }
 TL_EXPORT void pulp_linear_fp16_bw_cl(void *a)
 {
     auto *c = (Linear_args_fp16 *)a;
+    if (c->skip_wg_grad == 0 && c->skip_in_grad == 0 && linear_bw_both<F16>(a)) return;
     if (c->skip_wg_grad == 0) pulp_linear_fp16_bw_param_grads_cl(a);
     if (c->skip_in_grad == 0) pulp_linear_fp16_bw_input_grads_cl(a);
 }

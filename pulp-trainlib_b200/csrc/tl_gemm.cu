@@ -408,6 +408,108 @@ template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx
     TL_LAUNCH((linear_ig_reduce_kernel<T>), ceil_div(in, 32), 1024, 0, part, dx, in, slabs);
 }
 
+// Both gradients of a batch-1 Linear layer in one launch [ref: lib/sources/pulp_linear_fp32.c:60-180, the two halves of
+// pulp_linear_fp32_bw_cl].  A CTA owns 32 column strips of 16 bytes in one row slab; its four warps take every fourth
+// row: for every row a thread loads its strip of W once, adds W * dy[o] to its dX partial and stores dy[o] * x[strip]
+// to dW (a warp moves 512 contiguous bytes each way per row).  The four warps' partials are added in warp order, the
+// slab's partial goes to `part`, and the CTA of a column block that finishes last (a ticket per column block) adds the
+// slabs' partials, always in the same order, so the result does not depend on which CTA that is: one launch instead of
+// three, W read once.
+static __device__ unsigned tl_linear_tickets[8192];                 // one per column block; zero between launches
+static constexpr int LBW_STRIPS = 32, LBW_LANES = 4;
+
+template <class T>
+__global__ void __launch_bounds__(LBW_STRIPS * LBW_LANES) linear_bw_fused_kernel(const T *__restrict__ W, const T *__restrict__ dy, const T *__restrict__ x,
+                                                                                 T *__restrict__ dW, float *__restrict__ part, T *__restrict__ dx,
+                                                                                 int out, int in, int rows_per_slab, int slabs)
+{
+    constexpr int V = 16 / sizeof(T);
+    __shared__ float red[LBW_LANES][LBW_STRIPS][V + 1];
+    __shared__ unsigned ticket_s;
+    const int cx = threadIdx.x % LBW_STRIPS, ry = threadIdx.x / LBW_STRIPS, slab = blockIdx.y;
+    const int o_end = min(out, (slab + 1) * rows_per_slab);
+    const int col0 = (blockIdx.x * LBW_STRIPS + cx) * V;
+    const bool live = col0 < in;                                    // in % V == 0 (host): a strip is inside or outside as a whole
+    float acc[V], xv[V];
+#pragma unroll
+    for (int q = 0; q < V; q++) { acc[q] = 0.f; xv[q] = live ? ld(x + col0 + q) : 0.f; }
+    if (live) {
+#pragma unroll 8
+        for (int o = slab * rows_per_slab + ry; o < o_end; o += LBW_LANES) {
+            const float g = ld(dy + o);
+            const long long e = (long long)o * in + col0;
+            if (sizeof(T) == 4) {
+                const float4 w = __ldcs((const float4 *)(W + e));
+                acc[0] = fmaf(w.x, g, acc[0]); acc[1] = fmaf(w.y, g, acc[1]); acc[2] = fmaf(w.z, g, acc[2]); acc[3] = fmaf(w.w, g, acc[3]);
+                __stcs((float4 *)(dW + e), make_float4(g * xv[0], g * xv[1], g * xv[2], g * xv[3]));
+            } else {
+                const uint4 w = __ldcs((const uint4 *)(W + e));
+                const __half2 *wh = (const __half2 *)&w;
+                uint4 r; __half2 *rh = (__half2 *)&r;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float2 f = __half22float2(wh[q]);
+                    acc[2 * q] = fmaf(f.x, g, acc[2 * q]); acc[2 * q + 1] = fmaf(f.y, g, acc[2 * q + 1]);
+                    rh[q] = __floats2half2_rn(g * xv[2 * q], g * xv[2 * q + 1]);
+                }
+                __stcs((uint4 *)(dW + e), r);
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < V; q++) red[ry][cx][q] = acc[q];
+    __syncthreads();
+    if (ry == 0 && live) {
+#pragma unroll
+        for (int q = 0; q < V; q++) __stcg(part + (long long)slab * in + col0 + q, ((red[0][cx][q] + red[1][cx][q]) + red[2][cx][q]) + red[3][cx][q]);
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) ticket_s = atomicAdd(&tl_linear_tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (ticket_s != (unsigned)(slabs - 1)) return;
+    __threadfence();                                                // the last CTA of this column block: every slab's partial is visible
+    float t[V];
+#pragma unroll
+    for (int q = 0; q < V; q++) t[q] = 0.f;
+    if (live)
+        for (int b = ry; b < slabs; b += LBW_LANES)                 // lane r adds slabs r, r + 4, ...
+#pragma unroll
+            for (int q = 0; q < V; q += 4) {
+                const float4 v = __ldcg((const float4 *)(part + (long long)b * in + col0 + q));
+                t[q] += v.x; t[q + 1] += v.y; t[q + 2] += v.z; t[q + 3] += v.w;
+            }
+#pragma unroll
+    for (int q = 0; q < V; q++) red[ry][cx][q] = t[q];
+    __syncthreads();
+    if (ry == 0 && live) {
+#pragma unroll
+        for (int q = 0; q < V; q++) st(dx + col0 + q, ((red[0][cx][q] + red[1][cx][q]) + red[2][cx][q]) + red[3][cx][q]);
+    }
+    if (threadIdx.x == 0) tl_linear_tickets[blockIdx.x] = 0;        // ready for the next launch on this device
+}
+
+// false: shape or alignment not covered (the caller issues the two separate kernels)
+template <class T> bool linear_bw_fused(Scope &sc, const T *W, const T *dy, const T *x, T *dW, T *dx, int out, int in)
+{
+    constexpr int V = 16 / sizeof(T);
+    if (in % V != 0 || ((((uintptr_t)W) | ((uintptr_t)dW) | ((uintptr_t)x) | ((uintptr_t)dx)) & 15) != 0) return false;
+    const int col_blocks = ceil_div(in / V, LBW_STRIPS);
+    if (col_blocks > 8192) return false;
+    // about four CTAs per SM, at least 8 rows each
+    int slabs = ceil_div(4 * sm_count(), col_blocks);
+    if (slabs > ceil_div(out, 8)) slabs = ceil_div(out, 8);
+    if (slabs < 1) slabs = 1;
+    const int rows_per_slab = ceil_div(out, slabs);
+    slabs = ceil_div(out, rows_per_slab);
+    float *part = sc.scratch<float>((size_t)slabs * in);
+    if (!part) return false;
+    TL_LAUNCH((linear_bw_fused_kernel<T>), dim3(col_blocks, slabs), LBW_STRIPS * LBW_LANES, 0, W, dy, x, dW, part, dx, out, in, rows_per_slab, slabs);
+    return true;
+}
+template bool linear_bw_fused<float>(Scope &, const float *, const float *, const float *, float *, float *, int, int);
+template bool linear_bw_fused<__half>(Scope &, const __half *, const __half *, const __half *, __half *, __half *, int, int);
+
 } // namespace tl
 
 // ------------------------------------------------------------------ Linear input gradient without any allocation

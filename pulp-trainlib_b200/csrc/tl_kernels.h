@@ -29,6 +29,8 @@ template <class T> void linear_fw_gemv(const T *W, const T *x, const T *bias, T 
 template <class T> void linear_wg_outer(const T *dy, const T *x, T *dW, int out, int in);
 template <class T> bool linear_wg_streams(Scope &sc, const T *dy, const T *x, T *dW, int n, int out, int in);
 template <class T> void linear_ig_gemv(Scope &sc, const T *W, const T *dy, T *dx, int out, int in);
+// dW and dX of a batch-1 layer in one launch; false = not covered, nothing launched
+template <class T> bool linear_bw_fused(Scope &sc, const T *W, const T *dy, const T *x, T *dW, T *dx, int out, int in);
 
 // ---------------------------------------------------------------- convolution
 struct ConvGeom {

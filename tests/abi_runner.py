@@ -154,7 +154,7 @@ class AbiRunner(object):
         self.call(self.fname("pulp_conv_dw_fp32_bw_cl"), args)
         return dict(y=Y.get().copy(), dw=dW.get().copy(), dx=dX.get().copy())
 
-    def linear(self, Wm, x, dy, bias=None, n=1):
+    def linear(self, Wm, x, dy, bias=None, n=1, one_backward_call=False):
         out, inn = Wm.shape
         W_, X, dY = self.t(Wm), self.t(x), self.t(dy)
         Y, dW, dX = self.zeros(n * out), self.zeros(out, inn), self.zeros(n * inn)
@@ -164,8 +164,11 @@ class AbiRunner(object):
                          output=self.blob(Y, dY, C=1, H=1, W=out, dim=out), skip_wg_grad=0, skip_in_grad=0,
                          opt_matmul_type_fw=0, opt_matmul_type_wg=0, opt_matmul_type_ig=0, use_biases=1 if bias is not None else 0)
         self.call(self.fname("pulp_linear_fp32_fw_cl"), args)
-        self.call(self.fname("pulp_linear_fp32_bw_param_grads_cl"), args)
-        self.call(self.fname("pulp_linear_fp32_bw_input_grads_cl"), args)
+        if one_backward_call:
+            self.call(self.fname("pulp_linear_fp32_bw_cl"), args)
+        else:
+            self.call(self.fname("pulp_linear_fp32_bw_param_grads_cl"), args)
+            self.call(self.fname("pulp_linear_fp32_bw_input_grads_cl"), args)
         return dict(y=Y.get().copy(), dW=dW.get().copy(), dx=dX.get().copy(), db=dB.get().copy())
 
     def mhsa(self, x, wq, wk, wv, bq, bk, bv, wo, dy, L, E, F, heads):

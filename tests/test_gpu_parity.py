@@ -141,6 +141,31 @@ def test_linear_config2(run, oracle, inn, out, half):
         assert_close(got[k].astype(F).reshape(want[k].shape), want[k], tol, "linear %s" % k)
 
 
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("inn,out,device", [(256, 256, True), (1024, 4096, True), (4096, 1024, True), (1024, 1000, False), (8, 3, True), (100, 37, True), (4104, 9, True)])
+def test_linear_backward_in_one_call(pkg, gpulib, run, oracle, inn, out, device, half):
+    """pulp_linear_*_bw_cl with both gradients wanted: one fused launch where the rows are whole 16-byte strips (the kernel
+    name proves it), the two separate kernels otherwise; device-resident and host buffers; against the reference and
+    bit-identical, launch after launch, with itself"""
+    rng = seeded(inn + 5 * out)
+    W = (rng.standard_normal((out, inn)) / np.sqrt(inn)).astype(F); x = rng.standard_normal(inn).astype(F); dy = rng.standard_normal(out).astype(F)
+    bias = rng.standard_normal(out).astype(F)
+    if half:
+        W, x, dy, bias = [a.astype(np.float16).astype(F) for a in (W, x, dy, bias)]
+    want = oracle.linear(W, x, dy, bias)
+    gpulib.trainlib_profile(1)
+    got = run(device=device, half=half).linear(W, x, dy, bias, one_backward_call=True)
+    gpulib.trainlib_profile(0)
+    names = [row[0] for row in pkg.profile_table(gpulib)]
+    assert any("linear_bw_fused_kernel" in nm for nm in names) == (inn % (8 if half else 4) == 0), names
+    tol = FP16_TOL if half else FP32_TOL
+    for k in ("y", "dW", "dx", "db"):
+        assert_close(got[k].astype(F).reshape(want[k].shape), want[k], tol, "linear %s" % k)
+    again = run(device=device, half=half).linear(W, x, dy, bias, one_backward_call=True)
+    for k in ("dW", "dx"):
+        assert np.array_equal(got[k], again[k]), "fused linear backward is not reproducible: %s" % k
+
+
 CONV_CASES = [geom(16, 32, 32, 32, 3, pad=1), geom(3, 32, 32, 16, 3, pad=1), geom(16, 32, 32, 32, 3, stride=2, pad=1),
               geom(32, 16, 16, 64, 3, stride=2, pad=1), geom(64, 8, 8, 64, 3, pad=1), geom(16, 32, 32, 32, 1, stride=2),
               geom(5, 11, 13, 7, 3, stride=2, pad=1), geom(3, 9, 9, 4, 5, stride=1, pad=2), geom(2, 12, 12, 3, 7, pad=3),
