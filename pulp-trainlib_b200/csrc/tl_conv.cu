@@ -919,12 +919,12 @@ template <> bool try_tc_wg<float>(Scope &sc, const ConvGeom &g, const float *x, 
     // channel (even and odd pixels), so it pays from 16 channels on.
     if (gemm_path() != 2 && (work < (1ll << 28) || g.Cin < (g.sh == 2 ? 16 : 32))) return false;
     int groups = 0;
-    if (!conv_wgt_run(x, dy, nullptr, sm_count(), &groups, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, true)) return false;
-    const long long nw = (long long)g.Cout * g.Cin * 9;
-    float *part = sc.scratch<float>((size_t)groups * nw);
+    long long group_floats = 0;
+    if (!conv_wgt_run(x, dy, nullptr, sm_count(), &groups, &group_floats, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, true)) return false;
+    float *part = sc.scratch<float>((size_t)groups * (size_t)group_floats);
     if (!part) return false;
-    if (!conv_wgt_run(x, dy, part, groups, &groups, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, false)) return false;
-    TL_LAUNCH((reduce_partials_kernel<float>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
+    if (!conv_wgt_run(x, dy, part, groups, &groups, &group_floats, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, false)) return false;
+    conv_wgt_reduce(part, dw, groups, g.Cin, g.Cout, g.sh);
     return true;
 }
 

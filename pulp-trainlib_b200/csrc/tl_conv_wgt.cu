@@ -18,8 +18,10 @@
 // Per k-step and M-block:  D (+)= X_hi * [dYb_hi | dYb_lo]^T ;  D[:, hi part] += X_lo * dYb_hi^T   (three N-wide MMAs
 // into one set of columns where 6*Cout > 256).  The accumulators stay in tensor memory for the CTA's whole run (all its
 // streams); each accumulator has exactly one issuing thread, k-steps are dealt round-robin to KS issuers with their
-// own accumulators, and the epilogue adds the sets in a fixed order and writes the CTA's partial dW, which
-// reduce_partials_kernel sums over the CTAs (fixed order: bit-reproducible).
+// own accumulators, and the epilogue adds the sets in a fixed order and writes the CTA's partial result in the
+// accumulators' own [row][column] layout (64 contiguous bytes per thread and store: scattering it to dW[co][ci][kh][kw]
+// from every CTA cost more than the arithmetic of a small launch); wgt_reduce_kernel sums the partials over the CTAs
+// (fixed order: bit-reproducible) and scatters once.
 //
 // Stride 2 (3x3, pad 1, input rows twice as long as dY rows): X[2y + a - 1][2x + b - 1].  The converters de-interleave
 // every input row into its even and odd pixels (two slots E and O per row and channel group, same 32-position K layout
@@ -195,13 +197,12 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
             if (warp_wait_or_abort(all_done, 0, abort_flag, p.status, 24, 64u, lane)) {
                 tc_fence_after();
                 const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-                const long long nw = (long long)p.Cout * p.Cin * 9;
-                float *out = p.part + (long long)blockIdx.x * nw;
+                // The partial leaves in the accumulators' own layout, [M row][column] with 16 consecutive columns (64 bytes) per
+                // thread and store; wgt_reduce_kernel maps rows and columns to dW[co][ci][kh][kw] once, after the sum.
                 const int NBc = p.ncopy * p.Cout;                      // columns of one product block
+                float *out = p.part + (long long)blockIdx.x * ((long long)p.MB * 128 * NBc);
                 for (int m = 0; m < p.MB; m++) {
-                    const int grp = m * 16 + (warp * 32 + lane) / 8, ci8 = lane & 7;
-                    const int a = grp / p.xg, par = (grp % p.xg) / p.cigs, cig = grp % p.cigs, ci = cig * 8 + ci8;
-                    const bool valid = grp < 3 * p.xg;
+                    float *orow = out + (long long)(m * 128 + warp * 32 + lane) * NBc;
                     for (int c0 = 0; c0 < NBc; c0 += 16) {
                         float acc[16];
 #pragma unroll
@@ -215,16 +216,8 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
 #pragma unroll
                             for (int i = 0; i < 16; i++) acc[i] += __uint_as_float(v[i]) + (p.stack ? __uint_as_float(w[i]) : 0.f);
                         }
-                        if (valid) {
 #pragma unroll
-                            for (int i = 0; i < 16; i++) {
-                                const int col = c0 + i, b = col / p.Cout, co = col % p.Cout;
-                                // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b;
-                                // stride 2: even pixels with dY[x] are column 1, odd pixels with dY[x] column 2, with dY[x + 1] column 0
-                                const int kw = !p.s2 ? b : (par == 0 ? (b == 1 ? 1 : -1) : (b == 1 ? 2 : 0));
-                                if (kw >= 0) out[((long long)co * p.Cin + ci) * 9 + a * 3 + kw] = acc[i];
-                            }
-                        }
+                        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4 *>(orow + c0 + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
                     }
                 }
             }
@@ -282,11 +275,49 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 void *tc_encode_tiled_fn();
 int *tc_status_word();
 
+// dW[co][ci][kh][kw] = sum over the CTAs' partials, which lie in the accumulators' layout: row = 8 channels x (filter row,
+// pixel parity, channel group), column = (copy of the dY row, co).  32 consecutive elements x 32 slices of the groups per
+// CTA (slice s adds groups s, s + 32, ...; the slices are added in slice order), as in reduce_partials_kernel.
+__global__ void __launch_bounds__(1024) wgt_reduce_kernel(const float *__restrict__ part, float *__restrict__ dw, int groups, int Cin, int Cout,
+                                                          int s2, int xg, int cigs, int ncopy, int MB)
+{
+    __shared__ float sm[32][33];
+    const int wx = threadIdx.x & 31, sl = threadIdx.x >> 5, NBc = ncopy * Cout;
+    const long long nn = (long long)MB * 128 * NBc, i = (long long)blockIdx.x * 32 + wx;
+    float s = 0.f;
+    if (i < nn)
+        for (int g = sl; g < groups; g += 32) s += part[(long long)g * nn + i];
+    sm[sl][wx] = s;
+    __syncthreads();
+    if (sl != 0 || i >= nn) return;
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; k++) t += sm[k][wx];
+    const int row = (int)(i / NBc), col = (int)(i % NBc);
+    const int grp = row / 8, ci8 = row & 7;                             // row = m * 128 + lane of the accumulator: 16 groups of 8 per M block
+    if (grp >= 3 * xg) return;                                          // padding rows of the last M block
+    const int a = grp / xg, par = (grp % xg) / cigs, ci = (grp % cigs) * 8 + ci8;
+    const int b = col / Cout, co = col % Cout;
+    // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b;
+    // stride 2: even pixels with dY[x] are column 1, odd pixels with dY[x] column 2, with dY[x + 1] column 0
+    const int kw = !s2 ? b : (par == 0 ? (b == 1 ? 1 : -1) : (b == 1 ? 2 : 0));
+    if (kw >= 0) dw[((long long)co * Cin + ci) * 9 + a * 3 + kw] = t;
+}
+// the second half of conv_wgt_run: sums `groups` partials into dW
+void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride)
+{
+    const int cigs = Cin / 8, s2 = stride == 2 ? 1 : 0, xg = s2 ? 2 * cigs : cigs, ncopy = s2 ? 2 : 3, MB = ceil_div(3 * xg, 16);
+    const long long nn = (long long)MB * 128 * ncopy * Cout;
+    TL_LAUNCH(wgt_reduce_kernel, ceil_div(nn, 32), 1024, 0, part, dw, groups, Cin, Cout, s2, xg, cigs, ncopy, MB);
+}
+
 // Weight gradient on the tensor cores for 3x3 / pad 1 with stride 1 or 2 and channel counts that are multiples of 8
 // (C_out a multiple of 16).  H x W is the size of the dY planes (rows of 32, 16 or 8 pixels; stride 2: 16 or 8), the X
-// planes are stride times as large.  Writes `*groups` partial results of Cout*Cin*9 floats each into `part` (capacity
-// part_groups); the caller sums them.  false = geometry not covered (nothing launched).
-bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, int stride, bool dry_run)
+// planes are stride times as large.  Writes `*groups_out` partial results of `*group_floats_out` floats each (the
+// accumulators' layout) into `part` (capacity part_groups); conv_wgt_reduce sums them into dW.  false = geometry not
+// covered (nothing launched).
+bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, long long *group_floats_out, int n, int Cin, int Cout, int H,
+                  int W, int stride, bool dry_run)
 {
     EncodeTiledFn enc = (EncodeTiledFn)tc_encode_tiled_fn();
     if (!enc) return false;
@@ -336,6 +367,7 @@ bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups,
     int ctas = sm_count();
     if (ctas > p.n_tiles) ctas = p.n_tiles;
     if (ctas > part_groups) return false;
+    *group_floats_out = (long long)p.MB * 128 * p.ncopy * Cout;
     if (dry_run) { *groups_out = ctas; return true; }
 
     CUtensorMap tx, tdy;

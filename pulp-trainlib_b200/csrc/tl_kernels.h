@@ -59,7 +59,9 @@ bool conv1x1s_fw(const ConvGeom &g, const float *x, const float *w, const float 
 bool conv1x1s_ig(const ConvGeom &g, const float *dy, const float *w, float *dx);   // dX += gradient
 bool conv1x1s_wg(const ConvGeom &g, const float *x, const float *dy, float *part, int part_groups, int *groups_out, bool dry_run);
 // tensor-core weight gradient (tl_conv_wgt.cu): partial results per CTA into `part`; false = geometry not covered
-bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, int n, int Cin, int Cout, int H, int W, int stride, bool dry_run);
+bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, long long *group_floats_out, int n, int Cin, int Cout, int H,
+                  int W, int stride, bool dry_run);
+void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride);
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
                                int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
 template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk, int Wk, int hwc);
