@@ -126,6 +126,19 @@ void  trainlib_instnorm_act_fp16_bw_cl(void *trainlib_instnorm_act_args);
 void  trainlib_conv2d_fp32_bw_input_grads_acc_cl(void *Conv2D_args);
 void  trainlib_conv2d_fp16_bw_input_grads_acc_cl(void *Conv2D_args_fp16);
 
+/* ---- Deferred reductions (off by default).  Weight gradients and norm-parameter gradients are produced as partial results
+ * and then summed by a small kernel per call; a network of thousands of streams issues two dozen such sums per backward
+ * pass.  While the mode is on, device-resident calls keep their partial results in a library-owned arena and the library
+ * runs ALL pending sums as ONE launch when pulp_gradient_descent_*, trainlib_synchronize, trainlib_memcpy_d2h,
+ * trainlib_timer_stop_ms, trainlib_graph_begin/_end or trainlib_set_stream is called, when the mode is switched off, or
+ * on trainlib_flush_reductions().  Until then the gradient buffers of the deferred calls do not hold their values: flush
+ * before anything outside the library (a collective, a kernel of your own, a cudaMemcpy) reads a gradient.  The values
+ * are those of the immediate mode (same summation trees).  The arena is sized at a flush from what the calls since the
+ * previous flush asked for: the first pass of a workload in this mode still sums at once, and so does any call whose
+ * partial results do not fit (after a graph capture the arena is never moved again). */
+void  trainlib_set_deferred_reductions(int on);
+void  trainlib_flush_reductions(void);
+
 /* ---- CUDA graphs.  Entry-point calls made between begin and end are recorded instead of executed (device pointers
  * only: a host pointer would need a synchronous copy); the handle replays them with one launch on the library's
  * stream.  The recorded launches keep the addresses they saw, including library scratch: run the same calls once

@@ -248,6 +248,7 @@ template <class F> void conv2d_wg_impl(void *args)
         const T *xc = hwc_in<T>(sc, x, g.n, g.Cin, g.Hin, g.Win), *dyc = hwc_in<T>(sc, dy, g.n, g.Cout, g.Hout, g.Wout);
         T *dwc = sc.scratch<T>((size_t)g.Cout * g.Cin * g.Hk * g.Wk);
         if (!xc || !dyc || !dwc) return;
+        sc.no_deferral();                           // the permutation below reads dwc at once
         conv_wg<T>(sc, g, xc, dyc, dwc, db);
         hwc_out<T>(dwc, dw, g.Cout, g.Cin, g.Hk, g.Wk);
         return;
@@ -741,6 +742,7 @@ template <class F> void sgd_impl(void *args)
 {
     auto *a = (typename F::optim_t *)args; typedef typename F::T T;
     const float lr = F::f(a->learning_rate), lambda = F::f(a->weight_decay_lambda);
+    if (ready()) defer_flush();                                   // the gradients read here may have their sums pending
     Scope sc;
     {
         const size_t n = (size_t)a->weights->dim;

@@ -60,6 +60,11 @@ public:
     template <class T> T *inout(T *p, size_t n) { return (T *)map((void *)p, n * sizeof(T), true, true); }
     template <class T> T *scratch(size_t n) { return (T *)alloc(n * sizeof(T)); }   // device-only temporary
     bool ok() const { return ok_; }
+    bool staged() const { return staged_; }   // some buffer of this call lives in host memory (mirrored in the arena)
+    // a reduction of this call may be deferred: every buffer is the caller's own device memory and the call does not go
+    // on to read the result itself
+    bool may_defer() const { return !staged_ && !no_defer_; }
+    void no_deferral() { no_defer_ = true; }
 private:
     struct Entry { void *host; void *dev; size_t bytes; bool write_back; bool copied_in; };
     void *map(void *p, size_t bytes, bool copy_in, bool copy_out);
@@ -68,9 +73,19 @@ private:
     size_t arena_mark_;
     bool ok_;
     bool staged_;
+    bool no_defer_ = false;
 };
 
 bool is_device_pointer(const void *p);
+bool arena_pinned();                // a captured graph holds addresses of library-owned device memory: never move it again
+
+// deferred reductions (tl_defer.cu): partial results kept until one batched launch sums them all
+bool defer_enabled();
+float *defer_alloc(size_t floats);
+void defer_plain(const float *part, float *out, long long n, int groups);
+void defer_columns(const float *part, float *out, int rows, int dim, int pairs);
+void defer_wgt(const float *part, float *out, int groups, long long group_floats, int Cin, int Cout, int s2, int xg, int cigs, int ncopy);
+void defer_flush();
 
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 

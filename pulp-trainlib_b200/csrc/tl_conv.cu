@@ -866,6 +866,13 @@ __global__ void __launch_bounds__(1024) reduce_partials_kernel(const float *__re
     }
 }
 
+// the sum of `groups` partial results into `out`: now, or noted for the batched launch of the deferred mode
+template <class T> static void reduce_partials(const float *part, T *out, long long n, int groups, bool deferred)
+{
+    if (deferred) { defer_plain(part, reinterpret_cast<float *>(out), n, groups); return; }       // deferred only ever with T = float
+    TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(n, 32), 1024, 0, part, out, n, groups);
+}
+
 // Fallback for filter windows above 5x5: one CTA per weight, block-wide reduction.
 template <class T>
 __global__ void __launch_bounds__(256) conv_wg_direct_kernel(ConvGeom g, const T *__restrict__ x, const T *__restrict__ dy, T *__restrict__ dw)
@@ -921,10 +928,11 @@ template <> bool try_tc_wg<float>(Scope &sc, const ConvGeom &g, const float *x, 
     int groups = 0;
     long long group_floats = 0;
     if (!conv_wgt_run(x, dy, nullptr, sm_count(), &groups, &group_floats, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, true)) return false;
-    float *part = sc.scratch<float>((size_t)groups * (size_t)group_floats);
+    bool deferred;
+    float *part = partials_alloc<float>(sc, (size_t)groups * (size_t)group_floats, deferred);
     if (!part) return false;
     if (!conv_wgt_run(x, dy, part, groups, &groups, &group_floats, g.n, g.Cin, g.Cout, g.Hout, g.Wout, g.sh, false)) return false;
-    conv_wgt_reduce(part, dw, groups, g.Cin, g.Cout, g.sh);
+    conv_wgt_reduce(part, dw, groups, g.Cin, g.Cout, g.sh, deferred);
     return true;
 }
 
@@ -935,10 +943,11 @@ template <> bool try_1x1_wg<float>(Scope &sc, const ConvGeom &g, const float *x,
     int groups = 0;
     if (!conv1x1s_wg(g, x, dy, nullptr, 8 * sm_count(), &groups, true)) return false;
     const long long nw = (long long)g.Cout * g.Cin;
-    float *part = sc.scratch<float>((size_t)groups * nw);
+    bool deferred;
+    float *part = partials_alloc<float>(sc, (size_t)groups * nw, deferred);
     if (!part) return false;
     if (!conv1x1s_wg(g, x, dy, part, groups, &groups, false)) return false;
-    TL_LAUNCH((reduce_partials_kernel<float>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
+    reduce_partials<float>(part, dw, nw, groups, deferred);
     return true;
 }
 
@@ -972,7 +981,8 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
             int groups = (2 * sm_count()) / (ci_tiles * co_tiles);
             if (groups > items) groups = (int)items;
             if (groups < 1) groups = 1;
-            float *part = sc.scratch<float>((size_t)groups * nw);
+            bool deferred;
+            float *part = partials_alloc<T>(sc, (size_t)groups * nw, deferred);
             if (!part) return;
             const int vec = sizeof(T) == 4 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
             dim3 grid(ci_tiles * co_tiles, groups);
@@ -992,7 +1002,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
 #undef TL_WG3_LAUNCH
 #undef TL_WG3_LAUNCH2
             profile_add_flops(conv_flops(g));
-            TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
+            reduce_partials<T>(part, dw, nw, groups, deferred);
             return;
         }
     }
@@ -1012,7 +1022,8 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     int groups = ceil_div(4 * sm_count(), ci_tiles * co_tiles);
     if (groups > items) groups = (int)items;
     if (groups < 1) groups = 1;
-    float *part = sc.scratch<float>((size_t)groups * nw);
+    bool deferred;
+    float *part = partials_alloc<T>(sc, (size_t)groups * nw, deferred);
     if (!part) return;
     dim3 grid(ci_tiles * co_tiles, groups);
 #define TL_WG_LAUNCH(KH_, KW_)                                                                                        \
@@ -1026,7 +1037,7 @@ template <class T> void conv_wg(Scope &sc, const ConvGeom &g, const T *x, const 
     else TL_WG_LAUNCH(5, 5);
 #undef TL_WG_LAUNCH
     profile_add_flops(conv_flops(g));
-    TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(nw, 32), 1024, 0, part, dw, nw, groups);
+    reduce_partials<T>(part, dw, nw, groups, deferred);
 }
 
 // ------------------------------------------------------------------ explicit im2row / im2col / blocktranspose

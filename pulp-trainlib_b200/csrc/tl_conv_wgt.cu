@@ -304,10 +304,11 @@ __global__ void __launch_bounds__(1024) wgt_reduce_kernel(const float *__restric
     if (kw >= 0) dw[((long long)co * Cin + ci) * 9 + a * 3 + kw] = t;
 }
 // the second half of conv_wgt_run: sums `groups` partials into dW
-void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride)
+void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride, bool deferred)
 {
     const int cigs = Cin / 8, s2 = stride == 2 ? 1 : 0, xg = s2 ? 2 * cigs : cigs, ncopy = s2 ? 2 : 3, MB = ceil_div(3 * xg, 16);
     const long long nn = (long long)MB * 128 * ncopy * Cout;
+    if (deferred) { defer_wgt(part, dw, groups, nn, Cin, Cout, s2, xg, cigs, ncopy); return; }
     TL_LAUNCH(wgt_reduce_kernel, ceil_div(nn, 32), 1024, 0, part, dw, groups, Cin, Cout, s2, xg, cigs, ncopy, MB);
 }
 

@@ -323,7 +323,11 @@ static bool column_sum_launch(Scope &sc, const TI *in, TO *out, int n, int dim, 
     return true;
 }
 // dgb = [sum of a | sum of b] over the streams of part[n][C] (a, b) pairs
-template <class T> static void instnorm_param_reduce(Scope &sc, const float *part, T *dgb, int n, int C) { column_sum_launch<float, T>(sc, part, dgb, n, 2 * C, C); }
+template <class T> static void instnorm_param_reduce(Scope &sc, const float *part, T *dgb, int n, int C, bool deferred = false)
+{
+    if (deferred) { defer_columns(part, reinterpret_cast<float *>(dgb), n, 2 * C, C); return; }     // deferred only ever with T = float
+    column_sum_launch<float, T>(sc, part, dgb, n, 2 * C, C);
+}
 template <class T> void column_sum(Scope &sc, const T *in, T *out, int n, int dim) { column_sum_launch<T, T>(sc, in, out, n, dim, 0); }
 
 // fp32 planes of up to 1024 elements (a multiple of 4): one warp per plane, the plane held in registers as NV 16-byte
@@ -661,21 +665,23 @@ template <class T>
 void instnorm_bw_param(Scope &sc, const T *x, const T *dy, T *dgb, const T *mean, const T *stdev, int n, int C, int D)
 {
     if (n * C <= 0) return;
-    float *part = sc.scratch<float>((size_t)2 * n * C);
+    bool deferred;
+    float *part = partials_alloc<T>(sc, (size_t)2 * n * C, deferred);
     if (!part) return;
     if (!instnorm_bw_warp(x, dy, (T *)nullptr, part, (const T *)nullptr, mean, (const T *)nullptr, stdev, n, C, D))
         TL_LAUNCH((instnorm_bw_param_kernel<T>), n * C, D >= 256 ? 256 : 64, 0, x, dy, part, mean, stdev, D);
-    instnorm_param_reduce<T>(sc, part, dgb, n, C);
+    instnorm_param_reduce<T>(sc, part, dgb, n, C, deferred);
 }
 // Both gradients of one layer in one pass over x and dy (falls back to the two separate passes).
 template <class T>
 void instnorm_bw_both(Scope &sc, const T *x, const T *dy, T *dx, T *dgb, const T *gamma, const T *mean, const T *var, const T *stdev, int n, int C, int D)
 {
     if (n * C <= 0) return;
-    float *part = sc.scratch<float>((size_t)2 * n * C);
+    bool deferred;
+    float *part = partials_alloc<T>(sc, (size_t)2 * n * C, deferred);
     if (!part) return;
     if (instnorm_bw_warp(x, dy, dx, part, gamma, mean, var, stdev, n, C, D)) {
-        instnorm_param_reduce<T>(sc, part, dgb, n, C);
+        instnorm_param_reduce<T>(sc, part, dgb, n, C, deferred);
         return;
     }
     instnorm_bw_param<T>(sc, x, dy, dgb, mean, stdev, n, C, D);
@@ -701,10 +707,11 @@ void instnorm_relu_bw(Scope &sc, const T *x, const T *y, T *dy, const T *dy2, T 
                       int n, int C, int D)
 {
     if (n * C <= 0) return;
-    float *part = sc.scratch<float>((size_t)2 * n * C);
+    bool deferred;
+    float *part = partials_alloc<T>(sc, (size_t)2 * n * C, deferred);
     if (!part) return;
     if (instnorm_bw_warp(x, dy, dx, part, gb, mean, var, stdev, n, C, D, true, dy2)) {
-        instnorm_param_reduce<T>(sc, part, dgb, n, C);
+        instnorm_param_reduce<T>(sc, part, dgb, n, C, deferred);
         return;
     }
     if (dy2) add<T>(dy2, dy, dy, (long long)n * C * D);

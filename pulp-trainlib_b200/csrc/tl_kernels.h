@@ -54,14 +54,25 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
                  int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false,
                  const ConvTcClass *cls = nullptr);
 int conv_tc_status();
-// 1x1 strided convolutions on CUDA cores (tl_conv1x1.cu); false = geometry not covered, nothing launched
+// Partial results of an fp32 reduction: from the deferred-reduction arena when that mode is on and every buffer of the call
+// is device-resident (`deferred` = true: the caller notes the sum with defer_*), else scratch of the call (the caller sums at once).
+template <class T> inline float *partials_alloc(Scope &sc, size_t floats, bool &deferred)
+{
+    deferred = false;
+    if (sizeof(T) == 4 && sc.may_defer()) {
+        float *p = defer_alloc(floats);
+        if (p) { deferred = true; return p; }
+    }
+    return sc.scratch<float>(floats);
+}
+// 1x1 strided convolutions (tl_conv1x1.cu); false = geometry not covered, nothing launched
 bool conv1x1s_fw(const ConvGeom &g, const float *x, const float *w, const float *bias, float *y);
 bool conv1x1s_ig(const ConvGeom &g, const float *dy, const float *w, float *dx);   // dX += gradient
 bool conv1x1s_wg(const ConvGeom &g, const float *x, const float *dy, float *part, int part_groups, int *groups_out, bool dry_run);
 // tensor-core weight gradient (tl_conv_wgt.cu): partial results per CTA into `part`; false = geometry not covered
 bool conv_wgt_run(const float *x, const float *dy, float *part, int part_groups, int *groups_out, long long *group_floats_out, int n, int Cin, int Cout, int H,
                   int W, int stride, bool dry_run);
-void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride);
+void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride, bool deferred);   // deferred: noted for the batched launch
 template <class T> void im2row(const T *src, T *buf, int C, int H, int W, int Hk, int Wk, int Ho, int Wo,
                                int sh, int sw, int padU, int padL, int mode_ig, int hwc, int transposed_buf);
 template <class T> void blocktransp(const T *w, T *bt, int Cin, int Cout, int Hk, int Wk, int hwc);

@@ -176,6 +176,8 @@ bool is_device_pointer(const void *p)
 }
 
 // ---------------------------------------------------------------- arena
+bool arena_pinned() { return g.arena_pinned; }
+
 static size_t arena_mark()
 {
     // position encoded as (chunk index << 48) | offset; scopes nest in stack order
@@ -296,7 +298,7 @@ void trainlib_clear_error(void) { if (!(g.err == TL_ERR_CUDA && g.cuda_sticky) &
 
 int trainlib_init(int device) { return init_device(device); }
 int trainlib_device(void) { return g.device; }
-void trainlib_set_stream(void *s) { if (ready()) g.cur_stream = s ? (cudaStream_t)s : g.own_stream; }
+void trainlib_set_stream(void *s) { if (ready()) { defer_flush(); g.cur_stream = s ? (cudaStream_t)s : g.own_stream; } }
 void *trainlib_stream(void) { return ready() ? (void *)g.cur_stream : nullptr; }
 static bool g_capturing_now();
 // A tensor-core kernel whose bounded wait gave up returns early and records the wait's id in a device word.  Every
@@ -311,7 +313,7 @@ static void check_tc_status()
     if (cudaStreamSynchronize(g.cur_stream) != cudaSuccess) { cudaGetLastError(); return; }
     if (h != 0) set_error(TL_ERR_TIMEOUT, "a tensor-core kernel gave up on bounded wait %d and returned early: its output is invalid", h);
 }
-void trainlib_synchronize(void) { if (ready() && TL_CUDA(cudaStreamSynchronize(g.cur_stream))) check_tc_status(); }
+void trainlib_synchronize(void) { if (!ready()) return; defer_flush(); if (TL_CUDA(cudaStreamSynchronize(g.cur_stream))) check_tc_status(); }
 
 void trainlib_set_memory_mode(int mode) { if (mode >= TL_MEM_AUTO && mode <= TL_MEM_HOST) g.mem_mode = mode; }
 int trainlib_memory_mode(void) { return g.mem_mode; }
@@ -340,6 +342,7 @@ int trainlib_memcpy_h2d(void *dev, const void *host, size_t bytes)
 int trainlib_memcpy_d2h(void *host, const void *dev, size_t bytes)
 {
     if (!ready()) return g.err;
+    defer_flush();                                  // the bytes read may be a gradient whose sum is still pending
     if (!TL_CUDA(cudaMemcpyAsync(host, dev, bytes, cudaMemcpyDeviceToHost, g.cur_stream))) return g.err;
     return TL_CUDA(cudaStreamSynchronize(g.cur_stream)) ? TL_OK : g.err;
 }
@@ -388,6 +391,7 @@ double trainlib_timer_stop_ms(void)
 {
     if (!ready()) return -1.0;
     float ms = 0.f;
+    defer_flush();                                  // pending sums belong to the timed work
     if (!TL_CUDA(cudaEventRecord(g.ev1, g.cur_stream))) return -1.0;
     if (!TL_CUDA(cudaEventSynchronize(g.ev1))) return -1.0;
     if (!TL_CUDA(cudaEventElapsedTime(&ms, g.ev0, g.ev1))) return -1.0;
@@ -405,6 +409,7 @@ int trainlib_graph_begin(void)
 {
     if (!ready()) return g.err;
     if (g_capturing) { set_error(TL_ERR_BAD_ARGS, "trainlib_graph_begin: a capture is already open"); return TL_ERR_BAD_ARGS; }
+    defer_flush();                                  // sums pending from before the capture run now, outside the graph
     if (!TL_CUDA(cudaStreamBeginCapture(g.cur_stream, cudaStreamCaptureModeRelaxed))) return g.err;
     g_capturing = true; g_capture_launches0 = g.launches;
     g.arena_pinned = true;
@@ -413,6 +418,7 @@ int trainlib_graph_begin(void)
 void *trainlib_graph_end(void)
 {
     if (!ready() || !g_capturing) return nullptr;
+    defer_flush();                                  // sums pending from the captured calls become the graph's last node
     g_capturing = false;
     cudaGraph_t graph = nullptr;
     if (!TL_CUDA(cudaStreamEndCapture(g.cur_stream, &graph)) || !graph) return nullptr;

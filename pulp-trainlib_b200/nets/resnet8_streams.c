@@ -435,6 +435,10 @@ static void stage_bw(int conv_a, int norm_a, int conv_b, int norm_b, int proj, i
 
 void resnet8_backward(void)
 {
+#ifndef NET_REFERENCE
+    /* the two dozen fixed-order sums of partial gradients run as one launch at the end of the pass (same values) */
+    if (g_fuse) trainlib_set_deferred_reductions(1);
+#endif
     loss_call(&a_loss, pulp_CrossEntropyLoss_backward);
     linear_bw(&a_fc);
     pool_call(&a_pool, pulp_avgpool_fp32_bw_cl);
@@ -444,6 +448,7 @@ void resnet8_backward(void)
     if (g_fuse) norm_relu_bw(&a_norm[0], b_sum[0].diff); else { relu_bw(&a_relu_n[0]); norm_bw(&a_norm[0]); }
     conv_bw(C0);
 #ifndef NET_REFERENCE
+    if (g_fuse) trainlib_set_deferred_reductions(0);   /* runs the pending sums: the gradient buffer is complete on return */
     if (g_host_slot >= 0) { trainlib_mark_consumed(g_host_slot); g_host_slot = -1; }   /* last reader of that batch copy */
 #endif
 }

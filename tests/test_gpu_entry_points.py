@@ -451,3 +451,58 @@ def test_profile_credits_useful_flops_to_the_kernel_that_ran(pkg, gpulib):
         r.close()
     finally:
         gpulib.trainlib_set_streams(1)
+
+
+@pytest.mark.gpu
+def test_deferred_reductions_give_the_same_bits_in_one_launch(pkg, gpulib):
+    """trainlib_set_deferred_reductions: the weight gradients of four convolutions (FFMA, tcgen05 stride 1 and 2, 1x1 strided
+    kernels) and the parameter gradient of an instance norm, issued back to back, are summed by one batched launch at
+    the flush, with the bits of the immediate mode"""
+    cases = [(geom(16, 32, 32, 16, 3, pad=1), 40), (geom(32, 16, 16, 32, 3, pad=1), 300), (geom(16, 32, 32, 32, 1, stride=2), 33),
+             (geom(32, 16, 16, 64, 3, stride=2, pad=1), 260)]
+    results = {}
+    for mode in (0, 1):
+        r = AbiRunner(pkg, gpulib, device=True)
+        outs, calls = [], []
+        for g, n in cases:
+            Ho, Wo = out_hw(g)
+            rs = np.random.default_rng(g["Cin"] + n)
+            xs = rs.uniform(-1, 1, (n, g["Cin"], g["Hin"], g["Win"])).astype(np.float32); dys = rs.standard_normal((n, g["Cout"], Ho, Wo)).astype(np.float32)
+            X, dY, dW, one = r.t(xs), r.t(dys), r.zeros(g["Cout"], g["Cin"], g["Hk"], g["Wk"]), r.zeros(1)
+            args = r.args("Conv2D_args", input=r.blob(X, one, C=g["Cin"], H=g["Hin"], W=g["Win"]), coeff=r.blob(one, dW, C=g["Cin"], H=g["Hk"], W=g["Wk"], dim=g["Cout"] * g["Cin"] * g["Hk"] * g["Wk"]),
+                          bias=r.blob(one, one), output=r.blob(one, dY, C=g["Cout"], H=Ho, W=Wo), Lpad=g["padL"], Rpad=g["padR"], Upad=g["padU"], Dpad=g["padD"],
+                          stride_h=g["sh"], stride_w=g["sw"], i2c_buffer=one, bt_buffer=one, USE_BIASES=0, USE_IM2COL=1, HWC=0)
+            calls.append((n, "pulp_conv2d_fp32_bw_param_grads_cl", args)); outs.append(dW)
+        n, C, H = 200, 16, 32
+        rng = seeded(123)
+        xs = rng.standard_normal((n, C, H, H)).astype(np.float32); dys = rng.standard_normal((n, C, H, H)).astype(np.float32)
+        X, dX, Y, dY, GB, dGB = r.t(xs), r.zeros(n, C, H, H), r.zeros(n, C, H, H), r.t(dys), r.t(np.ones(2 * C, np.float32)), r.zeros(2 * C)
+        m, v, s = r.zeros(n * C), r.zeros(n * C), r.zeros(n * C)
+        nargs = r.args("InstNorm_args", input=r.blob(X, dX, C=C, H=H, W=H), output=r.blob(Y, dY, C=C, H=H, W=H), coeff=r.blob(GB, dGB, dim=2 * C, W=2 * C),
+                       running_mean=m, running_var=v, running_stdev=s, freeze_running_params=0, skip_wg_grad=0, skip_in_grad=0)
+        gpulib.trainlib_set_streams(n); r.call("pulp_instnorm_fp32_fw_cl", nargs)
+        calls.append((n, "pulp_instnorm_fp32_bw_cl", nargs)); outs.append(dGB)
+        gpulib.trainlib_set_deferred_reductions(mode)
+        for n_, fn, a in calls:                     # the first pass in the mode sizes the arena of partial results (its sums run at once)
+            gpulib.trainlib_set_streams(n_); r.call(fn, a)
+        gpulib.trainlib_flush_reductions()
+        for o in outs:
+            gpulib.trainlib_memset(o.dev.ptr, 0, o.dev.nbytes)
+        gpulib.trainlib_profile(1)
+        try:
+            for n_, fn, a in calls:
+                gpulib.trainlib_set_streams(n_); r.call(fn, a)
+            gpulib.trainlib_flush_reductions()
+        finally:
+            gpulib.trainlib_profile(0); gpulib.trainlib_set_deferred_reductions(0); gpulib.trainlib_set_streams(1)
+        table = {row[0].strip("()").split("<")[0]: row[1] for row in pkg.profile_table(gpulib)}
+        sums = sum(table.get(k, 0) for k in ("reduce_partials_kernel", "wgt_reduce_kernel", "column_direct_kernel", "column_partial_kernel"))
+        if mode:
+            assert table.get("deferred_reduce_kernel", 0) == 1 and sums == 0, table
+        else:
+            assert "deferred_reduce_kernel" not in table and sums == 5, table
+        results[mode] = [o.get().copy() for o in outs]
+        r.close()
+    for k, (a, b) in enumerate(zip(results[0], results[1])):
+        assert np.abs(a).max() > 0 and np.array_equal(a, b), "deferred and immediate sums differ: output %d, %d of %d elements, max |a| %g, max |a - b| %g" % (
+            k, int((a != b).sum()), a.size, float(np.abs(a).max()), float(np.abs(a - b).max()))
