@@ -203,6 +203,7 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                 float *out = p.part + (long long)blockIdx.x * ((long long)p.MB * 128 * NBc);
                 for (int m = 0; m < p.MB; m++) {
                     float *orow = out + (long long)(m * 128 + warp * 32 + lane) * NBc;
+                    const bool valid = m * 16 + (warp * 32 + lane) / 8 < 3 * p.xg;     // rows past the last channel group are never read
                     for (int c0 = 0; c0 < NBc; c0 += 16) {
                         float acc[16];
 #pragma unroll
@@ -217,7 +218,7 @@ conv_wgt_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constan
                             for (int i = 0; i < 16; i++) acc[i] += __uint_as_float(v[i]) + (p.stack ? __uint_as_float(w[i]) : 0.f);
                         }
 #pragma unroll
-                        for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4 *>(orow + c0 + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                        for (int i = 0; i < 16; i += 4) if (valid) *reinterpret_cast<float4 *>(orow + c0 + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
                     }
                 }
             }
@@ -284,18 +285,18 @@ __global__ void __launch_bounds__(1024) wgt_reduce_kernel(const float *__restric
     __shared__ float sm[32][33];
     const int wx = threadIdx.x & 31, sl = threadIdx.x >> 5, NBc = ncopy * Cout;
     const long long nn = (long long)MB * 128 * NBc, i = (long long)blockIdx.x * 32 + wx;
+    const int row = (int)(i / NBc), col = (int)(i % NBc);
+    const int grp = row / 8, ci8 = row & 7;                             // row = m * 128 + lane of the accumulator: 16 groups of 8 per M block
+    const bool used = i < nn && grp < 3 * xg;                           // not a padding row of the last M block (those are never written)
     float s = 0.f;
-    if (i < nn)
+    if (used)
         for (int g = sl; g < groups; g += 32) s += part[(long long)g * nn + i];
     sm[sl][wx] = s;
     __syncthreads();
-    if (sl != 0 || i >= nn) return;
+    if (sl != 0 || !used) return;
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; k++) t += sm[k][wx];
-    const int row = (int)(i / NBc), col = (int)(i % NBc);
-    const int grp = row / 8, ci8 = row & 7;                             // row = m * 128 + lane of the accumulator: 16 groups of 8 per M block
-    if (grp >= 3 * xg) return;                                          // padding rows of the last M block
     const int a = grp / xg, par = (grp % xg) / cigs, ci = (grp % cigs) * 8 + ci8;
     const int b = col / Cout, co = col % Cout;
     // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b;

@@ -37,6 +37,13 @@ static struct {
     DeferBatch batch = {};
 } d;
 
+// One CTA = 32 consecutive elements of one job x 32 slices of its partial results: thread (slice, lane) adds the partials
+// slice, slice + 32, ... of element lane, the 32 slice sums of an element are then added in slice order.  That is the
+// summation tree of reduce_partials_kernel / wgt_reduce_kernel (PLAIN, WGT) and of column_direct_kernel (COLUMNS, up to
+// 1024 rows); above 1024 rows a lane keeps eight running sums instead of four so that more loads are in flight (the
+// immediate mode takes two passes there).  (128 elements per CTA with four per thread measured slower: 89 against 70 us
+// for the sums of a 4096-stream backward pass.)
+static constexpr int DEFER_ELEMS = 32;
 __global__ void __launch_bounds__(1024) deferred_reduce_kernel(const __grid_constant__ DeferBatch b)
 {
     __shared__ float sm[32][33];
@@ -46,11 +53,22 @@ __global__ void __launch_bounds__(1024) deferred_reduce_kernel(const __grid_cons
     const long long n = b.job[j].n;
     const int groups = b.job[j].groups, kind = b.job[j].kind;
     const int wx = threadIdx.x & 31, sl = threadIdx.x >> 5;
-    const long long i = (long long)((int)blockIdx.x - b.job[j].first_cta) * 32 + wx;
+    const long long i = (long long)((int)blockIdx.x - b.job[j].first_cta) * DEFER_ELEMS + wx;
     float s = 0.f;
-    if (i < n) {
-        if (kind == DEFER_COLUMNS) {
-            // a lane walks rows sl, sl + 32, ... four at a time; the four sums are added in a fixed order
+    bool used = i < n;
+    if (kind == DEFER_WGT && used) used = (int)(i / (b.job[j].a5 * b.job[j].a1)) / 8 < 3 * b.job[j].a3;   // padding rows are never written
+    if (used) {
+        if (kind == DEFER_COLUMNS && groups > 1024) {
+            float a[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) a[q] = 0.f;
+            int r = sl;
+            for (; r + 224 < groups; r += 256)
+#pragma unroll
+                for (int q = 0; q < 8; q++) a[q] += part[(long long)(r + 32 * q) * n + i];
+            for (; r < groups; r += 32) a[0] += part[(long long)r * n + i];
+            s = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+        } else if (kind == DEFER_COLUMNS) {
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             int r = sl;
             for (; r + 96 < groups; r += 128) {
@@ -65,7 +83,7 @@ __global__ void __launch_bounds__(1024) deferred_reduce_kernel(const __grid_cons
     }
     sm[sl][wx] = s;
     __syncthreads();
-    if (sl != 0 || i >= n) return;
+    if (sl != 0 || !used) return;
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; k++) t += sm[k][wx];
@@ -124,7 +142,7 @@ static void defer_push(const DeferJob &job)
     DeferJob &J = d.batch.job[d.batch.count++];
     J = job;
     J.first_cta = d.batch.ctas;
-    d.batch.ctas += ceil_div(job.n, 32);
+    d.batch.ctas += ceil_div(job.n, DEFER_ELEMS);
 }
 void defer_plain(const float *part, float *out, long long n, int groups)
 {
