@@ -866,11 +866,28 @@ __global__ void __launch_bounds__(1024) reduce_partials_kernel(const float *__re
     }
 }
 
+// fp32 results: 512 consecutive weights per CTA, 16-byte loads (partial_sums_quad; the deferred mode uses the same function)
+__global__ void __launch_bounds__(1024) reduce_partials_f32_kernel(const float *__restrict__ part, float *__restrict__ out, long long n, int groups)
+{
+    __shared__ float4 sm[8][128];
+    const long long i = (long long)blockIdx.x * PSUM_ELEMS + (threadIdx.x & 127) * 4;
+    float4 t;
+    if (!partial_sums_quad(part, n, groups, i, true, t, sm)) return;
+    out[i] = t.x;
+    if (i + 1 < n) out[i + 1] = t.y;
+    if (i + 2 < n) out[i + 2] = t.z;
+    if (i + 3 < n) out[i + 3] = t.w;
+}
 // the sum of `groups` partial results into `out`: now, or noted for the batched launch of the deferred mode
 template <class T> static void reduce_partials(const float *part, T *out, long long n, int groups, bool deferred)
 {
-    if (deferred) { defer_plain(part, reinterpret_cast<float *>(out), n, groups); return; }       // deferred only ever with T = float
-    TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(n, 32), 1024, 0, part, out, n, groups);
+    if constexpr (sizeof(T) == 4) {
+        float *o = reinterpret_cast<float *>(out);
+        if (deferred) defer_plain(part, o, n, groups);
+        else TL_LAUNCH(reduce_partials_f32_kernel, ceil_div(n, PSUM_ELEMS), 1024, 0, part, o, n, groups);
+    } else {
+        TL_LAUNCH((reduce_partials_kernel<T>), ceil_div(n, 32), 1024, 0, part, out, n, groups);
+    }
 }
 
 // Fallback for filter windows above 5x5: one CTA per weight, block-wide reduction.

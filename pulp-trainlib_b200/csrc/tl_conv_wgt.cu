@@ -277,32 +277,22 @@ void *tc_encode_tiled_fn();
 int *tc_status_word();
 
 // dW[co][ci][kh][kw] = sum over the CTAs' partials, which lie in the accumulators' layout: row = 8 channels x (filter row,
-// pixel parity, channel group), column = (copy of the dY row, co).  32 consecutive elements x 32 slices of the groups per
-// CTA (slice s adds groups s, s + 32, ...; the slices are added in slice order), as in reduce_partials_kernel.
+// pixel parity, channel group), column = (copy of the dY row, co).  512 consecutive elements per CTA (partial_sums_quad).
 __global__ void __launch_bounds__(1024) wgt_reduce_kernel(const float *__restrict__ part, float *__restrict__ dw, int groups, int Cin, int Cout,
                                                           int s2, int xg, int cigs, int ncopy, int MB)
 {
-    __shared__ float sm[32][33];
-    const int wx = threadIdx.x & 31, sl = threadIdx.x >> 5, NBc = ncopy * Cout;
-    const long long nn = (long long)MB * 128 * NBc, i = (long long)blockIdx.x * 32 + wx;
-    const int row = (int)(i / NBc), col = (int)(i % NBc);
-    const int grp = row / 8, ci8 = row & 7;                             // row = m * 128 + lane of the accumulator: 16 groups of 8 per M block
-    const bool used = i < nn && grp < 3 * xg;                           // not a padding row of the last M block (those are never written)
-    float s = 0.f;
-    if (used)
-        for (int g = sl; g < groups; g += 32) s += part[(long long)g * nn + i];
-    sm[sl][wx] = s;
-    __syncthreads();
-    if (sl != 0 || !used) return;
-    float t = 0.f;
+    __shared__ float4 sm[8][128];
+    const int NBc = ncopy * Cout;
+    const long long nn = (long long)MB * 128 * NBc, i = (long long)blockIdx.x * PSUM_ELEMS + (threadIdx.x & 127) * 4;
+    const bool used = i < nn && (int)(i / NBc) / 8 < 3 * xg;            // a quad lies inside one row (NBc is a multiple of 16)
+    float4 t;
+    if (!partial_sums_quad(part, nn, groups, i, used, t, sm)) return;
+    const float v[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-    for (int k = 0; k < 32; k++) t += sm[k][wx];
-    const int a = grp / xg, par = (grp % xg) / cigs, ci = (grp % cigs) * 8 + ci8;
-    const int b = col / Cout, co = col % Cout;
-    // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b;
-    // stride 2: even pixels with dY[x] are column 1, odd pixels with dY[x] column 2, with dY[x + 1] column 0
-    const int kw = !s2 ? b : (par == 0 ? (b == 1 ? 1 : -1) : (b == 1 ? 2 : 0));
-    if (kw >= 0) dw[((long long)co * Cin + ci) * 9 + a * 3 + kw] = t;
+    for (int e = 0; e < 4; e++) {
+        const long long o = wgt_partial_index(i + e, Cin, Cout, s2, xg, cigs, ncopy);
+        if (o >= 0) dw[o] = v[e];
+    }
 }
 // the second half of conv_wgt_run: sums `groups` partials into dW
 void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout, int stride, bool deferred)
@@ -310,7 +300,7 @@ void conv_wgt_reduce(const float *part, float *dw, int groups, int Cin, int Cout
     const int cigs = Cin / 8, s2 = stride == 2 ? 1 : 0, xg = s2 ? 2 * cigs : cigs, ncopy = s2 ? 2 : 3, MB = ceil_div(3 * xg, 16);
     const long long nn = (long long)MB * 128 * ncopy * Cout;
     if (deferred) { defer_wgt(part, dw, groups, nn, Cin, Cout, s2, xg, cigs, ncopy); return; }
-    TL_LAUNCH(wgt_reduce_kernel, ceil_div(nn, 32), 1024, 0, part, dw, groups, Cin, Cout, s2, xg, cigs, ncopy, MB);
+    TL_LAUNCH(wgt_reduce_kernel, ceil_div(nn, PSUM_ELEMS), 1024, 0, part, dw, groups, Cin, Cout, s2, xg, cigs, ncopy, MB);
 }
 
 // Weight gradient on the tensor cores for 3x3 / pad 1 with stride 1 or 2 and channel counts that are multiples of 8

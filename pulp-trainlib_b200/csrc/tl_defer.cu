@@ -37,28 +37,41 @@ static struct {
     DeferBatch batch = {};
 } d;
 
-// One CTA = 32 consecutive elements of one job x 32 slices of its partial results: thread (slice, lane) adds the partials
-// slice, slice + 32, ... of element lane, the 32 slice sums of an element are then added in slice order.  That is the
-// summation tree of reduce_partials_kernel / wgt_reduce_kernel (PLAIN, WGT) and of column_direct_kernel (COLUMNS, up to
-// 1024 rows); above 1024 rows a lane keeps eight running sums instead of four so that more loads are in flight (the
-// immediate mode takes two passes there).  (128 elements per CTA with four per thread measured slower: 89 against 70 us
-// for the sums of a 4096-stream backward pass.)
-static constexpr int DEFER_ELEMS = 32;
+// A CTA serves one job.  Weight-gradient partials (PLAIN, WGT): 512 consecutive elements through partial_sums_quad, the
+// function the immediate kernels use.  Norm-parameter partials (COLUMNS: few columns, one row per stream): 32 columns x 32
+// slices of the rows, thread (slice, column) adds rows slice, slice + 32, ... four at a time, the 32 slice sums are added
+// in slice order: the tree of column_direct_kernel up to 1024 rows; above, a lane keeps eight running sums so that more
+// loads are in flight (the immediate mode takes two passes there).
 __global__ void __launch_bounds__(1024) deferred_reduce_kernel(const __grid_constant__ DeferBatch b)
 {
-    __shared__ float sm[32][33];
+    __shared__ float4 sm4[8][128];
     int j = 0;
     while (j + 1 < b.count && (int)blockIdx.x >= b.job[j + 1].first_cta) j++;
     const float *__restrict__ part = b.job[j].part;
+    float *out = b.job[j].out;
     const long long n = b.job[j].n;
-    const int groups = b.job[j].groups, kind = b.job[j].kind;
+    const int groups = b.job[j].groups, kind = b.job[j].kind, cta = (int)blockIdx.x - b.job[j].first_cta;
+    if (kind != DEFER_COLUMNS) {
+        const int Cin = b.job[j].a0, Cout = b.job[j].a1, s2 = b.job[j].a2, xg = b.job[j].a3, cigs = b.job[j].a4, ncopy = b.job[j].a5;
+        const long long i = (long long)cta * PSUM_ELEMS + (threadIdx.x & 127) * 4;
+        const bool used = kind == DEFER_PLAIN || (i < n && (int)(i / (ncopy * Cout)) / 8 < 3 * xg);
+        float4 t;
+        if (!partial_sums_quad(part, n, groups, i, used, t, sm4)) return;
+        const float v[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            if (i + e >= n) break;
+            const long long o = kind == DEFER_PLAIN ? i + e : wgt_partial_index(i + e, Cin, Cout, s2, xg, cigs, ncopy);
+            if (o >= 0) out[o] = v[e];
+        }
+        return;
+    }
+    float (*sm)[33] = reinterpret_cast<float (*)[33]>(sm4);          // 32 x 33 floats of the 16 KB
     const int wx = threadIdx.x & 31, sl = threadIdx.x >> 5;
-    const long long i = (long long)((int)blockIdx.x - b.job[j].first_cta) * DEFER_ELEMS + wx;
+    const long long i = (long long)cta * 32 + wx;
     float s = 0.f;
-    bool used = i < n;
-    if (kind == DEFER_WGT && used) used = (int)(i / (b.job[j].a5 * b.job[j].a1)) / 8 < 3 * b.job[j].a3;   // padding rows are never written
-    if (used) {
-        if (kind == DEFER_COLUMNS && groups > 1024) {
+    if (i < n) {
+        if (groups > 1024) {
             float a[8];
 #pragma unroll
             for (int q = 0; q < 8; q++) a[q] = 0.f;
@@ -68,7 +81,7 @@ __global__ void __launch_bounds__(1024) deferred_reduce_kernel(const __grid_cons
                 for (int q = 0; q < 8; q++) a[q] += part[(long long)(r + 32 * q) * n + i];
             for (; r < groups; r += 32) a[0] += part[(long long)r * n + i];
             s = ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
-        } else if (kind == DEFER_COLUMNS) {
+        } else {
             float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
             int r = sl;
             for (; r + 96 < groups; r += 128) {
@@ -77,29 +90,16 @@ __global__ void __launch_bounds__(1024) deferred_reduce_kernel(const __grid_cons
             }
             for (; r < groups; r += 32) s0 += part[(long long)r * n + i];
             s = (s0 + s1) + (s2 + s3);
-        } else {
-            for (int g = sl; g < groups; g += 32) s += part[(long long)g * n + i];
         }
     }
     sm[sl][wx] = s;
     __syncthreads();
-    if (sl != 0 || !used) return;
+    if (sl != 0 || i >= n) return;
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 32; k++) t += sm[k][wx];
-    float *out = b.job[j].out;
-    if (kind == DEFER_PLAIN) { out[i] = t; return; }
-    if (kind == DEFER_COLUMNS) { const int pairs = b.job[j].a0; out[pairs > 0 ? (i & 1) * pairs + (i >> 1) : i] = t; return; }
-    // DEFER_WGT: the accumulator layout of conv_wgt_kernel -> dW[co][ci][kh][kw] (see wgt_reduce_kernel)
-    const int Cin = b.job[j].a0, Cout = b.job[j].a1, s2 = b.job[j].a2, xg = b.job[j].a3, cigs = b.job[j].a4, ncopy = b.job[j].a5;
-    const int NBc = ncopy * Cout;
-    const int row = (int)(i / NBc), col = (int)(i % NBc);
-    const int grp = row / 8, ci8 = row & 7;
-    if (grp >= 3 * xg) return;
-    const int a = grp / xg, par = (grp % xg) / cigs, ci = (grp % cigs) * 8 + ci8;
-    const int bb = col / Cout, co = col % Cout;
-    const int kw = !s2 ? bb : (par == 0 ? (bb == 1 ? 1 : -1) : (bb == 1 ? 2 : 0));
-    if (kw >= 0) out[((long long)co * Cin + ci) * 9 + a * 3 + kw] = t;
+    const int pairs = b.job[j].a0;
+    out[pairs > 0 ? (i & 1) * pairs + (i >> 1) : i] = t;
 }
 
 bool defer_enabled() { return d.on; }
@@ -142,7 +142,7 @@ static void defer_push(const DeferJob &job)
     DeferJob &J = d.batch.job[d.batch.count++];
     J = job;
     J.first_cta = d.batch.ctas;
-    d.batch.ctas += ceil_div(job.n, DEFER_ELEMS);
+    d.batch.ctas += ceil_div(job.n, job.kind == DEFER_COLUMNS ? 32 : PSUM_ELEMS);
 }
 void defer_plain(const float *part, float *out, long long n, int groups)
 {

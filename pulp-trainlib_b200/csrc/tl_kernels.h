@@ -54,6 +54,59 @@ bool conv_tc_run(Scope &sc, const float *src, const float *w, const float *bias,
                  int Hk, int Wk, int sh, int sw, int padU, int padL, int Cout_w, int Cin_w, bool flip, bool dry_run = false,
                  const ConvTcClass *cls = nullptr);
 int conv_tc_status();
+#ifdef __CUDACC__
+// Fixed-order sum of `groups` partial results (each n floats) for the four consecutive elements i .. i + 3, by a CTA of 1024
+// threads = 8 slices x 128 element quads: thread (slice, quad) adds the groups slice, slice + 8, ... with 16-byte loads
+// (every load of a thread is independent of the others: the memory system sees them all at once), the eight slice sums
+// are then added in slice order.  `used` = false skips the loads of a quad nobody needs.  True in the threads of slice 0
+// that hold a result (`t`; components at or past n are zero).  Every kernel that sums weight-gradient partials goes through
+// this function, so the immediate and the deferred reductions give the same bits.
+static constexpr int PSUM_ELEMS = 512;                  // elements per CTA
+__device__ __forceinline__ bool partial_sums_quad(const float *__restrict__ part, long long n, int groups, long long i, bool used, float4 &t, float4 (*sm)[128])
+{
+    const int q = threadIdx.x & 127, sl = threadIdx.x >> 7;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (used && i < n) {
+        if ((n & 3) == 0 && (((uintptr_t)part) & 15) == 0) {
+#pragma unroll 4
+            for (int g = sl; g < groups; g += 8) {
+                const float4 v = __ldcs(reinterpret_cast<const float4 *>(part + (long long)g * n + i));
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        } else {
+            for (int g = sl; g < groups; g += 8) {
+                const float *src = part + (long long)g * n + i;
+                acc.x += src[0];
+                if (i + 1 < n) acc.y += src[1];
+                if (i + 2 < n) acc.z += src[2];
+                if (i + 3 < n) acc.w += src[3];
+            }
+        }
+    }
+    sm[sl][q] = acc;
+    __syncthreads();
+    if (sl != 0 || !used || i >= n) return false;
+    t = sm[0][q];
+#pragma unroll
+    for (int k = 1; k < 8; k++) { const float4 v = sm[k][q]; t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w; }
+    return true;
+}
+// element e (one of the four of a quad) of the accumulator layout of conv_wgt_kernel -> its place in dW[co][ci][kh][kw], or -1
+__device__ __forceinline__ long long wgt_partial_index(long long e, int Cin, int Cout, int s2, int xg, int cigs, int ncopy)
+{
+    const int NBc = ncopy * Cout;
+    const int row = (int)(e / NBc), col = (int)(e % NBc);
+    const int grp = row / 8, ci8 = row & 7;                             // row = m * 128 + lane of the accumulator: 16 groups of 8 per M block
+    if (grp >= 3 * xg) return -1;                                       // padding rows of the last M block (never written)
+    const int a = grp / xg, par = (grp % xg) / cigs, ci = (grp % cigs) * 8 + ci8;
+    const int b = col / Cout, co = col % Cout;
+    // copy b of the dY row holds dY[x - b + 1], which pairs X[x] with filter column kw = b;
+    // stride 2: even pixels with dY[x] are column 1, odd pixels with dY[x] column 2, with dY[x + 1] column 0
+    const int kw = !s2 ? b : (par == 0 ? (b == 1 ? 1 : -1) : (b == 1 ? 2 : 0));
+    return kw >= 0 ? ((long long)co * Cin + ci) * 9 + a * 3 + kw : -1;
+}
+#endif
+
 // Partial results of an fp32 reduction: from the deferred-reduction arena when that mode is on and every buffer of the call
 // is device-resident (`deferred` = true: the caller notes the sum with defer_*), else scratch of the call (the caller sums at once).
 template <class T> inline float *partials_alloc(Scope &sc, size_t floats, bool &deferred)

@@ -496,7 +496,7 @@ def test_deferred_reductions_give_the_same_bits_in_one_launch(pkg, gpulib):
         finally:
             gpulib.trainlib_profile(0); gpulib.trainlib_set_deferred_reductions(0); gpulib.trainlib_set_streams(1)
         table = {row[0].strip("()").split("<")[0]: row[1] for row in pkg.profile_table(gpulib)}
-        sums = sum(table.get(k, 0) for k in ("reduce_partials_kernel", "wgt_reduce_kernel", "column_direct_kernel", "column_partial_kernel"))
+        sums = sum(table.get(k, 0) for k in ("reduce_partials_kernel", "reduce_partials_f32_kernel", "wgt_reduce_kernel", "column_direct_kernel", "column_partial_kernel"))
         if mode:
             assert table.get("deferred_reduce_kernel", 0) == 1 and sums == 0, table
         else:
