@@ -118,12 +118,19 @@ conv_mn_kernel(const __grid_constant__ CUtensorMap tmap, const ConvMnParams p)
     // window column b, source channel g*8 + k4*4 + j: the WK columns of 16 output channels sit side by side,
     // so the epilogue fetches them with one wide load.
     {
-        // one item = one row of one step: its 8 source channels are fetched, split and stored as two 16-byte chunks (hi) + two (lo)
-        const int steps = p.cigs * p.Hk, items = steps * p.NB;
+        // one item = one row of one step: its 8 source channels are fetched, split and stored as two 16-byte chunks (hi) + two (lo).
+        // Items are dealt so that the lanes of a warp read neighbouring addresses: the filter tap runs fastest (9 contiguous
+        // floats of the stored filters in every role), then the index that is contiguous next: the channel group of a
+        // forward filter (a whole row W[co][:][:][:] is contiguous), the output row otherwise (W[k][ci][:][:] for
+        // neighbouring ci).  (Dealt by operand row, every one of the 8 loads of a lane fetched a sector of its own; the launch
+        // times did not change with the dealing, the filters come from L1 / L2 either way.)
+        const int taps = p.Hk * WK, items = taps * p.cigs * p.NT;
+        const bool by_group = !p.cls && !p.flip;
         for (int it = threadIdx.x; it < items; it += nthreads) {
-            const int r = it % p.NB, step = it / p.NB;
-            const int a = step % p.Hk, g = step / p.Hk;
-            const int chunk = r / (WK * 16), b = (r % (WK * 16)) >> 4, c = chunk * 16 + (r & 15);
+            const int tap = it % taps, rest = it / taps;
+            const int a = tap / WK, b = tap % WK;
+            const int g = by_group ? rest % p.cigs : rest / p.NT, c = by_group ? rest / p.cigs : rest % p.NT;
+            const int chunk = c >> 4, r = chunk * (WK * 16) + b * 16 + (c & 15), step = g * p.Hk + a;
             const int n_out = blockIdx.y * p.NT + c;
             const float *src; long long kstride; int k_lim; bool row_ok;
             if (p.cls) {
