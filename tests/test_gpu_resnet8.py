@@ -119,9 +119,9 @@ def param_slices(net):
 
 
 def test_resnet8_2048_streams_against_the_reference(pkg, gpulib):
-    """The size the benchmark runs per GPU at N = 2 (and the kernel choices that go with it: two-pass column sums for
-    d(gamma), d(beta) and the Linear bias, which only launches of more than 1024 streams take; long persistent loops in
-    the convolutions).  Streams 0-63 and 1984-2047 of one 2048-stream launch against the reference's own C code
+    """The size the benchmark runs per GPU at N = 2 (and the kernel choices that go with it: the column sums of d(gamma),
+    d(beta) over more than 1024 rows -- eight running sums per lane in the batched reduction, two passes for the Linear
+    bias -- which only launches of more than 1024 streams take; long persistent loops in the convolutions).  Streams 0-63 and 1984-2047 of one 2048-stream launch against the reference's own C code
     (tests/golden/resnet8_streams_golden.npz, written by make_resnet8_golden.py): per-stream logits and loss at 1e-5.
 
     Gradients summed over all 2048 streams are checked twice: against reference(0-63) + GPU(64-1983, a launch of its
