@@ -173,7 +173,7 @@ class MhsaStep(_Layer):
     def roofline(self, ms, pk):
         tf = self.flops / (ms * 1e-3) / 1e12
         return {"bound": "ffma", "achieved": tf, "peak": 72.8, "unit": "TFLOP/s", "frac": tf / 72.8, "traffic": None, "peak_source": pk["source"],
-                "kernel": "attention forward + backward: 15 launches (fused score-softmax-value kernel and its two backward kernels, projections and weight gradients as strided FFMA GEMMs)", "algorithmic_flops": self.flops,
+                "kernel": "attention forward + backward: 11 launches (fused score-softmax-value kernel and its two backward kernels, projections and weight gradients as strided FFMA GEMMs)", "algorithmic_flops": self.flops,
                 "algorithmic_bytes": self.bytes, "us_per_step": 1e3 * ms,
                 "peak_note": "FFMA peak measured on this part (125 MAC/clk/SM); the 256^3 products stay on the FFMA tiles because their summation "
                              "order keeps the backward inside 1e-5 of the reference"}

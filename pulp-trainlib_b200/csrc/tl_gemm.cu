@@ -16,104 +16,27 @@ template <class T, int BM, int BN, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_ffma_kernel(GemmDesc<T> d)
 {
-    constexpr int BK = 16;
-    constexpr int NT = (BM / TM) * (BN / TN);
-    constexpr int AE = BM * BK / NT, BE = BN * BK / NT;      // elements of the A / B tile each thread moves
-    static_assert(BM * BK % NT == 0 && BN * BK % NT == 0, "tile must divide over the threads");
-    // two shared-memory stages: the global loads of tile t+1 are issued before tile t is multiplied and stored
-    // afterwards, so their latency hides behind the FMAs and one barrier per K step is enough
-    __shared__ __align__(16) float As[2][BK][BM + 4];
-    __shared__ __align__(16) float Bs[2][BK][BN + 4];
-
-    const int tid = threadIdx.x;
-    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
-    const int i0 = blockIdx.y * BM, j0 = blockIdx.x * BN;
     const int b = blockIdx.z;
     const T *A = d.A + (long long)b * d.a_bs;
     const T *B = d.B + (long long)b * d.b_bs;
     T *C = d.C + (long long)b * d.c_bs;
 
-    float acc[TM][TN];
-#pragma unroll
-    for (int r = 0; r < TM; r++)
-#pragma unroll
-        for (int c = 0; c < TN; c++) acc[r][c] = 0.f;
+#include "tl_gemm_body.inc"
+}
 
-    const bool a_k_contig = (d.a_cs == 1);
-    const bool b_k_contig = (d.b_rs == 1);
-    float ra[AE], rb[BE];
-    auto fetch = [&](int k0) {
-#pragma unroll
-        for (int q = 0; q < AE; q++) {
-            const int e = tid + q * NT;
-            int i, k;
-            if (a_k_contig) { i = e / BK; k = e % BK; } else { k = e / BM; i = e % BM; }
-            ra[q] = (i0 + i < d.N && k0 + k < d.K) ? ld(A + (long long)(i0 + i) * d.a_rs + (long long)(k0 + k) * d.a_cs) : 0.f;
-        }
-#pragma unroll
-        for (int q = 0; q < BE; q++) {
-            const int e = tid + q * NT;
-            int j, k;
-            if (b_k_contig) { j = e / BK; k = e % BK; } else { k = e / BN; j = e % BN; }
-            rb[q] = (j0 + j < d.M && k0 + k < d.K) ? ld(B + (long long)(k0 + k) * d.b_rs + (long long)(j0 + j) * d.b_cs) : 0.f;
-        }
-    };
-    auto stash = [&](int stage) {
-#pragma unroll
-        for (int q = 0; q < AE; q++) {
-            const int e = tid + q * NT;
-            int i, k;
-            if (a_k_contig) { i = e / BK; k = e % BK; } else { k = e / BM; i = e % BM; }
-            As[stage][k][i] = ra[q];
-        }
-#pragma unroll
-        for (int q = 0; q < BE; q++) {
-            const int e = tid + q * NT;
-            int j, k;
-            if (b_k_contig) { j = e / BK; k = e % BK; } else { k = e / BN; j = e % BN; }
-            Bs[stage][k][j] = rb[q];
-        }
-    };
-
-    fetch(0);
-    stash(0);
-    __syncthreads();
-    int cur = 0;
-    for (int k0 = 0; k0 < d.K; k0 += BK, cur ^= 1) {
-        const bool more = k0 + BK < d.K;
-        if (more) fetch(k0 + BK);
-#pragma unroll
-        for (int k = 0; k < BK; k++) {
-            float a[TM], bb[TN];
-#pragma unroll
-            for (int r = 0; r < TM; r++) a[r] = As[cur][k][ty * TM + r];
-#pragma unroll
-            for (int c = 0; c < TN; c++) bb[c] = Bs[cur][k][tx * TN + c];
-#pragma unroll
-            for (int r = 0; r < TM; r++)
-#pragma unroll
-                for (int c = 0; c < TN; c++) acc[r][c] = fmaf(a[r], bb[c], acc[r][c]);
-        }
-        if (more) stash(cur ^ 1);
-        __syncthreads();
-    }
-
-#pragma unroll
-    for (int r = 0; r < TM; r++) {
-        int i = i0 + ty * TM + r;
-        if (i >= d.N) continue;
-#pragma unroll
-        for (int c = 0; c < TN; c++) {
-            int j = j0 + tx * TN + c;
-            if (j >= d.M) continue;
-            T *p = C + (long long)i * d.c_rs + (long long)j * d.c_cs;
-            float v = acc[r][c] * d.alpha;
-            if (d.accumulate) v += ld(p);
-            if (d.bias_mode == 1) v += ld(d.bias + i);
-            else if (d.bias_mode == 2) v += ld(d.bias + j);
-            st(p, v);
-        }
-    }
+// The same tiles for up to three products of one shape whose operands are separate allocations: blockIdx.z picks the product
+// (with selects: indexing a kernel parameter by a run-time value would move it to local memory).
+template <class T, int BM, int BN, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_ffma_list_kernel(GemmDesc<T> d, GemmList<T> l)
+{
+    const int b = blockIdx.z;
+    const T *A = b == 0 ? l.A[0] : b == 1 ? l.A[1] : l.A[2];
+    const T *B = b == 0 ? l.B[0] : b == 1 ? l.B[1] : l.B[2];
+    T *C = b == 0 ? l.C[0] : b == 1 ? l.C[1] : l.C[2];
+    d.bias = b == 0 ? l.bias[0] : b == 1 ? l.bias[1] : l.bias[2];
+    if (!d.bias) d.bias_mode = 0;
+#include "tl_gemm_body.inc"
 }
 
 // Tensor-core path (tl_gemm_tc.cu); returns false when the shape/layout does not qualify.
@@ -133,6 +56,30 @@ template <class T> void gemm(const GemmDesc<T> &d)
     } else {
         dim3 grid(ceil_div(d.M, 32), ceil_div(d.N, 32), d.batch);
         TL_LAUNCH((gemm_ffma_kernel<T, 32, 32, 2, 2>), grid, 256, 0, d);
+    }
+}
+
+template <class T> void gemm_list(const GemmDesc<T> &shape, const GemmList<T> &l, int count)
+{
+    if (shape.N <= 0 || shape.M <= 0 || count <= 0) return;
+    if (count > 3) { set_error(TL_ERR_BAD_ARGS, "gemm_list: %d products (3 at most)", count); return; }
+    // products large enough for the tensor-core kernels, and forced paths, go one by one
+    if (gemm_path() > 1 || (long long)shape.N * shape.M * shape.K >= (1ll << 26)) {
+        for (int p = 0; p < count; p++) {
+            GemmDesc<T> one = shape; one.batch = 1; one.A = l.A[p]; one.B = l.B[p]; one.C = l.C[p]; one.bias = l.bias[p];
+            if (!one.bias) one.bias_mode = 0;
+            gemm<T>(one);
+        }
+        return;
+    }
+    GemmDesc<T> d = shape;
+    const long long tiles64 = (long long)ceil_div(d.N, 64) * ceil_div(d.M, 64) * count;
+    if (tiles64 >= sm_count() || (d.N > 32 && d.M > 32 && tiles64 * 4 >= 2 * sm_count())) {
+        dim3 grid(ceil_div(d.M, 64), ceil_div(d.N, 64), count);
+        TL_LAUNCH((gemm_ffma_list_kernel<T, 64, 64, 4, 4>), grid, 256, 0, d, l);
+    } else {
+        dim3 grid(ceil_div(d.M, 32), ceil_div(d.N, 32), count);
+        TL_LAUNCH((gemm_ffma_list_kernel<T, 32, 32, 2, 2>), grid, 256, 0, d, l);
     }
 }
 
@@ -567,6 +514,7 @@ namespace tl {
 
 #define INST(T)                                                                                             \
     template void gemm<T>(const GemmDesc<T> &);                                                             \
+    template void gemm_list<T>(const GemmDesc<T> &, const GemmList<T> &, int);                              \
     template void mm_contract<T>(const T *, const T *, T *, int, int, int, int, bool);                      \
     template void linear_fw_gemv<T>(const T *, const T *, const T *, T *, int, int);                        \
     template void linear_wg_outer<T>(const T *, const T *, T *, int, int);                                  \

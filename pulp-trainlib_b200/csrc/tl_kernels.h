@@ -20,6 +20,10 @@ template <class T> struct GemmDesc {
     int bias_mode = 0;              // 1: bias[i] (per row), 2: bias[j] (per column)
 };
 template <class T> void gemm(const GemmDesc<T> &d);
+// Up to three products of one shape whose operands are separate allocations (the q, k, v projections of an attention layer)
+// as one launch: `shape` gives sizes, strides, alpha, accumulate and bias_mode; A, B, C and bias come from the list.
+template <class T> struct GemmList { const T *A[3]; const T *B[3]; const T *bias[3]; T *C[3]; };
+template <class T> void gemm_list(const GemmDesc<T> &shape, const GemmList<T> &l, int count);
 
 // Reference-contract product: C[N x M] = A[N x K] * B, B is [K x M] or (trans_B) [M x K].
 template <class T> void mm_contract(const T *A, const T *B, T *C, int N, int K, int M, int trans_B, bool accumulate);
