@@ -20,7 +20,8 @@
 namespace tl {
 
 static constexpr int ATT_THREADS = 256;
-static constexpr int ATT_TQ = 8;                 // queries (or keys) per CTA = accumulators per thread
+static constexpr int ATT_TQ = 4;                 // queries (or keys) per CTA = accumulators per thread (4 or 8).  Four: 256 CTAs for 4 heads x 256
+                                                 // tokens, two per SM on most SMs; with eight (128 CTAs of 8 warps) the kernels ran at an eighth of the warp slots
 
 // tile[t][j] = sum_d a_tile[d][t] * M[d][j]  for t < ATT_TQ, j < L: thread per column j, the H-long contraction in
 // registers.  a_tile is [H][ATT_TQ] in shared memory (broadcast reads), M rows are read coalesced.
@@ -33,9 +34,12 @@ __device__ __forceinline__ void tile_from_rows(const float *a_tile, const T *__r
         for (int t = 0; t < ATT_TQ; t++) acc[t] = 0.f;
         for (int d = 0; d < H; d++) {
             const float m = ld(M + (size_t)d * L + j);
-            const float4 a0 = *reinterpret_cast<const float4 *>(a_tile + d * ATT_TQ), a1 = *reinterpret_cast<const float4 *>(a_tile + d * ATT_TQ + 4);
+            const float4 a0 = *reinterpret_cast<const float4 *>(a_tile + d * ATT_TQ);
             acc[0] = fmaf(a0.x, m, acc[0]); acc[1] = fmaf(a0.y, m, acc[1]); acc[2] = fmaf(a0.z, m, acc[2]); acc[3] = fmaf(a0.w, m, acc[3]);
-            acc[4] = fmaf(a1.x, m, acc[4]); acc[5] = fmaf(a1.y, m, acc[5]); acc[6] = fmaf(a1.z, m, acc[6]); acc[7] = fmaf(a1.w, m, acc[7]);
+            if constexpr (ATT_TQ == 8) {
+                const float4 a1 = *reinterpret_cast<const float4 *>(a_tile + d * ATT_TQ + 4);
+                acc[4] = fmaf(a1.x, m, acc[4]); acc[5] = fmaf(a1.y, m, acc[5]); acc[6] = fmaf(a1.z, m, acc[6]); acc[7] = fmaf(a1.w, m, acc[7]);
+            }
         }
 #pragma unroll
         for (int t = 0; t < ATT_TQ; t++) tile[t * Lp + j] = __fmul_rn(acc[t], alpha);
